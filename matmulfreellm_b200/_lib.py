@@ -1,0 +1,104 @@
+"""ctypes binding of libmmfree_b200.so (the C ABI declared in include/mmfree_b200.h).
+
+There is no CPU or PyTorch fallback behind these bindings: if the shared library is
+missing, or the device is not a B200-class GPU, the calls raise.
+"""
+from __future__ import annotations
+
+import ctypes
+from ctypes import c_char_p, c_double, c_float, c_int, c_int64, c_void_p
+from pathlib import Path
+
+LIB_PATH = Path(__file__).resolve().parent / "libmmfree_b200.so"
+
+F32, BF16, F16 = 0, 1, 2
+KERNEL_AUTO, KERNEL_GEMV, KERNEL_MMA = 0, 1, 2
+TILE_ROWS, TILE_K = 128, 64
+ABSMEAN_PARTIALS = 1024
+ABI_VERSION = 1
+
+_ERR_NAMES = {
+    -1: "MMF_ERR_BAD_ARG", -2: "MMF_ERR_BAD_SHAPE", -3: "MMF_ERR_ALIGN", -4: "MMF_ERR_CUDA",
+    -5: "MMF_ERR_ARCH", -6: "MMF_ERR_WORKSPACE", -7: "MMF_ERR_TIMEOUT",
+}
+
+# name -> (restype, argtypes); must list every symbol include/mmfree_b200.h declares
+PROTOTYPES = {
+    "mmf_last_error": (c_char_p, []),
+    "mmf_abi_version": (c_int, []),
+    "mmf_check_device": (c_int, []),
+    "mmf_absmean_f32": (c_int, [c_void_p, c_int64, c_void_p, c_void_p, c_void_p]),
+    "mmf_packed_bytes": (c_int64, [c_int64, c_int64]),
+    "mmf_pack_ternary": (c_int, [c_void_p, c_int64, c_int64, c_void_p, c_void_p, c_void_p]),
+    "mmf_unpack_ternary": (c_int, [c_void_p, c_int64, c_int64, c_void_p, c_void_p]),
+    "mmf_act_quant": (c_int, [c_void_p, c_int, c_int64, c_void_p, c_int, c_float, c_void_p, c_void_p, c_void_p,
+                              c_int64, c_int64, c_void_p]),
+    "mmf_bitlinear_workspace_bytes": (c_int64, [c_int64, c_int64, c_int64]),
+    "mmf_bitlinear": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int64,
+                              c_void_p, c_int64, c_int64, c_int64, c_void_p, c_int64, c_int, c_void_p]),
+    "mmf_hgrn_workspace_bytes": (c_int64, [c_int64, c_int64, c_int64]),
+    "mmf_hgrn_scan": (c_int, [c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_int, c_void_p, c_int64,
+                              c_int64, c_int64, c_int, c_void_p, c_int64, c_void_p]),
+    "mmf_rmsnorm": (c_int, [c_void_p, c_int, c_void_p, c_int, c_void_p, c_float, c_void_p, c_void_p, c_int64,
+                            c_int64, c_void_p]),
+    "mmf_rmsnorm_swishgate": (c_int, [c_void_p, c_void_p, c_int, c_void_p, c_float, c_void_p, c_int64, c_int64,
+                                      c_void_p]),
+    "mmf_swiglu": (c_int, [c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_int64, c_int, c_int64, c_int64,
+                           c_void_p]),
+    "mmf_argmax_rows": (c_int, [c_void_p, c_int, c_int64, c_int64, c_int64, c_void_p, c_void_p]),
+    "mmf_embedding": (c_int, [c_void_p, c_int, c_int64, c_int64, c_void_p, c_void_p, c_int64, c_void_p]),
+}
+
+
+class MMFreeError(RuntimeError):
+    """A C-ABI call returned a negative status."""
+
+    def __init__(self, fn: str, code: int, text: str):
+        self.code = code
+        super().__init__(f"{fn} failed with {_ERR_NAMES.get(code, code)}: {text}")
+
+
+_lib = None
+
+
+def load() -> ctypes.CDLL:
+    """Load the shared library (once) and attach prototypes. Raises if it has not been built."""
+    global _lib
+    if _lib is not None:
+        return _lib
+    if not LIB_PATH.exists():
+        raise RuntimeError(
+            f"{LIB_PATH} is missing. Build it with `python -m matmulfreellm_b200._build` "
+            "(needs nvcc); there is no fallback implementation.")
+    lib = ctypes.CDLL(str(LIB_PATH))
+    for name, (res, args) in PROTOTYPES.items():
+        fn = getattr(lib, name)  # AttributeError here = header and library out of sync
+        fn.restype = res
+        fn.argtypes = args
+    if lib.mmf_abi_version() != ABI_VERSION:
+        raise RuntimeError(f"libmmfree_b200 ABI {lib.mmf_abi_version()} != binding ABI {ABI_VERSION}")
+    _lib = lib
+    return lib
+
+
+def call(name: str, *args) -> None:
+    """Invoke an int-returning entry point and raise MMFreeError on a negative status."""
+    lib = load()
+    rc = getattr(lib, name)(*args)
+    if rc != 0:
+        raise MMFreeError(name, rc, lib.mmf_last_error().decode(errors="replace"))
+
+
+_device_checked = set()
+
+
+def require_device(index: int) -> None:
+    """Fail loudly (once per device) unless `index` is a compute-capability-10.x GPU."""
+    if index in _device_checked:
+        return
+    import torch
+    if not torch.cuda.is_available():
+        raise RuntimeError("matmulfreellm_b200 needs a CUDA device (B200, sm_100a); none is available")
+    with torch.cuda.device(index):
+        call("mmf_check_device")
+    _device_checked.add(index)

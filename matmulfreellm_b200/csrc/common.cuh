@@ -1,0 +1,158 @@
+// Shared device/host helpers for libmmfree_b200 (sm_100a only).
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "../../include/mmfree_b200.h"
+
+// ---------------------------------------------------------------------------------------
+// host-side error plumbing
+// ---------------------------------------------------------------------------------------
+int mmf_set_error(int code, const char* fmt, ...);
+
+#define MMF_REQUIRE(cond, code, ...)                       \
+    do {                                                   \
+        if (!(cond)) return mmf_set_error(code, __VA_ARGS__); \
+    } while (0)
+
+#define MMF_CUDA(call)                                                                  \
+    do {                                                                                \
+        cudaError_t e__ = (call);                                                       \
+        if (e__ != cudaSuccess)                                                         \
+            return mmf_set_error(MMF_ERR_CUDA, "%s failed: %s", #call, cudaGetErrorString(e__)); \
+    } while (0)
+
+#define MMF_LAUNCH_CHECK(name)                                                          \
+    do {                                                                                \
+        cudaError_t e__ = cudaGetLastError();                                           \
+        if (e__ != cudaSuccess)                                                         \
+            return mmf_set_error(MMF_ERR_CUDA, "launch of %s failed: %s", name,         \
+                                 cudaGetErrorString(e__));                              \
+    } while (0)
+
+static inline bool mmf_aligned(const void* p, size_t a) { return (reinterpret_cast<uintptr_t>(p) % a) == 0; }
+static inline bool mmf_dtype_ok(int dt) { return dt == MMF_F32 || dt == MMF_BF16 || dt == MMF_F16; }
+static inline int mmf_dtype_size(int dt) { return dt == MMF_F32 ? 4 : 2; }
+
+// Run `...` with `T` bound to the C++ type of dtype code `dt`.
+#define MMF_DISPATCH(dt, T, ...)                         \
+    switch (dt) {                                        \
+        case MMF_F32: { using T = float; __VA_ARGS__; break; }          \
+        case MMF_BF16: { using T = __nv_bfloat16; __VA_ARGS__; break; } \
+        default: { using T = __half; __VA_ARGS__; break; }              \
+    }
+
+// ---------------------------------------------------------------------------------------
+// element conversion (round-to-nearest-even on store, exact on load)
+// ---------------------------------------------------------------------------------------
+__device__ __forceinline__ float to_f32(float v) { return v; }
+__device__ __forceinline__ float to_f32(__nv_bfloat16 v) { return __bfloat162float(v); }
+__device__ __forceinline__ float to_f32(__half v) { return __half2float(v); }
+
+template <typename T> __device__ __forceinline__ T from_f32(float v);
+template <> __device__ __forceinline__ float from_f32<float>(float v) { return v; }
+template <> __device__ __forceinline__ __nv_bfloat16 from_f32<__nv_bfloat16>(float v) { return __float2bfloat16_rn(v); }
+template <> __device__ __forceinline__ __half from_f32<__half>(float v) { return __float2half_rn(v); }
+
+// value of v after a round trip through T (models an intermediate tensor of dtype T)
+template <typename T> __device__ __forceinline__ float round_to(float v) { return to_f32(from_f32<T>(v)); }
+
+// 16-byte vector of T: 4 floats or 8 halves
+template <typename T> struct Vec16 { static constexpr int N = 16 / sizeof(T); T v[N]; };
+
+template <typename T>
+__device__ __forceinline__ void load16(const T* p, float (&out)[16 / sizeof(T)]) {
+    uint4 raw = *reinterpret_cast<const uint4*>(p);
+    const T* e = reinterpret_cast<const T*>(&raw);
+#pragma unroll
+    for (int i = 0; i < (int)(16 / sizeof(T)); ++i) out[i] = to_f32(e[i]);
+}
+
+template <typename T>
+__device__ __forceinline__ void store16(T* p, const float (&in)[16 / sizeof(T)]) {
+    uint4 raw;
+    T* e = reinterpret_cast<T*>(&raw);
+#pragma unroll
+    for (int i = 0; i < (int)(16 / sizeof(T)); ++i) e[i] = from_f32<T>(in[i]);
+    *reinterpret_cast<uint4*>(p) = raw;
+}
+
+// ---------------------------------------------------------------------------------------
+// block reductions (blockDim.x a multiple of 32, <= 1024); result broadcast to all threads
+// `red` is shared scratch of >= 33 elements of T.
+// ---------------------------------------------------------------------------------------
+__device__ __forceinline__ double warp_sum(double v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    return v;
+}
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+    return v;
+}
+__device__ __forceinline__ int warp_sum(int v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    return v;
+}
+
+__device__ __forceinline__ double block_sum(double v, double* red) {
+    const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5, nw = blockDim.x >> 5;
+    v = warp_sum(v);
+    __syncthreads();  // protect `red` from the previous use
+    if (lane == 0) red[wid] = v;
+    __syncthreads();
+    if (wid == 0) {
+        double t = lane < nw ? red[lane] : 0.0;
+        t = warp_sum(t);
+        if (lane == 0) red[32] = t;
+    }
+    __syncthreads();
+    return red[32];
+}
+__device__ __forceinline__ float block_max(float v, float* red) {
+    const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5, nw = blockDim.x >> 5;
+    v = warp_max(v);
+    __syncthreads();
+    if (lane == 0) red[wid] = v;
+    __syncthreads();
+    if (wid == 0) {
+        float t = lane < nw ? red[lane] : 0.0f;  // callers reduce non-negative values
+        t = warp_max(t);
+        if (lane == 0) red[32] = t;
+    }
+    __syncthreads();
+    return red[32];
+}
+__device__ __forceinline__ int block_sum(int v, int* red) {
+    const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5, nw = blockDim.x >> 5;
+    v = warp_sum(v);
+    __syncthreads();
+    if (lane == 0) red[wid] = v;
+    __syncthreads();
+    if (wid == 0) {
+        int t = lane < nw ? red[lane] : 0;
+        t = warp_sum(t);
+        if (lane == 0) red[32] = t;
+    }
+    __syncthreads();
+    return red[32];
+}
+
+// ---------------------------------------------------------------------------------------
+// the exact arithmetic of the quantisation path (mirrored by the CPU oracle): every step is
+// a single IEEE round-to-nearest fp32 operation, never contracted into an fma.
+// ---------------------------------------------------------------------------------------
+__device__ __forceinline__ float rstd_from_sumsq(double sumsq, int64_t K, float eps) {
+    const float mean = (float)(sumsq / (double)K);
+    return __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(mean, eps)));
+}
+__device__ __forceinline__ float silu_mul(float x, float y) {
+    // float(x) * float(y) / (1.0f + exp(-float(x)))
+    return __fdiv_rn(__fmul_rn(x, y), __fadd_rn(1.0f, expf(-x)));
+}
+__device__ __forceinline__ float sigmoidf_(float x) { return __fdiv_rn(1.0f, __fadd_rn(1.0f, expf(-x))); }

@@ -1,0 +1,312 @@
+"""Tensor-level wrappers around the C ABI: shape/dtype checks, output allocation, stream.
+
+PyTorch is used here for device memory and streams only; all arithmetic happens in
+libmmfree_b200.so.  Every function requires CUDA tensors and raises otherwise.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+from typing import Optional, Sequence, Tuple
+
+import torch
+
+from . import _lib
+from ._lib import BF16, F16, F32, KERNEL_AUTO, KERNEL_GEMV, KERNEL_MMA, TILE_K, TILE_ROWS  # noqa: F401
+
+_DT = {torch.float32: F32, torch.bfloat16: BF16, torch.float16: F16}
+
+
+def _code(dtype: torch.dtype) -> int:
+    try:
+        return _DT[dtype]
+    except KeyError:
+        raise TypeError(f"unsupported dtype {dtype}; expected float32, bfloat16 or float16") from None
+
+
+def _need_cuda(*tensors: Optional[torch.Tensor]) -> torch.device:
+    dev = None
+    for t in tensors:
+        if t is None:
+            continue
+        if not t.is_cuda:
+            raise RuntimeError("matmulfreellm_b200 kernels take CUDA tensors only (no CPU fallback exists)")
+        if dev is None:
+            dev = t.device
+        elif t.device != dev:
+            raise RuntimeError(f"tensors on different devices: {dev} and {t.device}")
+    assert dev is not None
+    _lib.require_device(dev.index if dev.index is not None else torch.cuda.current_device())
+    return dev
+
+
+def _ptr(t: Optional[torch.Tensor]):
+    return None if t is None else t.data_ptr()
+
+
+def _stream() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+# ------------------------------------------------------------------------------------------
+# packed ternary weights
+# ------------------------------------------------------------------------------------------
+@dataclass
+class PackedWeight:
+    """2-bit packed ternary weight of one BitLinear (or of `groups` BitLinears stacked along N)."""
+    packed: torch.Tensor   # uint8, tile-major layout (see include/mmfree_b200.h)
+    scale: torch.Tensor    # float32 [groups]: mean|w| of each group
+    N: int                 # total output features (all groups)
+    K: int
+    groups: int = 1
+
+    @property
+    def device(self) -> torch.device:
+        return self.packed.device
+
+
+def absmean(w: torch.Tensor) -> torch.Tensor:
+    """clamp(mean|w|, 1e-5) as a float32[1] tensor (fp64 accumulation, deterministic)."""
+    _need_cuda(w)
+    if w.dtype != torch.float32 or not w.is_contiguous():
+        raise TypeError("absmean expects a contiguous float32 tensor (the fp32 latent weight)")
+    partials = torch.empty(_lib.ABSMEAN_PARTIALS, dtype=torch.float64, device=w.device)
+    out = torch.empty(1, dtype=torch.float32, device=w.device)
+    _lib.call("mmf_absmean_f32", w.data_ptr(), w.numel(), partials.data_ptr(), out.data_ptr(), _stream())
+    return out
+
+
+def pack_weight(w: torch.Tensor) -> PackedWeight:
+    """Absmean-ternarise an fp32 latent weight [N,K] and pack it (offline step)."""
+    _need_cuda(w)
+    if w.dim() != 2:
+        raise ValueError("weight must be [N, K]")
+    w = w.detach()
+    if w.dtype != torch.float32:
+        w = w.float()
+    w = w.contiguous()
+    N, K = w.shape
+    if K % TILE_K:
+        raise ValueError(f"in_features must be a multiple of {TILE_K}, got {K}")
+    mean = absmean(w)
+    nbytes = _lib.load().mmf_packed_bytes(N, K)
+    packed = torch.empty(nbytes, dtype=torch.uint8, device=w.device)
+    _lib.call("mmf_pack_ternary", w.data_ptr(), N, K, mean.data_ptr(), packed.data_ptr(), _stream())
+    return PackedWeight(packed, mean, N, K, 1)
+
+
+def stack_packed(parts: Sequence[PackedWeight]) -> PackedWeight:
+    """Stack BitLinears that share their input along N so they run as one grouped launch."""
+    K = parts[0].K
+    n = parts[0].N
+    for p in parts:
+        if p.K != K or p.N != n or p.groups != 1:
+            raise ValueError("grouped BitLinears need identical [N,K]")
+    if n % TILE_ROWS:
+        raise ValueError(f"grouped BitLinears need out_features % {TILE_ROWS} == 0")
+    return PackedWeight(torch.cat([p.packed for p in parts]), torch.cat([p.scale for p in parts]), n * len(parts), K,
+                        len(parts))
+
+
+def unpack_codes(pw: PackedWeight) -> torch.Tensor:
+    """int8 ternary codes [N,K] recovered from the packed buffer."""
+    codes = torch.empty(pw.N, pw.K, dtype=torch.int8, device=pw.device)
+    _lib.call("mmf_unpack_ternary", pw.packed.data_ptr(), pw.N, pw.K, codes.data_ptr(), _stream())
+    return codes
+
+
+# ------------------------------------------------------------------------------------------
+# BitLinear
+# ------------------------------------------------------------------------------------------
+def act_quant(x: torch.Tensor, norm_weight: Optional[torch.Tensor], eps: float, use_norm: bool = True,
+              out: Optional[Tuple[torch.Tensor, torch.Tensor, torch.Tensor]] = None):
+    """RMSNorm + per-row int8 absmax quantisation of x [M,K] -> (codes int8, dq fp32[M], rowsum int32[M])."""
+    _need_cuda(x, norm_weight)
+    if x.dim() != 2 or x.stride(1) != 1:
+        raise ValueError("x must be [M,K] with unit inner stride")
+    M, K = x.shape
+    if norm_weight is not None:
+        if norm_weight.dtype != torch.float32 or norm_weight.shape != (K,) or not norm_weight.is_contiguous():
+            raise TypeError("norm weight must be contiguous float32 [K]")
+    if out is None:
+        q = torch.empty(M, K, dtype=torch.int8, device=x.device)
+        dq = torch.empty(M, dtype=torch.float32, device=x.device)
+        rs = torch.empty(M, dtype=torch.int32, device=x.device)
+    else:
+        q, dq, rs = out
+    _lib.call("mmf_act_quant", x.data_ptr(), _code(x.dtype), x.stride(0), _ptr(norm_weight), int(use_norm), float(eps),
+              q.data_ptr(), dq.data_ptr(), rs.data_ptr(), M, K, _stream())
+    return q, dq, rs
+
+
+_ws_cache: dict = {}
+
+
+def _workspace(device: torch.device, nbytes: int) -> torch.Tensor:
+    """Zero-initialised split-K workspace, one per (device, stream); kernels leave it zeroed."""
+    key = (device.index, _stream())
+    ws = _ws_cache.get(key)
+    if ws is None or ws.numel() < nbytes:
+        ws = torch.zeros(max(nbytes, 1 << 20), dtype=torch.uint8, device=device)
+        _ws_cache[key] = ws
+    return ws
+
+
+def bitlinear(q: torch.Tensor, dq: torch.Tensor, rowsum: torch.Tensor, pw: PackedWeight, out_dtype: torch.dtype,
+              kernel: int = KERNEL_AUTO, return_acc: bool = False, out: Optional[torch.Tensor] = None):
+    """Integer BitLinear contraction + dequantising epilogue.
+
+    q/dq/rowsum are [groups*M, K] / [groups*M] / [groups*M] (group-major) as produced by act_quant.
+    Returns out [M, N] (and the raw int32 accumulators when return_acc).
+    """
+    _need_cuda(q, dq, rowsum, pw.packed)
+    G = pw.groups
+    if q.dtype != torch.int8 or q.dim() != 2 or not q.is_contiguous() or q.shape[1] != pw.K or q.shape[0] % G:
+        raise ValueError("q must be contiguous int8 [groups*M, K]")
+    M = q.shape[0] // G
+    if dq.numel() != G * M or rowsum.numel() != G * M or dq.dtype != torch.float32 or rowsum.dtype != torch.int32:
+        raise ValueError("dq / rowsum must be float32 / int32 [groups*M]")
+    if out is None:
+        out = torch.empty(M, pw.N, dtype=out_dtype, device=q.device)
+    elif out.shape != (M, pw.N) or out.stride(1) != 1 or out.dtype != out_dtype:
+        raise ValueError("bad `out` tensor")
+    acc = torch.empty(M, pw.N, dtype=torch.int32, device=q.device) if return_acc else None
+    nbytes = _lib.load().mmf_bitlinear_workspace_bytes(M, pw.N, pw.K)
+    ws = _workspace(q.device, nbytes)
+    try:
+        _lib.call("mmf_bitlinear", q.data_ptr(), dq.data_ptr(), rowsum.data_ptr(), pw.packed.data_ptr(),
+                  pw.scale.data_ptr(), G, out.data_ptr(), _code(out_dtype), out.stride(0), _ptr(acc), M, pw.N, pw.K,
+                  ws.data_ptr(), ws.numel(), kernel, _stream())
+    except _lib.MMFreeError:
+        _ws_cache.clear()  # a failed launch may have left partial sums behind
+        raise
+    return (out, acc) if return_acc else out
+
+
+# ------------------------------------------------------------------------------------------
+# HGRN recurrence
+# ------------------------------------------------------------------------------------------
+def hgrn_scan(x: torch.Tensor, g: torch.Tensor, initial_state: Optional[torch.Tensor], output_final_state: bool,
+              gate_is_log: bool, state_dtype: Optional[torch.dtype] = None, final_state_out: Optional[torch.Tensor] = None):
+    """x, g: [..., T, D] contiguous; leading dims are independent sequences. Returns (o, final_state|None)."""
+    _need_cuda(x, g, initial_state)
+    if x.shape != g.shape or x.dim() < 2:
+        raise ValueError("x and g must have the same shape [..., T, D]")
+    x = x.contiguous()
+    g = g.contiguous()
+    *lead, T, D = x.shape
+    B = 1
+    for s in lead:
+        B *= s
+    sdt = state_dtype or (initial_state.dtype if initial_state is not None else torch.float32)
+    h0 = None
+    if initial_state is not None:
+        if initial_state.numel() != B * D:
+            raise ValueError("initial_state must hold one value per (sequence, channel)")
+        h0 = initial_state.detach().to(sdt).contiguous()
+    ht = None
+    if output_final_state:
+        ht = final_state_out if final_state_out is not None else torch.empty(*lead, D, dtype=sdt, device=x.device)
+    o = torch.empty_like(x)
+    nbytes = _lib.load().mmf_hgrn_workspace_bytes(B, T, D)
+    ws = torch.empty(nbytes, dtype=torch.uint8, device=x.device) if nbytes else None
+    _lib.call("mmf_hgrn_scan", x.data_ptr(), _code(x.dtype), g.data_ptr(), _code(g.dtype), _ptr(h0), _ptr(ht),
+              _code(sdt), o.data_ptr(), B, T, D, int(gate_is_log), _ptr(ws), nbytes, _stream())
+    return o, ht
+
+
+# ------------------------------------------------------------------------------------------
+# norms / activations / sampling helpers
+# ------------------------------------------------------------------------------------------
+def _as_rows(x: torch.Tensor) -> torch.Tensor:
+    return x.reshape(-1, x.shape[-1]).contiguous()
+
+
+def rmsnorm(x: torch.Tensor, weight: Optional[torch.Tensor], eps: float, residual: Optional[torch.Tensor] = None,
+            prenorm: bool = False, residual_in_fp32: bool = False):
+    """RMSNorm with the optional fused residual add; mirrors rms_norm_fn's return convention."""
+    _need_cuda(x, weight, residual)
+    shape = x.shape
+    x2 = _as_rows(x)
+    M, D = x2.shape
+    w = None if weight is None else weight.detach().float().contiguous()
+    res2 = None
+    res_dtype = x.dtype
+    if residual is not None:
+        if residual.shape != shape:
+            raise AssertionError("residual must have the shape of x")
+        res2 = _as_rows(residual)
+        res_dtype = residual.dtype
+    elif residual_in_fp32:
+        res_dtype = torch.float32
+    if res_dtype not in (x.dtype, torch.float32):
+        raise TypeError("residual dtype must equal x dtype or be float32")
+    y = torch.empty_like(x2)
+    need_res_out = residual is not None or res_dtype != x.dtype
+    res_out = torch.empty(M, D, dtype=res_dtype, device=x.device) if need_res_out else None
+    _lib.call("mmf_rmsnorm", x2.data_ptr(), _code(x.dtype), _ptr(res2), _code(res_dtype), _ptr(w), float(eps),
+              y.data_ptr(), _ptr(res_out), M, D, _stream())
+    y = y.reshape(shape)
+    if not prenorm:
+        return y
+    return y, (res_out.reshape(shape) if res_out is not None else x)
+
+
+def rmsnorm_swishgate(x: torch.Tensor, o: torch.Tensor, weight: Optional[torch.Tensor], eps: float) -> torch.Tensor:
+    _need_cuda(x, o, weight)
+    if x.shape != o.shape or x.dtype != o.dtype:
+        raise ValueError("x and o must agree in shape and dtype")
+    shape = x.shape
+    x2, o2 = _as_rows(x), _as_rows(o)
+    w = None if weight is None else weight.detach().float().contiguous()
+    y = torch.empty_like(x2)
+    _lib.call("mmf_rmsnorm_swishgate", x2.data_ptr(), o2.data_ptr(), _code(x.dtype), _ptr(w), float(eps), y.data_ptr(),
+              x2.shape[0], x2.shape[1], _stream())
+    return y.reshape(shape)
+
+
+def swiglu(x: torch.Tensor, y: torch.Tensor) -> torch.Tensor:
+    """x * sigmoid(x) * y; x and y may be strided views (e.g. the halves of a chunk(2, -1))."""
+    _need_cuda(x, y)
+    if x.shape != y.shape or x.dtype != y.dtype:
+        raise ValueError("x and y must agree in shape and dtype")
+    shape = x.shape
+    D = shape[-1]
+
+    def rows(t):
+        if t.stride(-1) != 1:
+            return t.contiguous().view(-1, D)
+        if t.dim() == 1:
+            return t.view(1, D)
+        # leading dims collapse into one row index when they are uniformly strided (true for chunk() views)
+        if all(t.stride(i) == t.stride(i + 1) * t.shape[i + 1] for i in range(t.dim() - 2)):
+            return t.as_strided((t.numel() // D, D), (t.stride(-2), 1))
+        return t.contiguous().view(-1, D)
+
+    x2, y2 = rows(x), rows(y)
+    out = torch.empty(x2.shape[0], D, dtype=x.dtype, device=x.device)
+    _lib.call("mmf_swiglu", x2.data_ptr(), x2.stride(0), y2.data_ptr(), y2.stride(0), out.data_ptr(), out.stride(0),
+              _code(x.dtype), x2.shape[0], D, _stream())
+    return out.view(shape)
+
+
+def argmax_rows(logits: torch.Tensor) -> torch.Tensor:
+    _need_cuda(logits)
+    l2 = logits.reshape(-1, logits.shape[-1])
+    if l2.stride(1) != 1:
+        l2 = l2.contiguous()
+    idx = torch.empty(l2.shape[0], dtype=torch.int64, device=logits.device)
+    _lib.call("mmf_argmax_rows", l2.data_ptr(), _code(l2.dtype), l2.stride(0), l2.shape[0], l2.shape[1],
+              idx.data_ptr(), _stream())
+    return idx.reshape(logits.shape[:-1])
+
+
+def embedding(table: torch.Tensor, ids: torch.Tensor) -> torch.Tensor:
+    _need_cuda(table, ids)
+    if ids.dtype != torch.int64:
+        ids = ids.long()
+    flat = ids.reshape(-1).contiguous()
+    table = table.contiguous()
+    out = torch.empty(flat.numel(), table.shape[1], dtype=table.dtype, device=table.device)
+    _lib.call("mmf_embedding", table.data_ptr(), _code(table.dtype), table.shape[0], table.shape[1], flat.data_ptr(),
+              out.data_ptr(), flat.numel(), _stream())
+    return out.reshape(*ids.shape, table.shape[1])
