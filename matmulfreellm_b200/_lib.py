@@ -81,12 +81,19 @@ def load() -> ctypes.CDLL:
     return lib
 
 
+# kernels each entry point launches per successful call (for launch accounting in benchmarks)
+_LAUNCHES = {"mmf_absmean_f32": 2}
+launch_count = 0
+
+
 def call(name: str, *args) -> None:
     """Invoke an int-returning entry point and raise MMFreeError on a negative status."""
+    global launch_count
     lib = load()
     rc = getattr(lib, name)(*args)
     if rc != 0:
         raise MMFreeError(name, rc, lib.mmf_last_error().decode(errors="replace"))
+    launch_count += _LAUNCHES.get(name, 1)
 
 
 _device_checked = set()

@@ -1,0 +1,71 @@
+"""Batch sharding of independent sequences across the GPUs of one box.
+
+Sequences never interact on this path (per-token statistics, per-sequence recurrent state, input-independent
+weight scales), so every rank holds a full replica of the packed weights and runs its contiguous slice of
+the batch with no collective on the data path.  NCCL (or gloo in CPU tests) is used once, to gather the
+generated tokens or logits.
+"""
+from __future__ import annotations
+
+from typing import Optional, Tuple
+
+import torch
+import torch.distributed as dist
+
+
+def shard_range(n_items: int, rank: int, world: int) -> Tuple[int, int]:
+    """Contiguous [lo, hi) slice of `n_items` for `rank`; the first n_items % world ranks get one extra."""
+    if world <= 0 or not 0 <= rank < world:
+        raise ValueError(f"bad rank/world {rank}/{world}")
+    base, extra = divmod(n_items, world)
+    lo = rank * base + min(rank, extra)
+    return lo, lo + base + (1 if rank < extra else 0)
+
+
+def shard_batch(t: torch.Tensor, rank: int, world: int) -> torch.Tensor:
+    lo, hi = shard_range(t.shape[0], rank, world)
+    return t[lo:hi]
+
+
+def gather_batch(local: torch.Tensor, n_total: int, group: Optional[dist.ProcessGroup] = None) -> torch.Tensor:
+    """All-gather the ranks' batch slices (dim 0) back into the full batch, on every rank.
+
+    Shards may be ragged (n_total not divisible by the world size): each rank pads its slice to the largest
+    shard, one all_gather_into_tensor moves the data, and the padding is dropped."""
+    if not dist.is_available() or not dist.is_initialized():
+        if local.shape[0] != n_total:
+            raise ValueError("no process group: the local shard must be the whole batch")
+        return local
+    world, rank = dist.get_world_size(group), dist.get_rank(group)
+    lo, hi = shard_range(n_total, rank, world)
+    if local.shape[0] != hi - lo:
+        raise ValueError(f"rank {rank} holds {local.shape[0]} rows, expected {hi - lo}")
+    width = -(-n_total // world)
+    padded = local
+    if local.shape[0] != width:
+        padded = local.new_zeros((width,) + tuple(local.shape[1:]))
+        padded[: local.shape[0]] = local
+    out = local.new_empty((world * width,) + tuple(local.shape[1:]))
+    dist.all_gather_into_tensor(out, padded.contiguous(), group=group)
+    pieces = []
+    for r in range(world):
+        rlo, rhi = shard_range(n_total, r, world)
+        pieces.append(out[r * width: r * width + (rhi - rlo)])
+    return torch.cat(pieces, dim=0)
+
+
+@torch.no_grad()
+def generate_sharded(model, input_ids: torch.Tensor, max_new_tokens: int, group: Optional[dist.ProcessGroup] = None,
+                     **generate_kwargs) -> torch.Tensor:
+    """Greedy-generate for the full batch `input_ids` [B, T] (identical on every rank): each rank decodes its
+    slice with `model.generate`, then one gather returns [B, T + new] on every rank.  Ranks whose slice is
+    empty (B < world) only take part in the gather."""
+    B = input_ids.shape[0]
+    world = dist.get_world_size(group) if dist.is_initialized() else 1
+    rank = dist.get_rank(group) if dist.is_initialized() else 0
+    mine = shard_batch(input_ids, rank, world)
+    if mine.shape[0]:
+        out = model.generate(mine, max_new_tokens=max_new_tokens, **generate_kwargs)
+    else:
+        out = input_ids.new_empty((0, input_ids.shape[1] + max_new_tokens))
+    return gather_batch(out, B, group)

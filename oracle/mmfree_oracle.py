@@ -273,8 +273,10 @@ class OracleHGRNBit:
         self.w = {k: v.detach().float() for k, v in weights.items()}
         self._codes: Dict[str, Tuple[np.ndarray, np.float32]] = {}
         lb = self.w["model.lower_bounds"].to(dtype)
-        lb = lb.softmax(0)                       # modeling_hgrn_bit.py:231-233
-        self.lower_bounds = lb.cumsum(0) - lb[0]
+        if lb.shape[0]:
+            lb = lb.softmax(0)                   # modeling_hgrn_bit.py:231-233
+            lb = lb.cumsum(0) - lb[0]
+        self.lower_bounds = lb
 
     # -- leaves -------------------------------------------------------------------------
     def _bl(self, x: torch.Tensor, name: str) -> torch.Tensor:

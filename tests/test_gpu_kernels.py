@@ -1,0 +1,325 @@
+"""GPU parity tests of the C-ABI kernels against the CPU oracle (run with `-m gpu` on a B200).
+
+Bit-exact: ternary codes and their packed layout, int8 activation codes, per-row scales, int32
+accumulators, and the fp32 dequantised output (its two fp32 products are ordered the same on both sides).
+Within tolerance: anything that passes through exp / sigmoid or a bf16 rounding (stated per test)."""
+import numpy as np
+import pytest
+import torch
+
+from oracle import mmfree_oracle as O
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def K():
+    from matmulfreellm_b200 import _lib, kernels
+    assert _lib.LIB_PATH.exists(), "libmmfree_b200.so has not been built"
+    assert torch.cuda.is_available()
+    return kernels
+
+
+def dev(t):
+    return t.cuda()
+
+
+# ----------------------------------------------------------------------------------------------------------
+# offline ternarisation + packing
+# ----------------------------------------------------------------------------------------------------------
+@pytest.mark.parametrize("N,Kdim", [(128, 64), (128, 256), (200, 192), (384, 704), (2048, 2048), (2560, 2560)])
+def test_pack_ternary_bit_exact(K, N, Kdim):
+    g = torch.Generator().manual_seed(N * 7 + Kdim)
+    w = torch.randn(N, Kdim, generator=g) * 0.02
+    codes, mean = O.ternary_codes(w)
+    pw = K.pack_weight(dev(w))
+    assert pw.scale.cpu().numpy()[0] == mean
+    got = pw.packed.cpu().numpy().view(np.uint32)
+    assert np.array_equal(got, O.pack_ternary(codes))
+    assert np.array_equal(K.unpack_codes(pw).cpu().numpy(), codes)
+
+
+def test_pack_ternary_edge_values(K):
+    """All-zero weights (mean clamps to 1e-5), exact ties (round half to even) and huge values (clamp to +-1)."""
+    w = torch.zeros(128, 64)
+    pw = K.pack_weight(dev(w))
+    assert pw.scale.item() == np.float32(1e-5) and int(K.unpack_codes(pw).abs().sum()) == 0
+    w = torch.full((128, 64), 1.0)
+    w[0, :8] = torch.tensor([0.5, -0.5, 1.5, -1.5, 2.5, 100.0, -100.0, 0.0])
+    codes, mean = O.ternary_codes(w)
+    pw = K.pack_weight(dev(w))
+    assert pw.scale.item() == mean
+    assert np.array_equal(K.unpack_codes(pw).cpu().numpy(), codes)
+
+
+def test_pack_matches_reference_weight_quant(K, golden):
+    q = golden["quant_cases"]
+    for idx, (M, Kd, N, seed) in enumerate(q["cases"]):
+        _, w, _ = O.bitlinear_case(int(M), int(Kd), int(N), seed=int(seed), dtype=torch.float32)
+        pw = K.pack_weight(dev(w))
+        assert np.array_equal(K.unpack_codes(pw).cpu().numpy(), q[f"c{idx}_wq_sign"])
+
+
+# ----------------------------------------------------------------------------------------------------------
+# RMSNorm + activation quantisation
+# ----------------------------------------------------------------------------------------------------------
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32, torch.float16])
+@pytest.mark.parametrize("M,Kdim", [(1, 256), (7, 704), (16, 2048), (5, 5632), (3, 2560), (2, 6912)])
+def test_act_quant_bit_exact(K, dtype, M, Kdim):
+    x, _, _ = O.bitlinear_case(M, Kdim, 128, seed=M + Kdim, dtype=dtype)
+    g = torch.Generator().manual_seed(5)
+    nw = 1.0 + 0.1 * torch.randn(Kdim, generator=g)
+    for eps, weight in [(1e-6, nw), (1e-8, None)]:
+        q_ref, dq_ref, rs_ref = O.act_codes(x, weight, eps)
+        q, dq, rs = K.act_quant(dev(x), None if weight is None else dev(weight), eps)
+        assert np.array_equal(q.cpu().numpy(), q_ref)
+        assert np.array_equal(dq.cpu().numpy(), dq_ref)
+        assert np.array_equal(rs.cpu().numpy(), rs_ref)
+
+
+def test_act_quant_edge_rows(K):
+    """Zero row (absmax clamps to 1e-5), a row with one huge outlier, no-norm mode, strided input, M = 0."""
+    x = torch.randn(4, 256)
+    x[1] = 0
+    x[2, 17] = 3e4
+    for use_norm in (True, False):
+        q_ref, dq_ref, rs_ref = O.act_codes(x, None, 1e-6, use_norm=use_norm)
+        q, dq, rs = K.act_quant(dev(x), None, 1e-6, use_norm=use_norm)
+        assert np.array_equal(q.cpu().numpy(), q_ref) and np.array_equal(dq.cpu().numpy(), dq_ref)
+        assert np.array_equal(rs.cpu().numpy(), rs_ref)
+    wide = dev(torch.randn(4, 512).bfloat16())
+    view = wide[:, :256]                      # row stride 512
+    q, dq, _ = K.act_quant(view, None, 1e-6)
+    q_ref, dq_ref, _ = O.act_codes(view.cpu(), None, 1e-6)
+    assert np.array_equal(q.cpu().numpy(), q_ref) and np.array_equal(dq.cpu().numpy(), dq_ref)
+    q, dq, rs = K.act_quant(dev(torch.zeros(0, 256)), None, 1e-6)
+    assert q.shape == (0, 256)
+
+
+def test_act_quant_matches_reference_activation_quant(K, golden):
+    """Against the reference's own activation_quant output: identical codes except at rounding ties that its
+    fp32-accumulated row norm resolves the other way."""
+    q = golden["quant_cases"]
+    for idx in range(len(q["cases"])):
+        x, nw, xn = torch.from_numpy(q[f"c{idx}_x"]), torch.from_numpy(q[f"c{idx}_nw"]), q[f"c{idx}_xn"]
+        codes, dq, _ = K.act_quant(dev(x), dev(nw), 1e-8)
+        s = np.float32(127.0) / np.maximum(np.abs(xn).max(-1, keepdims=True), np.float32(1e-5))
+        ref_codes = np.rint(q[f"c{idx}_actq"] * s)
+        pre = xn * s
+        near_tie = np.abs(np.abs(pre - np.floor(pre)) - 0.5) < 1e-3
+        diff = codes.cpu().numpy() != ref_codes
+        assert np.all(~diff | near_tie) and diff.sum() <= 2
+
+
+# ----------------------------------------------------------------------------------------------------------
+# BitLinear contraction
+# ----------------------------------------------------------------------------------------------------------
+def _bitlinear_check(K, M, Kdim, N, kernel, dtype=torch.bfloat16, seed=0):
+    x, w, _ = O.bitlinear_case(M, Kdim, N, seed=seed, dtype=dtype)
+    codes, mean = O.ternary_codes(w)
+    out_ref, acc_ref, q_ref, dq_ref = O.bitlinear_int(x, None, codes, mean, 1e-6, out_dtype=torch.float32)
+    pw = K.pack_weight(dev(w))
+    q, dq, rs = K.act_quant(dev(x), None, 1e-6)
+    assert np.array_equal(q.cpu().numpy(), q_ref)
+    out, acc = K.bitlinear(q, dq, rs, pw, torch.float32, kernel=kernel, return_acc=True)
+    assert np.array_equal(acc.cpu().numpy(), acc_ref), "int32 accumulators differ"
+    assert np.array_equal(out.cpu().numpy(), out_ref.numpy()), "dequantised fp32 output differs"
+    # and the activation-dtype output is the correctly rounded fp32 one
+    out_b = K.bitlinear(q, dq, rs, pw, dtype, kernel=kernel)
+    assert torch.equal(out_b.cpu(), out_ref.to(dtype))
+    # the split-K workspace must be left zeroed: a second call gives the same answer
+    out2 = K.bitlinear(q, dq, rs, pw, torch.float32, kernel=kernel)
+    assert torch.equal(out2, out)
+    return out_ref
+
+
+GEMV_CASES = [(1, 256, 128), (1, 2048, 2048), (2, 704, 256), (3, 2048, 384), (4, 5632, 2048), (5, 2560, 2560),
+              (8, 2048, 11264), (16, 2048, 2048), (33, 704, 256), (1, 2048, 200)]
+
+
+@pytest.mark.parametrize("M,Kdim,N", GEMV_CASES)
+def test_bitlinear_gemv_bit_exact(K, M, Kdim, N):
+    _bitlinear_check(K, M, Kdim, N, K.KERNEL_GEMV)
+
+
+MMA_CASES = [(8, 256, 128), (16, 2048, 2048), (32, 2048, 11264), (64, 5632, 2048), (256, 2560, 2560),
+             (5, 704, 256), (33, 2048, 384), (100, 2048, 200), (256, 2048, 2048), (1, 2048, 2048)]
+
+
+@pytest.mark.parametrize("M,Kdim,N", MMA_CASES)
+def test_bitlinear_mma_bit_exact(K, M, Kdim, N):
+    _bitlinear_check(K, M, Kdim, N, K.KERNEL_MMA)
+
+
+@pytest.mark.parametrize("M", [1, 4, 32])
+def test_bitlinear_grouped(K, M):
+    """Three projections sharing an input row but not a norm weight, run as one grouped launch."""
+    Kdim = N = 256
+    x, _, _ = O.bitlinear_case(M, Kdim, N, seed=3)
+    g = torch.Generator().manual_seed(11)
+    ws = [torch.randn(N, Kdim, generator=g) * 0.02 for _ in range(3)]
+    nws = [1.0 + 0.1 * torch.randn(Kdim, generator=g) for _ in range(3)]
+    pw = K.stack_packed([K.pack_weight(dev(w)) for w in ws])
+    qs = [K.act_quant(dev(x), dev(nw), 1e-6) for nw in nws]
+    q = torch.cat([t[0] for t in qs]); dq = torch.cat([t[1] for t in qs]); rs = torch.cat([t[2] for t in qs])
+    out = K.bitlinear(q, dq, rs, pw, torch.float32)
+    for gi in range(3):
+        codes, mean = O.ternary_codes(ws[gi])
+        ref = O.bitlinear_int(x, nws[gi], codes, mean, 1e-6)[0]
+        assert torch.equal(out[:, gi * N:(gi + 1) * N].cpu(), ref)
+
+
+def test_bitlinear_matches_reference_output(K, golden):
+    """Against BitLinear.forward of the reference (fp32): agreement to fp32 accuracy."""
+    q = golden["quant_cases"]
+    for idx, (M, Kd, N, seed) in enumerate(q["cases"]):
+        x, nw = torch.from_numpy(q[f"c{idx}_x"]), torch.from_numpy(q[f"c{idx}_nw"])
+        _, w, _ = O.bitlinear_case(int(M), int(Kd), int(N), seed=int(seed), dtype=torch.float32)
+        pw = K.pack_weight(dev(w))
+        qq, dq, rs = K.act_quant(dev(x), dev(nw), 1e-8)
+        out = K.bitlinear(qq, dq, rs, pw, torch.float32).cpu().numpy()
+        ref = q[f"c{idx}_y"]
+        d = np.abs(out - ref)
+        # a code flipped at a tie moves one row by <= dq*mean|w| ~ 1e-3 of the output scale
+        assert np.quantile(d, 0.5) <= 2e-6 * np.abs(ref).max() and d.max() <= 5e-3 * np.abs(ref).max()
+
+
+def test_bitlinear_large_m_properties(K):
+    """BASELINE-size M: rows are independent, so a slice of a 4096-row call equals the same rows run alone,
+    and the first rows match the oracle."""
+    M, Kdim, N = 4096, 2048, 2048
+    x, w, _ = O.bitlinear_case(M, Kdim, N, seed=9)
+    pw = K.pack_weight(dev(w))
+    q, dq, rs = K.act_quant(dev(x), None, 1e-6)
+    out, acc = K.bitlinear(q, dq, rs, pw, torch.float32, return_acc=True)
+    sl = slice(1000, 1016)
+    out_s, acc_s = K.bitlinear(q[sl].contiguous(), dq[sl].contiguous(), rs[sl].contiguous(), pw, torch.float32,
+                               return_acc=True)
+    assert torch.equal(out[sl], out_s) and torch.equal(acc[sl], acc_s)
+    codes, mean = O.ternary_codes(w)
+    ref, acc_ref, _, _ = O.bitlinear_int(x[:32], None, codes, mean, 1e-6)
+    assert np.array_equal(acc[:32].cpu().numpy(), acc_ref) and torch.equal(out[:32].cpu(), ref)
+    # column checksum: sum over rows of acc equals (sum of codes rows) . weights, computed in int64
+    colsum = q.long().sum(0).cpu().numpy()
+    assert np.array_equal(acc.long().sum(0).cpu().numpy(), codes.astype(np.int64) @ colsum)
+
+
+# ----------------------------------------------------------------------------------------------------------
+# HGRN recurrence
+# ----------------------------------------------------------------------------------------------------------
+def _hgrn_check(K, x, g, h0, log, rtol_o, rtol_h):
+    o_ref, ht_ref = (O.chunk_hgrn_ref if log else O.naive_recurrent_hgrn)(x, g, h0, True)
+    o, ht = K.hgrn_scan(dev(x), dev(g), None if h0 is None else dev(h0), True, gate_is_log=log,
+                        state_dtype=torch.float32)
+    so = o_ref.float().abs().max().item()
+    assert (o.cpu().float() - o_ref.float()).abs().max().item() <= rtol_o * so
+    assert (ht.cpu() - ht_ref).abs().max().item() <= rtol_h * ht_ref.abs().max().item()
+
+
+def test_hgrn_matches_reference_fixture(K, golden):
+    h = golden["hgrn_cases"]
+    x, g, h0 = (torch.from_numpy(h[k]) for k in ("x", "g", "h0"))
+    o, ht = K.hgrn_scan(dev(x), dev(g), dev(h0), True, gate_is_log=False, state_dtype=torch.float32)
+    assert np.abs(o.cpu().numpy() - h["o"]).max() <= 1e-5 and np.abs(ht.cpu().numpy() - h["ht"]).max() <= 1e-5
+    o, none = K.hgrn_scan(dev(x), dev(g), None, False, gate_is_log=False)
+    assert none is None and np.abs(o.cpu().numpy() - h["o_nostate"]).max() <= 1e-5
+    ob, htb = K.hgrn_scan(dev(x).bfloat16(), dev(g).bfloat16(), dev(h0), True, gate_is_log=False,
+                          state_dtype=torch.float32)
+    # bf16 outputs: one rounding of an fp32 state that matches to 1e-5 -> at most one bf16 ulp (2^-8 relative)
+    assert np.abs(ob.float().cpu().numpy() - h["o_bf16"]).max() <= 2 ** -7 * np.abs(h["o_bf16"]).max()
+    assert np.abs(htb.cpu().numpy() - h["ht_bf16"]).max() <= 1e-4 * np.abs(h["ht_bf16"]).max()
+
+
+@pytest.mark.parametrize("B,T,D", [(2, 1, 64), (3, 37, 72), (2, 300, 256), (1, 2048, 128), (8, 512, 2048)])
+@pytest.mark.parametrize("log", [False, True])
+def test_hgrn_scan_vs_oracle(K, B, T, D, log):
+    """fp32 state: rel 1e-4; bf16 outputs: rel 1e-2 (tolerances of the hot-path specification).  (1,2048,128)
+    takes the time-chunked two-pass path."""
+    x, g_log = O.hgrn_case(B, T, D, seed=B + T, dtype=torch.bfloat16)
+    g = g_log if log else torch.exp(g_log)
+    h0 = torch.randn(B, 1, D, generator=torch.Generator().manual_seed(1))
+    _hgrn_check(K, x, g, h0, log, 1e-2, 1e-4)
+    _hgrn_check(K, x.float(), g, None, log, 1e-4, 1e-4)
+
+
+def test_hgrn_full_size_against_torch_loop(K):
+    """B=8, D=2048, T=2048 (BASELINE size) against a plain fp32 PyTorch loop on the same device."""
+    x, g_log = O.hgrn_case(8, 2048, 2048, seed=0, dtype=torch.bfloat16)
+    xd, gd = dev(x).squeeze(1), dev(g_log).squeeze(1)
+    o, ht = K.hgrn_scan(xd, gd, None, True, gate_is_log=True, state_dtype=torch.float32)
+    h = torch.zeros(8, 2048, device="cuda")
+    f = torch.exp(gd)
+    worst = 0.0
+    for t in range(2048):
+        h = f[:, t] * h + xd[:, t].float()
+        if t % 256 == 255 or t == 2047:
+            worst = max(worst, (o[:, t].float() - h).abs().max().item() / h.abs().max().item())
+    assert worst <= 1e-2
+    assert (ht - h).abs().max().item() <= 1e-4 * h.abs().max().item()
+    # decode-shaped call: B=256, T=1, state updated in place
+    st = torch.randn(256, 2048, device="cuda")
+    x1 = torch.randn(256, 1, 2048, device="cuda").bfloat16()
+    g1 = torch.rand(256, 1, 2048, device="cuda")
+    want = g1[:, 0] * st + x1[:, 0].float()
+    o1, st2 = K.hgrn_scan(x1, g1, st, True, gate_is_log=False, state_dtype=torch.float32, final_state_out=st)
+    assert st2.data_ptr() == st.data_ptr()
+    assert (st - want).abs().max().item() <= 1e-5 and (o1[:, 0].float() - want).abs().max().item() <= 2e-2
+
+
+# ----------------------------------------------------------------------------------------------------------
+# norms, activations, helpers
+# ----------------------------------------------------------------------------------------------------------
+def test_norms_match_reference_fixture(K, golden):
+    n = golden["norm_cases"]
+    x, w, res, og = (dev(torch.from_numpy(n[k])) for k in ("x", "w", "res", "o"))
+    assert np.abs(K.rmsnorm(x, w, 1e-6).cpu().numpy() - n["y"]).max() <= 2e-6
+    y2, r2 = K.rmsnorm(x, w, 1e-6, residual=res, prenorm=True)
+    assert np.abs(y2.cpu().numpy() - n["y_res"]).max() <= 2e-6 and np.array_equal(r2.cpu().numpy(), n["res_out"])
+    assert np.abs(K.rmsnorm_swishgate(x, og, w, 1e-6).cpu().numpy() - n["gate"]).max() <= 5e-6
+    assert np.abs(K.swiglu(x, og).cpu().numpy() - n["swiglu"]).max() <= 5e-6
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16, torch.float32])
+@pytest.mark.parametrize("D", [256, 2048, 100])
+def test_rowwise_ops_vs_oracle(K, dtype, D):
+    g = torch.Generator().manual_seed(D)
+    M = 9
+    x = (torch.randn(M, D, generator=g) * 2).to(dtype)
+    o = torch.randn(M, D, generator=g).to(dtype)
+    res = torch.randn(M, D, generator=g).to(dtype)
+    w = 1.0 + 0.1 * torch.randn(D, generator=g)
+    tol = 1e-5 if dtype == torch.float32 else (2 ** -7 if dtype == torch.bfloat16 else 2 ** -10)
+
+    def close(a, b):
+        return (a.float().cpu() - b.float()).abs().max().item() <= tol * max(1.0, b.float().abs().max().item())
+
+    assert close(K.rmsnorm(dev(x), dev(w), 1e-6), O.rms_norm_ref(x, w, eps=1e-6))
+    y, r = K.rmsnorm(dev(x), dev(w), 1e-6, residual=dev(res), prenorm=True)
+    y_ref, r_ref = O.rms_norm_ref(x, w, residual=res, eps=1e-6, prenorm=True)
+    assert close(y, y_ref) and close(r, r_ref)
+    y, r = K.rmsnorm(dev(x), dev(w), 1e-6, residual=dev(res).float(), prenorm=True)      # fp32 residual stream
+    assert r.dtype == torch.float32 and close(y, y_ref)
+    assert close(K.rmsnorm_swishgate(dev(x), dev(o), dev(w), 1e-6), O.swish_gate_norm_ref(x, o, w, 1e-6))
+    assert close(K.swiglu(dev(x), dev(o)), O.swiglu_ref(x, o))
+
+
+def test_swiglu_on_chunk_views(K):
+    y = torch.randn(2, 5, 512, generator=torch.Generator().manual_seed(0)).bfloat16()
+    gate, up = dev(y).chunk(2, -1)
+    ref = O.swiglu_ref(*y.chunk(2, -1))
+    assert (K.swiglu(gate, up).cpu().float() - ref.float()).abs().max().item() <= 2 ** -7 * ref.float().abs().max().item()
+
+
+def test_argmax_and_embedding(K):
+    g = torch.Generator().manual_seed(0)
+    logits = torch.randn(7, 32000, generator=g)
+    logits[3, 100] = logits[3, 20000] = 50.0          # tie -> first index
+    for dt in (torch.float32, torch.bfloat16):
+        l = logits.to(dt)
+        assert torch.equal(K.argmax_rows(dev(l)).cpu(), l.float().argmax(-1))
+    assert K.argmax_rows(dev(logits))[3].item() == 100
+    table = torch.randn(1000, 256, generator=g).bfloat16()
+    ids = torch.randint(0, 1000, (3, 5), generator=g)
+    assert torch.equal(K.embedding(dev(table), dev(ids)).cpu(), table[ids])
+EOF
+echo written

@@ -1,0 +1,204 @@
+"""GPU parity tests of the mirrored `mmfreelm` API (modules, layer, model, generate) against the CPU oracle
+and the reference fixtures.  Run with `-m gpu` on a B200."""
+import numpy as np
+import pytest
+import torch
+
+from oracle import mmfree_oracle as O
+
+pytestmark = pytest.mark.gpu
+
+
+def _close_up_to_code_flips(got, ref, typical, worst):
+    """See tests/test_oracle_golden.py: quantisation is discontinuous, so two correct implementations agree
+    to `typical` on almost every element and to `worst` on all (relative to max|ref|)."""
+    scale = np.abs(ref).max()
+    d = np.abs(got - ref)
+    assert np.quantile(d, 0.5) <= typical * scale, ("typical", np.quantile(d, 0.5) / scale)
+    assert d.max() <= worst * scale, ("worst", d.max() / scale)
+
+
+@pytest.fixture(scope="module")
+def mm():
+    import matmulfreellm_b200 as pkg
+    pkg.install_as_mmfreelm()
+    assert torch.cuda.is_available()
+    return pkg
+
+
+def tiny_cfg():
+    return O.OracleConfig(vocab_size=32000, hidden_size=256, num_hidden_layers=2, intermediate_size=704)
+
+
+def build_gpu_model(sd, cfg, dtype):
+    """Load the oracle's fp32 state dict into the CUDA model, pack from fp32, then cast."""
+    from mmfreelm.models import HGRNBitConfig, HGRNBitForCausalLM
+    hf = HGRNBitConfig(vocab_size=cfg.vocab_size, hidden_size=cfg.hidden_size, num_hidden_layers=cfg.num_hidden_layers,
+                       intermediate_size=cfg.intermediate_size, rms_norm_eps=cfg.rms_norm_eps)
+    model = HGRNBitForCausalLM(hf).eval()
+    missing, unexpected = model.load_state_dict(sd, strict=True)
+    assert not missing and not unexpected
+    model = model.cuda()
+    model.pack_weights()
+    return model.to(dtype)
+
+
+def test_mmfreelm_import_paths(mm):
+    import mmfreelm
+    from mmfreelm import HGRNBitForCausalLM, HGRNBitModel  # noqa: F401
+    from mmfreelm.layers import HGRNBitAttention  # noqa: F401
+    from mmfreelm.models import HGRNBitConfig  # noqa: F401
+    from mmfreelm.models.utils import RecurrentCache  # noqa: F401
+    from mmfreelm.modules import FusedRMSNormSwishGate, RMSNorm  # noqa: F401
+    from mmfreelm.modules.activations import swiglu  # noqa: F401
+    from mmfreelm.ops import fused_recurrent_hgrn  # noqa: F401
+    from mmfreelm.ops.fusedbitnet import BitLinear, FusedBitLinear, activation_quant, weight_quant  # noqa: F401
+    from mmfreelm.ops.hgrn import chunk_hgrn  # noqa: F401
+    assert mmfreelm.__version__ == "0.1"
+
+
+def test_fused_bitlinear_module(mm):
+    """FusedBitLinear(x) for bf16 [..., K] input: equal to the integer oracle rounded to bf16; and within the
+    stated bf16 tolerance (rel 1e-2) of the reference's float BitLinear math."""
+    from mmfreelm.ops.fusedbitnet import BitLinear, FusedBitLinear, activation_quant, weight_quant
+    x, w, _ = O.bitlinear_case(2 * 5, 2048, 384, seed=4)
+    g = torch.Generator().manual_seed(8)
+    nw = 1.0 + 0.1 * torch.randn(2048, generator=g)
+    for cls, eps in ((FusedBitLinear, 1e-6), (BitLinear, 1e-8)):
+        lin = cls(2048, 384)
+        with torch.no_grad():
+            lin.weight.copy_(w)
+            lin.norm.weight.copy_(nw)
+        lin = lin.cuda()
+        y = lin(x.view(2, 5, 2048).cuda())
+        assert y.shape == (2, 5, 384) and y.dtype == torch.bfloat16
+        codes, mean = O.ternary_codes(w)
+        ref_int = O.bitlinear_int(x, nw, codes, mean, eps, out_dtype=torch.bfloat16)[0]
+        assert torch.equal(y.cpu().view(10, 384), ref_int)
+        ref_float = O.bitlinear_ref(x.float(), nw, w, eps=eps)
+        assert (y.cpu().float().view(10, 384) - ref_float).abs().max() <= 1e-2 * ref_float.abs().max()
+    xf = torch.randn(6, 256, generator=g)
+    assert torch.allclose(activation_quant(xf.cuda()).cpu(), O.activation_quant(xf), rtol=1e-6, atol=1e-7)
+    wf = torch.randn(128, 256, generator=g) * 0.02
+    assert torch.allclose(weight_quant(wf.cuda()).cpu(), O.weight_quant(wf), rtol=1e-6, atol=1e-9)
+
+
+def test_hgrn_ops_reference_selfcheck_shapes(mm):
+    """The reference's own self-check (recurrent_fuse.py:188-217): B,H,T,D = 8,4,512,128, bf16, seed 42,
+    g = sigmoid(randn), x = (1-g)*randn, random h0 — fused op against the naive loop."""
+    from mmfreelm.ops.hgrn import chunk_hgrn, fused_recurrent_hgrn
+    torch.manual_seed(42)
+    B, H, T, D = 8, 4, 512, 128
+    g = torch.randn(B, H, T, D).sigmoid()
+    x = ((1 - g) * torch.randn(B, H, T, D)).bfloat16()
+    g = g.bfloat16()
+    h0 = torch.randn(B, H, D).bfloat16()
+    o_ref, ht_ref = O.naive_recurrent_hgrn(x, g, h0, True)
+    o, ht = fused_recurrent_hgrn(x.cuda(), g.cuda(), h0.cuda(), output_final_state=True)
+    assert o.dtype == torch.bfloat16 and ht.dtype == torch.bfloat16 and ht.shape == (B, H, D)
+    assert (o.cpu().float() - o_ref.float()).abs().max() <= 1e-2 * o_ref.float().abs().max()
+    assert (ht.cpu().float() - ht_ref).abs().max() <= 1e-2 * ht_ref.abs().max()
+    o2, none = fused_recurrent_hgrn(x.cuda(), g.cuda())
+    assert none is None
+    # chunk_hgrn takes the LOG gate and returns an fp32 state
+    oc, htc = chunk_hgrn(x.cuda(), g.float().log().cuda(), h0.cuda(), output_final_state=True)
+    assert htc.dtype == torch.float32
+    assert (oc.cpu().float() - o_ref.float()).abs().max() <= 1e-2 * o_ref.float().abs().max()
+    assert (htc.cpu() - ht_ref).abs().max() <= 1e-4 * ht_ref.abs().max()
+
+
+def test_norm_modules(mm):
+    from mmfreelm.modules import FusedRMSNormSwishGate, RMSNorm
+    g = torch.Generator().manual_seed(3)
+    x = torch.randn(2, 7, 256, generator=g).bfloat16()
+    o = torch.randn(2, 7, 256, generator=g).bfloat16()
+    res = torch.randn(2, 7, 256, generator=g).bfloat16()
+    norm = RMSNorm(256, eps=1e-6).cuda()
+    gate = FusedRMSNormSwishGate(256, eps=1e-6).cuda()
+    w = torch.ones(256)
+    y, r = norm(x.cuda(), res.cuda(), True)
+    y_ref, r_ref = O.rms_norm_ref(x, w, residual=res, eps=1e-6, prenorm=True)
+    assert (y.cpu().float() - y_ref.float()).abs().max() <= 2 ** -7 * y_ref.float().abs().max()
+    assert torch.equal(r.cpu(), r_ref)
+    yg = gate(x.cuda(), o.cuda())
+    ref = O.swish_gate_norm_ref(x, o, w, 1e-6)
+    assert (yg.cpu().float() - ref.float()).abs().max() <= 2 ** -7 * ref.float().abs().max()
+    assert "RMSNorm(256, eps=1e-06)" == repr(norm)
+
+
+def test_tiny_model_fp32_vs_oracle_and_reference(mm, golden):
+    """BASELINE config 1 (2 layers, hidden 256, intermediate 704, vocab 32000, batch 2 x 128, fp32): logits and
+    final HGRN states against the integer oracle and against the reference's own output."""
+    g = golden["tiny_model"]
+    cfg = tiny_cfg()
+    sd = O.random_weights(cfg, seed=0)
+    sd["model.lower_bounds"] = torch.from_numpy(g["lower_bounds"])
+    ids = torch.from_numpy(g["ids"])
+    model = build_gpu_model(sd, cfg, torch.float32)
+    out = model(ids.cuda(), use_cache=True)
+    logits = out.logits.cpu()
+    states = [s[0].cpu() for s in out.past_key_values]
+    assert logits.shape == (2, 128, 32000) and states[0].shape == (2, 1, 256) and states[0].dtype == torch.float32
+
+    oracle = O.OracleHGRNBit(cfg, sd, dtype=torch.float32, linear="int", bitlinear_eps=1e-6)
+    ref_logits, ref_states = oracle.forward(ids)
+    _close_up_to_code_flips(logits.numpy(), ref_logits.numpy(), 2e-6, 2e-2)
+    for s, r in zip(states, ref_states):
+        _close_up_to_code_flips(s.numpy(), r.numpy(), 1e-5, 2e-2)      # fp32 state: typical << 1e-4
+    assert (logits.argmax(-1) == ref_logits.argmax(-1)).float().mean() >= 0.97
+
+    # the reference itself (its CPU-runnable variant uses eps 1e-8 inside BitLinear, the GPU path 1e-6)
+    _close_up_to_code_flips(logits[:, g["logits_pos"]].numpy(), g["logits_at"], 5e-5, 5e-2)
+    for i, s in enumerate(states):
+        _close_up_to_code_flips(s.numpy(), g["states"][i], 5e-5, 5e-2)
+
+    # prefill + one cached step == one longer forward (incremental decoding is consistent)
+    full = model(ids[:, :65].cuda(), use_cache=False).logits[:, -1]
+    o1 = model(ids[:, :64].cuda(), use_cache=True)
+    o2 = model(ids[:, 64:65].cuda(), past_key_values=o1.past_key_values, use_cache=True).logits[:, -1]
+    _close_up_to_code_flips(o2.cpu().numpy(), full.cpu().numpy(), 2e-6, 2e-2)
+
+
+@pytest.mark.parametrize("dtype,typical,worst", [(torch.float32, 1e-5, 3e-2), (torch.bfloat16, 1e-2, 1e-1)])
+def test_greedy_decode_64_steps_matches_oracle(mm, dtype, typical, worst):
+    """Greedy decoding for 64 steps, batch 2, prompt 32.  Tokens must equal the oracle's; because a random-init
+    model has near-flat logits, a sequence may leave the oracle's path only at a step where the oracle's own
+    top-2 margin is below the code-flip noise, and the teacher-forced logits must stay within tolerance."""
+    cfg = tiny_cfg()
+    sd = O.random_weights(cfg, seed=5)
+    ids = torch.randint(0, 32000, (2, 32), generator=torch.Generator().manual_seed(6))
+    model = build_gpu_model(sd, cfg, dtype)
+    oracle = O.OracleHGRNBit(cfg, sd, dtype=dtype, linear="int", bitlinear_eps=1e-6)
+    ref_tokens, margins = oracle.greedy(ids, 64)
+    got = model.generate(ids.cuda(), max_new_tokens=64)
+    assert got.shape == (2, 96) and torch.equal(got[:, :32].cpu(), ids)
+    new = got[:, 32:].cpu()
+    same = new == ref_tokens
+    noise = worst * 0.5      # logit scale ~0.5 for this model
+    for b in range(2):
+        if not same[b].all():
+            first = int(torch.nonzero(~same[b])[0])
+            assert margins[b, first] < noise, f"sequence {b} diverged at step {first} with margin {margins[b, first]}"
+    # teacher-forced: feed the oracle's tokens and compare every step's logits
+    seq = torch.cat([ids, ref_tokens], 1)
+    ref_logits, _ = oracle.forward(seq)
+    logits = model(seq.cuda(), use_cache=False).logits.float().cpu()
+    _close_up_to_code_flips(logits.numpy(), ref_logits.float().numpy(), typical, worst)
+    print(f"[greedy {dtype}] identical tokens: {same.float().mean().item():.3f}; min oracle top-2 margin "
+          f"{margins.min().item():.2e}")
+
+
+def test_generate_api(mm):
+    cfg = tiny_cfg()
+    sd = O.random_weights(cfg, seed=1)
+    model = build_gpu_model(sd, cfg, torch.bfloat16)
+    ids = torch.randint(0, 32000, (3, 5), generator=torch.Generator().manual_seed(0)).cuda()
+    a = model.generate(ids, max_new_tokens=4)
+    b = model.generate(ids, max_length=9)
+    assert a.shape == (3, 9) and torch.equal(a, b)
+    with pytest.raises(ValueError):
+        model.model(input_ids=ids, inputs_embeds=torch.zeros(3, 5, 256, device="cuda"))
+    with pytest.raises(ValueError):
+        model.model()
+    with pytest.raises(NotImplementedError):
+        model.generate(ids, do_sample=True)
