@@ -133,6 +133,8 @@ def act_quant(x: torch.Tensor, norm_weight: Optional[torch.Tensor], eps: float, 
         rs = torch.empty(M, dtype=torch.int32, device=x.device)
     else:
         q, dq, rs = out
+    if M == 0:
+        return q, dq, rs
     _lib.call("mmf_act_quant", x.data_ptr(), _code(x.dtype), x.stride(0), _ptr(norm_weight), int(use_norm), float(eps),
               q.data_ptr(), dq.data_ptr(), rs.data_ptr(), M, K, _stream())
     return q, dq, rs
@@ -170,6 +172,8 @@ def bitlinear(q: torch.Tensor, dq: torch.Tensor, rowsum: torch.Tensor, pw: Packe
     elif out.shape != (M, pw.N) or out.stride(1) != 1 or out.dtype != out_dtype:
         raise ValueError("bad `out` tensor")
     acc = torch.empty(M, pw.N, dtype=torch.int32, device=q.device) if return_acc else None
+    if M == 0:
+        return (out, acc) if return_acc else out
     nbytes = _lib.load().mmf_bitlinear_workspace_bytes(M, pw.N, pw.K)
     ws = _workspace(q.device, nbytes)
     try:

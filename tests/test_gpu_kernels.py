@@ -321,5 +321,3 @@ def test_argmax_and_embedding(K):
     table = torch.randn(1000, 256, generator=g).bfloat16()
     ids = torch.randint(0, 1000, (3, 5), generator=g)
     assert torch.equal(K.embedding(dev(table), dev(ids)).cpu(), table[ids])
-EOF
-echo written

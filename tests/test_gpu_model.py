@@ -147,10 +147,19 @@ def test_tiny_model_fp32_vs_oracle_and_reference(mm, golden):
         _close_up_to_code_flips(s.numpy(), r.numpy(), 1e-5, 2e-2)      # fp32 state: typical << 1e-4
     assert (logits.argmax(-1) == ref_logits.argmax(-1)).float().mean() >= 0.97
 
-    # the reference itself (its CPU-runnable variant uses eps 1e-8 inside BitLinear, the GPU path 1e-6)
-    _close_up_to_code_flips(logits[:, g["logits_pos"]].numpy(), g["logits_at"], 5e-5, 5e-2)
-    for i, s in enumerate(states):
-        _close_up_to_code_flips(s.numpy(), g["states"][i], 5e-5, 5e-2)
+    # the reference itself: its CPU-runnable variant (BitLinear.forward) uses eps 1e-8 inside BitLinear where
+    # the fused GPU call uses 1e-6, so the fixture is compared with the modules switched to 1e-8
+    from mmfreelm.ops.fusedbitnet import BitLinear
+    for m in model.modules():
+        if isinstance(m, BitLinear):
+            m.NORM_EPS = 1e-8
+    out8 = model(ids.cuda(), use_cache=True)
+    _close_up_to_code_flips(out8.logits[:, g["logits_pos"]].cpu().numpy(), g["logits_at"], 2e-5, 5e-2)
+    for i, s in enumerate(out8.past_key_values):
+        _close_up_to_code_flips(s[0].cpu().numpy(), g["states"][i], 2e-5, 5e-2)
+    for m in model.modules():
+        if isinstance(m, BitLinear):
+            del m.NORM_EPS
 
     # prefill + one cached step == one longer forward (incremental decoding is consistent)
     full = model(ids[:, :65].cuda(), use_cache=False).logits[:, -1]
