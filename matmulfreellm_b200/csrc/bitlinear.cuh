@@ -19,7 +19,10 @@ struct BitLinearArgs {
     int64_t ws_bytes;
 };
 
-// workspace geometry (in 32-bit words): [counters: n_tiles * MMF_WS_MBLK] [acc: min(M,MMF_SPLITK_MAX_M) * n_tiles*128]
+// workspace geometry (in 32-bit words):
+//   [header: MMF_WS_HEADER words, word 0 = status (0 = ok, 1 = a bounded device-side wait gave up)]
+//   [counters: n_tiles * MMF_WS_MBLK] [acc: min(M,MMF_SPLITK_MAX_M) * n_tiles*128]
+constexpr int MMF_WS_HEADER = 64;
 constexpr int MMF_WS_MBLK = 64;
 constexpr int MMF_SPLITK_MAX_M = 256;
 

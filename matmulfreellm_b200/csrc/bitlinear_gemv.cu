@@ -72,8 +72,8 @@ bitlinear_gemv_kernel(BitLinearArgs a, int KC, int kc_per_cta, int ksplit, int n
     const int Npad = n_tiles * MMF_TILE_ROWS;
     bool do_epilogue = true;
     if (ksplit > 1) {
-        uint32_t* cnt = reinterpret_cast<uint32_t*>(a.ws) + tile * MMF_WS_MBLK + mblk;
-        int32_t* wacc = a.ws + (int64_t)n_tiles * MMF_WS_MBLK;
+        uint32_t* cnt = reinterpret_cast<uint32_t*>(a.ws) + MMF_WS_HEADER + tile * MMF_WS_MBLK + mblk;
+        int32_t* wacc = a.ws + MMF_WS_HEADER + (int64_t)n_tiles * MMF_WS_MBLK;
 #pragma unroll
         for (int m = 0; m < MB; ++m)
             if (m0 + m < a.M) atomicAdd(wacc + (int64_t)(m0 + m) * Npad + n, acc[m]);
@@ -118,7 +118,7 @@ int bitlinear_gemv_launch(const BitLinearArgs& a, cudaStream_t st) {
     const int MB = a.M <= 1 ? 1 : a.M <= 2 ? 2 : a.M <= 4 ? 4 : 8;
     const int mblocks = (a.M + MB - 1) / MB;
     int ksplit = 1;
-    const int64_t need_words = (int64_t)n_tiles * MMF_WS_MBLK + (int64_t)a.M * n_tiles * MMF_TILE_ROWS;
+    const int64_t need_words = MMF_WS_HEADER + (int64_t)n_tiles * MMF_WS_MBLK + (int64_t)a.M * n_tiles * MMF_TILE_ROWS;
     const bool can_split = a.ws && a.M <= MMF_SPLITK_MAX_M && mblocks <= MMF_WS_MBLK && a.ws_bytes >= need_words * 4;
     if (can_split) {
         const int64_t base = (int64_t)n_tiles * mblocks;
@@ -159,7 +159,7 @@ extern "C" int64_t mmf_bitlinear_workspace_bytes(int64_t M, int64_t N, int64_t K
     if (M <= 0 || N <= 0 || K <= 0) return 0;
     const int64_t n_tiles = (N + MMF_TILE_ROWS - 1) / MMF_TILE_ROWS;
     const int64_t rows = M < MMF_SPLITK_MAX_M ? M : MMF_SPLITK_MAX_M;
-    const int64_t words = n_tiles * MMF_WS_MBLK + rows * n_tiles * MMF_TILE_ROWS;
+    const int64_t words = MMF_WS_HEADER + n_tiles * MMF_WS_MBLK + rows * n_tiles * MMF_TILE_ROWS;
     return ((words * 4 + 255) / 256) * 256;
 }
 

@@ -153,6 +153,17 @@ def _workspace(device: torch.device, nbytes: int) -> torch.Tensor:
     return ws
 
 
+def check_status() -> None:
+    """Synchronise and raise if any BitLinear kernel reported a device-side wait that gave up (status word
+    at the start of the split-K workspace).  Costs a device sync; meant for tests and debugging."""
+    for key, ws in list(_ws_cache.items()):
+        torch.cuda.synchronize(ws.device)
+        status = int(ws[:4].view(torch.int32).item())
+        if status != 0:
+            _ws_cache.pop(key, None)
+            raise _lib.MMFreeError("mmf_bitlinear", -7, f"device-side wait timed out (status word {status})")
+
+
 def bitlinear(q: torch.Tensor, dq: torch.Tensor, rowsum: torch.Tensor, pw: PackedWeight, out_dtype: torch.dtype,
               kernel: int = KERNEL_AUTO, return_acc: bool = False, out: Optional[torch.Tensor] = None):
     """Integer BitLinear contraction + dequantising epilogue.
