@@ -125,7 +125,8 @@ int mmf_act_quant(const void* x, int dtype, int64_t ld_x, const float* norm_w, i
 #define MMF_MMA_MIN_M 5
 
 /* Bytes of int32 workspace mmf_bitlinear may need for split-K partial sums (a multiple of
- * 256; includes the tile counters).  The workspace must be ZERO before its first use; the
+ * 256; includes a 256-byte header whose first word is a status flag — 0, or 1 if a bounded
+ * device-side wait gave up — and the tile counters).  The workspace must be ZERO before its first use; the
  * kernels leave it zero again, so it can be reused by the next call on the same stream.
  * Concurrent calls on different streams need separate workspaces. */
 int64_t mmf_bitlinear_workspace_bytes(int64_t M, int64_t N, int64_t K);
@@ -163,6 +164,54 @@ int64_t mmf_hgrn_workspace_bytes(int64_t B, int64_t T, int64_t D);
 int mmf_hgrn_scan(const void* x, int x_dtype, const void* g, int g_dtype, const void* h0,
                   void* ht, int state_dtype, void* o, int64_t B, int64_t T, int64_t D,
                   int gate_is_log, void* workspace, int64_t workspace_bytes, void* stream);
+
+/* Gated recurrence straight from the raw i/f projection outputs, i.e. the element-wise glue of
+ * HGRNBitAttention.forward fused into the scan: mmfreelm/layers/hgrn_bit.py:113-125
+ *   f = sigmoid(f_raw);  if lower_bound: f = lb + (1 - lb) * f;  x = silu(i_raw) * (1 - f);
+ *   h_t = f_t * h_{t-1} + x_t;  o_t = h_t
+ * with every intermediate rounded to `dtype` where the reference materialises a tensor.
+ * i_raw, f_raw: [B, T, *] rows `ld` elements apart (two column slabs of one projection output);
+ * lower_bound: [D] of `dtype` or NULL; state: fp32 [B, D], read as h_0 and overwritten with h_T
+ * (decode-step update in place when T = 1); o: [B, T, D] contiguous.  D % 8 == 0.
+ * workspace: mmf_hgrn_workspace_bytes(B, T, D) bytes. */
+int mmf_hgrn_gated(const void* i_raw, const void* f_raw, int64_t ld, int dtype,
+                   const void* lower_bound, float* state, void* o, int64_t B, int64_t T, int64_t D,
+                   void* workspace, int64_t workspace_bytes, void* stream);
+
+/* ------------------------------------------------------------------------------------
+ * Fused producers of BitLinear inputs: each emits the int8 codes (+ dq, rowsum, laid out
+ * [groups][M][D] / [groups][M]) that mmf_bitlinear consumes, so no activation tensor is
+ * written between two contractions.  D % 16 == 0, D <= 16384, rows 16-byte aligned.
+ * ------------------------------------------------------------------------------------ */
+
+/* s = x [+ residual]; residual_out = s (optional); y = rmsnorm(s; norm_w, eps_norm) rounded to
+ * `dtype` (optionally stored to y_out); then for each of `groups` (0, 1 or 3) BitLinear norm
+ * weights nw_g: codes of rmsnorm(y; nw_g, eps_bl) as in mmf_act_quant.
+ * round_sum_first = 1 rounds s to `dtype` before the statistics (the reference's separate
+ * `residual + hidden_states` tensor add, modeling_hgrn_bit.py:109, followed by the next block's
+ * attn_norm, :98); 0 normalises the fp32 sum (the fused add of mlp_norm, :107, i.e.
+ * _layer_norm_fwd_1pass_kernel, modules/layernorm.py:136-153).
+ * Replaces: HGRNBitBlock.forward's attn_norm / mlp_norm (modeling_hgrn_bit.py:98,107) followed by
+ * the RMSNorm+quant prologue of the BitLinears they feed (ops/fusedbitnet.py:63-131). */
+int mmf_prenorm_quant(const void* x, int64_t ld_x, const void* residual, int64_t ld_res, int dtype,
+                      int round_sum_first, const float* norm_w, float eps_norm, void* residual_out,
+                      void* y_out, int groups, const float* nw0, const float* nw1, const float* nw2,
+                      float eps_bl, int8_t* q, float* dq, int32_t* rowsum, int64_t M, int64_t D,
+                      void* stream);
+
+/* y = (rmsnorm(g; gnorm_w, eps_g)) * o * sigmoid(o) rounded to `dtype`, then the BitLinear
+ * prologue with norm weight nw.  Replaces: FusedRMSNormSwishGate (modules/fused_norm_gate.py:68-131)
+ * + o_proj's prologue, layers/hgrn_bit.py:139-140. */
+int mmf_gatenorm_quant(const void* g, int64_t ld_g, const void* o, int64_t ld_o, int dtype,
+                       const float* gnorm_w, float eps_g, const float* nw, float eps_bl, int8_t* q,
+                       float* dq, int32_t* rowsum, int64_t M, int64_t D, void* stream);
+
+/* z = silu(gate) * up rounded to `dtype`, then the BitLinear prologue with norm weight nw.
+ * gate/up: the two halves of gate_proj's output, rows `ld` elements apart.
+ * Replaces: swiglu (modules/activations.py:115-119) + down_proj's prologue, modeling_hgrn_bit.py:57-58. */
+int mmf_swiglu_quant(const void* gate, const void* up, int64_t ld, int dtype, const float* nw,
+                     float eps_bl, int8_t* q, float* dq, int32_t* rowsum, int64_t M, int64_t D,
+                     void* stream);
 
 /* ------------------------------------------------------------------------------------
  * Row-wise norms and activations.

@@ -39,6 +39,15 @@ PROTOTYPES = {
     "mmf_hgrn_workspace_bytes": (c_int64, [c_int64, c_int64, c_int64]),
     "mmf_hgrn_scan": (c_int, [c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_int, c_void_p, c_int64,
                               c_int64, c_int64, c_int, c_void_p, c_int64, c_void_p]),
+    "mmf_hgrn_gated": (c_int, [c_void_p, c_void_p, c_int64, c_int, c_void_p, c_void_p, c_void_p, c_int64, c_int64,
+                               c_int64, c_void_p, c_int64, c_void_p]),
+    "mmf_prenorm_quant": (c_int, [c_void_p, c_int64, c_void_p, c_int64, c_int, c_int, c_void_p, c_float, c_void_p,
+                                  c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_float, c_void_p, c_void_p, c_void_p,
+                                  c_int64, c_int64, c_void_p]),
+    "mmf_gatenorm_quant": (c_int, [c_void_p, c_int64, c_void_p, c_int64, c_int, c_void_p, c_float, c_void_p, c_float,
+                                   c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_void_p]),
+    "mmf_swiglu_quant": (c_int, [c_void_p, c_void_p, c_int64, c_int, c_void_p, c_float, c_void_p, c_void_p, c_void_p,
+                                 c_int64, c_int64, c_void_p]),
     "mmf_rmsnorm": (c_int, [c_void_p, c_int, c_void_p, c_int, c_void_p, c_float, c_void_p, c_void_p, c_int64,
                             c_int64, c_void_p]),
     "mmf_rmsnorm_swishgate": (c_int, [c_void_p, c_void_p, c_int, c_void_p, c_float, c_void_p, c_int64, c_int64,

@@ -16,8 +16,10 @@
 // bounded and reports through a status word instead of hanging.
 //
 // Weights are stored biased (+1); sum_k (t+1)*x = acc + rowsum(x) and the epilogue subtracts the
-// per-token code sum.  For few tokens the K range is split over CTAs to fill the GPU; partial
-// tiles meet in an int32 workspace with atomics (deterministic), the last CTA dequantises.
+// per-token code sum.  For few tokens the K range is split over the CTAs of a thread-block cluster
+// (2, 4 or 8) to fill the GPU; each CTA parks its partial int32 tile in its own shared memory and,
+// after a cluster barrier, reduces its share of the token columns over its peers' tiles through
+// distributed shared memory (integer adds: deterministic) and dequantises them.
 #include <cuda.h>
 
 #include "bitlinear.cuh"
@@ -145,6 +147,17 @@ __device__ __forceinline__ void named_bar_sync(int id, int count) {
     asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(count) : "memory");
 }
 
+__device__ __forceinline__ void cluster_sync_all() {
+    asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ int32_t ld_peer_s32(const void* my_smem, uint32_t peer_rank) {
+    uint32_t remote;
+    int32_t v;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(smem_u32(my_smem)), "r"(peer_rank));
+    asm volatile("ld.shared::cluster.s32 %0, [%1];" : "=r"(v) : "r"(remote) : "memory");
+    return v;
+}
+
 // K-major operand tile in shared memory, 128-byte swizzle: rows of 128 bytes, 8-row groups 1024 B apart.
 __device__ __forceinline__ uint64_t make_b_desc(uint32_t smem_addr) {
     uint64_t d = 0;
@@ -175,7 +188,6 @@ bitlinear_mma_kernel(const __grid_constant__ CUtensorMap q_map, BitLinearArgs a,
     __shared__ Barriers bars;
     __shared__ uint32_t s_tmem_base;
     __shared__ int s_abort;
-    __shared__ int s_last;
     __shared__ float s_dq[256];
     __shared__ int s_rs[256];
 
@@ -292,23 +304,21 @@ bitlinear_mma_kernel(const __grid_constant__ CUtensorMap q_map, BitLinearArgs a,
         // epilogue: thread <-> weight row n, columns <-> tokens
         ok = __all_sync(0xffffffffu, ok && mbar_wait(&bars.acc_full, 0, abort_flag));
         tc_fence_after();
-        const int n = tile * MMF_TILE_ROWS + tid;
-        const int Npad = p.n_tiles * MMF_TILE_ROWS;
-        const float wsc = a.w_scale[g];
-        uint32_t* cnt = reinterpret_cast<uint32_t*>(a.ws) + MMF_WS_HEADER + tile * MMF_WS_MBLK + mt;
-        int32_t* wacc = a.ws + MMF_WS_HEADER + (int64_t)p.n_tiles * MMF_WS_MBLK;
         if (ok) {
+            const int n = tile * MMF_TILE_ROWS + tid;
+            const float wsc = a.w_scale[g];
+            int32_t* part = reinterpret_cast<int32_t*>(b_ring);   // [NT][128] partial tile (the ring is idle now)
             for (int c0 = 0; c0 < p.NT; c0 += 16) {
                 uint32_t v[16];
                 tmem_ld16(tmem_base + lane_addr + c0, v);
                 tmem_wait_ld();
 #pragma unroll
                 for (int j = 0; j < 16; ++j) {
-                    const int m = m0 + c0 + j;
-                    if (m < a.M) {
-                        if (p.ksplit > 1) {
-                            atomicAdd(wacc + (int64_t)m * Npad + n, (int32_t)v[j]);
-                        } else if (n < a.N) {
+                    if (p.ksplit > 1) {
+                        part[(c0 + j) * MMF_TILE_ROWS + tid] = (int32_t)v[j];
+                    } else {
+                        const int m = m0 + c0 + j;
+                        if (m < a.M && n < a.N) {
                             const int32_t acc = (int32_t)v[j] - s_rs[c0 + j];
                             if (a.acc_out) a.acc_out[(int64_t)m * a.N + n] = acc;
                             store_out(a.out, a.out_dtype, (int64_t)m * a.ld_out + n, bitlinear_dequant(acc, s_dq[c0 + j], wsc));
@@ -316,27 +326,29 @@ bitlinear_mma_kernel(const __grid_constant__ CUtensorMap q_map, BitLinearArgs a,
                     }
                 }
             }
-            if (p.ksplit > 1) {
-                __threadfence();
-                named_bar_sync(1, 128);
-                if (tid == 0) s_last = (atomicAdd(cnt, 1u) == (uint32_t)(p.ksplit - 1));
-                named_bar_sync(1, 128);
-                if (s_last) {
-                    __threadfence();
-                    const int mend = min(a.M, m0 + p.NT);
-                    for (int m = m0; m < mend; ++m) {
-                        int32_t* ptr = wacc + (int64_t)m * Npad + n;
-                        const int32_t acc = __ldcg(ptr) - s_rs[m - m0];
-                        __stcg(ptr, 0);
-                        if (n < a.N) {
-                            if (a.acc_out) a.acc_out[(int64_t)m * a.N + n] = acc;
-                            store_out(a.out, a.out_dtype, (int64_t)m * a.ld_out + n, bitlinear_dequant(acc, s_dq[m - m0], wsc));
-                        }
-                    }
-                    if (tid == 0) *cnt = 0u;
+        }
+    }
+
+    if (p.ksplit > 1) {
+        // split-K: every CTA of the cluster has parked its partial tile; reduce my share of the token columns
+        cluster_sync_all();
+        if (warp < 4 && !*abort_flag) {
+            const int n = tile * MMF_TILE_ROWS + tid;
+            const float wsc = a.w_scale[g];
+            const int32_t* part = reinterpret_cast<const int32_t*>(b_ring);
+            const int per = p.NT / p.ksplit;
+            for (int c = ks * per; c < (ks + 1) * per; ++c) {
+                int32_t acc = 0;
+                for (int peer = 0; peer < p.ksplit; ++peer) acc += ld_peer_s32(part + c * MMF_TILE_ROWS + tid, (uint32_t)peer);
+                const int m = m0 + c;
+                if (m < a.M && n < a.N) {
+                    acc -= s_rs[c];
+                    if (a.acc_out) a.acc_out[(int64_t)m * a.N + n] = acc;
+                    store_out(a.out, a.out_dtype, (int64_t)m * a.ld_out + n, bitlinear_dequant(acc, s_dq[c], wsc));
                 }
             }
         }
+        cluster_sync_all();   // peers may still be reading this CTA's shared memory
     }
 
     // teardown: everyone meets, TMEM goes back; on the error path give copies in flight time to land first
@@ -375,17 +387,14 @@ int bitlinear_mma_launch(const BitLinearArgs& a, cudaStream_t st) {
     p.NT = a.M >= 256 ? 256 : ((a.M + 15) / 16) * 16;
     const int m_tiles = (a.M + p.NT - 1) / p.NT;
     const int total_stages = (p.KC + 1) / 2;
+    // split K over a cluster of 2/4/8 CTAs until the grid covers the GPU
     p.ksplit = 1;
-    const int64_t need_words = MMF_WS_HEADER + (int64_t)p.n_tiles * MMF_WS_MBLK + (int64_t)a.M * p.n_tiles * MMF_TILE_ROWS;
-    const bool can_split = a.ws && a.M <= MMF_SPLITK_MAX_M && m_tiles <= MMF_WS_MBLK && a.ws_bytes >= need_words * 4;
-    if (can_split) {
-        const int64_t base = (int64_t)p.n_tiles * m_tiles;
-        const int64_t target = p.NT <= 128 ? 2 * 148 : 148;
-        if (base < target) p.ksplit = (int)((target + base - 1) / base);
-        if (p.ksplit > total_stages) p.ksplit = total_stages;
-    }
+    while (p.ksplit < 8 && (int64_t)p.n_tiles * m_tiles * p.ksplit < 148 && p.ksplit * 2 <= total_stages) p.ksplit *= 2;
     p.stages_per_cta = (total_stages + p.ksplit - 1) / p.ksplit;
-    p.ksplit = (total_stages + p.stages_per_cta - 1) / p.stages_per_cta;
+    while (p.ksplit > 1 && p.stages_per_cta * (p.ksplit - 1) >= total_stages) {   // every CTA must own >= 1 stage
+        p.ksplit /= 2;
+        p.stages_per_cta = (total_stages + p.ksplit - 1) / p.ksplit;
+    }
     int cols = 32;
     while (cols < p.NT + SA * 16) cols *= 2;
     p.tmem_cols = cols;
@@ -408,7 +417,19 @@ int bitlinear_mma_launch(const BitLinearArgs& a, cudaStream_t st) {
     MMF_CUDA(cudaFuncSetAttribute(bitlinear_mma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     const dim3 grid((unsigned)p.ksplit, (unsigned)p.n_tiles, (unsigned)m_tiles);
     MMF_REQUIRE(m_tiles <= 65535 && p.n_tiles <= 65535, MMF_ERR_BAD_SHAPE, "mmf_bitlinear(mma): problem too large");
-    bitlinear_mma_kernel<<<grid, MM_THREADS, smem, st>>>(q_map, a, p);
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = dim3(MM_THREADS);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = (unsigned)p.ksplit;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    MMF_CUDA(cudaLaunchKernelEx(&cfg, bitlinear_mma_kernel, q_map, a, p));
     MMF_LAUNCH_CHECK("bitlinear_mma_kernel");
     return MMF_OK;
 }

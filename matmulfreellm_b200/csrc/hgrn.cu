@@ -48,11 +48,20 @@ struct HgrnWs {
     float* agg_h;
 };
 
+// gate conventions
+constexpr int HG_LINEAR = 0;  // g is the forget gate itself           (fused_recurrent_hgrn)
+constexpr int HG_LOG = 1;     // g is its logarithm                     (chunk_hgrn)
+constexpr int HG_RAW = 2;     // x, g are the raw i/f projection outputs (HGRNBitAttention's gate math fused in):
+                              //   f = round(sigmoid(g)); with a lower bound lb: f = round(lb + round(round(1-lb)*f))
+                              //   x = round(silu(x_raw) * round(1-f));  every round() is to the activation dtype TX
+
 // AGG = true : pass 1, chunks 0..NT-2 -> aggregates (no o written)
 // AGG = false: pass 2 (or the only pass when NT == 1) -> o, ht
-template <typename TX, typename TG, bool LOG, bool AGG>
+// x and g rows may be strided (ld_x, ld_g elements); o is [B,T,D] contiguous.
+template <typename TX, typename TG, int MODE, bool AGG>
 __global__ void __launch_bounds__(HG_BD)
-hgrn_scan_kernel(const TX* __restrict__ x, const TG* __restrict__ g, const void* __restrict__ h0, void* __restrict__ ht,
+hgrn_scan_kernel(const TX* __restrict__ x, int64_t ld_x, const TG* __restrict__ g, int64_t ld_g,
+                 const TX* __restrict__ lb, const void* __restrict__ h0, void* __restrict__ ht,
                  int state_dt, TX* __restrict__ o, int T, int D, int NT, int chunk_len, HgrnWs ws) {
     extern __shared__ __align__(16) uint8_t smem_raw[];
     constexpr int XB = HG_TS * HG_BD * sizeof(TX);  // bytes of one x stage
@@ -71,8 +80,8 @@ hgrn_scan_kernel(const TX* __restrict__ x, const TG* __restrict__ g, const void*
     const int t_end = min(T, t_begin + chunk_len);
     const int nsteps = t_end - t_begin;
     const int nstage = (nsteps + HG_TS - 1) / HG_TS;
-    const TX* xb = x + (b * T + t_begin) * (int64_t)D + d0;
-    const TG* gb = g + (b * T + t_begin) * (int64_t)D + d0;
+    const TX* xb = x + (b * T + t_begin) * ld_x + d0;
+    const TG* gb = g + (b * T + t_begin) * ld_g + d0;
     TX* ob = AGG ? nullptr : o + (b * T + t_begin) * (int64_t)D + d0;
 
     constexpr int XV = 16 / sizeof(TX), GV = 16 / sizeof(TG);   // channels per 16-byte piece
@@ -84,11 +93,11 @@ hgrn_scan_kernel(const TX* __restrict__ x, const TG* __restrict__ g, const void*
             const int rows = min(HG_TS, nsteps - s * HG_TS);
             for (int p = tid; p < rows * XP; p += HG_BD) {
                 const int r = p / XP, pc = (p % XP) * XV;
-                if (d0 + pc < D) cp_async16(sx + (buf * HG_TS + r) * HG_BD + pc, xb + (int64_t)(s * HG_TS + r) * D + pc);
+                if (d0 + pc < D) cp_async16(sx + (buf * HG_TS + r) * HG_BD + pc, xb + (int64_t)(s * HG_TS + r) * ld_x + pc);
             }
             for (int p = tid; p < rows * GP; p += HG_BD) {
                 const int r = p / GP, pc = (p % GP) * GV;
-                if (d0 + pc < D) cp_async16(sg + (buf * HG_TS + r) * HG_BD + pc, gb + (int64_t)(s * HG_TS + r) * D + pc);
+                if (d0 + pc < D) cp_async16(sg + (buf * HG_TS + r) * HG_BD + pc, gb + (int64_t)(s * HG_TS + r) * ld_g + pc);
             }
         }
         cp_async_commit();  // always commit so that group counting stays uniform
@@ -97,6 +106,12 @@ hgrn_scan_kernel(const TX* __restrict__ x, const TG* __restrict__ g, const void*
 #pragma unroll
     for (int s = 0; s < HG_STAGES - 1; ++s) issue(s);
 
+    const bool has_lb = MODE == HG_RAW && lb != nullptr && ch_ok;
+    float lbv = 0.0f, oml = 1.0f;
+    if (has_lb) {
+        lbv = to_f32(lb[ch]);
+        oml = round_to<TX>(__fsub_rn(1.0f, lbv));
+    }
     // carry-in
     float h = 0.0f, a = 1.0f;
     if (!AGG && ch_ok) {
@@ -122,9 +137,14 @@ hgrn_scan_kernel(const TX* __restrict__ x, const TG* __restrict__ g, const void*
             const TG* pg = sg + buf * HG_TS * HG_BD + tid;
 #pragma unroll 8
             for (int r = 0; r < rows; ++r) {
-                const float xv = to_f32(px[r * HG_BD]);
+                float xv = to_f32(px[r * HG_BD]);
                 float f = to_f32(pg[r * HG_BD]);
-                if (LOG) f = expf(f);
+                if (MODE == HG_LOG) f = expf(f);
+                if (MODE == HG_RAW) {
+                    f = round_to<TX>(sigmoidf_(f));
+                    if (has_lb) f = round_to<TX>(__fadd_rn(lbv, round_to<TX>(__fmul_rn(oml, f))));
+                    xv = round_to<TX>(silu_mul(xv, round_to<TX>(__fsub_rn(1.0f, f))));
+                }
                 h = fmaf(f, h, xv);
                 if (AGG) a *= f;
                 else so[r * HG_BD + tid] = from_f32<TX>(h);
@@ -168,24 +188,41 @@ size_t hgrn_smem_bytes() {
     return (size_t)HG_STAGES * HG_TS * HG_BD * (sizeof(TX) + sizeof(TG)) + (size_t)HG_TS * HG_BD * sizeof(TX);
 }
 
-template <typename TX, typename TG, bool LOG>
-int hgrn_launch(const void* x, const void* g, const void* h0, void* ht, int state_dt, void* o, int64_t B, int64_t T,
-                int64_t D, int NT, HgrnWs ws, cudaStream_t st) {
+template <typename TX, typename TG, int MODE>
+int hgrn_launch(const void* x, int64_t ld_x, const void* g, int64_t ld_g, const void* lb, const void* h0, void* ht,
+                int state_dt, void* o, int64_t B, int64_t T, int64_t D, int NT, HgrnWs ws, cudaStream_t st) {
     const size_t smem = hgrn_smem_bytes<TX, TG>();
     const int chunk_len = (int)((T + NT - 1) / NT);
     const dim3 grid((unsigned)((D + HG_BD - 1) / HG_BD), (unsigned)NT, (unsigned)B);
     if (NT > 1) {
-        auto k1 = hgrn_scan_kernel<TX, TG, LOG, true>;
+        auto k1 = hgrn_scan_kernel<TX, TG, MODE, true>;
         MMF_CUDA(cudaFuncSetAttribute(k1, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
         const dim3 grid1(grid.x, (unsigned)(NT - 1), grid.z);
-        k1<<<grid1, HG_BD, smem, st>>>((const TX*)x, (const TG*)g, h0, nullptr, state_dt, nullptr, (int)T, (int)D, NT,
-                                        chunk_len, ws);
+        k1<<<grid1, HG_BD, smem, st>>>((const TX*)x, ld_x, (const TG*)g, ld_g, (const TX*)lb, h0, nullptr, state_dt, nullptr,
+                                        (int)T, (int)D, NT, chunk_len, ws);
         MMF_LAUNCH_CHECK("hgrn_scan_kernel<aggregate>");
     }
-    auto k2 = hgrn_scan_kernel<TX, TG, LOG, false>;
+    auto k2 = hgrn_scan_kernel<TX, TG, MODE, false>;
     MMF_CUDA(cudaFuncSetAttribute(k2, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    k2<<<grid, HG_BD, smem, st>>>((const TX*)x, (const TG*)g, h0, ht, state_dt, (TX*)o, (int)T, (int)D, NT, chunk_len, ws);
+    k2<<<grid, HG_BD, smem, st>>>((const TX*)x, ld_x, (const TG*)g, ld_g, (const TX*)lb, h0, ht, state_dt, (TX*)o, (int)T,
+                                  (int)D, NT, chunk_len, ws);
     MMF_LAUNCH_CHECK("hgrn_scan_kernel<scan>");
+    return MMF_OK;
+}
+
+int hgrn_setup_ws(int64_t B, int64_t T, int64_t D, void* workspace, int64_t workspace_bytes, int& NT, HgrnWs& ws,
+                  const char* who) {
+    NT = hgrn_num_chunks(B, T, D);
+    ws = HgrnWs{nullptr, nullptr, nullptr};
+    if (NT > 1) {
+        const int64_t need = mmf_hgrn_workspace_bytes(B, T, D);
+        MMF_REQUIRE(workspace && workspace_bytes >= need, MMF_ERR_WORKSPACE, "%s: workspace of %lld bytes needed, %lld given",
+                    who, (long long)need, (long long)workspace_bytes);
+        MMF_REQUIRE(mmf_aligned(workspace, 16), MMF_ERR_ALIGN, "%s: workspace must be 16-byte aligned", who);
+        ws.h0c = (float*)workspace;
+        ws.agg_a = ws.h0c + B * D;
+        ws.agg_h = ws.agg_a + B * NT * D;
+    }
     return MMF_OK;
 }
 
@@ -209,22 +246,15 @@ extern "C" int mmf_hgrn_scan(const void* x, int x_dtype, const void* g, int g_dt
     MMF_REQUIRE(mmf_aligned(x, 16) && mmf_aligned(g, 16) && mmf_aligned(o, 16), MMF_ERR_ALIGN,
                 "mmf_hgrn_scan: x, g, o must be 16-byte aligned");
     if (B == 0 || T == 0) return MMF_OK;
-    const int NT = hgrn_num_chunks(B, T, D);
-    HgrnWs ws{nullptr, nullptr, nullptr};
-    if (NT > 1) {
-        const int64_t need = mmf_hgrn_workspace_bytes(B, T, D);
-        MMF_REQUIRE(workspace && workspace_bytes >= need, MMF_ERR_WORKSPACE,
-                    "mmf_hgrn_scan: workspace of %lld bytes needed, %lld given", (long long)need, (long long)workspace_bytes);
-        MMF_REQUIRE(mmf_aligned(workspace, 16), MMF_ERR_ALIGN, "mmf_hgrn_scan: workspace must be 16-byte aligned");
-        ws.h0c = (float*)workspace;
-        ws.agg_a = ws.h0c + B * D;
-        ws.agg_h = ws.agg_a + B * NT * D;
-    }
+    int NT;
+    HgrnWs ws;
+    const int rc0 = hgrn_setup_ws(B, T, D, workspace, workspace_bytes, NT, ws, "mmf_hgrn_scan");
+    if (rc0 != MMF_OK) return rc0;
     cudaStream_t st = (cudaStream_t)stream;
     int rc = MMF_OK;
-#define HG_GO(TX, TG)                                                                                              \
-    rc = gate_is_log ? hgrn_launch<TX, TG, true>(x, g, h0, ht, state_dtype, o, B, T, D, NT, ws, st)                \
-                     : hgrn_launch<TX, TG, false>(x, g, h0, ht, state_dtype, o, B, T, D, NT, ws, st)
+#define HG_GO(TX, TG)                                                                                                  \
+    rc = gate_is_log ? hgrn_launch<TX, TG, HG_LOG>(x, D, g, D, nullptr, h0, ht, state_dtype, o, B, T, D, NT, ws, st)     \
+                     : hgrn_launch<TX, TG, HG_LINEAR>(x, D, g, D, nullptr, h0, ht, state_dtype, o, B, T, D, NT, ws, st)
     if (x_dtype == MMF_F32 && g_dtype == MMF_F32) { HG_GO(float, float); }
     else if (x_dtype == MMF_BF16 && g_dtype == MMF_BF16) { HG_GO(__nv_bfloat16, __nv_bfloat16); }
     else if (x_dtype == MMF_BF16 && g_dtype == MMF_F32) { HG_GO(__nv_bfloat16, float); }
@@ -232,5 +262,28 @@ extern "C" int mmf_hgrn_scan(const void* x, int x_dtype, const void* g, int g_dt
     else if (x_dtype == MMF_F16 && g_dtype == MMF_F32) { HG_GO(__half, float); }
     else return mmf_set_error(MMF_ERR_BAD_ARG, "mmf_hgrn_scan: unsupported dtype pair x=%d g=%d", x_dtype, g_dtype);
 #undef HG_GO
+    return rc;
+}
+
+extern "C" int mmf_hgrn_gated(const void* i_raw, const void* f_raw, int64_t ld, int dtype, const void* lower_bound,
+                              float* state, void* o, int64_t B, int64_t T, int64_t D, void* workspace,
+                              int64_t workspace_bytes, void* stream) {
+    MMF_REQUIRE(i_raw && f_raw && state && o, MMF_ERR_BAD_ARG, "mmf_hgrn_gated: null pointer");
+    MMF_REQUIRE(mmf_dtype_ok(dtype), MMF_ERR_BAD_ARG, "mmf_hgrn_gated: unknown dtype %d", dtype);
+    MMF_REQUIRE(B >= 0 && B < 65536 && T >= 0 && T < (1ll << 31) && D > 0 && D < (1ll << 31) && D % 8 == 0 && ld >= D,
+                MMF_ERR_BAD_SHAPE, "mmf_hgrn_gated: bad sizes (D must be a multiple of 8)");
+    const int es = mmf_dtype_size(dtype);
+    MMF_REQUIRE(mmf_aligned(i_raw, 16) && mmf_aligned(f_raw, 16) && mmf_aligned(o, 16) && (ld * es) % 16 == 0, MMF_ERR_ALIGN,
+                "mmf_hgrn_gated: rows must be 16-byte aligned");
+    if (B == 0 || T == 0) return MMF_OK;
+    int NT;
+    HgrnWs ws;
+    const int rc0 = hgrn_setup_ws(B, T, D, workspace, workspace_bytes, NT, ws, "mmf_hgrn_gated");
+    if (rc0 != MMF_OK) return rc0;
+    int rc = MMF_OK;
+    MMF_DISPATCH(dtype, Ty, {
+        rc = hgrn_launch<Ty, Ty, HG_RAW>(i_raw, ld, f_raw, ld, lower_bound, state, state, MMF_F32, o, B, T, D, NT, ws,
+                                         (cudaStream_t)stream);
+    });
     return rc;
 }

@@ -96,6 +96,107 @@ class GreedyDecoder:
         return torch.cat([prompt_ids, toks], dim=1)
 
 
+class FusedRunner:
+    """The HGRNBit forward as a chain of fused kernels: per block four BitLinear contractions, each fed int8
+    codes by one fused row-wise kernel, plus the gated recurrence scan — eight launches per block.
+
+    Mathematically this is HGRNBitBlock.forward / HGRNBitAttention.forward / HGRNBitMLP.forward of the module
+    path with the same rounding points; the i/f/g projections, which share their input row, run as one
+    grouped contraction.  Built lazily from a model; rebuilt when a weight is repacked."""
+
+    def __init__(self, lm):
+        self.lm = lm
+        model = lm.model
+        cfg = lm.config
+        self.h = cfg.hidden_size
+        self.eps = cfg.rms_norm_eps
+        self.layers = []
+        for blk in model.layers:
+            at, mlp = blk.attn, blk.mlp
+            if at.input_dim != self.h:
+                raise NotImplementedError("fused path needs expand_ratio == 1")
+            self.layers.append(dict(
+                attn_norm_w=self._w32(blk.attn_norm.weight),
+                ifg=kernels.stack_packed([at.i_proj.packed(), at.f_proj.packed(), at.g_proj.packed()]),
+                ifg_nw=[at.i_proj.norm_weight_f32(), at.f_proj.norm_weight_f32(), at.g_proj.norm_weight_f32()],
+                gnorm_w=self._w32(at.g_norm.weight), gnorm_eps=at.g_norm.eps,
+                o=at.o_proj.packed(), o_nw=at.o_proj.norm_weight_f32(),
+                mlp_norm_w=self._w32(blk.mlp_norm.weight),
+                gate=mlp.gate_proj.packed(), gate_nw=mlp.gate_proj.norm_weight_f32(),
+                down=mlp.down_proj.packed(), down_nw=mlp.down_proj.norm_weight_f32(),
+                eps_bl=at.i_proj.NORM_EPS,
+            ))
+        self.final_norm_w = self._w32(model.norm.weight)
+        self.head = lm.lm_head.packed()
+        self.head_nw = lm.lm_head.norm_weight_f32()
+        self.head_eps = lm.lm_head.NORM_EPS
+        self.dtype = model.embeddings.weight.dtype
+        self.key = self.fingerprint(lm)
+
+    @staticmethod
+    def _w32(w):
+        return None if w is None else w.detach().float().contiguous()
+
+    @staticmethod
+    def fingerprint(lm):
+        """Changes whenever a parameter is replaced, cast or modified in place."""
+        return tuple((p.data_ptr(), p._version, p.dtype) for p in lm.parameters())
+
+    @torch.no_grad()
+    def forward(self, input_ids, inputs_embeds, states, last_only: bool, want_logits: bool = True,
+                want_hidden: bool = False):
+        """states: list of fp32 [B, ..., h]-shaped tensors advanced in place.  Returns (logits | None, hidden | None)."""
+        model = self.lm.model
+        if inputs_embeds is None:
+            x = kernels.embedding(model.embeddings.weight, input_ids)
+        else:
+            x = inputs_embeds.to(self.dtype)
+        B, T, h = x.shape
+        M = B * T
+        x = x.reshape(M, h)
+        lbs = model.layer_lower_bounds()
+        stream, z = x, None                      # residual stream, last block's MLP output
+        for i, L in enumerate(self.layers):
+            if i == 0:
+                q, dq, rs, _, _ = kernels.prenorm_quant(x, None, L["attn_norm_w"], self.eps, L["ifg_nw"], L["eps_bl"], False)
+            else:   # the reference adds residual + mlp output as a tensor op, then normalises the rounded sum
+                q, dq, rs, stream, _ = kernels.prenorm_quant(z, stream, L["attn_norm_w"], self.eps, L["ifg_nw"], L["eps_bl"],
+                                                             True, want_residual_out=True)
+            ifg = kernels.bitlinear(q, dq, rs, L["ifg"], self.dtype).view(B, T, 3 * h)
+            lb = lbs[i].contiguous() if (lbs is not None and i > 0) else None
+            o = kernels.hgrn_gated(ifg[:, :, :h], ifg[:, :, h:2 * h], lb, states[i].view(B, h))
+            q, dq, rs = kernels.gatenorm_quant(ifg.view(M, 3 * h)[:, 2 * h:], o.view(M, h), L["gnorm_w"], L["gnorm_eps"],
+                                               L["o_nw"], L["eps_bl"])
+            attn_out = kernels.bitlinear(q, dq, rs, L["o"], self.dtype)
+            q, dq, rs, stream, _ = kernels.prenorm_quant(attn_out, stream, L["mlp_norm_w"], self.eps, [L["gate_nw"]], L["eps_bl"],
+                                                         False, want_residual_out=True)
+            gu = kernels.bitlinear(q, dq, rs, L["gate"], self.dtype)
+            q, dq, rs = kernels.swiglu_quant(gu, L["down_nw"], L["eps_bl"])
+            z = kernels.bitlinear(q, dq, rs, L["down"], self.dtype)
+        if z is None:                             # no blocks: final norm of the embeddings
+            z_rows, s_rows, round_first = stream, None, False
+        else:
+            z_rows, s_rows, round_first = z, stream, True
+        if last_only:                             # only the last position of every sequence feeds lm_head
+            z_rows = z_rows.view(B, T, h)[:, -1]
+            s_rows = None if s_rows is None else s_rows.view(B, T, h)[:, -1]
+        Tn = 1 if last_only else T
+        q, dq, rs, _, hidden = kernels.prenorm_quant(z_rows, s_rows, self.final_norm_w, self.eps,
+                                                     [self.head_nw] if want_logits else [], self.head_eps, round_first,
+                                                     want_y=want_hidden)
+        logits = kernels.bitlinear(q, dq, rs, self.head, self.dtype).view(B, Tn, -1) if want_logits else None
+        return logits, (hidden.view(B, Tn, h) if hidden is not None else None)
+
+
+def fused_runner(lm) -> FusedRunner:
+    """The model's cached FusedRunner, rebuilt if any parameter changed since it was made."""
+    r = getattr(lm, "_fused_runner", None)
+    if r is None or r.key != FusedRunner.fingerprint(lm):
+        r = FusedRunner(lm)
+        object.__setattr__(lm, "_fused_runner", r)
+    return r
+
+
 def bitlinear_modules(model) -> List[BitLinear]:
     """Every BitLinear of the model in execution order."""
     return [m for m in model.modules() if isinstance(m, BitLinear)]

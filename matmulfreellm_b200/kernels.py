@@ -229,6 +229,86 @@ def hgrn_scan(x: torch.Tensor, g: torch.Tensor, initial_state: Optional[torch.Te
     return o, ht
 
 
+def hgrn_gated(i_raw: torch.Tensor, f_raw: torch.Tensor, lower_bound: Optional[torch.Tensor], state: torch.Tensor,
+               out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Gated recurrence from the raw i/f projections: i_raw, f_raw are [B,T,D] views with unit inner stride
+    and a common row stride (e.g. column slabs of one [B,T,3D] tensor); `state` fp32 [B,D] is advanced in
+    place; returns o [B,T,D]."""
+    _need_cuda(i_raw, f_raw, state, lower_bound)
+    B, T, D = i_raw.shape
+    ld = i_raw.stride(1)
+    if (i_raw.stride(2) != 1 or f_raw.stride(2) != 1 or f_raw.stride(1) != ld or i_raw.stride(0) != T * ld
+            or f_raw.stride(0) != T * ld or f_raw.shape != i_raw.shape or f_raw.dtype != i_raw.dtype):
+        raise ValueError("i_raw / f_raw must be [B,T,D] slabs of one row-major tensor")
+    if state.dtype != torch.float32 or state.numel() != B * D or not state.is_contiguous():
+        raise ValueError("state must be contiguous float32 with B*D elements")
+    if lower_bound is not None and (lower_bound.dtype != i_raw.dtype or lower_bound.numel() != D
+                                    or not lower_bound.is_contiguous()):
+        raise ValueError("lower_bound must be contiguous [D] in the activation dtype")
+    o = out if out is not None else torch.empty(B, T, D, dtype=i_raw.dtype, device=i_raw.device)
+    nbytes = _lib.load().mmf_hgrn_workspace_bytes(B, T, D)
+    ws = torch.empty(nbytes, dtype=torch.uint8, device=i_raw.device) if nbytes else None
+    _lib.call("mmf_hgrn_gated", i_raw.data_ptr(), f_raw.data_ptr(), ld, _code(i_raw.dtype), _ptr(lower_bound),
+              state.data_ptr(), o.data_ptr(), B, T, D, _ptr(ws), nbytes, _stream())
+    return o
+
+
+# ------------------------------------------------------------------------------------------
+# fused producers of BitLinear inputs
+# ------------------------------------------------------------------------------------------
+def _codes_buffers(G: int, M: int, D: int, device):
+    return (torch.empty(G * M, D, dtype=torch.int8, device=device), torch.empty(G * M, dtype=torch.float32, device=device),
+            torch.empty(G * M, dtype=torch.int32, device=device))
+
+
+def prenorm_quant(x: torch.Tensor, residual: Optional[torch.Tensor], norm_w: Optional[torch.Tensor], eps_norm: float,
+                  bl_norm_ws: Sequence[Optional[torch.Tensor]], eps_bl: float, round_sum_first: bool,
+                  want_residual_out: bool = False, want_y: bool = False):
+    """[x + residual] -> RMSNorm -> len(bl_norm_ws) (0, 1 or 3) BitLinear prologues.  x / residual: [M,D] with unit
+    inner stride (rows may be strided).  Returns (q, dq, rowsum, residual_out | None, y | None)."""
+    _need_cuda(x, residual, norm_w)
+    M, D = x.shape
+    G = len(bl_norm_ws)
+    q = dq = rs = None
+    if G:
+        q, dq, rs = _codes_buffers(G, M, D, x.device)
+    res_out = torch.empty(M, D, dtype=x.dtype, device=x.device) if want_residual_out else None
+    y = torch.empty(M, D, dtype=x.dtype, device=x.device) if want_y else None
+    nws = list(bl_norm_ws) + [None] * (3 - G)
+    if M:
+        _lib.call("mmf_prenorm_quant", x.data_ptr(), x.stride(0), _ptr(residual), residual.stride(0) if residual is not None else 0,
+                  _code(x.dtype), int(round_sum_first), _ptr(norm_w), float(eps_norm), _ptr(res_out), _ptr(y), G,
+                  _ptr(nws[0]), _ptr(nws[1]), _ptr(nws[2]), float(eps_bl), _ptr(q), _ptr(dq), _ptr(rs), M, D, _stream())
+    return q, dq, rs, res_out, y
+
+
+def gatenorm_quant(g: torch.Tensor, o: torch.Tensor, gnorm_w: Optional[torch.Tensor], eps_g: float,
+                   bl_norm_w: Optional[torch.Tensor], eps_bl: float):
+    """rmsnorm(g)*w*o*sigmoid(o) -> BitLinear prologue.  g, o: [M,D], unit inner stride, rows may be strided."""
+    _need_cuda(g, o, gnorm_w, bl_norm_w)
+    M, D = g.shape
+    q, dq, rs = _codes_buffers(1, M, D, g.device)
+    if M:
+        _lib.call("mmf_gatenorm_quant", g.data_ptr(), g.stride(0), o.data_ptr(), o.stride(0), _code(g.dtype), _ptr(gnorm_w),
+                  float(eps_g), _ptr(bl_norm_w), float(eps_bl), q.data_ptr(), dq.data_ptr(), rs.data_ptr(), M, D, _stream())
+    return q, dq, rs
+
+
+def swiglu_quant(gate_up: torch.Tensor, bl_norm_w: Optional[torch.Tensor], eps_bl: float):
+    """silu(gate)*up for gate_up = [gate | up] ([M, 2D], contiguous) -> BitLinear prologue."""
+    _need_cuda(gate_up, bl_norm_w)
+    M, D2 = gate_up.shape
+    D = D2 // 2
+    if gate_up.stride(1) != 1:
+        raise ValueError("gate_up must have unit inner stride")
+    q, dq, rs = _codes_buffers(1, M, D, gate_up.device)
+    if M:
+        es = gate_up.element_size()
+        _lib.call("mmf_swiglu_quant", gate_up.data_ptr(), gate_up.data_ptr() + D * es, gate_up.stride(0), _code(gate_up.dtype),
+                  _ptr(bl_norm_w), float(eps_bl), q.data_ptr(), dq.data_ptr(), rs.data_ptr(), M, D, _stream())
+    return q, dq, rs
+
+
 # ------------------------------------------------------------------------------------------
 # norms / activations / sampling helpers
 # ------------------------------------------------------------------------------------------

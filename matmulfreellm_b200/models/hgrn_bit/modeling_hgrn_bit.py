@@ -231,6 +231,14 @@ class HGRNBitForCausalLM(HGRNBitPreTrainedModel):
             raise NotImplementedError("the training loss is outside the inference hot path")
         if return_dict is None:
             return_dict = bool(getattr(self.config, "return_dict", True))
+        if use_cache is None:
+            use_cache = self.config.use_cache if not self.training else False
+        if self._can_fuse(input_ids, inputs_embeds, attention_mask, output_hidden_states):
+            logits, cache = self._forward_fused(input_ids, inputs_embeds, past_key_values, use_cache, last_token_only)
+            if not return_dict:
+                return tuple(x for x in (logits, cache) if x is not None)
+            return CausalLMOutputWithPast(loss=None, logits=logits, past_key_values=cache, hidden_states=None,
+                                          attentions=None)
         outputs = self.model(input_ids=input_ids, attention_mask=attention_mask, inputs_embeds=inputs_embeds,
                              past_key_values=past_key_values, use_cache=use_cache,
                              output_attentions=output_attentions, output_hidden_states=output_hidden_states,
@@ -243,6 +251,40 @@ class HGRNBitForCausalLM(HGRNBitPreTrainedModel):
             return tuple(x for x in (logits, outputs.past_key_values, outputs.hidden_states) if x is not None)
         return CausalLMOutputWithPast(loss=None, logits=logits, past_key_values=outputs.past_key_values,
                                       hidden_states=outputs.hidden_states, attentions=None)
+
+    # -- fused execution -------------------------------------------------------------------------------------
+    fuse = True   # set False to run module by module (same kernels, unfused; used to cross-check the fused chain)
+
+    def _can_fuse(self, input_ids, inputs_embeds, attention_mask, output_hidden_states) -> bool:
+        if not self.fuse or (input_ids is None) == (inputs_embeds is None):
+            return False
+        if output_hidden_states or (output_hidden_states is None and getattr(self.config, "output_hidden_states", False)):
+            return False
+        if self.config.expand_ratio != 1 or self.config.hidden_size % 16 or self.config.intermediate_size is not None \
+                and self.config.intermediate_size % 16:
+            return False
+        if attention_mask is not None and not bool(attention_mask.all()):   # left padding: module path
+            return False
+        return True
+
+    def _forward_fused(self, input_ids, inputs_embeds, past_key_values, use_cache, last_token_only):
+        from ...engine import fused_runner
+        ref = input_ids if input_ids is not None else inputs_embeds
+        B = ref.shape[0]
+        layers = self.model.layers
+        if use_cache and past_key_values is not None:
+            cache = past_key_values if isinstance(past_key_values, RecurrentCache) \
+                else RecurrentCache.from_legacy_cache(past_key_values)
+            for layer_states in cache.states:
+                if layer_states[-1].dtype != torch.float32:
+                    raise TypeError("recurrent states are kept in float32")
+        else:
+            cache = RecurrentCache.from_legacy_cache([layer.attn.init_state(B) for layer in layers])
+        states = [cache.states[i][-1] for i in range(len(layers))]
+        logits, _ = fused_runner(self).forward(input_ids, inputs_embeds, states, last_token_only)
+        if use_cache and past_key_values is not None and len(layers):
+            cache._seen_tokens += ref.shape[1]
+        return logits, (cache.to_legacy_cache() if use_cache else None)
 
     @torch.no_grad()
     def generate(self, input_ids: torch.LongTensor, max_new_tokens: int = 20, max_length: Optional[int] = None,

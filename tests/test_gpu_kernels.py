@@ -322,3 +322,102 @@ def test_argmax_and_embedding(K):
     table = torch.randn(1000, 256, generator=g).bfloat16()
     ids = torch.randint(0, 1000, (3, 5), generator=g)
     assert torch.equal(K.embedding(dev(table), dev(ids)).cpu(), table[ids])
+
+
+# ----------------------------------------------------------------------------------------------------------
+# fused producers of BitLinear inputs (the kernels between two contractions of a block)
+# ----------------------------------------------------------------------------------------------------------
+def _codes_close(q, dq, q_ref, dq_ref, exact):
+    """exact: bit-identical codes and scales.  Otherwise (a sigmoid / exp sits upstream, whose last-ulp result may
+    round an activation to the neighbouring bf16 value): scales agree to 1e-2, codes differ by at most 1 level
+    on at most 0.5% of the entries."""
+    q, dq = q.cpu().numpy().astype(np.int32), dq.cpu().numpy()
+    if exact:
+        assert np.array_equal(q, q_ref) and np.array_equal(dq, dq_ref)
+    else:
+        assert np.allclose(dq, dq_ref, rtol=1e-2)
+        d = np.abs(q - q_ref.astype(np.int32))
+        assert d.max() <= 1 and (d != 0).mean() <= 5e-3, (d.max(), (d != 0).mean())
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
+def test_prenorm_quant_bit_exact(K, dtype):
+    g = torch.Generator().manual_seed(21)
+    M, D = 6, 704
+    x = (torch.randn(M, D, generator=g) * 2).to(dtype)
+    res = torch.randn(M, D, generator=g).to(dtype)
+    nw = 1.0 + 0.1 * torch.randn(D, generator=g)
+    bl = [1.0 + 0.1 * torch.randn(D, generator=g) for _ in range(3)]
+    # (a) attn_norm -> i/f/g prologues, no residual
+    y_ref = O.rms_norm_ref(x, nw, eps=1e-6)
+    q, dq, rs, res_out, y = K.prenorm_quant(dev(x), None, dev(nw), 1e-6, [dev(b) for b in bl], 1e-6, False, want_y=True)
+    assert res_out is None
+    # RMSNorm output: fp64-accumulated statistics on the GPU, fp32 in torch -> allow one rounding step of dtype
+    assert (y.cpu().float() - y_ref.float()).abs().max() <= (2 ** -7 if dtype == torch.bfloat16 else 1e-6) * y_ref.float().abs().max()
+    for gi in range(3):   # the codes are exact functions of the GPU's own normed row
+        q_ref, dq_ref, rs_ref = O.act_codes(y.cpu(), bl[gi], 1e-6)
+        assert np.array_equal(q[gi * M:(gi + 1) * M].cpu().numpy(), q_ref)
+        assert np.array_equal(dq[gi * M:(gi + 1) * M].cpu().numpy(), dq_ref)
+        assert np.array_equal(rs[gi * M:(gi + 1) * M].cpu().numpy(), rs_ref)
+    # (b) mlp_norm: fused residual add, statistics on the unrounded sum, residual_out rounded
+    y_ref, r_ref = O.rms_norm_ref(x, nw, residual=res, eps=1e-6, prenorm=True)
+    q, dq, rs, res_out, y = K.prenorm_quant(dev(x), dev(res), dev(nw), 1e-6, [dev(bl[0])], 1e-6, False,
+                                            want_residual_out=True, want_y=True)
+    assert torch.equal(res_out.cpu(), r_ref)
+    q_ref, dq_ref, _ = O.act_codes(y.cpu(), bl[0], 1e-6)
+    assert np.array_equal(q.cpu().numpy(), q_ref) and np.array_equal(dq.cpu().numpy(), dq_ref)
+    # (c) next block's attn_norm: the sum is a tensor of its own in the reference -> rounded before the statistics
+    h = x + res
+    y_ref = O.rms_norm_ref(h, nw, eps=1e-6)
+    q, dq, rs, res_out, y = K.prenorm_quant(dev(x), dev(res), dev(nw), 1e-6, [], 1e-6, True, want_residual_out=True,
+                                            want_y=True)
+    assert q is None and torch.equal(res_out.cpu(), h)
+    assert (y.cpu().float() - y_ref.float()).abs().max() <= (2 ** -7 if dtype == torch.bfloat16 else 1e-6) * y_ref.float().abs().max()
+    # strided rows (last position of every sequence)
+    x3 = dev(x).view(2, 3, D)
+    q2, dq2, _, _, _ = K.prenorm_quant(x3[:, -1], None, dev(nw), 1e-6, [dev(bl[0])], 1e-6, False)
+    qa, dqa, _, _, _ = K.prenorm_quant(x3[:, -1].contiguous(), None, dev(nw), 1e-6, [dev(bl[0])], 1e-6, False)
+    assert torch.equal(q2, qa) and torch.equal(dq2, dqa)
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
+def test_gatenorm_and_swiglu_quant(K, dtype):
+    g = torch.Generator().manual_seed(22)
+    M, D = 5, 256
+    ifg = (torch.randn(M, 3 * D, generator=g)).to(dtype)
+    o = torch.randn(M, D, generator=g).to(dtype)
+    gw = 1.0 + 0.1 * torch.randn(D, generator=g)
+    nw = 1.0 + 0.1 * torch.randn(D, generator=g)
+    y_ref = O.swish_gate_norm_ref(ifg[:, 2 * D:], o, gw, 1e-6)
+    q_ref, dq_ref, _ = O.act_codes(y_ref, nw, 1e-6)
+    q, dq, rs = K.gatenorm_quant(dev(ifg)[:, 2 * D:], dev(o), dev(gw), 1e-6, dev(nw), 1e-6)
+    _codes_close(q, dq, q_ref, dq_ref, exact=False)
+    assert np.array_equal(rs.cpu().numpy(), q.cpu().numpy().astype(np.int32).sum(-1))
+    gu = torch.randn(M, 2 * 704, generator=g).to(dtype)
+    nw2 = 1.0 + 0.1 * torch.randn(704, generator=g)
+    z_ref = O.swiglu_ref(gu[:, :704], gu[:, 704:])
+    q_ref, dq_ref, _ = O.act_codes(z_ref, nw2, 1e-6)
+    q, dq, rs = K.swiglu_quant(dev(gu), dev(nw2), 1e-6)
+    _codes_close(q, dq, q_ref, dq_ref, exact=False)
+
+
+@pytest.mark.parametrize("dtype,tol", [(torch.bfloat16, 1e-2), (torch.float32, 1e-4)])
+@pytest.mark.parametrize("B,T,D", [(3, 1, 256), (2, 70, 128), (1, 1024, 64)])
+def test_hgrn_gated_vs_oracle(K, dtype, tol, B, T, D):
+    """The attention layer's gate glue + recurrence (layers/hgrn_bit.py:113-125) in one kernel, state in place."""
+    g = torch.Generator().manual_seed(B * 100 + T)
+    ifg = torch.randn(B, T, 3 * D, generator=g).to(dtype)
+    lb = (torch.rand(D, generator=g) * 0.5).to(dtype)
+    h0 = torch.randn(B, D, generator=g)
+    for bound in (lb, None):
+        f = ifg[..., D:2 * D].sigmoid()
+        if bound is not None:
+            f = bound + (1 - bound) * f
+        i = O.swiglu_ref(ifg[..., :D], 1 - f)
+        o_ref, ht_ref = O.naive_recurrent_hgrn(i.unsqueeze(1), f.unsqueeze(1), h0.unsqueeze(1), True)
+        state = dev(h0.clone())
+        d_ifg = dev(ifg)
+        o = K.hgrn_gated(d_ifg[..., :D], d_ifg[..., D:2 * D], None if bound is None else dev(bound), state)
+        so = o_ref.float().abs().max().item()
+        assert (o.cpu().float() - o_ref.squeeze(1).float()).abs().max().item() <= tol * so
+        assert (state.cpu() - ht_ref.squeeze(1)).abs().max().item() <= max(tol, 1e-4) * ht_ref.abs().max().item()

@@ -153,6 +153,7 @@ def test_tiny_model_fp32_vs_oracle_and_reference(mm, golden):
     for m in model.modules():
         if isinstance(m, BitLinear):
             m.NORM_EPS = 1e-8
+    model._fused_runner = None          # the fused chain caches each layer's eps when it is built
     out8 = model(ids.cuda(), use_cache=True)
     _close_up_to_code_flips(out8.logits[:, g["logits_pos"]].cpu().numpy(), g["logits_at"], 2e-5, 5e-2)
     for i, s in enumerate(out8.past_key_values):
@@ -160,6 +161,7 @@ def test_tiny_model_fp32_vs_oracle_and_reference(mm, golden):
     for m in model.modules():
         if isinstance(m, BitLinear):
             del m.NORM_EPS
+    model._fused_runner = None
 
     # prefill + one cached step == one longer forward (incremental decoding is consistent)
     full = model(ids[:, :65].cuda(), use_cache=False).logits[:, -1]
@@ -195,6 +197,30 @@ def test_greedy_decode_64_steps_matches_oracle(mm, dtype, typical, worst):
     _close_up_to_code_flips(logits.numpy(), ref_logits.float().numpy(), typical, worst)
     print(f"[greedy {dtype}] identical tokens: {same.float().mean().item():.3f}; min oracle top-2 margin "
           f"{margins.min().item():.2e}")
+
+
+def test_fused_chain_equals_module_path(mm):
+    """HGRNBitForCausalLM.forward runs a chain of fused kernels; with `fuse = False` it runs module by module
+    (RMSNorm, FusedBitLinear, swiglu, ... each as its own call).  Same arithmetic, same rounding points."""
+    cfg = tiny_cfg()
+    sd = O.random_weights(cfg, seed=9)
+    sd["model.lower_bounds"] = 0.5 * torch.randn(2, 256, generator=torch.Generator().manual_seed(3))
+    ids = torch.randint(0, 32000, (3, 40), generator=torch.Generator().manual_seed(10)).cuda()
+    for dtype, typical, worst in ((torch.float32, 1e-6, 2e-2), (torch.bfloat16, 4e-3, 1e-1)):
+        model = build_gpu_model(sd, cfg, dtype)
+        fused = model(ids, use_cache=True)
+        model.fuse = False
+        plain = model(ids, use_cache=True)
+        del model.fuse
+        _close_up_to_code_flips(fused.logits.float().cpu().numpy(), plain.logits.float().cpu().numpy(), typical, worst)
+        for a, b in zip(fused.past_key_values, plain.past_key_values):
+            _close_up_to_code_flips(a[0].cpu().numpy(), b[0].cpu().numpy(), typical, worst)
+        # last_token_only and a cached step agree with the full forward
+        last = model(ids, use_cache=False, last_token_only=True).logits
+        assert torch.equal(last[:, 0], fused.logits[:, -1])
+        o1 = model(ids[:, :39], use_cache=True)
+        o2 = model(ids[:, 39:], past_key_values=o1.past_key_values, use_cache=True)
+        _close_up_to_code_flips(o2.logits[:, -1].float().cpu().numpy(), fused.logits[:, -1].float().cpu().numpy(), typical, worst)
 
 
 def test_generate_api(mm):
