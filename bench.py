@@ -47,6 +47,7 @@ def parse_args():
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
     ap.add_argument("--layers", type=int, default=MODEL["num_hidden_layers"], help=argparse.SUPPRESS)
     ap.add_argument("--no-extras", action="store_true", help="skip the secondary measurements (batch 1/256, prefill)")
+    ap.add_argument("--skip-cpu", action="store_true", help="skip the CPU-baseline leg (for profiler runs)")
     return ap.parse_args()
 
 
@@ -308,7 +309,7 @@ def run_ours(args):
         extras["prefill_4x2048_tokens_per_s"] = pf.numel() / (m * 1e-3)
 
     cpu = None
-    if rank == 0 and world == 1:
+    if rank == 0 and world == 1 and not args.skip_cpu:
         full_step, threads, sample = cpu_reference_step_time(B, steps=2, warmup=1, budget_s=25.0)
         cpu = {"value": B / full_step, "unit": "tokens/s", "cores": threads, "kind": "port", "sample": sample}
 

@@ -146,6 +146,14 @@ int mmf_bitlinear(const int8_t* q, const float* dq, const int32_t* rowsum, const
                   int32_t* acc_out, int64_t M, int64_t N, int64_t K, void* workspace,
                   int64_t workspace_bytes, int kernel, void* stream);
 
+/* Tuning hook for experiments: overrides the automatic choice of the tensor-core kernel's
+ * configuration for all later mmf_bitlinear calls of this process (value 0 = automatic again).
+ * No counterpart in the reference. */
+#define MMF_TUNE_KSPLIT 0     /* K split / cluster size: 1, 2, 4 or 8                          */
+#define MMF_TUNE_TOKEN_TILE 1 /* token rows per tile: 16..128 (multiple of 16) or 256           */
+#define MMF_TUNE_DEEP_RING 2  /* 1 = prefer the deep-ring (no split) variant, 2 = never use it  */
+int mmf_tuning(int knob, int value);
+
 /* ------------------------------------------------------------------------------------
  * HGRN recurrence  h_t = f_t * h_{t-1} + x_t  (element-wise, fp32 state).
  * Replaces: fused_recurrent_hgrn (linear-domain gate), mmfreelm/ops/hgrn/recurrent_fuse.py:32-68,
@@ -181,7 +189,7 @@ int mmf_hgrn_gated(const void* i_raw, const void* f_raw, int64_t ld, int dtype,
 /* ------------------------------------------------------------------------------------
  * Fused producers of BitLinear inputs: each emits the int8 codes (+ dq, rowsum, laid out
  * [groups][M][D] / [groups][M]) that mmf_bitlinear consumes, so no activation tensor is
- * written between two contractions.  D % 16 == 0, D <= 16384, rows 16-byte aligned.
+ * written between two contractions.  D % 16 == 0, D <= 8192, rows and norm weights 16-byte aligned.
  * ------------------------------------------------------------------------------------ */
 
 /* s = x [+ residual]; residual_out = s (optional); y = rmsnorm(s; norm_w, eps_norm) rounded to
@@ -205,6 +213,15 @@ int mmf_prenorm_quant(const void* x, int64_t ld_x, const void* residual, int64_t
 int mmf_gatenorm_quant(const void* g, int64_t ld_g, const void* o, int64_t ld_o, int dtype,
                        const float* gnorm_w, float eps_g, const float* nw, float eps_bl, int8_t* q,
                        float* dq, int32_t* rowsum, int64_t M, int64_t D, void* stream);
+
+/* Single-token (decode) step of the token mixer in one kernel: for each of M sequences, the gate math
+ * and state update of mmf_hgrn_gated with T = 1 (state fp32 [M, D], updated in place) followed by
+ * mmf_gatenorm_quant on the same row.  ifg: [M, ld] rows holding the i | f | g projections as three
+ * consecutive D-wide slabs (ld >= 3*D).
+ * Replaces: mmfreelm/layers/hgrn_bit.py:113-140 for a one-token forward. */
+int mmf_decode_mix(const void* ifg, int64_t ld, int dtype, const void* lower_bound, float* state,
+                   const float* gnorm_w, float eps_g, const float* nw, float eps_bl, int8_t* q, float* dq,
+                   int32_t* rowsum, int64_t M, int64_t D, void* stream);
 
 /* z = silu(gate) * up rounded to `dtype`, then the BitLinear prologue with norm weight nw.
  * gate/up: the two halves of gate_proj's output, rows `ld` elements apart.

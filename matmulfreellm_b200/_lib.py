@@ -36,6 +36,7 @@ PROTOTYPES = {
     "mmf_bitlinear_workspace_bytes": (c_int64, [c_int64, c_int64, c_int64]),
     "mmf_bitlinear": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int64,
                               c_void_p, c_int64, c_int64, c_int64, c_void_p, c_int64, c_int, c_void_p]),
+    "mmf_tuning": (c_int, [c_int, c_int]),
     "mmf_hgrn_workspace_bytes": (c_int64, [c_int64, c_int64, c_int64]),
     "mmf_hgrn_scan": (c_int, [c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_int, c_void_p, c_int64,
                               c_int64, c_int64, c_int, c_void_p, c_int64, c_void_p]),
@@ -46,6 +47,8 @@ PROTOTYPES = {
                                   c_int64, c_int64, c_void_p]),
     "mmf_gatenorm_quant": (c_int, [c_void_p, c_int64, c_void_p, c_int64, c_int, c_void_p, c_float, c_void_p, c_float,
                                    c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_void_p]),
+    "mmf_decode_mix": (c_int, [c_void_p, c_int64, c_int, c_void_p, c_void_p, c_void_p, c_float, c_void_p, c_float, c_void_p,
+                               c_void_p, c_void_p, c_int64, c_int64, c_void_p]),
     "mmf_swiglu_quant": (c_int, [c_void_p, c_void_p, c_int64, c_int, c_void_p, c_float, c_void_p, c_void_p, c_void_p,
                                  c_int64, c_int64, c_void_p]),
     "mmf_rmsnorm": (c_int, [c_void_p, c_int, c_void_p, c_int, c_void_p, c_float, c_void_p, c_void_p, c_int64,

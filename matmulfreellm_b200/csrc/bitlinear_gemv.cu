@@ -22,6 +22,7 @@ __global__ void __launch_bounds__(GV_THREADS)
 bitlinear_gemv_kernel(BitLinearArgs a, int KC, int kc_per_cta, int ksplit, int n_tiles, int group_tiles) {
     extern __shared__ __align__(16) int8_t xs[];  // [MB][kc_per_cta*64]
     __shared__ int s_last;
+    pdl_trigger();
     const int ks = blockIdx.x, tile = blockIdx.y, mblk = blockIdx.z;
     const int r = threadIdx.x;
     const int m0 = mblk * MB;
@@ -30,6 +31,14 @@ bitlinear_gemv_kernel(BitLinearArgs a, int KC, int kc_per_cta, int ksplit, int n
     const int kc1 = min(KC, kc0 + kc_per_cta);
     const int kslice = (kc1 - kc0) * MMF_TILE_K;  // bytes of activation codes per row in this CTA
     const int row_stride = kc_per_cta * MMF_TILE_K;
+
+    // the first weight pieces do not depend on the preceding kernel: request them before the dependency wait
+    const uint4* wp = a.packed + ((int64_t)tile * KC + kc0) * MMF_TILE_ROWS + r;
+    const int nkc = kc1 - kc0;
+    uint4 w_first[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) w_first[i] = i < nkc ? __ldg(wp + (int64_t)i * MMF_TILE_ROWS) : make_uint4(0, 0, 0, 0);
+    pdl_wait();
 
     // stage the activation codes of this K slice (16-byte pieces)
     const int8_t* qg = a.q + ((int64_t)g * a.M) * a.K + (int64_t)kc0 * MMF_TILE_K;
@@ -46,11 +55,7 @@ bitlinear_gemv_kernel(BitLinearArgs a, int KC, int kc_per_cta, int ksplit, int n
 #pragma unroll
     for (int m = 0; m < MB; ++m) acc[m] = 0;
 
-    const uint4* wp = a.packed + ((int64_t)tile * KC + kc0) * MMF_TILE_ROWS + r;
-    const int nkc = kc1 - kc0;
-#pragma unroll 4
-    for (int kc = 0; kc < nkc; ++kc) {
-        const uint4 wv = __ldg(wp + (int64_t)kc * MMF_TILE_ROWS);
+    auto consume = [&](const uint4& wv, int kc) {
         const uint32_t words[4] = {wv.x, wv.y, wv.z, wv.w};
 #pragma unroll
         for (int qd = 0; qd < 4; ++qd) {
@@ -66,7 +71,12 @@ bitlinear_gemv_kernel(BitLinearArgs a, int KC, int kc_per_cta, int ksplit, int n
                 acc[m] = __dp4a((int)b[3], xv.w, acc[m]);
             }
         }
-    }
+    };
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+        if (i < nkc) consume(w_first[i], i);
+#pragma unroll 4
+    for (int kc = 4; kc < nkc; ++kc) consume(__ldg(wp + (int64_t)kc * MMF_TILE_ROWS), kc);
 
     const int n = tile * MMF_TILE_ROWS + r;
     const int Npad = n_tiles * MMF_TILE_ROWS;
@@ -142,7 +152,7 @@ int bitlinear_gemv_launch(const BitLinearArgs& a, cudaStream_t st) {
     {                                                                                                               \
         auto kfn = bitlinear_gemv_kernel<MBV>;                                                                      \
         if (smem > 48 * 1024) MMF_CUDA(cudaFuncSetAttribute(kfn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)); \
-        kfn<<<grid, GV_THREADS, smem, st>>>(a, KC, kc_per_cta, ksplit, n_tiles, group_tiles);                       \
+        MMF_CUDA(mmf_launch_pdl(kfn, grid, dim3(GV_THREADS), smem, st, a, KC, kc_per_cta, ksplit, n_tiles, group_tiles)); \
     }
     switch (MB) {
         case 1: GV_LAUNCH(1); break;

@@ -9,11 +9,13 @@
 // The token operand (int8 activation codes, K-major) is fetched by tiled TMA with the 128-byte
 // swizzle into a shared-memory ring and read through a UMMA shared-memory descriptor.
 //
-// Warp roles (224 threads): warps 0-3 unpack (thread t <-> TMEM lane t <-> weight row t) and
-// later run the epilogue; warp 4 = activation-tile TMA producer; warp 5 = TMEM owner + MMA
-// issuer; warp 6 = packed-weight TMA producer.  Three rings (packed weights in smem, unpacked
-// A chunks in TMEM, activation tiles in smem) are synchronised with mbarriers; every wait is
-// bounded and reports through a status word instead of hanging.
+// Warp roles (352 threads): warps 0-7 unpack — two groups of four warps that alternate 128-K
+// stages, lane <-> TMEM lane <-> weight row — and later run the epilogue; warp 8 = activation-tile
+// TMA producer; warp 9 = TMEM owner + MMA issuer; warp 10 = packed-weight TMA producer.  Three
+// rings (packed weights in smem, unpacked A stages in TMEM, activation tiles in smem) are
+// synchronised with mbarriers; every wait is bounded and reports through a status word instead
+// of hanging.  The weight stream does not depend on the preceding kernel, so it is started
+// before the grid-dependency wait (programmatic dependent launch).
 //
 // Weights are stored biased (+1); sum_k (t+1)*x = acc + rowsum(x) and the epilogue subtracts the
 // per-token code sum.  For few tokens the K range is split over the CTAs of a thread-block cluster
@@ -26,10 +28,14 @@
 
 namespace {
 
-constexpr int MM_THREADS = 224;
-constexpr int SA = 8;             // A chunks (64 K each, 16 TMEM columns) in flight
-constexpr int SB = 4;             // activation stages (128 K each)
-constexpr int SW = 12;            // packed-weight stages (128 K = 4 KB each)
+constexpr int NUM_UNPACK_WARPS = 8;
+constexpr int UNPACK_THREADS = NUM_UNPACK_WARPS * 32;
+constexpr int WARP_B = 8, WARP_MMA = 9, WARP_W = 10;
+constexpr int MM_THREADS = 11 * 32;
+// ring depths are chosen per launch (MmaParams); these are the capacities of the barrier table
+constexpr int MAX_SA = 16;        // A stages (128 K = 32 TMEM columns each) in flight
+constexpr int MAX_SB = 32;        // activation stages (128 K each)
+constexpr int MAX_SW = 32;        // packed-weight stages (128 K = 4 KB each)
 constexpr int W_STAGE_BYTES = 2 * MMF_TILE_ROWS * 16;  // two 64-K chunks
 constexpr long long WAIT_LIMIT_CYCLES = 2000000000ll;
 
@@ -39,7 +45,9 @@ struct MmaParams {
     int NT;              // token rows per tile (multiple of 16, <= 256)
     int ksplit;          // CTAs sharing one output tile along K
     int stages_per_cta;  // 128-K stages per CTA
-    int tmem_cols;       // power of two >= NT + SA*16
+    int tmem_cols;       // power of two >= nacc*NT + SA*32
+    int nacc;            // independent accumulators (NT columns each) that consecutive MMAs rotate through
+    int SA, SB, SW;      // ring depths: unpacked-A stages in TMEM, activation stages, packed-weight stages
     uint32_t idesc;
 };
 
@@ -143,19 +151,13 @@ __device__ __forceinline__ void tmem_ld16(uint32_t addr, uint32_t (&r)[16]) {
 }
 __device__ __forceinline__ void tmem_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
 __device__ __forceinline__ void tmem_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
-__device__ __forceinline__ void named_bar_sync(int id, int count) {
-    asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(count) : "memory");
-}
 
-__device__ __forceinline__ void cluster_sync_all() {
-    asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
-}
-__device__ __forceinline__ int32_t ld_peer_s32(const void* my_smem, uint32_t peer_rank) {
-    uint32_t remote;
-    int32_t v;
-    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(smem_u32(my_smem)), "r"(peer_rank));
-    asm volatile("ld.shared::cluster.s32 %0, [%1];" : "=r"(v) : "r"(remote) : "memory");
-    return v;
+__device__ __forceinline__ void cluster_arrive() { asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory"); }
+__device__ __forceinline__ void cluster_wait() { asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory"); }
+// optional phase trace of CTA (0,0,0): armed by writing MMF_TRACE_MAGIC into workspace word 1
+constexpr int MMF_TRACE_MAGIC = 0x7ace;
+__device__ __forceinline__ void trace_mark(long long* trace, int slot) {
+    if (trace) trace[slot] = clock64();
 }
 
 // K-major operand tile in shared memory, 128-byte swizzle: rows of 128 bytes, 8-row groups 1024 B apart.
@@ -169,186 +171,320 @@ __device__ __forceinline__ uint64_t make_b_desc(uint32_t smem_addr) {
     return d;
 }
 
-struct __align__(8) Barriers {
-    uint64_t b_full[SB], b_empty[SB];
-    uint64_t w_full[SW], w_empty[SW];
-    uint64_t a_full[SA], a_empty[SA];
-    uint64_t acc_full;
-};
+// barrier table: index ranges inside one uint64 array
+constexpr int BAR_B_FULL = 0, BAR_B_EMPTY = BAR_B_FULL + MAX_SB, BAR_W_FULL = BAR_B_EMPTY + MAX_SB,
+              BAR_W_EMPTY = BAR_W_FULL + MAX_SW, BAR_A_FULL = BAR_W_EMPTY + MAX_SW, BAR_A_EMPTY = BAR_A_FULL + MAX_SA,
+              BAR_ACC = BAR_A_EMPTY + MAX_SA, NUM_BARS = BAR_ACC + 1;
 
-__global__ void __launch_bounds__(MM_THREADS, 1)
+__device__ __forceinline__ uint32_t bar_count(int i) {
+    // arrivals per phase: the 128 threads of one unpack group for "weights consumed" and "A stage written",
+    // one (producer's expect_tx arrive or a tcgen05.commit) for everything else
+    return (i >= BAR_W_EMPTY && i < BAR_A_EMPTY) ? 128u : 1u;
+}
+
+
+__device__ __forceinline__ void st_peer_v4(void* my_smem_addr, uint32_t peer_rank, const int4& v) {
+    uint32_t remote;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(smem_u32(my_smem_addr)), "r"(peer_rank));
+    asm volatile("st.shared::cluster.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(remote), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
+}
+
+// Finish 8 consecutive outputs (rows n..n+7 of the weight tile) of token m: subtract the +1 bias, dequantise,
+// convert and store as one 16-byte (2-byte dtypes) or two 16-byte (fp32) stores when the row allows it.
+__device__ __forceinline__ void finish8(const BitLinearArgs& a, int32_t (&acc)[8], int m, int n, int rowsum, float scale) {
+    if (n >= a.N) return;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) acc[i] -= rowsum;
+    const bool full = n + 8 <= a.N;
+    if (a.acc_out) {
+        int32_t* dst = a.acc_out + (int64_t)m * a.N + n;
+        if (full && (a.N & 3) == 0) {
+            reinterpret_cast<int4*>(dst)[0] = make_int4(acc[0], acc[1], acc[2], acc[3]);
+            reinterpret_cast<int4*>(dst)[1] = make_int4(acc[4], acc[5], acc[6], acc[7]);
+        } else {
+            for (int i = 0; i < 8 && n + i < a.N; ++i) dst[i] = acc[i];
+        }
+    }
+    float f[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) f[i] = __fmul_rn((float)acc[i], scale);
+    const int64_t off = (int64_t)m * a.ld_out + n;
+    if (a.out_dtype == MMF_F32) {
+        float* dst = reinterpret_cast<float*>(a.out) + off;
+        if (full && (a.ld_out & 3) == 0) {
+            reinterpret_cast<float4*>(dst)[0] = make_float4(f[0], f[1], f[2], f[3]);
+            reinterpret_cast<float4*>(dst)[1] = make_float4(f[4], f[5], f[6], f[7]);
+        } else {
+            for (int i = 0; i < 8 && n + i < a.N; ++i) dst[i] = f[i];
+        }
+    } else {
+        uint32_t w[4];
+        if (a.out_dtype == MMF_BF16) {
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                const __nv_bfloat162 h = __floats2bfloat162_rn(f[2 * i], f[2 * i + 1]);
+                w[i] = *reinterpret_cast<const uint32_t*>(&h);
+            }
+        } else {
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                const __half2 h = __floats2half2_rn(f[2 * i], f[2 * i + 1]);
+                w[i] = *reinterpret_cast<const uint32_t*>(&h);
+            }
+        }
+        uint16_t* dst = reinterpret_cast<uint16_t*>(a.out) + off;
+        if (full && (a.ld_out & 7) == 0) {
+            *reinterpret_cast<uint4*>(dst) = make_uint4(w[0], w[1], w[2], w[3]);
+        } else {
+            const uint16_t* h = reinterpret_cast<const uint16_t*>(w);
+            for (int i = 0; i < 8 && n + i < a.N; ++i) dst[i] = h[i];
+        }
+    }
+}
+
+__global__ void __launch_bounds__(MM_THREADS, 2)
 bitlinear_mma_kernel(const __grid_constant__ CUtensorMap q_map, BitLinearArgs a, MmaParams p) {
     extern __shared__ uint8_t smem_raw[];
-    // carve: [B ring | W ring] aligned to 1024 B (required by the 128-byte swizzle atoms)
+    // carve (1024-byte aligned for the 128-byte swizzle atoms): [activation ring | packed-weight ring | landing zone]
     uint8_t* base = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     const int b_stage_bytes = p.NT * 128;
     uint8_t* b_ring = base;
+    const int SA = p.SA, SB = p.SB, SW = p.SW;
     uint8_t* w_ring = base + SB * b_stage_bytes;
+    int32_t* stg = reinterpret_cast<int32_t*>(b_ring);   // [NT][128] this CTA's int32 tile; reuses the idle activation ring
+    // split-K landing zone [ksplit][NT/ksplit][128] int32: peers push the token columns this CTA finishes
+    int32_t* part = reinterpret_cast<int32_t*>(w_ring + SW * W_STAGE_BYTES);
 
-    __shared__ Barriers bars;
+    __shared__ __align__(8) uint64_t bars[NUM_BARS];
     __shared__ uint32_t s_tmem_base;
     __shared__ int s_abort;
     __shared__ float s_dq[256];
     __shared__ int s_rs[256];
 
     const int tid = threadIdx.x;
-    const int warp = tid >> 5;
+    const int warp = tid >> 5, lane = tid & 31;
     const int ks = blockIdx.x, tile = blockIdx.y, mt = blockIdx.z;
+    long long* trace = nullptr;
+    if (tid == 0 && a.ws && a.ws[1] == MMF_TRACE_MAGIC && (blockIdx.x | blockIdx.y | blockIdx.z) == 0)
+        trace = reinterpret_cast<long long*>(a.ws + 8);
+    trace_mark(trace, 0);
+    pdl_trigger();   // the next kernel may start its own prologue (and weight stream) right away
     const int g = tile / p.group_tiles;
     const int m0 = mt * p.NT;
     const int stage0 = ks * p.stages_per_cta;
     const int total_stages = (p.KC + 1) / 2;
     const int nstages = min(p.stages_per_cta, total_stages - stage0);   // >= 1 by construction
 
-    if (tid == 0) {
-        for (int i = 0; i < SB; ++i) { mbar_init(&bars.b_full[i], 1); mbar_init(&bars.b_empty[i], 1); }
-        for (int i = 0; i < SW; ++i) { mbar_init(&bars.w_full[i], 1); mbar_init(&bars.w_empty[i], 128); }
-        for (int i = 0; i < SA; ++i) { mbar_init(&bars.a_full[i], 128); mbar_init(&bars.a_empty[i], 1); }
-        mbar_init(&bars.acc_full, 1);
-        s_abort = 0;
-        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-    }
-    for (int i = tid; i < p.NT; i += MM_THREADS) {
-        const int m = m0 + i;
-        const bool ok = m < a.M;
-        s_dq[i] = ok ? a.dq[(int64_t)g * a.M + m] : 0.0f;
-        s_rs[i] = ok ? a.rowsum[(int64_t)g * a.M + m] : 0;
-    }
-    if (warp == 5) tmem_alloc(&s_tmem_base, (uint32_t)p.tmem_cols);
+    static_assert(NUM_BARS <= MM_THREADS, "one thread initialises one barrier");
+    if (tid < NUM_BARS) mbar_init(&bars[tid], bar_count(tid));
+    if (tid == NUM_BARS) s_abort = 0;
+    if (warp == WARP_MMA) tmem_alloc(&s_tmem_base, (uint32_t)p.tmem_cols);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
+    // cluster barrier #1 (arrive now, wait before the first remote store): a peer's shared memory may only be
+    // written once that peer is known to be running
+    if (p.ksplit > 1) cluster_arrive();
+    trace_mark(trace, 1);
     const uint32_t tmem_base = s_tmem_base;
-    const uint32_t tmem_a = tmem_base + (uint32_t)p.NT;   // A stages follow the accumulator columns
+    const uint32_t tmem_a = tmem_base + (uint32_t)(p.nacc * p.NT);   // A stages (32 columns each) follow the accumulators
     volatile int* abort_flag = &s_abort;
 
-    if (warp == 4) {
-        // ------------------------------------------------------------ activation tiles (TMA, swizzled)
-        if (elect_one()) {
-            for (int i = 0; i < nstages; ++i) {
-                const int s = i % SB;
-                if (!mbar_wait(&bars.b_empty[s], ((i / SB) & 1) ^ 1, abort_flag)) break;
-                mbar_expect_tx(&bars.b_full[s], (uint32_t)b_stage_bytes);
-                tma_load_2d(b_ring + s * b_stage_bytes, &q_map, &bars.b_full[s], (stage0 + i) * 128, g * a.M + m0);
-            }
-        }
-    } else if (warp == 6) {
+    // ring cursors advance by increment-and-wrap (no division in the hot loops); `ph` is the barrier phase bit
+    struct Ring {
+        int slot, ph, depth;
+        __device__ __forceinline__ void next() { if (++slot == depth) { slot = 0; ph ^= 1; } }
+        __device__ __forceinline__ void next2() { next(); next(); }
+    };
+
+    if (warp == WARP_W) {
         // ------------------------------------------------------------ packed weights (bulk TMA)
+        // Weights do not depend on the preceding kernel: their stream starts before the grid dependency wait.
         if (elect_one()) {
-            const uint8_t* src = reinterpret_cast<const uint8_t*>(a.packed) + ((int64_t)tile * p.KC) * (MMF_TILE_ROWS * 16);
-            for (int i = 0; i < nstages; ++i) {
-                const int s = i % SW;
-                if (!mbar_wait(&bars.w_empty[s], ((i / SW) & 1) ^ 1, abort_flag)) break;
-                const int kc = (stage0 + i) * 2;
-                const uint32_t bytes = (uint32_t)min(2, p.KC - kc) * (MMF_TILE_ROWS * 16);
-                mbar_expect_tx(&bars.w_full[s], bytes);
-                bulk_load_1d(w_ring + s * W_STAGE_BYTES, src + (int64_t)kc * (MMF_TILE_ROWS * 16), bytes, &bars.w_full[s]);
+            const uint8_t* src = reinterpret_cast<const uint8_t*>(a.packed) +
+                                 ((int64_t)tile * p.KC + (int64_t)stage0 * 2) * (MMF_TILE_ROWS * 16);
+            Ring w{0, 0, SW};
+            for (int i = 0; i < nstages; ++i, w.next()) {
+                if (!mbar_wait(&bars[BAR_W_EMPTY + w.slot], w.ph ^ 1, abort_flag)) break;
+                const uint32_t bytes = (uint32_t)min(2, p.KC - (stage0 + i) * 2) * (MMF_TILE_ROWS * 16);
+                mbar_expect_tx(&bars[BAR_W_FULL + w.slot], bytes);
+                bulk_load_1d(w_ring + w.slot * W_STAGE_BYTES, src + (int64_t)i * W_STAGE_BYTES, bytes, &bars[BAR_W_FULL + w.slot]);
             }
         }
-    } else if (warp == 5) {
-        // ------------------------------------------------------------ MMA issue
+    } else if (warp == WARP_B) {
+        // ------------------------------------------------------------ activation tiles (TMA, swizzled)
+        pdl_wait();   // the codes are the preceding kernel's output
         if (elect_one()) {
-            int ac = 0;  // running A-chunk counter
-            bool ok = true;
-            for (int i = 0; i < nstages && ok; ++i) {
-                const int s = i % SB;
-                ok = mbar_wait(&bars.b_full[s], (i / SB) & 1, abort_flag);
-                if (!ok) break;
-                const uint32_t b_addr = smem_u32(b_ring + s * b_stage_bytes);
-                const int nch = min(2, p.KC - (stage0 + i) * 2);
-                for (int h = 0; h < nch; ++h, ++ac) {
-                    const int as = ac % SA;
-                    ok = mbar_wait(&bars.a_full[as], (ac / SA) & 1, abort_flag);
-                    if (!ok) break;
-                    tc_fence_after();
-#pragma unroll
-                    for (int j = 0; j < 2; ++j) {
-                        const uint64_t bd = make_b_desc(b_addr + h * 64 + j * 32);
-                        mma_i8_ts(tmem_base, tmem_a + as * 16 + j * 8, bd, p.idesc, (ac | j) != 0 ? 1u : 0u);
-                    }
-                    tc_commit(&bars.a_empty[as]);   // frees the A chunk when these MMAs retire
-                }
-                tc_commit(&bars.b_empty[s]);
+            Ring bq{0, 0, SB};
+            const int y = g * a.M + m0;
+            for (int i = 0; i < nstages; ++i, bq.next()) {
+                if (!mbar_wait(&bars[BAR_B_EMPTY + bq.slot], bq.ph ^ 1, abort_flag)) break;
+                mbar_expect_tx(&bars[BAR_B_FULL + bq.slot], (uint32_t)b_stage_bytes);
+                tma_load_2d(b_ring + bq.slot * b_stage_bytes, &q_map, &bars[BAR_B_FULL + bq.slot], (stage0 + i) * 128, y);
             }
-            tc_commit(&bars.acc_full);
+        }
+    } else if (warp == WARP_MMA) {
+        // ------------------------------------------------------------ MMA issue
+        // One thread feeds the tensor core; the loop carries no division and builds descriptors by addition so
+        // that it stays well under the ~88 (N <= 128) / 130 (N = 256) cycles one MMA occupies the pipe.
+        if (elect_one()) {
+            Ring bq{0, 0, SB}, aq{0, 0, SA};
+            const uint64_t b_desc0 = make_b_desc(smem_u32(b_ring));
+            const uint32_t b_desc_step = (uint32_t)b_stage_bytes >> 4;
+            // consecutive MMAs rotate through `nacc` independent accumulators; the epilogue adds them (exact)
+            int acc = 0;
+            uint32_t started = 0;     // MMAs issued so far, saturating at nacc: the first use of an accumulator overwrites
+            const uint32_t nacc = (uint32_t)p.nacc, NTc = (uint32_t)p.NT;
+            for (int i = 0; i < nstages; ++i, bq.next(), aq.next()) {
+                if (!mbar_wait(&bars[BAR_B_FULL + bq.slot], bq.ph, abort_flag)) break;
+                if (!mbar_wait(&bars[BAR_A_FULL + aq.slot], aq.ph, abort_flag)) break;
+                tc_fence_after();
+                const uint64_t bd = b_desc0 + (uint64_t)(bq.slot * b_desc_step);
+                const uint32_t a_addr = tmem_a + aq.slot * 32;
+                const int nmma = min(2, p.KC - (stage0 + i) * 2) * 2;
+#pragma unroll
+                for (int k = 0; k < 4; ++k) {
+                    if (k < nmma) {
+                        mma_i8_ts(tmem_base + acc * NTc, a_addr + k * 8, bd + (uint64_t)(k * 2), p.idesc, started >= nacc ? 1u : 0u);
+                        if (++acc == (int)nacc) acc = 0;
+                        if (started < nacc) ++started;
+                    }
+                }
+                tc_commit(&bars[BAR_A_EMPTY + aq.slot]);   // frees the A stage when these MMAs retire
+                tc_commit(&bars[BAR_B_EMPTY + bq.slot]);
+            }
+            tc_commit(&bars[BAR_ACC]);
         }
     } else {
-        // ------------------------------------------------------------ unpack (warps 0-3), then epilogue
-        const uint32_t lane_addr = (uint32_t)(warp * 32) << 16;
-        int ac = 0;
+        // ------------------------------------------------------------ unpack (two groups of 4 warps), then epilogue
+        const int qd = warp & 3, gp = warp >> 2;
+        const int row = qd * 32 + lane;                      // weight row in the tile == TMEM lane
+        const uint32_t lane_addr = (uint32_t)(qd * 32) << 16;
         bool ok = true;
-        for (int i = 0; i < nstages && ok; ++i) {
-            const int s = i % SW;
-            ok = __all_sync(0xffffffffu, mbar_wait(&bars.w_full[s], (i / SW) & 1, abort_flag));   // warp-uniform
+        Ring w{0, 0, SW}, aq{0, 0, SA};
+        if (gp) { w.next(); aq.next(); }
+        for (int i = gp; i < nstages && ok; i += 2, w.next2(), aq.next2()) {        // the groups alternate stages
+            ok = __all_sync(0xffffffffu, mbar_wait(&bars[BAR_W_FULL + w.slot], w.ph, abort_flag));   // warp-uniform
             if (!ok) break;
+            if (i == 0) trace_mark(trace, 2);
             const int nch = min(2, p.KC - (stage0 + i) * 2);
-            for (int h = 0; h < nch; ++h, ++ac) {
-                const uint4 wv = *reinterpret_cast<const uint4*>(w_ring + s * W_STAGE_BYTES + h * (MMF_TILE_ROWS * 16) + tid * 16);
-                const int as = ac % SA;
-                ok = __all_sync(0xffffffffu, mbar_wait(&bars.a_empty[as], ((ac / SA) & 1) ^ 1, abort_flag));
-                if (!ok) break;   // uniform per warp: the .sync.aligned tcgen05 ops below need the whole warp
-                const uint32_t words[4] = {wv.x, wv.y, wv.z, wv.w};
-                uint32_t r[16];
+            const uint8_t* wsrc = w_ring + w.slot * W_STAGE_BYTES + row * 16;
+            uint4 wv[2];
+            wv[0] = *reinterpret_cast<const uint4*>(wsrc);
+            wv[1] = nch > 1 ? *reinterpret_cast<const uint4*>(wsrc + MMF_TILE_ROWS * 16) : wv[0];
+            mbar_arrive(&bars[BAR_W_EMPTY + w.slot]);         // the packed bytes are in registers now
+            ok = __all_sync(0xffffffffu, mbar_wait(&bars[BAR_A_EMPTY + aq.slot], aq.ph ^ 1, abort_flag));
+            if (!ok) break;   // uniform per warp: the .sync.aligned tcgen05 ops below need the whole warp
 #pragma unroll
-                for (int qd = 0; qd < 4; ++qd)
+            for (int h = 0; h < 2; ++h) {
+                if (h < nch) {
+                    const uint32_t words[4] = {wv[h].x, wv[h].y, wv[h].z, wv[h].w};
+                    uint32_t r[16];
 #pragma unroll
-                    for (int k4 = 0; k4 < 4; ++k4) r[qd * 4 + k4] = (words[qd] >> (2 * k4)) & 0x03030303u;
-                tmem_st16(tmem_a + lane_addr + as * 16, r);
-                tmem_wait_st();
-                tc_fence_before();
-                mbar_arrive(&bars.a_full[as]);
+                    for (int w4 = 0; w4 < 4; ++w4)
+#pragma unroll
+                        for (int k4 = 0; k4 < 4; ++k4) r[w4 * 4 + k4] = (words[w4] >> (2 * k4)) & 0x03030303u;
+                    tmem_st16(tmem_a + lane_addr + aq.slot * 32 + h * 16, r);
+                }
             }
-            mbar_arrive(&bars.w_empty[s]);
+            tmem_wait_st();
+            tc_fence_before();
+            mbar_arrive(&bars[BAR_A_FULL + aq.slot]);
         }
+        trace_mark(trace, 3);
 
-        // epilogue: thread <-> weight row n, columns <-> tokens
-        ok = __all_sync(0xffffffffu, ok && mbar_wait(&bars.acc_full, 0, abort_flag));
+        // ---- epilogue phase A: accumulator tile TMEM -> shared memory [token][row]
+        pdl_wait();                                       // dq / rowsum come from the preceding kernel
+        for (int i = tid; i < p.NT; i += UNPACK_THREADS) {
+            const int m = m0 + i;
+            const bool in = m < a.M;
+            s_dq[i] = in ? a.dq[(int64_t)g * a.M + m] : 0.0f;
+            s_rs[i] = in ? a.rowsum[(int64_t)g * a.M + m] : 0;
+        }
+        ok = __all_sync(0xffffffffu, ok && mbar_wait(&bars[BAR_ACC], 0, abort_flag));
         tc_fence_after();
+        trace_mark(trace, 4);
         if (ok) {
-            const int n = tile * MMF_TILE_ROWS + tid;
-            const float wsc = a.w_scale[g];
-            int32_t* part = reinterpret_cast<int32_t*>(b_ring);   // [NT][128] partial tile (the ring is idle now)
-            for (int c0 = 0; c0 < p.NT; c0 += 16) {
-                uint32_t v[16];
-                tmem_ld16(tmem_base + lane_addr + c0, v);
+            const int ngroups = p.NT >> 4;
+            const int total_mma = (min(p.KC, (stage0 + nstages) * 2) - stage0 * 2) * 2;   // MMAs this CTA issued
+            const int nused = min(p.nacc, total_mma);                                      // accumulators that hold data
+            for (int gi = gp; gi < ngroups; gi += 2) {        // groups of 16 columns, alternating between the warp groups
+                uint32_t v0[16], v1[16];
+                tmem_ld16(tmem_base + lane_addr + gi * 16, v0);
+                for (int acc = 1; acc < nused; ++acc) {       // fold the other accumulators in
+                    tmem_ld16(tmem_base + lane_addr + acc * p.NT + gi * 16, v1);
+                    tmem_wait_ld();
+#pragma unroll
+                    for (int j = 0; j < 16; ++j) v0[j] += v1[j];
+                }
                 tmem_wait_ld();
 #pragma unroll
-                for (int j = 0; j < 16; ++j) {
-                    if (p.ksplit > 1) {
-                        part[(c0 + j) * MMF_TILE_ROWS + tid] = (int32_t)v[j];
-                    } else {
-                        const int m = m0 + c0 + j;
-                        if (m < a.M && n < a.N) {
-                            const int32_t acc = (int32_t)v[j] - s_rs[c0 + j];
-                            if (a.acc_out) a.acc_out[(int64_t)m * a.N + n] = acc;
-                            store_out(a.out, a.out_dtype, (int64_t)m * a.ld_out + n, bitlinear_dequant(acc, s_dq[c0 + j], wsc));
+                for (int j = 0; j < 16; ++j) stg[(gi * 16 + j) * MMF_TILE_ROWS + row] = (int32_t)v0[j];
+            }
+        }
+        asm volatile("bar.sync 1, %0;" ::"n"(UNPACK_THREADS) : "memory");   // the 8 epilogue warps only
+        trace_mark(trace, 5);
+
+        // ---- phase B: 16 threads per token column, 8 consecutive weight rows each
+        const int cth = tid >> 4, n8 = (tid & 15) * 8;
+        const int n = tile * MMF_TILE_ROWS + n8;
+        const float wsc = a.w_scale[g];
+        if (p.ksplit == 1) {
+            if (ok) {
+                for (int c = cth; c < p.NT; c += UNPACK_THREADS / 16) {
+                    const int m = m0 + c;
+                    if (m >= a.M) break;
+                    const int4 x0 = *reinterpret_cast<const int4*>(stg + c * MMF_TILE_ROWS + n8);
+                    const int4 x1 = *reinterpret_cast<const int4*>(stg + c * MMF_TILE_ROWS + n8 + 4);
+                    int32_t acc[8] = {x0.x, x0.y, x0.z, x0.w, x1.x, x1.y, x1.z, x1.w};
+                    finish8(a, acc, m, n, s_rs[c], __fmul_rn(s_dq[c], wsc));
+                }
+            }
+        } else {
+            const int per = p.NT / p.ksplit;                  // token columns each CTA of the cluster finishes
+            cluster_wait();                                   // barrier #1: every CTA of the cluster is running
+            if (ok) {
+                // push the columns owned by peer o into its landing zone, slot [my rank]
+                const int vecs = per * (MMF_TILE_ROWS / 4);   // int4 pieces per slice
+                for (int o = 0; o < p.ksplit; ++o) {
+                    if (o == ks) continue;
+                    const int4* src = reinterpret_cast<const int4*>(stg + o * per * MMF_TILE_ROWS);
+                    int4* dst = reinterpret_cast<int4*>(part + ks * per * MMF_TILE_ROWS);
+                    for (int idx = tid; idx < vecs; idx += UNPACK_THREADS) st_peer_v4(dst + idx, (uint32_t)o, src[idx]);
+                }
+            }
+            cluster_arrive();                                 // barrier #2 orders all pushes before the owners' reads
+            cluster_wait();
+            trace_mark(trace, 6);
+            if (ok && !*abort_flag) {
+                for (int cl = cth; cl < per; cl += UNPACK_THREADS / 16) {
+                    const int c = ks * per + cl;
+                    const int m = m0 + c;
+                    if (m >= a.M) break;
+                    const int4 x0 = *reinterpret_cast<const int4*>(stg + c * MMF_TILE_ROWS + n8);
+                    const int4 x1 = *reinterpret_cast<const int4*>(stg + c * MMF_TILE_ROWS + n8 + 4);
+                    int32_t acc[8] = {x0.x, x0.y, x0.z, x0.w, x1.x, x1.y, x1.z, x1.w};
+#pragma unroll
+                    for (int peer = 0; peer < 8; ++peer) {
+                        if (peer < p.ksplit && peer != ks) {
+                            const int4 y0 = *reinterpret_cast<const int4*>(part + (peer * per + cl) * MMF_TILE_ROWS + n8);
+                            const int4 y1 = *reinterpret_cast<const int4*>(part + (peer * per + cl) * MMF_TILE_ROWS + n8 + 4);
+                            acc[0] += y0.x; acc[1] += y0.y; acc[2] += y0.z; acc[3] += y0.w;
+                            acc[4] += y1.x; acc[5] += y1.y; acc[6] += y1.z; acc[7] += y1.w;
                         }
                     }
+                    finish8(a, acc, m, n, s_rs[c], __fmul_rn(s_dq[c], wsc));
                 }
             }
         }
+        trace_mark(trace, 7);
     }
 
-    if (p.ksplit > 1) {
-        // split-K: every CTA of the cluster has parked its partial tile; reduce my share of the token columns
-        cluster_sync_all();
-        if (warp < 4 && !*abort_flag) {
-            const int n = tile * MMF_TILE_ROWS + tid;
-            const float wsc = a.w_scale[g];
-            const int32_t* part = reinterpret_cast<const int32_t*>(b_ring);
-            const int per = p.NT / p.ksplit;
-            for (int c = ks * per; c < (ks + 1) * per; ++c) {
-                int32_t acc = 0;
-                for (int peer = 0; peer < p.ksplit; ++peer) acc += ld_peer_s32(part + c * MMF_TILE_ROWS + tid, (uint32_t)peer);
-                const int m = m0 + c;
-                if (m < a.M && n < a.N) {
-                    acc -= s_rs[c];
-                    if (a.acc_out) a.acc_out[(int64_t)m * a.N + n] = acc;
-                    store_out(a.out, a.out_dtype, (int64_t)m * a.ld_out + n, bitlinear_dequant(acc, s_dq[c], wsc));
-                }
-            }
-        }
-        cluster_sync_all();   // peers may still be reading this CTA's shared memory
+    if (p.ksplit > 1 && warp >= NUM_UNPACK_WARPS) {   // the three service warps take part in both cluster barriers
+        cluster_wait();
+        cluster_arrive();
+        cluster_wait();
     }
 
     // teardown: everyone meets, TMEM goes back; on the error path give copies in flight time to land first
@@ -358,7 +494,7 @@ bitlinear_mma_kernel(const __grid_constant__ CUtensorMap q_map, BitLinearArgs a,
     }
     tc_fence_before();
     __syncthreads();
-    if (warp == 5) tmem_dealloc(tmem_base, (uint32_t)p.tmem_cols);
+    if (warp == WARP_MMA) tmem_dealloc(tmem_base, (uint32_t)p.tmem_cols);
 }
 
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
@@ -379,25 +515,99 @@ EncodeTiledFn get_encode_tiled() {
 
 }  // namespace
 
+// tuning overrides (0 = automatic), see mmf_tuning()
+static int g_force_ksplit = 0, g_force_nt = 0, g_force_deep = 0;
+
+extern "C" int mmf_tuning(int knob, int value) {
+    switch (knob) {
+        case MMF_TUNE_KSPLIT: g_force_ksplit = value; return MMF_OK;
+        case MMF_TUNE_TOKEN_TILE: g_force_nt = value; return MMF_OK;
+        case MMF_TUNE_DEEP_RING: g_force_deep = value; return MMF_OK;
+        default: return mmf_set_error(MMF_ERR_BAD_ARG, "mmf_tuning: unknown knob %d", knob);
+    }
+}
+
+namespace {
+
+// Pick token tile, K split and ring depths.  Two regimes:
+//  * "deep ring" (few tokens, no K split): the CTA owns all of TMEM (512 columns), so up to 14 unpacked A
+//    stages plus a 24-stage packed ring hold most of a weight tile BEFORE the activations exist — under
+//    programmatic dependent launch the weight stream and its unpacking overlap the preceding kernels, and
+//    what is left after the dependency wait is the activation load, the MMAs and the epilogue;
+//  * "split" (more tokens / few weight tiles): 4 A stages, K split over a cluster when that fills the GPU.
+// The estimate below is a latency model in microseconds fitted to measured phase times of this kernel.
+bool choose_config(const BitLinearArgs& a, MmaParams& best, size_t& best_smem) {
+    const int KC = a.K / MMF_TILE_K;
+    const int n_tiles = (a.N + MMF_TILE_ROWS - 1) / MMF_TILE_ROWS;
+    const int total_stages = (KC + 1) / 2;
+    double best_cost = 1e30;
+    bool found = false;
+    int nts[3], n_nt = 0;
+    if (a.M <= 128) nts[n_nt++] = ((a.M + 15) / 16) * 16;
+    else { nts[n_nt++] = 128; nts[n_nt++] = 256; }
+    for (int ni = 0; ni < n_nt; ++ni) {
+        const int NT = nts[ni];
+        if (g_force_nt && NT != g_force_nt) continue;
+        const int m_tiles = (a.M + NT - 1) / NT;
+        for (int ks = 1; ks <= 8; ks *= 2) {
+            if (ks > 1 && (NT > 128 || ks > total_stages)) break;
+            if (g_force_ksplit && ks != g_force_ksplit) continue;
+            const int stages = (total_stages + ks - 1) / ks;
+            if (ks > 1 && stages * (ks - 1) >= total_stages) continue;   // every CTA must own >= 1 stage
+            for (int deep = 0; deep <= 1; ++deep) {
+                if (deep && (ks != 1 || NT > 64 || g_force_deep != 1)) continue;   // deep ring only on request
+                if (g_force_deep == 1 && !deep && ks == 1 && NT <= 64) continue;
+                if (g_force_deep == 2 && deep) continue;
+                MmaParams p;
+                p.KC = KC; p.n_tiles = n_tiles; p.group_tiles = n_tiles / a.groups; p.NT = NT; p.ksplit = ks;
+                p.stages_per_cta = stages;
+                size_t smem;
+                int occ;
+                if (deep) {
+                    p.tmem_cols = 512;
+                    p.nacc = 256 / NT < 8 ? 256 / NT : 8;
+                    p.SA = (512 - p.nacc * NT) / 32; if (p.SA > MAX_SA) p.SA = MAX_SA;
+                    p.SW = stages < 24 ? stages : 24;
+                    const size_t room = 220 * 1024 - (size_t)p.SW * W_STAGE_BYTES;
+                    p.SB = (int)(room / ((size_t)NT * 128));
+                    if (p.SB > stages) p.SB = stages;
+                    if (p.SB > MAX_SB) p.SB = MAX_SB;
+                    smem = 1024 + (size_t)p.SB * NT * 128 + (size_t)p.SW * W_STAGE_BYTES;
+                    if (smem < 120 * 1024) smem = 120 * 1024;   // one CTA per SM: it holds all 512 TMEM columns
+                    occ = 1;
+                } else {
+                    p.SA = 4; p.SB = 4; p.SW = 12;
+                    p.nacc = NT >= 128 ? 1 : (128 / NT < 4 ? 128 / NT : 4);
+                    int cols = 32;
+                    while (cols < p.nacc * NT + p.SA * 32) cols *= 2;
+                    p.tmem_cols = cols;
+                    smem = 1024 + (size_t)p.SB * NT * 128 + (size_t)p.SW * W_STAGE_BYTES + (ks > 1 ? (size_t)NT * MMF_TILE_ROWS * 4 : 0);
+                    occ = (smem <= 110 * 1024 && cols <= 256) ? 2 : 1;
+                }
+                if (smem > 227 * 1024) continue;
+                const int64_t ctas = (int64_t)n_tiles * m_tiles * ks;
+                const int64_t waves = (ctas + 148 * occ - 1) / (148 * occ);
+                // fitted to measured phase times (us): per 128-K stage 4 MMAs of >= 88 cycles each (130 at 256 token
+                // columns) plus issue overhead; fixed launch/set-up/first-TMA latency; epilogue; cluster reduction
+                const double t_stage = NT > 128 ? 0.30 : 0.24;
+                double t = 2.5 + stages * t_stage + 0.5 + NT * 0.012;
+                if (ks > 1) t += 1.5 + NT * 0.012;
+                const double cost = waves * t;
+                if (cost < best_cost) { best_cost = cost; best = p; best_smem = smem; found = true; }
+            }
+        }
+    }
+    return found;
+}
+
+}  // namespace
+
 int bitlinear_mma_launch(const BitLinearArgs& a, cudaStream_t st) {
     MmaParams p;
-    p.KC = a.K / MMF_TILE_K;
-    p.n_tiles = (a.N + MMF_TILE_ROWS - 1) / MMF_TILE_ROWS;
-    p.group_tiles = p.n_tiles / a.groups;
-    p.NT = a.M >= 256 ? 256 : ((a.M + 15) / 16) * 16;
+    size_t smem = 0;
+    MMF_REQUIRE(choose_config(a, p, smem), MMF_ERR_BAD_SHAPE, "mmf_bitlinear(mma): no kernel configuration fits M=%d N=%d K=%d", a.M,
+                a.N, a.K);
     const int m_tiles = (a.M + p.NT - 1) / p.NT;
-    const int total_stages = (p.KC + 1) / 2;
-    // split K over a cluster of 2/4/8 CTAs until the grid covers the GPU
-    p.ksplit = 1;
-    while (p.ksplit < 8 && (int64_t)p.n_tiles * m_tiles * p.ksplit < 148 && p.ksplit * 2 <= total_stages) p.ksplit *= 2;
-    p.stages_per_cta = (total_stages + p.ksplit - 1) / p.ksplit;
-    while (p.ksplit > 1 && p.stages_per_cta * (p.ksplit - 1) >= total_stages) {   // every CTA must own >= 1 stage
-        p.ksplit /= 2;
-        p.stages_per_cta = (total_stages + p.ksplit - 1) / p.ksplit;
-    }
-    int cols = 32;
-    while (cols < p.NT + SA * 16) cols *= 2;
-    p.tmem_cols = cols;
     // instruction descriptor: D=S32, A=S8 (TMEM), B=S8 (smem, K-major), M=128, N=NT
     p.idesc = (2u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(p.NT >> 3) << 17) | ((uint32_t)(128 >> 4) << 24);
 
@@ -413,7 +623,6 @@ int bitlinear_mma_launch(const BitLinearArgs& a, cudaStream_t st) {
                                CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     MMF_REQUIRE(cr == CUDA_SUCCESS, MMF_ERR_CUDA, "mmf_bitlinear(mma): cuTensorMapEncodeTiled failed (%d)", (int)cr);
 
-    const size_t smem = 1024 + (size_t)SB * p.NT * 128 + (size_t)SW * W_STAGE_BYTES;
     MMF_CUDA(cudaFuncSetAttribute(bitlinear_mma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     const dim3 grid((unsigned)p.ksplit, (unsigned)p.n_tiles, (unsigned)m_tiles);
     MMF_REQUIRE(m_tiles <= 65535 && p.n_tiles <= 65535, MMF_ERR_BAD_SHAPE, "mmf_bitlinear(mma): problem too large");
@@ -422,13 +631,15 @@ int bitlinear_mma_launch(const BitLinearArgs& a, cudaStream_t st) {
     cfg.blockDim = dim3(MM_THREADS);
     cfg.dynamicSmemBytes = smem;
     cfg.stream = st;
-    cudaLaunchAttribute attr[1];
+    cudaLaunchAttribute attr[2];
     attr[0].id = cudaLaunchAttributeClusterDimension;
     attr[0].val.clusterDim.x = (unsigned)p.ksplit;
     attr[0].val.clusterDim.y = 1;
     attr[0].val.clusterDim.z = 1;
+    attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[1].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
-    cfg.numAttrs = 1;
+    cfg.numAttrs = 2;
     MMF_CUDA(cudaLaunchKernelEx(&cfg, bitlinear_mma_kernel, q_map, a, p));
     MMF_LAUNCH_CHECK("bitlinear_mma_kernel");
     return MMF_OK;

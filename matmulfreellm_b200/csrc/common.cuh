@@ -18,11 +18,11 @@ int mmf_set_error(int code, const char* fmt, ...);
         if (!(cond)) return mmf_set_error(code, __VA_ARGS__); \
     } while (0)
 
-#define MMF_CUDA(call)                                                                  \
+#define MMF_CUDA(...)                                                                   \
     do {                                                                                \
-        cudaError_t e__ = (call);                                                       \
+        cudaError_t e__ = (__VA_ARGS__);                                                \
         if (e__ != cudaSuccess)                                                         \
-            return mmf_set_error(MMF_ERR_CUDA, "%s failed: %s", #call, cudaGetErrorString(e__)); \
+            return mmf_set_error(MMF_ERR_CUDA, "%s failed: %s", #__VA_ARGS__, cudaGetErrorString(e__)); \
     } while (0)
 
 #define MMF_LAUNCH_CHECK(name)                                                          \
@@ -44,6 +44,32 @@ static inline int mmf_dtype_size(int dt) { return dt == MMF_F32 ? 4 : 2; }
         case MMF_BF16: { using T = __nv_bfloat16; __VA_ARGS__; break; } \
         default: { using T = __half; __VA_ARGS__; break; }              \
     }
+
+// ---------------------------------------------------------------------------------------
+// programmatic dependent launch: the kernels of a decode step are launched with the
+// programmatic-stream-serialization attribute, so kernel N+1 may start (and run whatever does not
+// depend on kernel N: barrier set-up, constants, the weight stream) while kernel N drains.  Every
+// such kernel calls pdl_trigger() at its top and pdl_wait() before it touches memory written by
+// its predecessors; pdl_wait() returns once those grids have completed and flushed.
+// ---------------------------------------------------------------------------------------
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
+template <typename... KArgs, typename... Args>
+inline cudaError_t mmf_launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st,
+                                  Args... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
 
 // ---------------------------------------------------------------------------------------
 // element conversion (round-to-nearest-even on store, exact on load)

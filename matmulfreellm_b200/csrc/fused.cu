@@ -10,85 +10,146 @@
 //                   + int8 quant) sharing one row statistic        (attn_norm -> i/f/g, mlp_norm -> gate)
 //   gatenorm_quant: RMSNorm(g) * w * o * sigmoid(o) -> T ; BitLinear RMSNorm + quant   (g_norm -> o_proj)
 //   swiglu_quant  : silu(gate) * up -> T ; BitLinear RMSNorm + quant                   (MLP -> down_proj)
-// (the gate math of the recurrence itself is fused into the scan kernel, hgrn.cu)
+//   decode_mix    : single-token step of the token mixer: gate math, state update in place, then
+//                   gatenorm_quant — one kernel between the i/f/g contraction and o_proj
+// (for T > 1 the gate math of the recurrence is fused into the scan kernel, hgrn.cu)
+//
+// These kernels are latency chains (one CTA per token row, a handful of block-wide reductions), so
+// the row lives in registers (<= 32 values per thread), the constant norm weights are copied to
+// shared memory BEFORE the grid-dependency wait (they do not depend on the preceding kernel), and
+// every block reduction costs a single __syncthreads.
 #include "common.cuh"
 
 namespace {
 
-constexpr int FT = 256;  // threads per row CTA
+constexpr int FT = 256;        // threads per row CTA
+constexpr int FW = FT / 32;    // warps
+constexpr int PER = 32;        // row values a thread can hold -> D <= FT * PER = 8192
+constexpr int MAX_D = FT * PER;
 
-__device__ __forceinline__ void block_max3(float (&v)[3], float* red /* >= 3*33 */) {
-    const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5, nw = blockDim.x >> 5;
+// One-sync block reductions: warp shuffle, lane 0 parks the partial in a slot that is used once per kernel,
+// one barrier, then every thread folds the FW partials in a fixed order.
+template <int K>
+__device__ __forceinline__ void block_sum_d(double (&v)[K], double* slot /* K*FW */) {
+    const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
 #pragma unroll
-    for (int k = 0; k < 3; ++k) v[k] = warp_max(v[k]);
-    __syncthreads();
-    if (lane == 0) { red[wid] = v[0]; red[33 + wid] = v[1]; red[66 + wid] = v[2]; }
-    __syncthreads();
-    if (wid == 0) {
+    for (int k = 0; k < K; ++k) v[k] = warp_sum(v[k]);
+    if (lane == 0) {
 #pragma unroll
-        for (int k = 0; k < 3; ++k) {
-            float t = lane < nw ? red[33 * k + lane] : 0.0f;
-            t = warp_max(t);
-            if (lane == 0) red[33 * k + 32] = t;
-        }
+        for (int k = 0; k < K; ++k) slot[k * FW + wid] = v[k];
     }
     __syncthreads();
 #pragma unroll
-    for (int k = 0; k < 3; ++k) v[k] = red[33 * k + 32];
-}
-
-// quantise the row cached in `row` (already = y1, the BitLinear's input in T precision) for projection g
-template <int V>
-__device__ __forceinline__ void quant_store(const float* row, int D, float rstd, const float* nw, float s,
-                                            int8_t* qr, int& lsum) {
-    for (int c = threadIdx.x * V; c < D; c += FT * V) {
-        int8_t codes[V];
+    for (int k = 0; k < K; ++k) {
+        double t = 0.0;
 #pragma unroll
-        for (int i = 0; i < V; ++i) {
-            float y = __fmul_rn(row[c + i], rstd);
-            if (nw) y = __fmul_rn(y, nw[c + i]);
-            float r = rintf(__fmul_rn(y, s));
-            r = fminf(fmaxf(r, -128.0f), 127.0f);
-            const int iv = (int)r;
-            codes[i] = (int8_t)iv;
-            lsum += iv;
-        }
-        if constexpr (V == 8) *reinterpret_cast<uint2*>(qr + c) = *reinterpret_cast<const uint2*>(codes);
-        else *reinterpret_cast<uint32_t*>(qr + c) = *reinterpret_cast<const uint32_t*>(codes);
+        for (int w = 0; w < FW; ++w) t += slot[k * FW + w];
+        v[k] = t;
+    }
+}
+template <int K>
+__device__ __forceinline__ void block_max_f(float (&v)[K], float* slot) {
+    const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
+#pragma unroll
+    for (int k = 0; k < K; ++k) v[k] = warp_max(v[k]);
+    if (lane == 0) {
+#pragma unroll
+        for (int k = 0; k < K; ++k) slot[k * FW + wid] = v[k];
+    }
+    __syncthreads();
+#pragma unroll
+    for (int k = 0; k < K; ++k) {
+        float t = 0.0f;
+#pragma unroll
+        for (int w = 0; w < FW; ++w) t = fmaxf(t, slot[k * FW + w]);
+        v[k] = t;
+    }
+}
+template <int K>
+__device__ __forceinline__ void block_sum_i(int (&v)[K], int* slot) {
+    const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
+#pragma unroll
+    for (int k = 0; k < K; ++k) v[k] = warp_sum(v[k]);
+    if (lane == 0) {
+#pragma unroll
+        for (int k = 0; k < K; ++k) slot[k * FW + wid] = v[k];
+    }
+    __syncthreads();
+#pragma unroll
+    for (int k = 0; k < K; ++k) {
+        int t = 0;
+#pragma unroll
+        for (int w = 0; w < FW; ++w) t += slot[k * FW + w];
+        v[k] = t;
     }
 }
 
-// BitLinear prologue on a row already cached in shared memory as T-precision floats:
-// one shared sum of squares, then per projection absmax -> scale -> codes.
+struct RedScratch {       // each member is written once per kernel -> no barrier needed to recycle it
+    double d0[3 * FW], d1[3 * FW];
+    float f0[3 * FW];
+    int i0[3 * FW];
+};
+
+// copy `n` floats (or ones, if src is null) into shared memory; all threads take part
+__device__ __forceinline__ void stage_weights(float* dst, const float* src, int n) {
+    for (int i = threadIdx.x * 4; i < n; i += FT * 4) {
+        float4 v = make_float4(1.0f, 1.0f, 1.0f, 1.0f);
+        if (src) v = *reinterpret_cast<const float4*>(src + i);
+        *reinterpret_cast<float4*>(dst + i) = v;
+    }
+}
+
+// iterate over the 16-byte vectors of a row held as v[PER]: vector `it` of this thread starts at column c
+#define ROW_FOREACH(V, D, it, c) \
+    _Pragma("unroll") for (int it = 0, c = threadIdx.x * (V); it < PER / (V); ++it, c += FT * (V)) if (c < (D))
+
+// BitLinear prologue on a register-resident row `v` (values already in T precision): shared sum of squares
+// `ss`, then per projection g: y = (v*rstd)*nw_g, absmax -> scale -> int8 codes, dq, rowsum.
 template <int V, int G>
-__device__ __forceinline__ void bitlinear_prologue(float* row, int D, double ss, float eps, const float* const* nws,
-                                                   int8_t* const* qs, float* const* dqs, int32_t* const* rss, int64_t m,
-                                                   double* redd, float* redf, int* redi) {
-    const float rstd = rstd_from_sumsq(block_sum(ss, redd), D, eps);
-    float amax[3] = {0.0f, 0.0f, 0.0f};
-    for (int c = threadIdx.x * V; c < D; c += FT * V) {
+__device__ __forceinline__ void bitlinear_prologue(const float (&v)[PER], int D, double ss, float eps, const float* snw /* smem [G][D] */,
+                                                   int8_t* q, float* dq, int32_t* rowsum, int64_t M, int64_t m, RedScratch& red) {
+    double s1[1] = {ss};
+    block_sum_d<1>(s1, red.d1);
+    const float rstd = rstd_from_sumsq(s1[0], D, eps);
+    float amax[G];
+#pragma unroll
+    for (int g = 0; g < G; ++g) amax[g] = 0.0f;
+    ROW_FOREACH(V, D, it, c) {
 #pragma unroll
         for (int i = 0; i < V; ++i) {
-            const float y = __fmul_rn(row[c + i], rstd);
+            const float y = __fmul_rn(v[it * V + i], rstd);
 #pragma unroll
-            for (int g = 0; g < G; ++g) {
-                const float yg = nws[g] ? __fmul_rn(y, nws[g][c + i]) : y;
-                amax[g] = fmaxf(amax[g], fabsf(yg));
-            }
+            for (int g = 0; g < G; ++g) amax[g] = fmaxf(amax[g], fabsf(__fmul_rn(y, snw[g * D + c + i])));
         }
     }
-    block_max3(amax, redf);
+    block_max_f<G>(amax, red.f0);
+    int lsum[G];
 #pragma unroll
     for (int g = 0; g < G; ++g) {
         const float a = fmaxf(amax[g], 1e-5f);
         const float s = __fdiv_rn(127.0f, a);
-        int lsum = 0;
-        quant_store<V>(row, D, rstd, nws[g], s, qs[g] + m * (int64_t)D, lsum);
-        lsum = block_sum(lsum, redi);
-        if (threadIdx.x == 0) {
-            dqs[g][m] = __fdiv_rn(a, 127.0f);
-            rss[g][m] = lsum;
+        int8_t* qr = q + ((int64_t)g * M + m) * D;
+        lsum[g] = 0;
+        ROW_FOREACH(V, D, it, c) {
+            int8_t codes[V];
+#pragma unroll
+            for (int i = 0; i < V; ++i) {
+                const float y = __fmul_rn(__fmul_rn(v[it * V + i], rstd), snw[g * D + c + i]);
+                float r = rintf(__fmul_rn(y, s));
+                r = fminf(fmaxf(r, -128.0f), 127.0f);
+                const int iv = (int)r;
+                codes[i] = (int8_t)iv;
+                lsum[g] += iv;
+            }
+            if constexpr (V == 8) *reinterpret_cast<uint2*>(qr + c) = *reinterpret_cast<const uint2*>(codes);
+            else *reinterpret_cast<uint32_t*>(qr + c) = *reinterpret_cast<const uint32_t*>(codes);
         }
+        if (threadIdx.x == 0) dq[(int64_t)g * M + m] = __fdiv_rn(a, 127.0f);
+    }
+    block_sum_i<G>(lsum, red.i0);
+    if (threadIdx.x == 0) {
+#pragma unroll
+        for (int g = 0; g < G; ++g) rowsum[(int64_t)g * M + m] = lsum[g];
     }
 }
 
@@ -107,133 +168,199 @@ struct PrenormArgs {
 template <typename T>
 __global__ void __launch_bounds__(FT)
 prenorm_quant_kernel(PrenormArgs a) {
-    extern __shared__ __align__(16) float row[];
-    __shared__ double redd[33];
-    __shared__ float redf[99];
-    __shared__ int redi[33];
+    extern __shared__ __align__(16) float sw[];   // [1 + G][D]: block norm weight, then the BitLinear norm weights
+    __shared__ RedScratch red;
     constexpr int V = 16 / sizeof(T);
-    const int64_t m = blockIdx.x;
     const int D = a.D;
+    pdl_trigger();
+    stage_weights(sw, a.norm_w, D);
+    for (int g = 0; g < a.G; ++g) stage_weights(sw + (1 + g) * D, a.nws[g], D);
+    pdl_wait();
+    __syncthreads();
+
+    const int64_t m = blockIdx.x;
     const T* xr = reinterpret_cast<const T*>(a.x) + m * a.ld_x;
     const T* rr = a.res ? reinterpret_cast<const T*>(a.res) + m * a.ld_res : nullptr;
     T* ro = a.res_out ? reinterpret_cast<T*>(a.res_out) + m * (int64_t)D : nullptr;
-
-    double ss = 0.0;
-    for (int c = threadIdx.x * V; c < D; c += FT * V) {
-        float v[V];
-        load16<T>(xr + c, v);
+    float v[PER];
+    double ss[1] = {0.0};
+    ROW_FOREACH(V, D, it, c) {
+        float x[V];
+        load16<T>(xr + c, x);
         if (rr) {
             float r[V];
             load16<T>(rr + c, r);
 #pragma unroll
-            for (int i = 0; i < V; ++i) v[i] = __fadd_rn(v[i], r[i]);
+            for (int i = 0; i < V; ++i) x[i] = __fadd_rn(x[i], r[i]);
         }
-        if (ro) store16<T>(ro + c, v);
+        if (ro) store16<T>(ro + c, x);
 #pragma unroll
         for (int i = 0; i < V; ++i) {
-            if (a.round_sum_first) v[i] = round_to<T>(v[i]);
-            row[c + i] = v[i];
-            ss += (double)v[i] * (double)v[i];
+            if (a.round_sum_first) x[i] = round_to<T>(x[i]);
+            v[it * V + i] = x[i];
+            ss[0] += (double)x[i] * (double)x[i];
         }
     }
-    const float rstd1 = rstd_from_sumsq(block_sum(ss, redd), D, a.eps_norm);
+    block_sum_d<1>(ss, red.d0);
+    const float rstd1 = rstd_from_sumsq(ss[0], D, a.eps_norm);
     T* yo = a.y_out ? reinterpret_cast<T*>(a.y_out) + m * (int64_t)D : nullptr;
     double ss2 = 0.0;
-    for (int c = threadIdx.x * V; c < D; c += FT * V) {
+    ROW_FOREACH(V, D, it, c) {
         float o[V];
 #pragma unroll
         for (int i = 0; i < V; ++i) {
-            float t = __fmul_rn(row[c + i], rstd1);
-            if (a.norm_w) t = __fmul_rn(t, a.norm_w[c + i]);
-            t = round_to<T>(t);
+            const float t = round_to<T>(__fmul_rn(__fmul_rn(v[it * V + i], rstd1), sw[c + i]));
             o[i] = t;
-            row[c + i] = t;
+            v[it * V + i] = t;
             ss2 += (double)t * (double)t;
         }
         if (yo) store16<T>(yo + c, o);
     }
-    if (a.G == 0) return;
-    const float* nws[3] = {a.nws[0], a.nws[1], a.nws[2]};
-    int8_t* qs[3]; float* dqs[3]; int32_t* rss[3];
-#pragma unroll
-    for (int g = 0; g < 3; ++g) {
-        qs[g] = a.q + (int64_t)g * a.M * D;
-        dqs[g] = a.dq + (int64_t)g * a.M;
-        rss[g] = a.rowsum + (int64_t)g * a.M;
-    }
-    if (a.G == 3) bitlinear_prologue<V, 3>(row, D, ss2, a.eps_bl, nws, qs, dqs, rss, m, redd, redf, redi);
-    else bitlinear_prologue<V, 1>(row, D, ss2, a.eps_bl, nws, qs, dqs, rss, m, redd, redf, redi);
+    if (a.G == 3) bitlinear_prologue<V, 3>(v, D, ss2, a.eps_bl, sw + D, a.q, a.dq, a.rowsum, a.M, m, red);
+    else if (a.G == 1) bitlinear_prologue<V, 1>(v, D, ss2, a.eps_bl, sw + D, a.q, a.dq, a.rowsum, a.M, m, red);
 }
 
-// y = round_T( ((g*rstd)*w) * o * sigmoid(o) ), then BitLinear prologue
+// y = round_T( ((g*rstd)*w) * o * sigmoid(o) ), then BitLinear prologue.  `ov` holds the gate row o in registers.
+template <typename T, int V>
+__device__ __forceinline__ void gatenorm_tail(float (&gv)[PER], const float (&ov)[PER], double ssg, int D, float eps_g, float eps_bl,
+                                              const float* sw /* [2][D]: g_norm weight, BitLinear norm weight */, int8_t* q, float* dq,
+                                              int32_t* rowsum, int64_t M, int64_t m, RedScratch& red) {
+    double s0[1] = {ssg};
+    block_sum_d<1>(s0, red.d0);
+    const float rstd = rstd_from_sumsq(s0[0], D, eps_g);
+    double ss2 = 0.0;
+    ROW_FOREACH(V, D, it, c) {
+#pragma unroll
+        for (int i = 0; i < V; ++i) {
+            const float o = ov[it * V + i];
+            float t = __fmul_rn(__fmul_rn(gv[it * V + i], rstd), sw[c + i]);
+            t = __fmul_rn(t, o);
+            t = round_to<T>(__fmul_rn(t, sigmoidf_(o)));
+            gv[it * V + i] = t;
+            ss2 += (double)t * (double)t;
+        }
+    }
+    bitlinear_prologue<V, 1>(gv, D, ss2, eps_bl, sw + D, q, dq, rowsum, M, m, red);
+}
+
 template <typename T>
 __global__ void __launch_bounds__(FT)
 gatenorm_quant_kernel(const T* __restrict__ gx, int64_t ld_g, const T* __restrict__ o, int64_t ld_o,
                       const float* __restrict__ gw, float eps_g, const float* __restrict__ nw, float eps_bl,
-                      int8_t* __restrict__ q, float* __restrict__ dq, int32_t* __restrict__ rowsum, int D) {
-    extern __shared__ __align__(16) float row[];
-    __shared__ double redd[33];
-    __shared__ float redf[99];
-    __shared__ int redi[33];
+                      int8_t* __restrict__ q, float* __restrict__ dq, int32_t* __restrict__ rowsum, int64_t M, int D) {
+    extern __shared__ __align__(16) float sw[];
+    __shared__ RedScratch red;
     constexpr int V = 16 / sizeof(T);
+    pdl_trigger();
+    stage_weights(sw, gw, D);
+    stage_weights(sw + D, nw, D);
+    pdl_wait();
+    __syncthreads();
     const int64_t m = blockIdx.x;
     const T* gr = gx + m * ld_g;
     const T* orow = o + m * ld_o;
+    float gv[PER], ov[PER];
     double ss = 0.0;
-    for (int c = threadIdx.x * V; c < D; c += FT * V) {
-        float v[V];
-        load16<T>(gr + c, v);
-#pragma unroll
-        for (int i = 0; i < V; ++i) { row[c + i] = v[i]; ss += (double)v[i] * (double)v[i]; }
-    }
-    const float rstd = rstd_from_sumsq(block_sum(ss, redd), D, eps_g);
-    double ss2 = 0.0;
-    for (int c = threadIdx.x * V; c < D; c += FT * V) {
-        float ov[V];
-        load16<T>(orow + c, ov);
+    ROW_FOREACH(V, D, it, c) {
+        float a[V], b[V];
+        load16<T>(gr + c, a);
+        load16<T>(orow + c, b);
 #pragma unroll
         for (int i = 0; i < V; ++i) {
-            float t = __fmul_rn(row[c + i], rstd);
-            if (gw) t = __fmul_rn(t, gw[c + i]);
-            t = __fmul_rn(t, ov[i]);
-            t = round_to<T>(__fmul_rn(t, sigmoidf_(ov[i])));
-            row[c + i] = t;
-            ss2 += (double)t * (double)t;
+            gv[it * V + i] = a[i];
+            ov[it * V + i] = b[i];
+            ss += (double)a[i] * (double)a[i];
         }
     }
-    const float* nws[3] = {nw, nullptr, nullptr};
-    int8_t* qs[3] = {q, nullptr, nullptr}; float* dqs[3] = {dq, nullptr, nullptr}; int32_t* rss[3] = {rowsum, nullptr, nullptr};
-    bitlinear_prologue<V, 1>(row, D, ss2, eps_bl, nws, qs, dqs, rss, m, redd, redf, redi);
+    gatenorm_tail<T, V>(gv, ov, ss, D, eps_g, eps_bl, sw, q, dq, rowsum, M, m, red);
+}
+
+// Single-token step of the token mixer for row b (mmfreelm/layers/hgrn_bit.py:113-140 with T = 1):
+//   f = round(sigmoid(f_raw)); with lb: f = round(lb + round(round(1-lb)*f));  x = round(silu(i_raw)*round(1-f))
+//   h = f*h + x  (fp32 state, updated in place);  o = round(h);  then gatenorm_quant(g_raw, o).
+template <typename T>
+__global__ void __launch_bounds__(FT)
+decode_mix_kernel(const T* __restrict__ ifg, int64_t ld, const T* __restrict__ lb, float* __restrict__ state,
+                  const float* __restrict__ gw, float eps_g, const float* __restrict__ nw, float eps_bl,
+                  int8_t* __restrict__ q, float* __restrict__ dq, int32_t* __restrict__ rowsum, int64_t M, int D) {
+    extern __shared__ __align__(16) float sw[];   // [3][D]: g_norm weight, BitLinear norm weight, lower bound (as float)
+    __shared__ RedScratch red;
+    constexpr int V = 16 / sizeof(T);
+    pdl_trigger();
+    stage_weights(sw, gw, D);
+    stage_weights(sw + D, nw, D);
+    pdl_wait();     // the lower bounds are computed by a preceding kernel of the same forward pass
+    if (lb)
+        for (int i = threadIdx.x; i < D; i += FT) sw[2 * D + i] = to_f32(lb[i]);
+    __syncthreads();
+    const int64_t m = blockIdx.x;
+    const T* ir = ifg + m * ld;
+    const T* fr = ir + D;
+    const T* gr = ir + 2 * D;
+    float* st = state + m * (int64_t)D;
+    float gv[PER], ov[PER];
+    double ss = 0.0;
+    ROW_FOREACH(V, D, it, c) {
+        float iv[V], fv[V], g8[V];
+        load16<T>(ir + c, iv);
+        load16<T>(fr + c, fv);
+        load16<T>(gr + c, g8);
+#pragma unroll
+        for (int i = 0; i < V; i += 4) {
+            float4 h4 = *reinterpret_cast<const float4*>(st + c + i);
+            float hh[4] = {h4.x, h4.y, h4.z, h4.w};
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                float f = round_to<T>(sigmoidf_(fv[i + j]));
+                if (lb) {
+                    const float lbv = sw[2 * D + c + i + j];
+                    const float oml = round_to<T>(__fsub_rn(1.0f, lbv));
+                    f = round_to<T>(__fadd_rn(lbv, round_to<T>(__fmul_rn(oml, f))));
+                }
+                const float x = round_to<T>(silu_mul(iv[i + j], round_to<T>(__fsub_rn(1.0f, f))));
+                hh[j] = fmaf(f, hh[j], x);
+                ov[it * V + i + j] = round_to<T>(hh[j]);
+            }
+            *reinterpret_cast<float4*>(st + c + i) = make_float4(hh[0], hh[1], hh[2], hh[3]);
+        }
+#pragma unroll
+        for (int i = 0; i < V; ++i) {
+            gv[it * V + i] = g8[i];
+            ss += (double)g8[i] * (double)g8[i];
+        }
+    }
+    gatenorm_tail<T, V>(gv, ov, ss, D, eps_g, eps_bl, sw, q, dq, rowsum, M, m, red);
 }
 
 // z = round_T(silu(gate)*up), then BitLinear prologue.  gate/up are the two halves of a [M, 2D] tensor.
 template <typename T>
 __global__ void __launch_bounds__(FT)
 swiglu_quant_kernel(const T* __restrict__ gate, const T* __restrict__ up, int64_t ld, const float* __restrict__ nw,
-                    float eps_bl, int8_t* __restrict__ q, float* __restrict__ dq, int32_t* __restrict__ rowsum, int D) {
-    extern __shared__ __align__(16) float row[];
-    __shared__ double redd[33];
-    __shared__ float redf[99];
-    __shared__ int redi[33];
+                    float eps_bl, int8_t* __restrict__ q, float* __restrict__ dq, int32_t* __restrict__ rowsum, int64_t M, int D) {
+    extern __shared__ __align__(16) float sw[];
+    __shared__ RedScratch red;
     constexpr int V = 16 / sizeof(T);
+    pdl_trigger();
+    stage_weights(sw, nw, D);
+    pdl_wait();
+    __syncthreads();
     const int64_t m = blockIdx.x;
     const T* gr = gate + m * ld;
     const T* ur = up + m * ld;
+    float v[PER];
     double ss = 0.0;
-    for (int c = threadIdx.x * V; c < D; c += FT * V) {
+    ROW_FOREACH(V, D, it, c) {
         float gv[V], uv[V];
         load16<T>(gr + c, gv);
         load16<T>(ur + c, uv);
 #pragma unroll
         for (int i = 0; i < V; ++i) {
             const float t = round_to<T>(silu_mul(gv[i], uv[i]));
-            row[c + i] = t;
+            v[it * V + i] = t;
             ss += (double)t * (double)t;
         }
     }
-    const float* nws[3] = {nw, nullptr, nullptr};
-    int8_t* qs[3] = {q, nullptr, nullptr}; float* dqs[3] = {dq, nullptr, nullptr}; int32_t* rss[3] = {rowsum, nullptr, nullptr};
-    bitlinear_prologue<V, 1>(row, D, ss, eps_bl, nws, qs, dqs, rss, m, redd, redf, redi);
+    bitlinear_prologue<V, 1>(v, D, ss, eps_bl, sw, q, dq, rowsum, M, m, red);
 }
 
 }  // namespace
@@ -243,8 +370,11 @@ swiglu_quant_kernel(const T* __restrict__ gate, const T* __restrict__ up, int64_
 // =========================================================================================================
 #define FUSED_ROW_CHECKS(name, D)                                                                                   \
     MMF_REQUIRE(mmf_dtype_ok(dtype), MMF_ERR_BAD_ARG, name ": unknown dtype %d", dtype);                             \
-    MMF_REQUIRE(M >= 0 && (D) > 0 && (D) <= 16384 && (D) % 16 == 0, MMF_ERR_BAD_SHAPE,                               \
-                name ": need 0 < D <= 16384 and D %% 16 == 0 (D=%lld)", (long long)(D));
+    MMF_REQUIRE(M >= 0 && (D) > 0 && (D) <= MAX_D && (D) % 16 == 0, MMF_ERR_BAD_SHAPE,                               \
+                name ": need 0 < D <= 8192 and D %% 16 == 0 (D=%lld)", (long long)(D));
+
+#define FUSED_SMEM_ATTR(kernel, smem) \
+    if ((smem) > 48 * 1024) MMF_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)(smem)))
 
 extern "C" int mmf_prenorm_quant(const void* x, int64_t ld_x, const void* residual, int64_t ld_res, int dtype,
                                  int round_sum_first, const float* norm_w, float eps_norm, void* residual_out,
@@ -257,17 +387,18 @@ extern "C" int mmf_prenorm_quant(const void* x, int64_t ld_x, const void* residu
     MMF_REQUIRE(groups == 0 || (q && dq && rowsum), MMF_ERR_BAD_ARG, "mmf_prenorm_quant: null output");
     const int es = mmf_dtype_size(dtype);
     MMF_REQUIRE(mmf_aligned(x, 16) && (ld_x * es) % 16 == 0 && (!residual || (mmf_aligned(residual, 16) && (ld_res * es) % 16 == 0)) &&
-                    (!residual_out || mmf_aligned(residual_out, 16)) && (!y_out || mmf_aligned(y_out, 16)) && (!q || mmf_aligned(q, 16)),
-                MMF_ERR_ALIGN, "mmf_prenorm_quant: rows must be 16-byte aligned");
+                    (!residual_out || mmf_aligned(residual_out, 16)) && (!y_out || mmf_aligned(y_out, 16)) && (!q || mmf_aligned(q, 16)) &&
+                    mmf_aligned(norm_w, 16) && mmf_aligned(nw0, 16) && mmf_aligned(nw1, 16) && mmf_aligned(nw2, 16),
+                MMF_ERR_ALIGN, "mmf_prenorm_quant: rows and norm weights must be 16-byte aligned");
     if (M == 0) return MMF_OK;
     PrenormArgs a;
     a.x = x; a.ld_x = ld_x; a.res = residual; a.ld_res = ld_res; a.res_out = residual_out; a.y_out = y_out;
     a.norm_w = norm_w; a.eps_norm = eps_norm; a.nws[0] = nw0; a.nws[1] = nw1; a.nws[2] = nw2; a.eps_bl = eps_bl;
     a.q = q; a.dq = dq; a.rowsum = rowsum; a.M = M; a.D = (int)D; a.G = groups; a.round_sum_first = round_sum_first;
-    const size_t smem = (size_t)D * sizeof(float);
+    const size_t smem = (size_t)(1 + groups) * D * sizeof(float);
     MMF_DISPATCH(dtype, T, {
-        if (smem > 48 * 1024) MMF_CUDA(cudaFuncSetAttribute(prenorm_quant_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-        prenorm_quant_kernel<T><<<(unsigned)M, FT, smem, (cudaStream_t)stream>>>(a);
+        FUSED_SMEM_ATTR(prenorm_quant_kernel<T>, smem);
+        MMF_CUDA(mmf_launch_pdl(prenorm_quant_kernel<T>, dim3((unsigned)M), dim3(FT), smem, (cudaStream_t)stream, a));
     });
     MMF_LAUNCH_CHECK("prenorm_quant_kernel");
     return MMF_OK;
@@ -279,16 +410,38 @@ extern "C" int mmf_gatenorm_quant(const void* g, int64_t ld_g, const void* o, in
     MMF_REQUIRE(g && o && q && dq && rowsum, MMF_ERR_BAD_ARG, "mmf_gatenorm_quant: null pointer");
     FUSED_ROW_CHECKS("mmf_gatenorm_quant", D);
     const int es = mmf_dtype_size(dtype);
-    MMF_REQUIRE(mmf_aligned(g, 16) && mmf_aligned(o, 16) && mmf_aligned(q, 16) && (ld_g * es) % 16 == 0 && (ld_o * es) % 16 == 0,
-                MMF_ERR_ALIGN, "mmf_gatenorm_quant: rows must be 16-byte aligned");
+    MMF_REQUIRE(mmf_aligned(g, 16) && mmf_aligned(o, 16) && mmf_aligned(q, 16) && (ld_g * es) % 16 == 0 && (ld_o * es) % 16 == 0 &&
+                    mmf_aligned(gnorm_w, 16) && mmf_aligned(nw, 16),
+                MMF_ERR_ALIGN, "mmf_gatenorm_quant: rows and norm weights must be 16-byte aligned");
     if (M == 0) return MMF_OK;
-    const size_t smem = (size_t)D * sizeof(float);
+    const size_t smem = (size_t)2 * D * sizeof(float);
     MMF_DISPATCH(dtype, T, {
-        if (smem > 48 * 1024) MMF_CUDA(cudaFuncSetAttribute(gatenorm_quant_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-        gatenorm_quant_kernel<T><<<(unsigned)M, FT, smem, (cudaStream_t)stream>>>((const T*)g, ld_g, (const T*)o, ld_o, gnorm_w, eps_g,
-                                                                                    nw, eps_bl, q, dq, rowsum, (int)D);
+        FUSED_SMEM_ATTR(gatenorm_quant_kernel<T>, smem);
+        MMF_CUDA(mmf_launch_pdl(gatenorm_quant_kernel<T>, dim3((unsigned)M), dim3(FT), smem, (cudaStream_t)stream, (const T*)g, ld_g,
+                                (const T*)o, ld_o, gnorm_w, eps_g, nw, eps_bl, q, dq, rowsum, M, (int)D));
     });
     MMF_LAUNCH_CHECK("gatenorm_quant_kernel");
+    return MMF_OK;
+}
+
+extern "C" int mmf_decode_mix(const void* ifg, int64_t ld, int dtype, const void* lower_bound, float* state,
+                              const float* gnorm_w, float eps_g, const float* nw, float eps_bl, int8_t* q, float* dq,
+                              int32_t* rowsum, int64_t M, int64_t D, void* stream) {
+    MMF_REQUIRE(ifg && state && q && dq && rowsum, MMF_ERR_BAD_ARG, "mmf_decode_mix: null pointer");
+    FUSED_ROW_CHECKS("mmf_decode_mix", D);
+    const int es = mmf_dtype_size(dtype);
+    MMF_REQUIRE(ld >= 3 * D, MMF_ERR_BAD_SHAPE, "mmf_decode_mix: ld must cover the three projections");
+    MMF_REQUIRE(mmf_aligned(ifg, 16) && (ld * es) % 16 == 0 && mmf_aligned(state, 16) && mmf_aligned(q, 16) &&
+                    mmf_aligned(gnorm_w, 16) && mmf_aligned(nw, 16),
+                MMF_ERR_ALIGN, "mmf_decode_mix: rows, state and norm weights must be 16-byte aligned");
+    if (M == 0) return MMF_OK;
+    const size_t smem = (size_t)3 * D * sizeof(float);
+    MMF_DISPATCH(dtype, T, {
+        FUSED_SMEM_ATTR(decode_mix_kernel<T>, smem);
+        MMF_CUDA(mmf_launch_pdl(decode_mix_kernel<T>, dim3((unsigned)M), dim3(FT), smem, (cudaStream_t)stream, (const T*)ifg, ld,
+                                (const T*)lower_bound, state, gnorm_w, eps_g, nw, eps_bl, q, dq, rowsum, M, (int)D));
+    });
+    MMF_LAUNCH_CHECK("decode_mix_kernel");
     return MMF_OK;
 }
 
@@ -297,14 +450,14 @@ extern "C" int mmf_swiglu_quant(const void* gate, const void* up, int64_t ld, in
     MMF_REQUIRE(gate && up && q && dq && rowsum, MMF_ERR_BAD_ARG, "mmf_swiglu_quant: null pointer");
     FUSED_ROW_CHECKS("mmf_swiglu_quant", D);
     const int es = mmf_dtype_size(dtype);
-    MMF_REQUIRE(mmf_aligned(gate, 16) && mmf_aligned(up, 16) && mmf_aligned(q, 16) && (ld * es) % 16 == 0, MMF_ERR_ALIGN,
-                "mmf_swiglu_quant: rows must be 16-byte aligned");
+    MMF_REQUIRE(mmf_aligned(gate, 16) && mmf_aligned(up, 16) && mmf_aligned(q, 16) && (ld * es) % 16 == 0 && mmf_aligned(nw, 16),
+                MMF_ERR_ALIGN, "mmf_swiglu_quant: rows and norm weight must be 16-byte aligned");
     if (M == 0) return MMF_OK;
     const size_t smem = (size_t)D * sizeof(float);
     MMF_DISPATCH(dtype, T, {
-        if (smem > 48 * 1024) MMF_CUDA(cudaFuncSetAttribute(swiglu_quant_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-        swiglu_quant_kernel<T><<<(unsigned)M, FT, smem, (cudaStream_t)stream>>>((const T*)gate, (const T*)up, ld, nw, eps_bl, q, dq,
-                                                                                  rowsum, (int)D);
+        FUSED_SMEM_ATTR(swiglu_quant_kernel<T>, smem);
+        MMF_CUDA(mmf_launch_pdl(swiglu_quant_kernel<T>, dim3((unsigned)M), dim3(FT), smem, (cudaStream_t)stream, (const T*)gate,
+                                (const T*)up, ld, nw, eps_bl, q, dq, rowsum, M, (int)D));
     });
     MMF_LAUNCH_CHECK("swiglu_quant_kernel");
     return MMF_OK;

@@ -63,6 +63,8 @@ __global__ void __launch_bounds__(HG_BD)
 hgrn_scan_kernel(const TX* __restrict__ x, int64_t ld_x, const TG* __restrict__ g, int64_t ld_g,
                  const TX* __restrict__ lb, const void* __restrict__ h0, void* __restrict__ ht,
                  int state_dt, TX* __restrict__ o, int T, int D, int NT, int chunk_len, HgrnWs ws) {
+    pdl_trigger();
+    pdl_wait();
     extern __shared__ __align__(16) uint8_t smem_raw[];
     constexpr int XB = HG_TS * HG_BD * sizeof(TX);  // bytes of one x stage
     constexpr int GB = HG_TS * HG_BD * sizeof(TG);
@@ -198,14 +200,14 @@ int hgrn_launch(const void* x, int64_t ld_x, const void* g, int64_t ld_g, const 
         auto k1 = hgrn_scan_kernel<TX, TG, MODE, true>;
         MMF_CUDA(cudaFuncSetAttribute(k1, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
         const dim3 grid1(grid.x, (unsigned)(NT - 1), grid.z);
-        k1<<<grid1, HG_BD, smem, st>>>((const TX*)x, ld_x, (const TG*)g, ld_g, (const TX*)lb, h0, nullptr, state_dt, nullptr,
-                                        (int)T, (int)D, NT, chunk_len, ws);
+        MMF_CUDA(mmf_launch_pdl(k1, grid1, dim3(HG_BD), smem, st, (const TX*)x, ld_x, (const TG*)g, ld_g, (const TX*)lb, h0,
+                                (void*)nullptr, state_dt, (TX*)nullptr, (int)T, (int)D, NT, chunk_len, ws));
         MMF_LAUNCH_CHECK("hgrn_scan_kernel<aggregate>");
     }
     auto k2 = hgrn_scan_kernel<TX, TG, MODE, false>;
     MMF_CUDA(cudaFuncSetAttribute(k2, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    k2<<<grid, HG_BD, smem, st>>>((const TX*)x, ld_x, (const TG*)g, ld_g, (const TX*)lb, h0, ht, state_dt, (TX*)o, (int)T,
-                                  (int)D, NT, chunk_len, ws);
+    MMF_CUDA(mmf_launch_pdl(k2, grid, dim3(HG_BD), smem, st, (const TX*)x, ld_x, (const TG*)g, ld_g, (const TX*)lb, h0, ht,
+                            state_dt, (TX*)o, (int)T, (int)D, NT, chunk_len, ws));
     MMF_LAUNCH_CHECK("hgrn_scan_kernel<scan>");
     return MMF_OK;
 }

@@ -36,6 +36,8 @@ __global__ void __launch_bounds__(ROW_THREADS)
 act_quant_kernel(const T* __restrict__ x, int64_t ld_x, const float* __restrict__ nw, int use_norm,
                  float eps, int8_t* __restrict__ q, float* __restrict__ dq,
                  int32_t* __restrict__ rowsum, int K) {
+    pdl_trigger();
+    pdl_wait();
     extern __shared__ __align__(16) float row[];
     __shared__ double redd[33];
     __shared__ float redf[33];
@@ -223,6 +225,8 @@ swiglu_kernel(const T* __restrict__ x, int64_t ld_x, const T* __restrict__ y, in
 template <typename T>
 __global__ void __launch_bounds__(256)
 argmax_kernel(const T* __restrict__ logits, int64_t ld, int V, int64_t* __restrict__ idx) {
+    pdl_trigger();
+    pdl_wait();
     __shared__ float sv[8];
     __shared__ int si[8];
     const T* r = logits + blockIdx.x * ld;
@@ -250,6 +254,8 @@ argmax_kernel(const T* __restrict__ logits, int64_t ld, int V, int64_t* __restri
 __global__ void __launch_bounds__(128)
 embedding_kernel(const uint8_t* __restrict__ table, int64_t V, int64_t row_bytes,
                  const int64_t* __restrict__ ids, uint8_t* __restrict__ out, int vec16) {
+    pdl_trigger();
+    pdl_wait();
     int64_t id = ids[blockIdx.x];
     id = id < 0 ? 0 : (id >= V ? V - 1 : id);  // clamp instead of faulting on a bad id
     const uint8_t* src = table + id * row_bytes;
@@ -284,8 +290,8 @@ extern "C" int mmf_act_quant(const void* x, int dtype, int64_t ld_x, const float
     MMF_DISPATCH(dtype, T, {
         if (smem > 48 * 1024)
             MMF_CUDA(cudaFuncSetAttribute(act_quant_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-        act_quant_kernel<T><<<(unsigned)M, ROW_THREADS, smem, st>>>((const T*)x, ld_x, norm_w, use_norm, eps, q,
-                                                                     dq, rowsum, (int)K);
+        MMF_CUDA(mmf_launch_pdl(act_quant_kernel<T>, dim3((unsigned)M), dim3(ROW_THREADS), smem, st, (const T*)x, ld_x, norm_w, use_norm, eps, q,
+                                                                     dq, rowsum, (int)K));
     });
     MMF_LAUNCH_CHECK("act_quant_kernel");
     return MMF_OK;
@@ -391,7 +397,7 @@ extern "C" int mmf_argmax_rows(const void* logits, int dtype, int64_t ld, int64_
     MMF_REQUIRE(M >= 0 && V > 0 && V < (1ll << 31) && ld >= V, MMF_ERR_BAD_SHAPE, "mmf_argmax_rows: bad sizes");
     if (M == 0) return MMF_OK;
     cudaStream_t st = (cudaStream_t)stream;
-    MMF_DISPATCH(dtype, T, { argmax_kernel<T><<<(unsigned)M, 256, 0, st>>>((const T*)logits, ld, (int)V, idx); });
+    MMF_DISPATCH(dtype, T, { MMF_CUDA(mmf_launch_pdl(argmax_kernel<T>, dim3((unsigned)M), dim3(256), 0, st, (const T*)logits, ld, (int)V, idx)); });
     MMF_LAUNCH_CHECK("argmax_kernel");
     return MMF_OK;
 }
@@ -404,8 +410,8 @@ extern "C" int mmf_embedding(const void* table, int dtype, int64_t V, int64_t D,
     if (M == 0) return MMF_OK;
     const int64_t row_bytes = D * mmf_dtype_size(dtype);
     const int vec16 = row_bytes % 16 == 0 && mmf_aligned(table, 16) && mmf_aligned(out, 16);
-    embedding_kernel<<<(unsigned)M, 128, 0, (cudaStream_t)stream>>>((const uint8_t*)table, V, row_bytes, ids,
-                                                                    (uint8_t*)out, vec16);
+    MMF_CUDA(mmf_launch_pdl(embedding_kernel, dim3((unsigned)M), dim3(128), 0, (cudaStream_t)stream, (const uint8_t*)table, V, row_bytes, ids,
+                                                                    (uint8_t*)out, vec16));
     MMF_LAUNCH_CHECK("embedding_kernel");
     return MMF_OK;
 }

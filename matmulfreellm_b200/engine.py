@@ -164,9 +164,13 @@ class FusedRunner:
                                                              True, want_residual_out=True)
             ifg = kernels.bitlinear(q, dq, rs, L["ifg"], self.dtype).view(B, T, 3 * h)
             lb = lbs[i].contiguous() if (lbs is not None and i > 0) else None
-            o = kernels.hgrn_gated(ifg[:, :, :h], ifg[:, :, h:2 * h], lb, states[i].view(B, h))
-            q, dq, rs = kernels.gatenorm_quant(ifg.view(M, 3 * h)[:, 2 * h:], o.view(M, h), L["gnorm_w"], L["gnorm_eps"],
+            if T == 1:   # decode: gates, state update, gate-norm and o_proj's prologue in one kernel
+                q, dq, rs = kernels.decode_mix(ifg.view(M, 3 * h), lb, states[i].view(B, h), L["gnorm_w"], L["gnorm_eps"],
                                                L["o_nw"], L["eps_bl"])
+            else:
+                o = kernels.hgrn_gated(ifg[:, :, :h], ifg[:, :, h:2 * h], lb, states[i].view(B, h))
+                q, dq, rs = kernels.gatenorm_quant(ifg.view(M, 3 * h)[:, 2 * h:], o.view(M, h), L["gnorm_w"], L["gnorm_eps"],
+                                                   L["o_nw"], L["eps_bl"])
             attn_out = kernels.bitlinear(q, dq, rs, L["o"], self.dtype)
             q, dq, rs, stream, _ = kernels.prenorm_quant(attn_out, stream, L["mlp_norm_w"], self.eps, [L["gate_nw"]], L["eps_bl"],
                                                          False, want_residual_out=True)
@@ -203,25 +207,42 @@ def bitlinear_modules(model) -> List[BitLinear]:
 
 
 class WeightStreamProbe:
-    """Runs the BitLinear contraction of every layer of `model` once, back to back, for M token rows with
-    pre-quantised activations — i.e. exactly the weight-streaming kernels of one decode step and nothing
-    else — so their device time can be measured with CUDA events."""
+    """Exactly the BitLinear contractions of one decode step (the grouped i/f/g projection, o, gate, down of
+    every block, then lm_head), with pre-quantised activations and nothing else, replayed from a CUDA graph so
+    that their device time can be measured with CUDA events."""
 
-    def __init__(self, model, M: int, out_dtype: torch.dtype):
-        self.items = []
-        dev = next(model.parameters()).device
+    def __init__(self, lm, M: int, out_dtype: torch.dtype):
+        runner = fused_runner(lm)
+        dev = next(lm.parameters()).device
         g = torch.Generator(device=dev).manual_seed(0)
+        self.items = []
         self.packed_bytes = 0
-        for m in bitlinear_modules(model):
-            pw = m.packed()
+        pws = []
+        for L in runner.layers:
+            pws += [L["ifg"], L["o"], L["gate"], L["down"]]
+        pws.append(runner.head)
+        for pw in pws:
             x = torch.randn(M, pw.K, generator=g, device=dev, dtype=torch.float32).to(out_dtype)
             q, dq, rs = kernels.act_quant(x, None, 1e-6)
+            if pw.groups > 1:
+                q, dq, rs = q.repeat(pw.groups, 1), dq.repeat(pw.groups), rs.repeat(pw.groups)
             out = torch.empty(M, pw.N, dtype=out_dtype, device=dev)
             self.items.append((q, dq, rs, pw, out))
             self.packed_bytes += pw.packed.numel()
         self.out_dtype = out_dtype
         self.launches = len(self.items)
+        self.graph = None
 
-    def run(self):
+    def run_eager(self):
         for q, dq, rs, pw, out in self.items:
             kernels.bitlinear(q, dq, rs, pw, self.out_dtype, out=out)
+
+    def run(self):
+        if self.graph is None:
+            self.run_eager()
+            torch.cuda.synchronize()
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph):
+                self.run_eager()
+            self.graph = graph
+        self.graph.replay()

@@ -294,6 +294,25 @@ def gatenorm_quant(g: torch.Tensor, o: torch.Tensor, gnorm_w: Optional[torch.Ten
     return q, dq, rs
 
 
+def decode_mix(ifg: torch.Tensor, lower_bound: Optional[torch.Tensor], state: torch.Tensor,
+               gnorm_w: Optional[torch.Tensor], eps_g: float, bl_norm_w: Optional[torch.Tensor], eps_bl: float):
+    """One decode step of the token mixer: ifg [M, 3D] = i | f | g projections of the new token of M sequences;
+    `state` fp32 [M, D] is advanced in place; returns o_proj's input codes (q, dq, rowsum)."""
+    _need_cuda(ifg, state, lower_bound, gnorm_w, bl_norm_w)
+    M, D3 = ifg.shape
+    D = D3 // 3
+    if ifg.stride(1) != 1 or state.dtype != torch.float32 or state.numel() != M * D or not state.is_contiguous():
+        raise ValueError("ifg must be [M, 3D] with unit inner stride and state contiguous float32 [M, D]")
+    if lower_bound is not None and (lower_bound.dtype != ifg.dtype or lower_bound.numel() != D or not lower_bound.is_contiguous()):
+        raise ValueError("lower_bound must be contiguous [D] in the activation dtype")
+    q, dq, rs = _codes_buffers(1, M, D, ifg.device)
+    if M:
+        _lib.call("mmf_decode_mix", ifg.data_ptr(), ifg.stride(0), _code(ifg.dtype), _ptr(lower_bound), state.data_ptr(),
+                  _ptr(gnorm_w), float(eps_g), _ptr(bl_norm_w), float(eps_bl), q.data_ptr(), dq.data_ptr(), rs.data_ptr(),
+                  M, D, _stream())
+    return q, dq, rs
+
+
 def swiglu_quant(gate_up: torch.Tensor, bl_norm_w: Optional[torch.Tensor], eps_bl: float):
     """silu(gate)*up for gate_up = [gate | up] ([M, 2D], contiguous) -> BitLinear prologue."""
     _need_cuda(gate_up, bl_norm_w)

@@ -421,3 +421,23 @@ def test_hgrn_gated_vs_oracle(K, dtype, tol, B, T, D):
         so = o_ref.float().abs().max().item()
         assert (o.cpu().float() - o_ref.squeeze(1).float()).abs().max().item() <= tol * so
         assert (state.cpu() - ht_ref.squeeze(1)).abs().max().item() <= max(tol, 1e-4) * ht_ref.abs().max().item()
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
+@pytest.mark.parametrize("M,D", [(1, 256), (5, 2048), (3, 2560)])
+def test_decode_mix_equals_scan_plus_gatenorm(K, dtype, M, D):
+    """The one-kernel decode step is the T = 1 case of hgrn_gated followed by gatenorm_quant: identical codes and
+    identical state."""
+    g = torch.Generator().manual_seed(M + D)
+    ifg = dev(torch.randn(M, 3 * D, generator=g).to(dtype))
+    lb = dev((torch.rand(D, generator=g) * 0.5).to(dtype))
+    h0 = dev(torch.randn(M, D, generator=g))
+    gw = dev(1.0 + 0.1 * torch.randn(D, generator=g))
+    nw = dev(1.0 + 0.1 * torch.randn(D, generator=g))
+    for bound in (lb, None):
+        s1, s2 = h0.clone(), h0.clone()
+        v = ifg.view(M, 1, 3 * D)
+        o = K.hgrn_gated(v[..., :D], v[..., D:2 * D], bound, s1)
+        q1, dq1, rs1 = K.gatenorm_quant(ifg[:, 2 * D:], o.view(M, D), gw, 1e-6, nw, 1e-6)
+        q2, dq2, rs2 = K.decode_mix(ifg, bound, s2, gw, 1e-6, nw, 1e-6)
+        assert torch.equal(s1, s2) and torch.equal(q1, q2) and torch.equal(dq1, dq2) and torch.equal(rs1, rs2)
