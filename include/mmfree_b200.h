@@ -146,6 +146,33 @@ int mmf_bitlinear(const int8_t* q, const float* dq, const int32_t* rowsum, const
                   int32_t* acc_out, int64_t M, int64_t N, int64_t K, void* workspace,
                   int64_t workspace_bytes, int kernel, void* stream);
 
+/* BitLinear for a few token rows WITHOUT caller-provided scratch and without any allocation.
+ * (No counterpart in the reference: it exists for hosts that must not allocate.)
+ *
+ * Some programs that embed this library cannot call cudaMalloc at the point where they run a decode
+ * step: an inference server whose device memory is one arena planned at start-up and owned by another
+ * runtime, a latency-critical loop where an allocation (which may synchronise the device) is forbidden,
+ * or a process running under a memory budget that leaves nothing to hand out.  mmf_bitlinear needs a
+ * zeroed split-K workspace from such a caller; this entry point instead keeps that workspace inside the
+ * library image, as a fixed array of MMF_STATIC_SCRATCH_BYTES in device global memory.  Every GPU that
+ * loads the library holds those bytes until the process exits.
+ *
+ * Same arithmetic and arguments as mmf_bitlinear with kernel = MMF_KERNEL_GEMV (the CUDA-core
+ * weight-streaming kernel meant for M <= 4; larger M works but is slow); there is no acc_out.  The call
+ * fails with MMF_ERR_WORKSPACE, launching nothing, when mmf_bitlinear_workspace_bytes(M, N, K) exceeds
+ * MMF_STATIC_SCRATCH_BYTES (e.g. M = 8 with N = 32000) — use mmf_bitlinear with your own workspace then.
+ *
+ * It calls no cudaMalloc / cudaFree and no allocating library routine.  The first call on each device
+ * looks up the array's device address (cudaGetSymbolAddress, with that device current) and remembers it;
+ * make that first call during start-up, before any stream capture.  Each call first clears the part of
+ * the array it will accumulate into (cudaMemsetAsync on `stream`), because the array keeps whatever the
+ * previous call left.  All calls on a device share the one array: two calls that overlap on the GPU (for
+ * example on different streams) race on it — serialise them or use mmf_bitlinear with separate workspaces. */
+#define MMF_STATIC_SCRATCH_BYTES (1 << 20)
+int mmf_bitlinear_gemv_static(const int8_t* q, const float* dq, const int32_t* rowsum, const void* packed,
+                              const float* w_scale, int groups, void* out, int out_dtype, int64_t ld_out,
+                              int64_t M, int64_t N, int64_t K, void* stream);
+
 /* Tuning hook for experiments: overrides the automatic choice of the tensor-core kernel's
  * configuration for all later mmf_bitlinear calls of this process (value 0 = automatic again).
  * No counterpart in the reference. */

@@ -11,6 +11,8 @@
 // 2048x2048 layer (1 MB of weights); partial sums meet in an int32 workspace with atomics
 // (integer adds commute, so the result is deterministic) and the last CTA of a tile runs
 // the epilogue and zeroes the workspace again.
+#include <mutex>
+
 #include "bitlinear.cuh"
 
 namespace {
@@ -199,4 +201,64 @@ extern "C" int mmf_bitlinear(const int8_t* q, const float* dq, const int32_t* ro
     cudaStream_t st = (cudaStream_t)stream;
     const bool use_mma = kernel == MMF_KERNEL_MMA || (kernel == MMF_KERNEL_AUTO && M >= MMF_MMA_MIN_M);
     return use_mma ? bitlinear_mma_launch(a, st) : bitlinear_gemv_launch(a, st);
+}
+
+// =========================================================================================================
+// Allocation-free variant of the small-batch BitLinear
+// =========================================================================================================
+// Split-K scratch that lives in the library image instead of in caller memory.  Every GPU that loads the
+// library carries these MMF_STATIC_SCRATCH_BYTES until the process exits.
+static __device__ __align__(256) int32_t g_gemv_scratch[MMF_STATIC_SCRATCH_BYTES / 4];
+
+// Device address of g_gemv_scratch on the CURRENT device.  In host code the symbol's name is only a handle;
+// the address a kernel can use comes from cudaGetSymbolAddress, asked once per device with that device
+// current and remembered.
+static int gemv_static_scratch(int32_t** out) {
+    static std::mutex mu;
+    static int32_t* per_device[64] = {nullptr};
+    int dev = -1;
+    MMF_CUDA(cudaGetDevice(&dev));
+    MMF_REQUIRE(dev >= 0 && dev < 64, MMF_ERR_CUDA, "mmf_bitlinear_gemv_static: unexpected device index %d", dev);
+    std::lock_guard<std::mutex> lock(mu);
+    if (!per_device[dev]) {
+        void* p = nullptr;
+        MMF_CUDA(cudaGetSymbolAddress(&p, g_gemv_scratch));
+        MMF_REQUIRE(p != nullptr, MMF_ERR_CUDA, "mmf_bitlinear_gemv_static: cudaGetSymbolAddress returned no address");
+        per_device[dev] = static_cast<int32_t*>(p);
+    }
+    *out = per_device[dev];
+    return MMF_OK;
+}
+
+extern "C" int mmf_bitlinear_gemv_static(const int8_t* q, const float* dq, const int32_t* rowsum, const void* packed,
+                                         const float* w_scale, int groups, void* out, int out_dtype, int64_t ld_out,
+                                         int64_t M, int64_t N, int64_t K, void* stream) {
+    MMF_REQUIRE(q && dq && rowsum && packed && w_scale && out, MMF_ERR_BAD_ARG, "mmf_bitlinear_gemv_static: null pointer");
+    MMF_REQUIRE(mmf_dtype_ok(out_dtype), MMF_ERR_BAD_ARG, "mmf_bitlinear_gemv_static: unknown dtype %d", out_dtype);
+    MMF_REQUIRE(M >= 0 && N > 0 && K > 0 && K % MMF_TILE_K == 0 && M < (1ll << 31) && N < (1ll << 31) && K <= 65536,
+                MMF_ERR_BAD_SHAPE, "mmf_bitlinear_gemv_static: need K %% 64 == 0 (M=%lld N=%lld K=%lld)", (long long)M,
+                (long long)N, (long long)K);
+    MMF_REQUIRE(groups >= 1 && N % groups == 0 && (groups == 1 || (N / groups) % MMF_TILE_ROWS == 0), MMF_ERR_BAD_SHAPE,
+                "mmf_bitlinear_gemv_static: N/groups must be a multiple of 128 when groups > 1");
+    MMF_REQUIRE(ld_out >= N, MMF_ERR_BAD_SHAPE, "mmf_bitlinear_gemv_static: ld_out < N");
+    MMF_REQUIRE(mmf_aligned(q, 16) && mmf_aligned(packed, 16), MMF_ERR_ALIGN,
+                "mmf_bitlinear_gemv_static: q and packed must be 16-byte aligned");
+    if (M == 0) return MMF_OK;
+    const int64_t need = mmf_bitlinear_workspace_bytes(M, N, K);
+    MMF_REQUIRE(need <= MMF_STATIC_SCRATCH_BYTES, MMF_ERR_WORKSPACE,
+                "mmf_bitlinear_gemv_static: M=%lld N=%lld needs %lld bytes of split-K scratch but the built-in array holds "
+                "%d; use mmf_bitlinear with a workspace of your own for this size",
+                (long long)M, (long long)N, (long long)need, MMF_STATIC_SCRATCH_BYTES);
+    int32_t* scratch = nullptr;
+    const int rc = gemv_static_scratch(&scratch);
+    if (rc != MMF_OK) return rc;
+    cudaStream_t st = (cudaStream_t)stream;
+    // the array still holds whatever the last call left: zero the part this call accumulates into
+    MMF_CUDA(cudaMemsetAsync(scratch, 0, (size_t)need, st));
+    BitLinearArgs a;
+    a.q = q; a.dq = dq; a.rowsum = rowsum; a.packed = (const uint4*)packed; a.w_scale = w_scale;
+    a.out = out; a.acc_out = nullptr; a.out_dtype = out_dtype; a.ld_out = ld_out;
+    a.M = (int)M; a.N = (int)N; a.K = (int)K; a.groups = groups;
+    a.ws = scratch; a.ws_bytes = MMF_STATIC_SCRATCH_BYTES;
+    return bitlinear_gemv_launch(a, st);
 }
