@@ -179,6 +179,7 @@ int mmf_bitlinear_gemv_static(const int8_t* q, const float* dq, const int32_t* r
 #define MMF_TUNE_KSPLIT 0     /* K split / cluster size: 1, 2, 4 or 8                          */
 #define MMF_TUNE_TOKEN_TILE 1 /* token rows per tile: 16..128 (multiple of 16) or 256           */
 #define MMF_TUNE_DEEP_RING 2  /* 1 = prefer the deep-ring (no split) variant, 2 = never use it  */
+#define MMF_TUNE_WEIGHT_TILES 3 /* weight tiles per CTA for large M: 1 or 2                       */
 int mmf_tuning(int knob, int value);
 
 /* ------------------------------------------------------------------------------------

@@ -46,6 +46,7 @@ struct MmaParams {
     int ksplit;          // CTAs sharing one output tile along K
     int stages_per_cta;  // 128-K stages per CTA
     int tmem_cols;       // power of two >= nacc*NT + SA*32
+    int wt;              // weight tiles (128 rows each) one CTA multiplies against each activation stage: 1 or 2
     int nacc;            // independent accumulators (NT columns each) that consecutive MMAs rotate through
     int SA, SB, SW;      // ring depths: unpacked-A stages in TMEM, activation stages, packed-weight stages
     uint32_t idesc;
@@ -263,7 +264,8 @@ bitlinear_mma_kernel(const __grid_constant__ CUtensorMap q_map, BitLinearArgs a,
 
     const int tid = threadIdx.x;
     const int warp = tid >> 5, lane = tid & 31;
-    const int ks = blockIdx.x, tile = blockIdx.y, mt = blockIdx.z;
+    const int ks = blockIdx.x, tile = blockIdx.y * p.wt, mt = blockIdx.z;
+    const int ntile = min(p.wt, p.n_tiles - tile);   // weight tiles this CTA owns (2 = dual-tile mode for large M)
     long long* trace = nullptr;
     if (tid == 0 && a.ws && a.ws[1] == MMF_TRACE_MAGIC && (blockIdx.x | blockIdx.y | blockIdx.z) == 0)
         trace = reinterpret_cast<long long*>(a.ws + 8);
@@ -288,7 +290,7 @@ bitlinear_mma_kernel(const __grid_constant__ CUtensorMap q_map, BitLinearArgs a,
     if (p.ksplit > 1) cluster_arrive();
     trace_mark(trace, 1);
     const uint32_t tmem_base = s_tmem_base;
-    const uint32_t tmem_a = tmem_base + (uint32_t)(p.nacc * p.NT);   // A stages (32 columns each) follow the accumulators
+    const uint32_t tmem_a = tmem_base + (uint32_t)(p.wt * p.nacc * p.NT);   // A stages (32 columns each) follow the accumulators
     volatile int* abort_flag = &s_abort;
 
     // ring cursors advance by increment-and-wrap (no division in the hot loops); `ph` is the barrier phase bit
@@ -302,14 +304,17 @@ bitlinear_mma_kernel(const __grid_constant__ CUtensorMap q_map, BitLinearArgs a,
         // ------------------------------------------------------------ packed weights (bulk TMA)
         // Weights do not depend on the preceding kernel: their stream starts before the grid dependency wait.
         if (elect_one()) {
-            const uint8_t* src = reinterpret_cast<const uint8_t*>(a.packed) +
-                                 ((int64_t)tile * p.KC + (int64_t)stage0 * 2) * (MMF_TILE_ROWS * 16);
             Ring w{0, 0, SW};
             for (int i = 0; i < nstages; ++i, w.next()) {
-                if (!mbar_wait(&bars[BAR_W_EMPTY + w.slot], w.ph ^ 1, abort_flag)) break;
                 const uint32_t bytes = (uint32_t)min(2, p.KC - (stage0 + i) * 2) * (MMF_TILE_ROWS * 16);
-                mbar_expect_tx(&bars[BAR_W_FULL + w.slot], bytes);
-                bulk_load_1d(w_ring + w.slot * W_STAGE_BYTES, src + (int64_t)i * W_STAGE_BYTES, bytes, &bars[BAR_W_FULL + w.slot]);
+                for (int t = 0; t < ntile; ++t) {
+                    const int slot = t * SW + w.slot;
+                    if (!mbar_wait(&bars[BAR_W_EMPTY + slot], w.ph ^ 1, abort_flag)) { i = nstages; break; }
+                    const uint8_t* src = reinterpret_cast<const uint8_t*>(a.packed) +
+                                         ((int64_t)(tile + t) * p.KC + (int64_t)(stage0 + i) * 2) * (MMF_TILE_ROWS * 16);
+                    mbar_expect_tx(&bars[BAR_W_FULL + slot], bytes);
+                    bulk_load_1d(w_ring + slot * W_STAGE_BYTES, src, bytes, &bars[BAR_W_FULL + slot]);
+                }
             }
         }
     } else if (warp == WARP_B) {
@@ -336,22 +341,33 @@ bitlinear_mma_kernel(const __grid_constant__ CUtensorMap q_map, BitLinearArgs a,
             int acc = 0;
             uint32_t started = 0;     // MMAs issued so far, saturating at nacc: the first use of an accumulator overwrites
             const uint32_t nacc = (uint32_t)p.nacc, NTc = (uint32_t)p.NT;
-            for (int i = 0; i < nstages; ++i, bq.next(), aq.next()) {
+            bool live = true;
+            for (int i = 0; i < nstages && live; ++i, bq.next(), aq.next()) {
                 if (!mbar_wait(&bars[BAR_B_FULL + bq.slot], bq.ph, abort_flag)) break;
-                if (!mbar_wait(&bars[BAR_A_FULL + aq.slot], aq.ph, abort_flag)) break;
-                tc_fence_after();
                 const uint64_t bd = b_desc0 + (uint64_t)(bq.slot * b_desc_step);
-                const uint32_t a_addr = tmem_a + aq.slot * 32;
                 const int nmma = min(2, p.KC - (stage0 + i) * 2) * 2;
+                for (int t = 0; t < ntile; ++t) {
+                    const int slot = t * SA + aq.slot;
+                    if (!mbar_wait(&bars[BAR_A_FULL + slot], aq.ph, abort_flag)) { live = false; break; }
+                    tc_fence_after();
+                    const uint32_t a_addr = tmem_a + slot * 32;
+                    if (p.wt == 2) {
+                        // dual-tile: one activation stage feeds two 128-row weight tiles (accumulators t*NT)
 #pragma unroll
-                for (int k = 0; k < 4; ++k) {
-                    if (k < nmma) {
-                        mma_i8_ts(tmem_base + acc * NTc, a_addr + k * 8, bd + (uint64_t)(k * 2), p.idesc, started >= nacc ? 1u : 0u);
-                        if (++acc == (int)nacc) acc = 0;
-                        if (started < nacc) ++started;
+                        for (int k = 0; k < 4; ++k)
+                            if (k < nmma) mma_i8_ts(tmem_base + t * NTc, a_addr + k * 8, bd + (uint64_t)(k * 2), p.idesc, (i | k) != 0 ? 1u : 0u);
+                    } else {
+#pragma unroll
+                        for (int k = 0; k < 4; ++k) {
+                            if (k < nmma) {
+                                mma_i8_ts(tmem_base + acc * NTc, a_addr + k * 8, bd + (uint64_t)(k * 2), p.idesc, started >= nacc ? 1u : 0u);
+                                if (++acc == (int)nacc) acc = 0;
+                                if (started < nacc) ++started;
+                            }
+                        }
                     }
+                    tc_commit(&bars[BAR_A_EMPTY + slot]);   // frees the A stage when these MMAs retire
                 }
-                tc_commit(&bars[BAR_A_EMPTY + aq.slot]);   // frees the A stage when these MMAs retire
                 tc_commit(&bars[BAR_B_EMPTY + bq.slot]);
             }
             tc_commit(&bars[BAR_ACC]);
@@ -362,19 +378,24 @@ bitlinear_mma_kernel(const __grid_constant__ CUtensorMap q_map, BitLinearArgs a,
         const int row = qd * 32 + lane;                      // weight row in the tile == TMEM lane
         const uint32_t lane_addr = (uint32_t)(qd * 32) << 16;
         bool ok = true;
+        // one weight tile per CTA: the two groups alternate stages; two tiles: group gp owns tile gp, every stage
         Ring w{0, 0, SW}, aq{0, 0, SA};
-        if (gp) { w.next(); aq.next(); }
-        for (int i = gp; i < nstages && ok; i += 2, w.next2(), aq.next2()) {        // the groups alternate stages
-            ok = __all_sync(0xffffffffu, mbar_wait(&bars[BAR_W_FULL + w.slot], w.ph, abort_flag));   // warp-uniform
+        const bool dual = p.wt == 2;
+        if (!dual && gp) { w.next(); aq.next(); }
+        const int w_off = dual ? gp * SW : 0, a_off = dual ? gp * SA : 0;
+        const int i_step = dual ? 1 : 2;
+        for (int i = dual ? 0 : gp; i < nstages && ok && (!dual || gp < ntile); i += i_step) {
+            const int ws = w_off + w.slot, as = a_off + aq.slot;
+            ok = __all_sync(0xffffffffu, mbar_wait(&bars[BAR_W_FULL + ws], w.ph, abort_flag));   // warp-uniform
             if (!ok) break;
             if (i == 0) trace_mark(trace, 2);
             const int nch = min(2, p.KC - (stage0 + i) * 2);
-            const uint8_t* wsrc = w_ring + w.slot * W_STAGE_BYTES + row * 16;
+            const uint8_t* wsrc = w_ring + ws * W_STAGE_BYTES + row * 16;
             uint4 wv[2];
             wv[0] = *reinterpret_cast<const uint4*>(wsrc);
             wv[1] = nch > 1 ? *reinterpret_cast<const uint4*>(wsrc + MMF_TILE_ROWS * 16) : wv[0];
-            mbar_arrive(&bars[BAR_W_EMPTY + w.slot]);         // the packed bytes are in registers now
-            ok = __all_sync(0xffffffffu, mbar_wait(&bars[BAR_A_EMPTY + aq.slot], aq.ph ^ 1, abort_flag));
+            mbar_arrive(&bars[BAR_W_EMPTY + ws]);             // the packed bytes are in registers now
+            ok = __all_sync(0xffffffffu, mbar_wait(&bars[BAR_A_EMPTY + as], aq.ph ^ 1, abort_flag));
             if (!ok) break;   // uniform per warp: the .sync.aligned tcgen05 ops below need the whole warp
 #pragma unroll
             for (int h = 0; h < 2; ++h) {
@@ -385,12 +406,13 @@ bitlinear_mma_kernel(const __grid_constant__ CUtensorMap q_map, BitLinearArgs a,
                     for (int w4 = 0; w4 < 4; ++w4)
 #pragma unroll
                         for (int k4 = 0; k4 < 4; ++k4) r[w4 * 4 + k4] = (words[w4] >> (2 * k4)) & 0x03030303u;
-                    tmem_st16(tmem_a + lane_addr + aq.slot * 32 + h * 16, r);
+                    tmem_st16(tmem_a + lane_addr + as * 32 + h * 16, r);
                 }
             }
             tmem_wait_st();
             tc_fence_before();
-            mbar_arrive(&bars[BAR_A_FULL + aq.slot]);
+            mbar_arrive(&bars[BAR_A_FULL + as]);
+            if (dual) { w.next(); aq.next(); } else { w.next2(); aq.next2(); }
         }
         trace_mark(trace, 3);
 
@@ -407,20 +429,33 @@ bitlinear_mma_kernel(const __grid_constant__ CUtensorMap q_map, BitLinearArgs a,
         trace_mark(trace, 4);
         if (ok) {
             const int ngroups = p.NT >> 4;
-            const int total_mma = (min(p.KC, (stage0 + nstages) * 2) - stage0 * 2) * 2;   // MMAs this CTA issued
-            const int nused = min(p.nacc, total_mma);                                      // accumulators that hold data
-            for (int gi = gp; gi < ngroups; gi += 2) {        // groups of 16 columns, alternating between the warp groups
-                uint32_t v0[16], v1[16];
-                tmem_ld16(tmem_base + lane_addr + gi * 16, v0);
-                for (int acc = 1; acc < nused; ++acc) {       // fold the other accumulators in
-                    tmem_ld16(tmem_base + lane_addr + acc * p.NT + gi * 16, v1);
+            if (dual) {
+                // group gp stages the accumulator of tile gp: stg[(gp*NT + column)][row]
+                if (gp < ntile) {
+                    for (int gi = 0; gi < ngroups; ++gi) {
+                        uint32_t v0[16];
+                        tmem_ld16(tmem_base + lane_addr + gp * p.NT + gi * 16, v0);
+                        tmem_wait_ld();
+#pragma unroll
+                        for (int j = 0; j < 16; ++j) stg[(gp * p.NT + gi * 16 + j) * MMF_TILE_ROWS + row] = (int32_t)v0[j];
+                    }
+                }
+            } else {
+                const int total_mma = (min(p.KC, (stage0 + nstages) * 2) - stage0 * 2) * 2;   // MMAs this CTA issued
+                const int nused = min(p.nacc, total_mma);                                      // accumulators that hold data
+                for (int gi = gp; gi < ngroups; gi += 2) {        // groups of 16 columns, alternating between the warp groups
+                    uint32_t v0[16], v1[16];
+                    tmem_ld16(tmem_base + lane_addr + gi * 16, v0);
+                    for (int acc = 1; acc < nused; ++acc) {       // fold the other accumulators in
+                        tmem_ld16(tmem_base + lane_addr + acc * p.NT + gi * 16, v1);
+                        tmem_wait_ld();
+#pragma unroll
+                        for (int j = 0; j < 16; ++j) v0[j] += v1[j];
+                    }
                     tmem_wait_ld();
 #pragma unroll
-                    for (int j = 0; j < 16; ++j) v0[j] += v1[j];
+                    for (int j = 0; j < 16; ++j) stg[(gi * 16 + j) * MMF_TILE_ROWS + row] = (int32_t)v0[j];
                 }
-                tmem_wait_ld();
-#pragma unroll
-                for (int j = 0; j < 16; ++j) stg[(gi * 16 + j) * MMF_TILE_ROWS + row] = (int32_t)v0[j];
             }
         }
         asm volatile("bar.sync 1, %0;" ::"n"(UNPACK_THREADS) : "memory");   // the 8 epilogue warps only
@@ -432,13 +467,16 @@ bitlinear_mma_kernel(const __grid_constant__ CUtensorMap q_map, BitLinearArgs a,
         const float wsc = a.w_scale[g];
         if (p.ksplit == 1) {
             if (ok) {
-                for (int c = cth; c < p.NT; c += UNPACK_THREADS / 16) {
-                    const int m = m0 + c;
-                    if (m >= a.M) break;
-                    const int4 x0 = *reinterpret_cast<const int4*>(stg + c * MMF_TILE_ROWS + n8);
-                    const int4 x1 = *reinterpret_cast<const int4*>(stg + c * MMF_TILE_ROWS + n8 + 4);
-                    int32_t acc[8] = {x0.x, x0.y, x0.z, x0.w, x1.x, x1.y, x1.z, x1.w};
-                    finish8(a, acc, m, n, s_rs[c], __fmul_rn(s_dq[c], wsc));
+                for (int t = 0; t < ntile; ++t) {
+                    const int32_t* src = stg + t * p.NT * MMF_TILE_ROWS;
+                    for (int c = cth; c < p.NT; c += UNPACK_THREADS / 16) {
+                        const int m = m0 + c;
+                        if (m >= a.M) break;
+                        const int4 x0 = *reinterpret_cast<const int4*>(src + c * MMF_TILE_ROWS + n8);
+                        const int4 x1 = *reinterpret_cast<const int4*>(src + c * MMF_TILE_ROWS + n8 + 4);
+                        int32_t acc[8] = {x0.x, x0.y, x0.z, x0.w, x1.x, x1.y, x1.z, x1.w};
+                        finish8(a, acc, m, n + t * MMF_TILE_ROWS, s_rs[c], __fmul_rn(s_dq[c], wsc));
+                    }
                 }
             }
         } else {
@@ -516,13 +554,14 @@ EncodeTiledFn get_encode_tiled() {
 }  // namespace
 
 // tuning overrides (0 = automatic), see mmf_tuning()
-static int g_force_ksplit = 0, g_force_nt = 0, g_force_deep = 0;
+static int g_force_ksplit = 0, g_force_nt = 0, g_force_deep = 0, g_force_wt = 0;
 
 extern "C" int mmf_tuning(int knob, int value) {
     switch (knob) {
         case MMF_TUNE_KSPLIT: g_force_ksplit = value; return MMF_OK;
         case MMF_TUNE_TOKEN_TILE: g_force_nt = value; return MMF_OK;
         case MMF_TUNE_DEEP_RING: g_force_deep = value; return MMF_OK;
+        case MMF_TUNE_WEIGHT_TILES: g_force_wt = value; return MMF_OK;
         default: return mmf_set_error(MMF_ERR_BAD_ARG, "mmf_tuning: unknown knob %d", knob);
     }
 }
@@ -554,12 +593,16 @@ bool choose_config(const BitLinearArgs& a, MmaParams& best, size_t& best_smem) {
             if (g_force_ksplit && ks != g_force_ksplit) continue;
             const int stages = (total_stages + ks - 1) / ks;
             if (ks > 1 && stages * (ks - 1) >= total_stages) continue;   // every CTA must own >= 1 stage
-            for (int deep = 0; deep <= 1; ++deep) {
+            for (int mode = 0; mode <= 2; ++mode) {          // 0 = plain, 1 = deep ring, 2 = two weight tiles per CTA
+                const int deep = mode == 1;
                 if (deep && (ks != 1 || NT > 64 || g_force_deep != 1)) continue;   // deep ring only on request
+                const int group_tiles = n_tiles / a.groups;
+                if (mode == 2 && (ks != 1 || NT != 128 || n_tiles < 2 || (a.groups > 1 && group_tiles % 2) || g_force_wt == 1)) continue;
+                if (mode != 2 && g_force_wt == 2 && ks == 1 && NT == 128 && n_tiles >= 2) continue;
                 if (g_force_deep == 1 && !deep && ks == 1 && NT <= 64) continue;
                 if (g_force_deep == 2 && deep) continue;
                 MmaParams p;
-                p.KC = KC; p.n_tiles = n_tiles; p.group_tiles = n_tiles / a.groups; p.NT = NT; p.ksplit = ks;
+                p.KC = KC; p.n_tiles = n_tiles; p.group_tiles = group_tiles; p.NT = NT; p.ksplit = ks; p.wt = mode == 2 ? 2 : 1;
                 p.stages_per_cta = stages;
                 size_t smem;
                 int occ;
@@ -575,8 +618,13 @@ bool choose_config(const BitLinearArgs& a, MmaParams& best, size_t& best_smem) {
                     smem = 1024 + (size_t)p.SB * NT * 128 + (size_t)p.SW * W_STAGE_BYTES;
                     if (smem < 120 * 1024) smem = 120 * 1024;   // one CTA per SM: it holds all 512 TMEM columns
                     occ = 1;
+                } else if (mode == 2) {
+                    p.SA = 4; p.SB = 4; p.SW = 8; p.nacc = 1;
+                    p.tmem_cols = 512;                              // 2 x 128 accumulator columns + 2 x 4 x 32 A columns
+                    smem = 1024 + (size_t)p.SB * NT * 128 + (size_t)2 * p.SW * W_STAGE_BYTES;
+                    occ = 1;
                 } else {
-                    p.SA = 4; p.SB = 4; p.SW = 12;
+                    p.SA = 4; p.SB = 4; p.SW = NT >= 128 ? 8 : 12;   // 8 keeps a 128-token tile under half an SM's shared memory
                     p.nacc = NT >= 128 ? 1 : (128 / NT < 4 ? 128 / NT : 4);
                     int cols = 32;
                     while (cols < p.nacc * NT + p.SA * 32) cols *= 2;
@@ -585,12 +633,12 @@ bool choose_config(const BitLinearArgs& a, MmaParams& best, size_t& best_smem) {
                     occ = (smem <= 110 * 1024 && cols <= 256) ? 2 : 1;
                 }
                 if (smem > 227 * 1024) continue;
-                const int64_t ctas = (int64_t)n_tiles * m_tiles * ks;
+                const int64_t ctas = (int64_t)((n_tiles + p.wt - 1) / p.wt) * m_tiles * ks;
                 const int64_t waves = (ctas + 148 * occ - 1) / (148 * occ);
                 // fitted to measured phase times (us): per 128-K stage 4 MMAs of >= 88 cycles each (130 at 256 token
                 // columns) plus issue overhead; fixed launch/set-up/first-TMA latency; epilogue; cluster reduction
-                const double t_stage = NT > 128 ? 0.30 : 0.24;
-                double t = 2.5 + stages * t_stage + 0.5 + NT * 0.012;
+                const double t_stage = mode == 2 ? 0.90 : NT > 128 ? 0.30 : 0.24;   // (two tiles per CTA measured slower: kept for experiments)
+                double t = 2.5 + stages * t_stage + 0.5 + p.wt * NT * 0.012;
                 if (ks > 1) t += 1.5 + NT * 0.012;
                 const double cost = waves * t;
                 if (cost < best_cost) { best_cost = cost; best = p; best_smem = smem; found = true; }
@@ -624,7 +672,7 @@ int bitlinear_mma_launch(const BitLinearArgs& a, cudaStream_t st) {
     MMF_REQUIRE(cr == CUDA_SUCCESS, MMF_ERR_CUDA, "mmf_bitlinear(mma): cuTensorMapEncodeTiled failed (%d)", (int)cr);
 
     MMF_CUDA(cudaFuncSetAttribute(bitlinear_mma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    const dim3 grid((unsigned)p.ksplit, (unsigned)p.n_tiles, (unsigned)m_tiles);
+    const dim3 grid((unsigned)p.ksplit, (unsigned)((p.n_tiles + p.wt - 1) / p.wt), (unsigned)m_tiles);
     MMF_REQUIRE(m_tiles <= 65535 && p.n_tiles <= 65535, MMF_ERR_BAD_SHAPE, "mmf_bitlinear(mma): problem too large");
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = grid;

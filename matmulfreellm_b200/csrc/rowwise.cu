@@ -224,7 +224,7 @@ swiglu_kernel(const T* __restrict__ x, int64_t ld_x, const T* __restrict__ y, in
 // -----------------------------------------------------------------------------------------
 template <typename T>
 __global__ void __launch_bounds__(256)
-argmax_kernel(const T* __restrict__ logits, int64_t ld, int V, int64_t* __restrict__ idx) {
+argmax_kernel(const T* __restrict__ logits, int64_t ld, int V, int64_t* __restrict__ idx, int vec16) {
     pdl_trigger();
     pdl_wait();
     __shared__ float sv[8];
@@ -232,9 +232,20 @@ argmax_kernel(const T* __restrict__ logits, int64_t ld, int V, int64_t* __restri
     const T* r = logits + blockIdx.x * ld;
     float best = -INFINITY;
     int bi = 0x7fffffff;
-    for (int c = threadIdx.x; c < V; c += blockDim.x) {
-        const float v = to_f32(r[c]);
-        if (v > best || (v == best && c < bi)) { best = v; bi = c; }
+    constexpr int VL = 16 / sizeof(T);
+    if (vec16) {   // 16-byte loads; a thread's columns ascend, so '>' keeps the first maximum it meets
+        for (int c = threadIdx.x * VL; c < V; c += blockDim.x * VL) {
+            float v[VL];
+            load16<T>(r + c, v);
+#pragma unroll
+            for (int i = 0; i < VL; ++i)
+                if (c + i < V && (v[i] > best || (v[i] == best && c + i < bi))) { best = v[i]; bi = c + i; }
+        }
+    } else {
+        for (int c = threadIdx.x; c < V; c += blockDim.x) {
+            const float v = to_f32(r[c]);
+            if (v > best || (v == best && c < bi)) { best = v; bi = c; }
+        }
     }
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) {
@@ -397,7 +408,9 @@ extern "C" int mmf_argmax_rows(const void* logits, int dtype, int64_t ld, int64_
     MMF_REQUIRE(M >= 0 && V > 0 && V < (1ll << 31) && ld >= V, MMF_ERR_BAD_SHAPE, "mmf_argmax_rows: bad sizes");
     if (M == 0) return MMF_OK;
     cudaStream_t st = (cudaStream_t)stream;
-    MMF_DISPATCH(dtype, T, { MMF_CUDA(mmf_launch_pdl(argmax_kernel<T>, dim3((unsigned)M), dim3(256), 0, st, (const T*)logits, ld, (int)V, idx)); });
+    const int es = mmf_dtype_size(dtype);
+    const int vec16 = mmf_aligned(logits, 16) && (ld * es) % 16 == 0 && V % (16 / es) == 0;
+    MMF_DISPATCH(dtype, T, { MMF_CUDA(mmf_launch_pdl(argmax_kernel<T>, dim3((unsigned)M), dim3(256), 0, st, (const T*)logits, ld, (int)V, idx, vec16)); });
     MMF_LAUNCH_CHECK("argmax_kernel");
     return MMF_OK;
 }

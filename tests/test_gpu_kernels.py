@@ -441,3 +441,34 @@ def test_decode_mix_equals_scan_plus_gatenorm(K, dtype, M, D):
         q1, dq1, rs1 = K.gatenorm_quant(ifg[:, 2 * D:], o.view(M, D), gw, 1e-6, nw, 1e-6)
         q2, dq2, rs2 = K.decode_mix(ifg, bound, s2, gw, 1e-6, nw, 1e-6)
         assert torch.equal(s1, s2) and torch.equal(q1, q2) and torch.equal(dq1, dq2) and torch.equal(rs1, rs2)
+
+
+def test_bitlinear_mma_configurations_agree(K):
+    """Every configuration the tensor-core kernel can be tuned into (K split over clusters of 2/4/8, the deep ring,
+    128- or 256-token tiles, two weight tiles per CTA) gives the same int32 accumulators as the CUDA-core kernel."""
+    from matmulfreellm_b200 import _lib
+    lib = _lib.load()
+    try:
+        for (M, Kd, N) in [(32, 2048, 2048), (40, 704, 384), (300, 2048, 512)]:
+            x, w, _ = O.bitlinear_case(M, Kd, N, seed=M)
+            pw = K.pack_weight(dev(w))
+            q, dq, rs = K.act_quant(dev(x), None, 1e-6)
+            ref, acc_ref = K.bitlinear(q, dq, rs, pw, torch.float32, kernel=K.KERNEL_GEMV, return_acc=True)
+            for knob, values in ((0, (1, 2, 4, 8)), (2, (1,)), (1, (128, 256)), (3, (2,))):
+                for v in values:
+                    lib.mmf_tuning(knob, v)
+                    if knob == 3:
+                        lib.mmf_tuning(1, 128)
+                    try:
+                        out, acc = K.bitlinear(q, dq, rs, pw, torch.float32, kernel=K.KERNEL_MMA, return_acc=True)
+                    except _lib.MMFreeError as e:      # a forced combination that does not exist for this shape
+                        assert e.code == -2
+                        continue
+                    finally:
+                        for kk in range(4):
+                            lib.mmf_tuning(kk, 0)
+                    K.check_status()
+                    assert torch.equal(acc, acc_ref) and torch.equal(out, ref), (M, Kd, N, knob, v)
+    finally:
+        for kk in range(4):
+            lib.mmf_tuning(kk, 0)
