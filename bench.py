@@ -301,12 +301,47 @@ def run_ours(args):
             extras[f"decode_batch{b}_tokens_per_s"] = b / (m * 1e-3)
             extras[f"decode_batch{b}_ms_per_step"] = m
             del d
-        pf = torch.randint(0, MODEL["vocab_size"], (4, 2048), generator=gen).to(device)
+        # prefill: 16 x 2048 tokens through the whole model (last-position logits only)
+        pf = torch.randint(0, MODEL["vocab_size"], (16, 2048), generator=gen).to(device)
         with torch.no_grad():
             model(input_ids=pf, use_cache=True, last_token_only=True)
             torch.cuda.synchronize()
             m = device_time_ms(lambda: model(input_ids=pf, use_cache=True, last_token_only=True), 2, stream)
-        extras["prefill_4x2048_tokens_per_s"] = pf.numel() / (m * 1e-3)
+        extras["prefill_16x2048_tokens_per_s"] = pf.numel() / (m * 1e-3)
+        extras["prefill_16x2048_ms"] = m
+        del pf
+        # int8 tensor-pipe peak of this GPU (bare tcgen05.mma kind::i8 loop) and the prefill BitLinear op against it
+        from matmulfreellm_b200 import kernels as K
+        peak_tops = K.int8_mma_peak_tops(256, 200000)
+        extras["int8_tensor_peak_tops_measured"] = peak_tops
+        ops = {}
+        for (Kd, N) in ((2048, 2048), (2048, 11264), (5632, 2048), (2560, 2560)):
+            Mtok = 16384
+            w = torch.randn(N, Kd, device=device) * 0.02
+            pw = K.pack_weight(w)
+            del w
+            q, dq, rs = K.act_quant(torch.randn(Mtok, Kd, device=device).bfloat16(), None, 1e-6)
+            out = torch.empty(Mtok, N, device=device, dtype=torch.bfloat16)
+            K.bitlinear(q, dq, rs, pw, torch.bfloat16, out=out)
+            torch.cuda.synchronize()
+            t = device_time_ms(lambda: K.bitlinear(q, dq, rs, pw, torch.bfloat16, out=out), 5, stream)
+            tops = 2.0 * Mtok * Kd * N / (t * 1e-3) / 1e12
+            ops[f"M16384_K{Kd}_N{N}"] = {"us": t * 1e3, "tops": tops, "frac_of_int8_peak": tops / peak_tops}
+            del pw, q, dq, rs, out
+        extras["prefill_bitlinear"] = ops
+        # HGRN recurrence op (B=8, D=2048, bf16 x/o, fp32 log gate): 8 algorithmic bytes per element
+        hg = {}
+        peak_gbs, _ = peaks()
+        for T in (2048, 8192):
+            x = torch.randn(8, T, 2048, device=device).bfloat16()
+            g = torch.nn.functional.logsigmoid(torch.randn(8, T, 2048, device=device))
+            K.hgrn_scan(x, g, None, True, gate_is_log=True, state_dtype=torch.float32)
+            torch.cuda.synchronize()
+            t = device_time_ms(lambda: K.hgrn_scan(x, g, None, True, gate_is_log=True, state_dtype=torch.float32), 5, stream)
+            gbs = 8.0 * x.numel() / (t * 1e-3) / 1e9
+            hg[f"B8_T{T}_D2048"] = {"us": t * 1e3, "gb_per_s": gbs, "frac_of_hbm_peak": gbs / peak_gbs}
+            del x, g
+        extras["hgrn_scan"] = hg
 
     cpu = None
     if rank == 0 and world == 1 and not args.skip_cpu:

@@ -173,6 +173,13 @@ int mmf_bitlinear_gemv_static(const int8_t* q, const float* dq, const int32_t* r
                               const float* w_scale, int groups, void* out, int out_dtype, int64_t ld_out,
                               int64_t M, int64_t N, int64_t K, void* stream);
 
+/* Measurement aid (no counterpart in the reference): the int8 tensor-pipe peak of the current GPU in
+ * TOP/s (2*M*N*K ops per MMA), measured with a bare tcgen05.mma kind::i8 loop of `iters` 128 x n_tokens x 32
+ * instructions per SM, one CTA per SM, timed with CUDA events.  Unlike the other entry points this one
+ * runs on the default stream and SYNCHRONISES; status_dev is one device int of scratch, tops_host a host
+ * double. */
+int mmf_int8_mma_peak(int n_tokens, int iters, int* status_dev, double* tops_host);
+
 /* Tuning hook for experiments: overrides the automatic choice of the tensor-core kernel's
  * configuration for all later mmf_bitlinear calls of this process (value 0 = automatic again).
  * No counterpart in the reference. */

@@ -1,7 +1,8 @@
 // HGRN recurrence h_t = f_t * h_{t-1} + x_t as an HBM-bound streaming scan.
 //
 // Work decomposition: one CTA owns 64 channels of one sequence and one chunk of the time
-// axis; one thread per channel keeps the fp32 state in a register.  [32 timesteps x 64
+// axis; four threads per channel each scan a quarter of a 32-timestep stage and are stitched
+// together through shared memory (fp32 state throughout).  [32 timesteps x 64
 // channels] tiles of x and g are staged in shared memory through a 6-deep cp.async ring
 // (about 70-100 KB in flight per CTA) and the outputs leave through a shared-memory tile as
 // 16-byte stores, so every access to HBM is a full sector and x, g, o are each touched
@@ -15,7 +16,9 @@
 
 namespace {
 
-constexpr int HG_BD = 64;      // channels per CTA (= threads per CTA)
+constexpr int HG_BD = 64;      // channels per CTA
+constexpr int HG_SUB = 4;      // threads per channel: each scans a quarter of a stage's timesteps
+constexpr int HG_THREADS = HG_BD * HG_SUB;
 constexpr int HG_TS = 32;      // timesteps per stage
 constexpr int HG_STAGES = 6;   // cp.async ring depth
 
@@ -58,8 +61,14 @@ constexpr int HG_RAW = 2;     // x, g are the raw i/f projection outputs (HGRNBi
 // AGG = true : pass 1, chunks 0..NT-2 -> aggregates (no o written)
 // AGG = false: pass 2 (or the only pass when NT == 1) -> o, ht
 // x and g rows may be strided (ld_x, ld_g elements); o is [B,T,D] contiguous.
+//
+// A CTA has 256 threads for its 64 channels: thread (channel, sub) scans 8 of the 32 timesteps of a stage
+// from a zero state, keeping the local states and the running gate products in registers; the four
+// sub-chunk aggregates of a channel meet in shared memory, each thread folds the ones before it (and the
+// carry of the previous stage) into its carry-in and fixes its eight states up: h_t = h_local_t + prod_t * carry.
+// Channel-parallel alone would leave 3-4 warps per SM, which cannot hide the latency of the scan loop.
 template <typename TX, typename TG, int MODE, bool AGG>
-__global__ void __launch_bounds__(HG_BD)
+__global__ void __launch_bounds__(HG_THREADS)
 hgrn_scan_kernel(const TX* __restrict__ x, int64_t ld_x, const TG* __restrict__ g, int64_t ld_g,
                  const TX* __restrict__ lb, const void* __restrict__ h0, void* __restrict__ ht,
                  int state_dt, TX* __restrict__ o, int T, int D, int NT, int chunk_len, HgrnWs ws) {
@@ -71,12 +80,16 @@ hgrn_scan_kernel(const TX* __restrict__ x, int64_t ld_x, const TG* __restrict__ 
     TX* sx = reinterpret_cast<TX*>(smem_raw);
     TG* sg = reinterpret_cast<TG*>(smem_raw + HG_STAGES * XB);
     TX* so = reinterpret_cast<TX*>(smem_raw + HG_STAGES * (XB + GB));
+    __shared__ float s_agg_a[HG_SUB][HG_BD], s_agg_h[HG_SUB][HG_BD];
+    __shared__ float s_carry[2][HG_BD];          // carry of the previous stage, double-buffered by stage parity
 
     const int d0 = blockIdx.x * HG_BD;
     const int c = blockIdx.y;
     const int64_t b = blockIdx.z;
     const int tid = threadIdx.x;
-    const int ch = d0 + tid;
+    const int lc = tid & (HG_BD - 1);            // channel inside the block
+    const int sub = tid / HG_BD;                 // which quarter of a stage's timesteps
+    const int ch = d0 + lc;
     const bool ch_ok = ch < D;
     const int t_begin = c * chunk_len;
     const int t_end = min(T, t_begin + chunk_len);
@@ -93,11 +106,11 @@ hgrn_scan_kernel(const TX* __restrict__ x, int64_t ld_x, const TG* __restrict__ 
         if (s < nstage) {
             const int buf = s % HG_STAGES;
             const int rows = min(HG_TS, nsteps - s * HG_TS);
-            for (int p = tid; p < rows * XP; p += HG_BD) {
+            for (int p = tid; p < rows * XP; p += HG_THREADS) {
                 const int r = p / XP, pc = (p % XP) * XV;
                 if (d0 + pc < D) cp_async16(sx + (buf * HG_TS + r) * HG_BD + pc, xb + (int64_t)(s * HG_TS + r) * ld_x + pc);
             }
-            for (int p = tid; p < rows * GP; p += HG_BD) {
+            for (int p = tid; p < rows * GP; p += HG_THREADS) {
                 const int r = p / GP, pc = (p % GP) * GV;
                 if (d0 + pc < D) cp_async16(sg + (buf * HG_TS + r) * HG_BD + pc, gb + (int64_t)(s * HG_TS + r) * ld_g + pc);
             }
@@ -114,47 +127,74 @@ hgrn_scan_kernel(const TX* __restrict__ x, int64_t ld_x, const TG* __restrict__ 
         lbv = to_f32(lb[ch]);
         oml = round_to<TX>(__fsub_rn(1.0f, lbv));
     }
-    // carry-in
-    float h = 0.0f, a = 1.0f;
-    if (!AGG && ch_ok) {
-        if (NT == 1) {
-            if (h0) h = load_state_dt(h0, b * D + ch, state_dt);
-        } else {
-            h = ws.h0c[b * D + ch];
-            for (int j = 0; j < c; ++j) {
-                const int64_t i = (b * NT + j) * (int64_t)D + ch;
-                h = fmaf(ws.agg_a[i], h, ws.agg_h[i]);
+    // carry into the first stage
+    if (sub == 0) {
+        float h = 0.0f;
+        if (!AGG && ch_ok) {
+            if (NT == 1) {
+                if (h0) h = load_state_dt(h0, b * D + ch, state_dt);
+            } else {
+                h = ws.h0c[b * D + ch];
+                for (int j = 0; j < c; ++j) {
+                    const int64_t i = (b * NT + j) * (int64_t)D + ch;
+                    h = fmaf(ws.agg_a[i], h, ws.agg_h[i]);
+                }
             }
         }
+        s_carry[0][lc] = h;
+        if (AGG && c == 0 && ch_ok) ws.h0c[b * D + ch] = h0 ? load_state_dt(h0, b * D + ch, state_dt) : 0.0f;
     }
-    if (AGG && c == 0 && ch_ok) ws.h0c[b * D + ch] = h0 ? load_state_dt(h0, b * D + ch, state_dt) : 0.0f;
+    float a_run = 1.0f;   // AGG: product of all gates of this chunk
 
     for (int s = 0; s < nstage; ++s) {
         cp_async_wait<HG_STAGES - 2>();
-        __syncthreads();
+        __syncthreads();                          // stage s has landed; s_carry[s&1] and `so` are free to use
         const int buf = s % HG_STAGES;
         const int rows = min(HG_TS, nsteps - s * HG_TS);
-        if (ch_ok) {
-            const TX* px = sx + buf * HG_TS * HG_BD + tid;
-            const TG* pg = sg + buf * HG_TS * HG_BD + tid;
-#pragma unroll 8
-            for (int r = 0; r < rows; ++r) {
-                float xv = to_f32(px[r * HG_BD]);
-                float f = to_f32(pg[r * HG_BD]);
-                if (MODE == HG_LOG) f = expf(f);
-                if (MODE == HG_RAW) {
-                    f = round_to<TX>(sigmoidf_(f));
-                    if (has_lb) f = round_to<TX>(__fadd_rn(lbv, round_to<TX>(__fmul_rn(oml, f))));
-                    xv = round_to<TX>(silu_mul(xv, round_to<TX>(__fsub_rn(1.0f, f))));
+        constexpr int SUBT = HG_TS / HG_SUB;      // timesteps per thread
+        float hl[SUBT], ap[SUBT];
+        {
+            const TX* px = sx + (buf * HG_TS + sub * SUBT) * HG_BD + lc;
+            const TG* pg = sg + (buf * HG_TS + sub * SUBT) * HG_BD + lc;
+            float h = 0.0f, a = 1.0f;
+#pragma unroll
+            for (int j = 0; j < SUBT; ++j) {
+                float xv = 0.0f, f = 1.0f;        // steps past the end of the sequence are the identity
+                if (ch_ok && sub * SUBT + j < rows) {
+                    xv = to_f32(px[j * HG_BD]);
+                    f = to_f32(pg[j * HG_BD]);
+                    if (MODE == HG_LOG) f = expf(f);
+                    if (MODE == HG_RAW) {
+                        f = round_to<TX>(sigmoidf_(f));
+                        if (has_lb) f = round_to<TX>(__fadd_rn(lbv, round_to<TX>(__fmul_rn(oml, f))));
+                        xv = round_to<TX>(silu_mul(xv, round_to<TX>(__fsub_rn(1.0f, f))));
+                    }
                 }
                 h = fmaf(f, h, xv);
-                if (AGG) a *= f;
-                else so[r * HG_BD + tid] = from_f32<TX>(h);
+                a *= f;
+                hl[j] = h;
+                ap[j] = a;
             }
+            s_agg_a[sub][lc] = a;
+            s_agg_h[sub][lc] = h;
         }
+        __syncthreads();
+        // carry-in of this thread's sub-chunk: previous stage's carry folded through the sub-chunks before it
+        float cin = s_carry[s & 1][lc];
+#pragma unroll
+        for (int q = 0; q < HG_SUB; ++q)
+            if (q < sub) cin = fmaf(s_agg_a[q][lc], cin, s_agg_h[q][lc]);
+        if (AGG) {
+#pragma unroll
+            for (int q = 0; q < HG_SUB; ++q) a_run *= s_agg_a[q][lc];
+        } else {
+#pragma unroll
+            for (int j = 0; j < SUBT; ++j) so[(sub * SUBT + j) * HG_BD + lc] = from_f32<TX>(fmaf(ap[j], cin, hl[j]));
+        }
+        if (sub == HG_SUB - 1) s_carry[(s + 1) & 1][lc] = fmaf(ap[SUBT - 1], cin, hl[SUBT - 1]);
         if (!AGG) {
             __syncthreads();
-            for (int p = tid; p < rows * XP; p += HG_BD) {
+            for (int p = tid; p < rows * XP; p += HG_THREADS) {
                 const int r = p / XP, pc = (p % XP) * XV;
                 if (d0 + pc < D)
                     *reinterpret_cast<uint4*>(ob + (int64_t)(s * HG_TS + r) * D + pc) =
@@ -164,14 +204,16 @@ hgrn_scan_kernel(const TX* __restrict__ x, int64_t ld_x, const TG* __restrict__ 
         issue(s + HG_STAGES - 1);
     }
     cp_async_wait<0>();
+    __syncthreads();
 
-    if (ch_ok) {
+    if (ch_ok && sub == 0) {
+        const float h_end = s_carry[nstage & 1][lc];
         if (AGG) {
             const int64_t i = (b * NT + c) * (int64_t)D + ch;
-            ws.agg_a[i] = a;
-            ws.agg_h[i] = h;
+            ws.agg_a[i] = a_run;
+            ws.agg_h[i] = h_end;
         } else if (ht && c == NT - 1) {
-            store_state_dt(ht, b * D + ch, state_dt, h);
+            store_state_dt(ht, b * D + ch, state_dt, h_end);
         }
     }
 }
@@ -200,13 +242,13 @@ int hgrn_launch(const void* x, int64_t ld_x, const void* g, int64_t ld_g, const 
         auto k1 = hgrn_scan_kernel<TX, TG, MODE, true>;
         MMF_CUDA(cudaFuncSetAttribute(k1, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
         const dim3 grid1(grid.x, (unsigned)(NT - 1), grid.z);
-        MMF_CUDA(mmf_launch_pdl(k1, grid1, dim3(HG_BD), smem, st, (const TX*)x, ld_x, (const TG*)g, ld_g, (const TX*)lb, h0,
+        MMF_CUDA(mmf_launch_pdl(k1, grid1, dim3(HG_THREADS), smem, st, (const TX*)x, ld_x, (const TG*)g, ld_g, (const TX*)lb, h0,
                                 (void*)nullptr, state_dt, (TX*)nullptr, (int)T, (int)D, NT, chunk_len, ws));
         MMF_LAUNCH_CHECK("hgrn_scan_kernel<aggregate>");
     }
     auto k2 = hgrn_scan_kernel<TX, TG, MODE, false>;
     MMF_CUDA(cudaFuncSetAttribute(k2, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    MMF_CUDA(mmf_launch_pdl(k2, grid, dim3(HG_BD), smem, st, (const TX*)x, ld_x, (const TG*)g, ld_g, (const TX*)lb, h0, ht,
+    MMF_CUDA(mmf_launch_pdl(k2, grid, dim3(HG_THREADS), smem, st, (const TX*)x, ld_x, (const TG*)g, ld_g, (const TX*)lb, h0, ht,
                             state_dt, (TX*)o, (int)T, (int)D, NT, chunk_len, ws));
     MMF_LAUNCH_CHECK("hgrn_scan_kernel<scan>");
     return MMF_OK;

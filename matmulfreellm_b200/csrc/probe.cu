@@ -1,0 +1,92 @@
+// Measurement aid: the int8 tensor-pipe peak of this GPU, measured with a bare tcgen05.mma kind::i8 issue
+// loop (128 x 256 x 32 per instruction, A operand in tensor memory, B in shared memory, int32 accumulators
+// in tensor memory), one CTA per SM.  Nothing is loaded or stored: operands are whatever the memories hold.
+#include "common.cuh"
+
+namespace {
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__global__ void __launch_bounds__(128)
+int8_mma_peak_kernel(int n_tokens, int iters, int* status) {
+    extern __shared__ uint8_t smem_raw[];
+    __shared__ __align__(8) uint64_t bar;
+    __shared__ uint32_t s_tmem;
+    uint8_t* base = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    for (int i = threadIdx.x; i < (n_tokens * 128) / 4; i += blockDim.x) reinterpret_cast<uint32_t*>(base)[i] = 0x01010101u;
+    if (threadIdx.x == 0) asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(smem_u32(&bar)) : "memory");
+    if (threadIdx.x < 32) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], 512;" ::"r"(smem_u32(&s_tmem)) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const uint32_t tmem = s_tmem;
+    if (threadIdx.x == 0) {
+        // shared-memory descriptor of a K-major, 128-byte-swizzled tile; instruction descriptor S32 += S8 x S8
+        uint64_t bd = 0;
+        bd |= (uint64_t)((smem_u32(base) & 0x3FFFFu) >> 4);
+        bd |= (uint64_t)1 << 16;
+        bd |= (uint64_t)(1024 >> 4) << 32;
+        bd |= (uint64_t)1 << 46;
+        bd |= (uint64_t)2 << 61;
+        const uint32_t idesc = (2u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(n_tokens >> 3) << 17) | ((uint32_t)(128 >> 4) << 24);
+#pragma unroll 4
+        for (int i = 0; i < iters; ++i) {
+            const uint32_t a_addr = tmem + 256 + (uint32_t)(i & 7) * 8;
+            const uint64_t b = bd + (uint64_t)((i & 3) * 2);
+            asm volatile(
+                "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+                "tcgen05.mma.cta_group::1.kind::i8 [%0], [%1], %2, %3, {%5, %5, %5, %5}, p;\n\t}"
+                ::"r"(tmem), "r"(a_addr), "l"(b), "r"(idesc), "r"(i > 0 ? 1u : 0u), "r"(0u)
+                : "memory");
+        }
+        asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(&bar)) : "memory");
+        const long long t0 = clock64();
+        uint32_t done = 0;
+        while (!done) {   // bounded wait for the MMAs to retire
+            asm volatile("{\n\t.reg .pred P1;\n\tmbarrier.try_wait.parity.shared::cta.b64 P1, [%1], %2;\n\tselp.b32 %0, 1, 0, P1;\n\t}"
+                         : "=r"(done) : "r"(smem_u32(&bar)), "r"(0u) : "memory");
+            if (clock64() - t0 > 4000000000ll) { atomicExch(status, 1); break; }
+        }
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    if (threadIdx.x < 32) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, 512;" ::"r"(tmem) : "memory");
+}
+
+}  // namespace
+
+extern "C" int mmf_int8_mma_peak(int n_tokens, int iters, int* status_dev, double* tops_host) {
+    MMF_REQUIRE(status_dev && tops_host, MMF_ERR_BAD_ARG, "mmf_int8_mma_peak: null pointer");
+    MMF_REQUIRE(n_tokens >= 16 && n_tokens <= 256 && n_tokens % 16 == 0 && iters > 0 && iters <= (1 << 22), MMF_ERR_BAD_SHAPE,
+                "mmf_int8_mma_peak: n_tokens must be a multiple of 16 in [16,256], iters in (0, 4M]");
+    int dev = 0, sms = 0;
+    MMF_CUDA(cudaGetDevice(&dev));
+    MMF_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
+    const size_t smem = 1024 + (size_t)n_tokens * 128;
+    MMF_CUDA(cudaFuncSetAttribute(int8_mma_peak_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)(150 * 1024)));
+    cudaEvent_t e0, e1;
+    MMF_CUDA(cudaEventCreate(&e0));
+    MMF_CUDA(cudaEventCreate(&e1));
+    MMF_CUDA(cudaMemset(status_dev, 0, sizeof(int)));
+    // 150 KB of shared memory per CTA keeps it at one CTA per SM (each allocates all of tensor memory)
+    int8_mma_peak_kernel<<<sms, 128, 150 * 1024>>>(n_tokens, 64, status_dev);     // warm-up
+    MMF_CUDA(cudaEventRecord(e0));
+    int8_mma_peak_kernel<<<sms, 128, 150 * 1024>>>(n_tokens, iters, status_dev);
+    MMF_CUDA(cudaEventRecord(e1));
+    MMF_CUDA(cudaEventSynchronize(e1));
+    MMF_LAUNCH_CHECK("int8_mma_peak_kernel");
+    float ms = 0.0f;
+    MMF_CUDA(cudaEventElapsedTime(&ms, e0, e1));
+    cudaEventDestroy(e0);
+    cudaEventDestroy(e1);
+    int status = 0;
+    MMF_CUDA(cudaMemcpy(&status, status_dev, sizeof(int), cudaMemcpyDeviceToHost));
+    MMF_REQUIRE(status == 0, MMF_ERR_TIMEOUT, "mmf_int8_mma_peak: the MMAs did not retire in time");
+    (void)smem;
+    *tops_host = 2.0 * 128.0 * n_tokens * 32.0 * (double)iters * sms / ((double)ms * 1e-3) / 1e12;
+    return MMF_OK;
+}

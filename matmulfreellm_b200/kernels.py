@@ -424,3 +424,14 @@ def embedding(table: torch.Tensor, ids: torch.Tensor) -> torch.Tensor:
     _lib.call("mmf_embedding", table.data_ptr(), _code(table.dtype), table.shape[0], table.shape[1], flat.data_ptr(),
               out.data_ptr(), flat.numel(), _stream())
     return out.reshape(*ids.shape, table.shape[1])
+
+
+def int8_mma_peak_tops(n_tokens: int = 256, iters: int = 200000) -> float:
+    """Measured int8 tensor-pipe peak (TOP/s) of the current GPU: bare tcgen05.mma kind::i8 loop. Synchronises."""
+    import ctypes
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    _lib.require_device(torch.cuda.current_device())
+    tops = ctypes.c_double(0.0)
+    torch.cuda.synchronize()
+    _lib.call("mmf_int8_mma_peak", n_tokens, iters, status.data_ptr(), ctypes.addressof(tops))
+    return tops.value
