@@ -26,7 +26,7 @@ constexpr int MMF_WS_HEADER = 64;
 constexpr int MMF_WS_MBLK = 64;
 constexpr int MMF_SPLITK_MAX_M = 256;
 
-int bitlinear_gemv_launch(const BitLinearArgs& a, cudaStream_t st);
+int bitlinear_gemv_launch(const BitLinearArgs& a, cudaStream_t st, bool force_split_k);
 int bitlinear_mma_launch(const BitLinearArgs& a, cudaStream_t st);
 
 // out = acc * (dq * w_scale), the one place the dequantising epilogue is defined

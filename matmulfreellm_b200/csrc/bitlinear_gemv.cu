@@ -1,6 +1,10 @@
 // BitLinear for a handful of token rows (decode): a weight-streaming GEMV on the integer
 // dot-product units.
 //
+// Two kernels live here.  bitlinear_gemv_rows_kernel (default) reduces over K inside the CTA; the older
+// bitlinear_gemv_kernel splits K ACROSS CTAs through an int32 workspace — it remains for shapes whose
+// activation rows do not fit in shared memory and behind mmf_bitlinear_gemv_static.
+//
 // The contraction is HBM-bound on the 2-bit weight stream (K*N/4 bytes; activations are a
 // few KB and live in shared memory).  One CTA = one 128-row weight tile x one slice of K;
 // thread r owns output row r, so each 16-byte load of a warp is one fully used 512-byte run
@@ -121,14 +125,120 @@ bitlinear_gemv_kernel(BitLinearArgs a, int KC, int kc_per_cta, int ksplit, int n
     }
 }
 
+// -----------------------------------------------------------------------------------------------------------
+// Variant without any cross-CTA reduction (the default): one CTA = 32 rows of a weight tile x all of K.
+// Warp w owns a 1/16 slice of K, lane l owns row l of the 32-row slice, so a warp's 16-byte loads are one
+// 512-byte run of the tile-major buffer; the 16 partial sums per output meet in shared memory.  With 4 CTAs per
+// weight tile even a 2048 x 2048 layer is spread over 64 CTAs and every thread has all its weight loads in
+// flight at once; the first of them are requested before the grid-dependency wait.
+// -----------------------------------------------------------------------------------------------------------
+constexpr int G2_WARPS = 16;
+constexpr int G2_THREADS = G2_WARPS * 32;
+constexpr int G2_PF = 6;   // weight vectors requested before the dependency wait
+
+template <int MB>
+__global__ void __launch_bounds__(G2_THREADS)
+bitlinear_gemv_rows_kernel(BitLinearArgs a, int KC, int group_tiles) {
+    extern __shared__ __align__(16) int8_t smem2[];
+    int8_t* xs = smem2;                                                  // [MB][K] activation codes
+    int* red = reinterpret_cast<int*>(smem2 + (size_t)MB * a.K);         // [G2_WARPS][MB][32]
+    pdl_trigger();
+    const int tile = blockIdx.x >> 2, rq = blockIdx.x & 3, mblk = blockIdx.y;
+    const int w = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int m0 = mblk * MB;
+    const int g = tile / group_tiles;
+    const int cpw = (KC + G2_WARPS - 1) / G2_WARPS;
+    const int kc0 = min(KC, w * cpw), kc1 = min(KC, kc0 + cpw);
+    const int nkc = kc1 - kc0;
+    const uint4* wp = a.packed + ((int64_t)tile * KC + kc0) * MMF_TILE_ROWS + rq * 32 + lane;
+    uint4 wf[G2_PF];
+#pragma unroll
+    for (int i = 0; i < G2_PF; ++i) wf[i] = i < nkc ? __ldg(wp + (int64_t)i * MMF_TILE_ROWS) : make_uint4(0, 0, 0, 0);
+    pdl_wait();
+
+    const int8_t* qg = a.q + ((int64_t)g * a.M) * a.K;
+    const int pieces_per_row = a.K / 16;
+    for (int p = threadIdx.x; p < MB * pieces_per_row; p += G2_THREADS) {
+        const int m = p / pieces_per_row, off = (p - m * pieces_per_row) * 16;
+        uint4 v = make_uint4(0, 0, 0, 0);
+        if (m0 + m < a.M) v = *reinterpret_cast<const uint4*>(qg + (int64_t)(m0 + m) * a.K + off);
+        *reinterpret_cast<uint4*>(xs + (size_t)m * a.K + off) = v;
+    }
+    __syncthreads();
+
+    int acc[MB];
+#pragma unroll
+    for (int m = 0; m < MB; ++m) acc[m] = 0;
+    auto consume = [&](const uint4& wv, int kc) {
+        const uint32_t words[4] = {wv.x, wv.y, wv.z, wv.w};
+#pragma unroll
+        for (int qd = 0; qd < 4; ++qd) {
+            uint32_t b[4];
+#pragma unroll
+            for (int i = 0; i < 4; ++i) b[i] = (words[qd] >> (2 * i)) & 0x03030303u;
+#pragma unroll
+            for (int m = 0; m < MB; ++m) {
+                const int4 xv = *reinterpret_cast<const int4*>(xs + (size_t)m * a.K + (size_t)(kc0 + kc) * MMF_TILE_K + qd * 16);
+                acc[m] = __dp4a((int)b[0], xv.x, acc[m]);
+                acc[m] = __dp4a((int)b[1], xv.y, acc[m]);
+                acc[m] = __dp4a((int)b[2], xv.z, acc[m]);
+                acc[m] = __dp4a((int)b[3], xv.w, acc[m]);
+            }
+        }
+    };
+#pragma unroll
+    for (int i = 0; i < G2_PF; ++i)
+        if (i < nkc) consume(wf[i], i);
+#pragma unroll 4
+    for (int kc = G2_PF; kc < nkc; ++kc) consume(__ldg(wp + (int64_t)kc * MMF_TILE_ROWS), kc);
+
+#pragma unroll
+    for (int m = 0; m < MB; ++m) red[(w * MB + m) * 32 + lane] = acc[m];
+    __syncthreads();
+    if (threadIdx.x < MB * 32) {
+        const int m = threadIdx.x >> 5, r = threadIdx.x & 31;
+        int v = 0;
+#pragma unroll
+        for (int ww = 0; ww < G2_WARPS; ++ww) v += red[(ww * MB + m) * 32 + r];
+        const int n = tile * MMF_TILE_ROWS + rq * 32 + r;
+        const int mm = m0 + m;
+        if (n < a.N && mm < a.M) {
+            const int64_t gm = (int64_t)g * a.M + mm;
+            v -= a.rowsum[gm];
+            if (a.acc_out) a.acc_out[(int64_t)mm * a.N + n] = v;
+            store_out(a.out, a.out_dtype, (int64_t)mm * a.ld_out + n, bitlinear_dequant(v, a.dq[gm], a.w_scale[g]));
+        }
+    }
+}
+
 }  // namespace
 
-int bitlinear_gemv_launch(const BitLinearArgs& a, cudaStream_t st) {
+int bitlinear_gemv_launch(const BitLinearArgs& a, cudaStream_t st, bool force_split_k) {
     const int KC = a.K / MMF_TILE_K;
     const int n_tiles = (a.N + MMF_TILE_ROWS - 1) / MMF_TILE_ROWS;
     const int group_tiles = n_tiles / a.groups;
     const int MB = a.M <= 1 ? 1 : a.M <= 2 ? 2 : a.M <= 4 ? 4 : 8;
     const int mblocks = (a.M + MB - 1) / MB;
+    MMF_REQUIRE(mblocks <= 65535, MMF_ERR_BAD_SHAPE, "mmf_bitlinear(gemv): M too large for the GEMV kernel");
+    const size_t smem_rows = (size_t)MB * a.K + (size_t)G2_WARPS * MB * 32 * sizeof(int);
+    if (!force_split_k && smem_rows <= 160 * 1024) {
+        const dim3 grid2((unsigned)(n_tiles * 4), (unsigned)mblocks);
+#define G2_LAUNCH(MBV)                                                                                              \
+    {                                                                                                               \
+        auto kfn = bitlinear_gemv_rows_kernel<MBV>;                                                                 \
+        if (smem_rows > 48 * 1024) MMF_CUDA(cudaFuncSetAttribute(kfn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_rows)); \
+        MMF_CUDA(mmf_launch_pdl(kfn, grid2, dim3(G2_THREADS), smem_rows, st, a, KC, group_tiles));                 \
+    }
+        switch (MB) {
+            case 1: G2_LAUNCH(1); break;
+            case 2: G2_LAUNCH(2); break;
+            case 4: G2_LAUNCH(4); break;
+            default: G2_LAUNCH(8); break;
+        }
+#undef G2_LAUNCH
+        MMF_LAUNCH_CHECK("bitlinear_gemv_rows_kernel");
+        return MMF_OK;
+    }
     int ksplit = 1;
     const int64_t need_words = MMF_WS_HEADER + (int64_t)n_tiles * MMF_WS_MBLK + (int64_t)a.M * n_tiles * MMF_TILE_ROWS;
     const bool can_split = a.ws && a.M <= MMF_SPLITK_MAX_M && mblocks <= MMF_WS_MBLK && a.ws_bytes >= need_words * 4;
@@ -200,7 +310,7 @@ extern "C" int mmf_bitlinear(const int8_t* q, const float* dq, const int32_t* ro
     a.ws = (int32_t*)workspace; a.ws_bytes = workspace ? workspace_bytes : 0;
     cudaStream_t st = (cudaStream_t)stream;
     const bool use_mma = kernel == MMF_KERNEL_MMA || (kernel == MMF_KERNEL_AUTO && M >= MMF_MMA_MIN_M);
-    return use_mma ? bitlinear_mma_launch(a, st) : bitlinear_gemv_launch(a, st);
+    return use_mma ? bitlinear_mma_launch(a, st) : bitlinear_gemv_launch(a, st, false);
 }
 
 // =========================================================================================================
@@ -260,5 +370,5 @@ extern "C" int mmf_bitlinear_gemv_static(const int8_t* q, const float* dq, const
     a.out = out; a.acc_out = nullptr; a.out_dtype = out_dtype; a.ld_out = ld_out;
     a.M = (int)M; a.N = (int)N; a.K = (int)K; a.groups = groups;
     a.ws = scratch; a.ws_bytes = MMF_STATIC_SCRATCH_BYTES;
-    return bitlinear_gemv_launch(a, st);
+    return bitlinear_gemv_launch(a, st, /*force_split_k=*/true);   // the split-K kernel is the one that needs scratch
 }

@@ -80,10 +80,17 @@ __device__ __forceinline__ bool mbar_try(uint64_t* bar, uint32_t parity) {
 // Bounded wait (about one second of SM clock): returns false, with *abort_flag set, if the phase never
 // completes or another role of this CTA already gave up.
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag) {
-    if (mbar_try(bar, parity)) return true;
-    const long long t0 = clock64();
-    for (;;) {
+    // try_wait suspends the thread in hardware for a while; the clock and the abort flag are only looked at
+    // now and then so that waiting warps do not compete with the MMA-issuing thread for issue slots
+#pragma unroll 1
+    for (int i = 0; i < 64; ++i)
         if (mbar_try(bar, parity)) return true;
+    const long long t0 = clock64();
+#pragma unroll 1
+    for (;;) {
+#pragma unroll 1
+        for (int i = 0; i < 32; ++i)
+            if (mbar_try(bar, parity)) return true;
         if (*abort_flag) return false;
         if (clock64() - t0 > WAIT_LIMIT_CYCLES) {
             *abort_flag = 1;

@@ -1,9 +1,9 @@
 // HGRN recurrence h_t = f_t * h_{t-1} + x_t as an HBM-bound streaming scan.
 //
 // Work decomposition: one CTA owns 64 channels of one sequence and one chunk of the time
-// axis; four threads per channel each scan a quarter of a 32-timestep stage and are stitched
-// together through shared memory (fp32 state throughout).  [32 timesteps x 64
-// channels] tiles of x and g are staged in shared memory through a 6-deep cp.async ring
+// axis; eight threads per channel each scan an eighth of a 64-timestep stage and are stitched
+// together through shared memory (fp32 state throughout).  [64 timesteps x 64
+// channels] tiles of x and g are staged in shared memory through a 4-deep cp.async ring
 // (about 70-100 KB in flight per CTA) and the outputs leave through a shared-memory tile as
 // 16-byte stores, so every access to HBM is a full sector and x, g, o are each touched
 // once (8 B per element for bf16 x/o and fp32 g).
@@ -17,10 +17,10 @@
 namespace {
 
 constexpr int HG_BD = 64;      // channels per CTA
-constexpr int HG_SUB = 4;      // threads per channel: each scans a quarter of a stage's timesteps
+constexpr int HG_SUB = 8;      // threads per channel: each scans an eighth of a stage's timesteps
 constexpr int HG_THREADS = HG_BD * HG_SUB;
-constexpr int HG_TS = 32;      // timesteps per stage
-constexpr int HG_STAGES = 6;   // cp.async ring depth
+constexpr int HG_TS = 64;      // timesteps per stage
+constexpr int HG_STAGES = 4;  // cp.async ring depth
 
 __device__ __forceinline__ void cp_async16(void* smem, const void* gmem) {
     const uint32_t s = (uint32_t)__cvta_generic_to_shared(smem);
@@ -62,8 +62,8 @@ constexpr int HG_RAW = 2;     // x, g are the raw i/f projection outputs (HGRNBi
 // AGG = false: pass 2 (or the only pass when NT == 1) -> o, ht
 // x and g rows may be strided (ld_x, ld_g elements); o is [B,T,D] contiguous.
 //
-// A CTA has 256 threads for its 64 channels: thread (channel, sub) scans 8 of the 32 timesteps of a stage
-// from a zero state, keeping the local states and the running gate products in registers; the four
+// A CTA has 512 threads for its 64 channels: thread (channel, sub) scans 8 of the 64 timesteps of a stage
+// from a zero state, keeping the local states and the running gate products in registers; the eight
 // sub-chunk aggregates of a channel meet in shared memory, each thread folds the ones before it (and the
 // carry of the previous stage) into its carry-in and fixes its eight states up: h_t = h_local_t + prod_t * carry.
 // Channel-parallel alone would leave 3-4 warps per SM, which cannot hide the latency of the scan loop.

@@ -131,6 +131,11 @@ class FusedRunner:
         self.head_nw = lm.lm_head.norm_weight_f32()
         self.head_eps = lm.lm_head.NORM_EPS
         self.dtype = model.embeddings.weight.dtype
+        # per-layer lower bounds of the forget gates depend on parameters only: evaluated once (in the parameter
+        # dtype, with the reference's op sequence) instead of on every forward
+        with torch.no_grad():
+            lbs = model.layer_lower_bounds()
+        self.lower_bounds = None if lbs is None else [lbs[i].contiguous() for i in range(lbs.shape[0])]
         self.key = self.fingerprint(lm)
 
     @staticmethod
@@ -154,7 +159,7 @@ class FusedRunner:
         B, T, h = x.shape
         M = B * T
         x = x.reshape(M, h)
-        lbs = model.layer_lower_bounds()
+        lbs = self.lower_bounds
         stream, z = x, None                      # residual stream, last block's MLP output
         for i, L in enumerate(self.layers):
             if i == 0:
@@ -163,7 +168,7 @@ class FusedRunner:
                 q, dq, rs, stream, _ = kernels.prenorm_quant(z, stream, L["attn_norm_w"], self.eps, L["ifg_nw"], L["eps_bl"],
                                                              True, want_residual_out=True)
             ifg = kernels.bitlinear(q, dq, rs, L["ifg"], self.dtype).view(B, T, 3 * h)
-            lb = lbs[i].contiguous() if (lbs is not None and i > 0) else None
+            lb = lbs[i] if (lbs is not None and i > 0) else None
             if T == 1:   # decode: gates, state update, gate-norm and o_proj's prologue in one kernel
                 q, dq, rs = kernels.decode_mix(ifg.view(M, 3 * h), lb, states[i].view(B, h), L["gnorm_w"], L["gnorm_eps"],
                                                L["o_nw"], L["eps_bl"])

@@ -1,0 +1,119 @@
+"""Op-level micro-benchmarks of the C-ABI kernels (also the command lines used for profiler captures).
+
+    python -m matmulfreellm_b200.opbench bitlinear --M 32 --K 2048 --N 11264 [--kernel auto|gemv|mma] [--iters 20]
+    python -m matmulfreellm_b200.opbench hgrn --B 8 --T 2048 --D 2048 [--gate log|linear]
+    python -m matmulfreellm_b200.opbench rowwise --M 4096 --D 2048
+    python -m matmulfreellm_b200.opbench int8peak
+
+Each prints one JSON line: device time per call (CUDA events, after 3 warm-ups) and the achieved GB/s of
+algorithmic bytes and/or TOP/s.  Inputs are seeded synthetic data; every repetition of `bitlinear` uses a
+different weight buffer (round-robin over --buffers) so that small layers are streamed from HBM, not from L2.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+
+import torch
+
+from . import kernels as K
+
+
+def _time(fn, iters):
+    for _ in range(3):
+        fn()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(iters):
+        fn()
+    e1.record()
+    e1.synchronize()
+    return e0.elapsed_time(e1) / iters * 1e-3
+
+
+def bitlinear(a):
+    dev = torch.device("cuda")
+    g = torch.Generator(device=dev).manual_seed(0)
+    nbuf = max(1, a.buffers)
+    pws = []
+    for _ in range(nbuf):
+        w = torch.randn(a.N, a.K, device=dev, generator=g) * 0.02
+        pws.append(K.pack_weight(w))
+        del w
+    x = torch.randn(a.M, a.K, device=dev, generator=g)
+    x[:, torch.randperm(a.K, device=dev, generator=g)[: a.K // 100]] *= 20
+    q, dq, rs = K.act_quant(x.bfloat16(), None, 1e-6)
+    out = torch.empty(a.M, a.N, device=dev, dtype=torch.bfloat16)
+    kern = {"auto": K.KERNEL_AUTO, "gemv": K.KERNEL_GEMV, "mma": K.KERNEL_MMA}[a.kernel]
+    state = {"i": 0}
+
+    def fn():
+        K.bitlinear(q, dq, rs, pws[state["i"] % nbuf], torch.bfloat16, kernel=kern, out=out)
+        state["i"] += 1
+
+    graph = None
+    if a.graph:      # replay `--graph` back-to-back launches from one CUDA graph (device time without host launch cost)
+        fn()
+        torch.cuda.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            for _ in range(a.graph):
+                fn()
+        t = _time(graph.replay, a.iters) / a.graph
+    else:
+        t = _time(fn, a.iters)
+    wbytes = a.K * a.N / 4
+    print(json.dumps({"op": "bitlinear", "M": a.M, "K": a.K, "N": a.N, "kernel": a.kernel, "us": t * 1e6,
+                      "weight_stream_gb_per_s": wbytes / t / 1e9, "tops": 2.0 * a.M * a.K * a.N / t / 1e12,
+                      "algorithmic_bytes": wbytes + a.M * a.K + 2 * a.M * a.N}))
+
+
+def hgrn(a):
+    dev = torch.device("cuda")
+    g = torch.Generator(device=dev).manual_seed(0)
+    glog = torch.nn.functional.logsigmoid(torch.randn(a.B, a.T, a.D, device=dev, generator=g))
+    x = ((1 - glog.exp()) * torch.nn.functional.silu(torch.randn(a.B, a.T, a.D, device=dev, generator=g))).bfloat16()
+    gate = glog if a.gate == "log" else glog.exp()
+    t = _time(lambda: K.hgrn_scan(x, gate, None, True, gate_is_log=a.gate == "log", state_dtype=torch.float32), a.iters)
+    nbytes = 8.0 * x.numel()
+    print(json.dumps({"op": "hgrn_scan", "B": a.B, "T": a.T, "D": a.D, "us": t * 1e6, "algorithmic_bytes": nbytes,
+                      "gb_per_s": nbytes / t / 1e9}))
+
+
+def rowwise(a):
+    dev = torch.device("cuda")
+    x = torch.randn(a.M, a.D, device=dev).bfloat16()
+    res = torch.randn(a.M, a.D, device=dev).bfloat16()
+    nw = torch.ones(a.D, device=dev)
+    t = _time(lambda: K.prenorm_quant(x, res, nw, 1e-6, [nw, nw, nw], 1e-6, False, want_residual_out=True), a.iters)
+    nbytes = a.M * a.D * (2 + 2 + 2 + 3)
+    print(json.dumps({"op": "prenorm_quant(3 groups)", "M": a.M, "D": a.D, "us": t * 1e6, "algorithmic_bytes": nbytes,
+                      "gb_per_s": nbytes / t / 1e9}))
+
+
+def int8peak(a):
+    print(json.dumps({"op": "int8_mma_peak", "tops_n256": K.int8_mma_peak_tops(256, 200000),
+                      "tops_n128": K.int8_mma_peak_tops(128, 200000), "tops_n32": K.int8_mma_peak_tops(32, 200000)}))
+
+
+def main():
+    ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
+    sub = ap.add_subparsers(dest="op", required=True)
+    b = sub.add_parser("bitlinear")
+    b.add_argument("--M", type=int, default=32); b.add_argument("--K", type=int, default=2048)
+    b.add_argument("--N", type=int, default=11264); b.add_argument("--kernel", default="auto")
+    b.add_argument("--iters", type=int, default=20); b.add_argument("--buffers", type=int, default=1)
+    b.add_argument("--graph", type=int, default=0)
+    h = sub.add_parser("hgrn")
+    h.add_argument("--B", type=int, default=8); h.add_argument("--T", type=int, default=2048)
+    h.add_argument("--D", type=int, default=2048); h.add_argument("--gate", default="log"); h.add_argument("--iters", type=int, default=10)
+    r = sub.add_parser("rowwise")
+    r.add_argument("--M", type=int, default=4096); r.add_argument("--D", type=int, default=2048); r.add_argument("--iters", type=int, default=10)
+    sub.add_parser("int8peak")
+    a = ap.parse_args()
+    {"bitlinear": bitlinear, "hgrn": hgrn, "rowwise": rowwise, "int8peak": int8peak}[a.op](a)
+
+
+if __name__ == "__main__":
+    main()
