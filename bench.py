@@ -47,6 +47,8 @@ def parse_args():
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
     ap.add_argument("--layers", type=int, default=MODEL["num_hidden_layers"], help=argparse.SUPPRESS)
     ap.add_argument("--no-extras", action="store_true", help="skip the secondary measurements (batch 1/256, prefill)")
+    ap.add_argument("--eager", action="store_true",
+                    help="decode step by step without the CUDA graph (for profiler launch lists; slower)")
     ap.add_argument("--skip-cpu", action="store_true", help="skip the CPU-baseline leg (for profiler runs)")
     return ap.parse_args()
 
@@ -232,7 +234,7 @@ def run_ours(args):
     gen = torch.Generator().manual_seed(100 + rank)
     prompt = torch.randint(0, MODEL["vocab_size"], (B, args.prompt), generator=gen)
 
-    dec = GreedyDecoder(model, B)
+    dec = GreedyDecoder(model, B, use_graph=not args.eager)
     dec.prefill(prompt.to(device))
     for _ in range(max(args.warmup, 3)):
         dec.step()
@@ -271,7 +273,7 @@ def run_ours(args):
     ms, e2e_ms = t.tolist()
 
     # ---- roofline of the dominant kernel: the BitLinear weight stream of one step -------------------------
-    probe = WeightStreamProbe(model, B, torch.bfloat16)
+    probe = WeightStreamProbe(model, B, torch.bfloat16, use_graph=not args.eager)
     for _ in range(3):
         probe.run()
     torch.cuda.synchronize()

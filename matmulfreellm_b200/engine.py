@@ -49,7 +49,9 @@ class GreedyDecoder:
         torch.cuda.current_stream().wait_stream(side)
         graph = torch.cuda.CUDAGraph()
         before = _lib.launch_count
-        with torch.cuda.graph(graph):
+        # capture on the warm-up stream: its split-K workspace already exists (and is zero), so no fill of a
+        # fresh workspace is recorded into the graph
+        with torch.cuda.graph(graph, stream=side):
             self._step_eager()
         self.kernels_per_step = _lib.launch_count - before
         self.graph = graph
@@ -216,7 +218,8 @@ class WeightStreamProbe:
     every block, then lm_head), with pre-quantised activations and nothing else, replayed from a CUDA graph so
     that their device time can be measured with CUDA events."""
 
-    def __init__(self, lm, M: int, out_dtype: torch.dtype):
+    def __init__(self, lm, M: int, out_dtype: torch.dtype, use_graph: bool = True):
+        self._use_graph = use_graph
         runner = fused_runner(lm)
         dev = next(lm.parameters()).device
         g = torch.Generator(device=dev).manual_seed(0)
@@ -243,11 +246,16 @@ class WeightStreamProbe:
             kernels.bitlinear(q, dq, rs, pw, self.out_dtype, out=out)
 
     def run(self):
+        if not self._use_graph:
+            return self.run_eager()
         if self.graph is None:
-            self.run_eager()
-            torch.cuda.synchronize()
+            side = torch.cuda.Stream(device=self.items[0][0].device)
+            side.wait_stream(torch.cuda.current_stream())
+            with torch.cuda.stream(side):          # the capture reuses this stream's (zeroed) workspace
+                self.run_eager()
+            torch.cuda.current_stream().wait_stream(side)
             graph = torch.cuda.CUDAGraph()
-            with torch.cuda.graph(graph):
+            with torch.cuda.graph(graph, stream=side):
                 self.run_eager()
             self.graph = graph
         self.graph.replay()
