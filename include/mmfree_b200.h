@@ -187,6 +187,9 @@ int mmf_int8_mma_peak(int n_tokens, int iters, int* status_dev, double* tops_hos
 #define MMF_TUNE_TOKEN_TILE 1 /* token rows per tile: 16..128 (multiple of 16) or 256           */
 #define MMF_TUNE_DEEP_RING 2  /* 1 = prefer the deep-ring (no split) variant, 2 = never use it  */
 #define MMF_TUNE_WEIGHT_TILES 3 /* weight tiles per CTA for large M: 1 or 2                       */
+#define MMF_TUNE_B_STAGES 4   /* activation-tile ring depth (128 K per stage)                  */
+#define MMF_TUNE_A_STAGES 5   /* unpacked-weight stages held in tensor memory (even)           */
+#define MMF_TUNE_W_STAGES 6   /* packed-weight ring depth (even)                               */
 int mmf_tuning(int knob, int value);
 
 /* ------------------------------------------------------------------------------------

@@ -561,7 +561,7 @@ EncodeTiledFn get_encode_tiled() {
 }  // namespace
 
 // tuning overrides (0 = automatic), see mmf_tuning()
-static int g_force_ksplit = 0, g_force_nt = 0, g_force_deep = 0, g_force_wt = 0;
+static int g_force_ksplit = 0, g_force_nt = 0, g_force_deep = 0, g_force_wt = 0, g_force_sb = 0, g_force_sa = 0, g_force_sw = 0;
 
 extern "C" int mmf_tuning(int knob, int value) {
     switch (knob) {
@@ -569,6 +569,9 @@ extern "C" int mmf_tuning(int knob, int value) {
         case MMF_TUNE_TOKEN_TILE: g_force_nt = value; return MMF_OK;
         case MMF_TUNE_DEEP_RING: g_force_deep = value; return MMF_OK;
         case MMF_TUNE_WEIGHT_TILES: g_force_wt = value; return MMF_OK;
+        case MMF_TUNE_B_STAGES: g_force_sb = value; return MMF_OK;
+        case MMF_TUNE_A_STAGES: g_force_sa = value; return MMF_OK;
+        case MMF_TUNE_W_STAGES: g_force_sw = value; return MMF_OK;
         default: return mmf_set_error(MMF_ERR_BAD_ARG, "mmf_tuning: unknown knob %d", knob);
     }
 }
@@ -633,6 +636,12 @@ bool choose_config(const BitLinearArgs& a, MmaParams& best, size_t& best_smem) {
                 } else {
                     p.SA = 4; p.SB = 4; p.SW = NT >= 128 ? 8 : 12;   // 8 keeps a 128-token tile under half an SM's shared memory
                     p.nacc = NT >= 128 ? 1 : (128 / NT < 4 ? 128 / NT : 4);
+                    if (g_force_sb) p.SB = g_force_sb < MAX_SB ? g_force_sb : MAX_SB;
+                    if (g_force_sa) p.SA = (g_force_sa < MAX_SA ? g_force_sa : MAX_SA) & ~1;   // the two unpack groups alternate slots
+                    if (g_force_sw) p.SW = (g_force_sw < MAX_SW ? g_force_sw : MAX_SW) & ~1;
+                    if (p.SA < 2 || p.SW < 2 || p.SB < 1 || p.nacc * NT + p.SA * 32 > 512) continue;
+                    // the epilogue parks the int32 tile [NT][128] in the (then idle) rings
+                    if ((size_t)p.SB * NT * 128 + (ks == 1 ? (size_t)p.SW * W_STAGE_BYTES : 0) < (size_t)NT * 512) continue;
                     int cols = 32;
                     while (cols < p.nacc * NT + p.SA * 32) cols *= 2;
                     p.tmem_cols = cols;
