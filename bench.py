@@ -58,6 +58,11 @@ def workload_name(args):
             f"state seeded by a {args.prompt}-token prompt")
 
 
+# dram__bytes_read+write of one bitlinear_mma_kernel launch (M=32, K=2048, N=11264) from the profiler, per byte of
+# packed weights that launch streams; DRAM traffic of this kernel is the weight stream plus the activation codes
+NCU_DRAM_BYTES_PER_WEIGHT_BYTE = 6.124 / 5.767
+
+
 def peaks():
     p = ROOT / "MEASURED_PEAKS.json"
     if p.exists():
@@ -283,7 +288,10 @@ def run_ours(args):
     achieved = probe.packed_bytes / (probe_ms * 1e-3) / 1e9
     roofline = {
         "bound": "hbm", "kernel": "bitlinear (2-bit weight stream; %d launches per step)" % probe.launches,
-        "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak, "traffic": None,
+        "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
+        "traffic": bytes_per_launch * NCU_DRAM_BYTES_PER_WEIGHT_BYTE if B == 32 else None,
+        "traffic_source": "ncu dram bytes of the gate_proj launch at batch 32 (6.124 MB for 5.767 MB of packed weights), "
+                          "scaled to the average launch by weight bytes; see profiles/bitlinear_mma_M32_K2048_N11264.md",
         "peak_source": peak_src, "bytes_per_launch": bytes_per_launch, "us_per_launch": probe_ms * 1e3 / probe.launches,
         "weight_bytes_per_step": probe.packed_bytes,
         "whole_step_frac": probe.packed_bytes / (ms * 1e-3) / 1e9 / peak,

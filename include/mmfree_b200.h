@@ -190,6 +190,7 @@ int mmf_int8_mma_peak(int n_tokens, int iters, int* status_dev, double* tops_hos
 #define MMF_TUNE_B_STAGES 4   /* activation-tile ring depth (128 K per stage)                  */
 #define MMF_TUNE_A_STAGES 5   /* unpacked-weight stages held in tensor memory (even)           */
 #define MMF_TUNE_W_STAGES 6   /* packed-weight ring depth (even)                               */
+#define MMF_TUNE_PERSISTENT 7 /* persistent large-M kernel: 1 = whenever M > 128, 2 = never     */
 int mmf_tuning(int knob, int value);
 
 /* ------------------------------------------------------------------------------------
@@ -223,6 +224,11 @@ int mmf_hgrn_scan(const void* x, int x_dtype, const void* g, int g_dtype, const 
 int mmf_hgrn_gated(const void* i_raw, const void* f_raw, int64_t ld, int dtype,
                    const void* lower_bound, float* state, void* o, int64_t B, int64_t T, int64_t D,
                    void* workspace, int64_t workspace_bytes, void* stream);
+
+/* Error reporting of the scan kernels (no counterpart in the reference): the kernels wait for their TMA
+ * stages with a bounded spin; *failed_host becomes 1 if any launch of this process ever gave up on such a
+ * wait (its outputs are then undefined).  Synchronises with the device. */
+int mmf_hgrn_status(int* failed_host);
 
 /* ------------------------------------------------------------------------------------
  * Fused producers of BitLinear inputs: each emits the int8 codes (+ dq, rowsum, laid out

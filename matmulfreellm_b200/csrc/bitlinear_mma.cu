@@ -25,6 +25,8 @@
 #include <cuda.h>
 
 #include "bitlinear.cuh"
+#include "tensor_map.cuh"
+#include "tcgen05.cuh"
 
 namespace {
 
@@ -37,7 +39,6 @@ constexpr int MAX_SA = 16;        // A stages (128 K = 32 TMEM columns each) in 
 constexpr int MAX_SB = 32;        // activation stages (128 K each)
 constexpr int MAX_SW = 32;        // packed-weight stages (128 K = 4 KB each)
 constexpr int W_STAGE_BYTES = 2 * MMF_TILE_ROWS * 16;  // two 64-K chunks
-constexpr long long WAIT_LIMIT_CYCLES = 2000000000ll;
 
 struct MmaParams {
     int KC;              // K / 64
@@ -52,134 +53,7 @@ struct MmaParams {
     uint32_t idesc;
 };
 
-// ---------------------------------------------------------------------------------------------
-// PTX wrappers
-// ---------------------------------------------------------------------------------------------
-__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
-
-__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
-    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count) : "memory");
-}
-__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
-    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
-}
-__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
-    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ bool mbar_try(uint64_t* bar, uint32_t parity) {
-    uint32_t ok;
-    asm volatile(
-        "{\n\t.reg .pred P1;\n\t"
-        "mbarrier.try_wait.parity.shared::cta.b64 P1, [%1], %2;\n\t"
-        "selp.b32 %0, 1, 0, P1;\n\t}"
-        : "=r"(ok)
-        : "r"(smem_u32(bar)), "r"(parity)
-        : "memory");
-    return ok != 0;
-}
-// Bounded wait (about one second of SM clock): returns false, with *abort_flag set, if the phase never
-// completes or another role of this CTA already gave up.
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag) {
-    // try_wait suspends the thread in hardware for a while; the clock and the abort flag are only looked at
-    // now and then so that waiting warps do not compete with the MMA-issuing thread for issue slots
-#pragma unroll 1
-    for (int i = 0; i < 64; ++i)
-        if (mbar_try(bar, parity)) return true;
-    const long long t0 = clock64();
-#pragma unroll 1
-    for (;;) {
-#pragma unroll 1
-        for (int i = 0; i < 32; ++i)
-            if (mbar_try(bar, parity)) return true;
-        if (*abort_flag) return false;
-        if (clock64() - t0 > WAIT_LIMIT_CYCLES) {
-            *abort_flag = 1;
-            return false;
-        }
-    }
-}
-
-__device__ __forceinline__ bool elect_one() {
-    uint32_t pred;
-    asm volatile(
-        "{\n\t.reg .pred P;\n\t.reg .b32 r;\n\t"
-        "elect.sync r|P, 0xffffffff;\n\t"
-        "selp.b32 %0, 1, 0, P;\n\t}"
-        : "=r"(pred));
-    return pred != 0;
-}
-
-__device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, uint64_t* bar, int x, int y) {
-    asm volatile(
-        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
-        ::"r"(smem_u32(dst)), "l"(map), "r"(smem_u32(bar)), "r"(x), "r"(y)
-        : "memory");
-}
-__device__ __forceinline__ void bulk_load_1d(void* dst, const void* src, uint32_t bytes, uint64_t* bar) {
-    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
-                 ::"r"(smem_u32(dst)), "l"(src), "r"(bytes), "r"(smem_u32(bar))
-                 : "memory");
-}
-
-__device__ __forceinline__ void tmem_alloc(uint32_t* slot, uint32_t cols) {
-    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(slot)), "r"(cols) : "memory");
-    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
-}
-__device__ __forceinline__ void tmem_dealloc(uint32_t addr, uint32_t cols) {
-    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(addr), "r"(cols) : "memory");
-}
-__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void tc_commit(uint64_t* bar) {
-    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
-}
-// D[tmem] (+)= A[tmem] * B[smem desc], int8 x int8 -> int32
-__device__ __forceinline__ void mma_i8_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "setp.ne.b32 p, %4, 0;\n\t"
-        "tcgen05.mma.cta_group::1.kind::i8 [%0], [%1], %2, %3, {%5, %5, %5, %5}, p;\n\t}"
-        ::"r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate), "r"(0u)
-        : "memory");
-}
-__device__ __forceinline__ void tmem_st16(uint32_t addr, const uint32_t (&r)[16]) {
-    asm volatile(
-        "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16};"
-        ::"r"(addr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]),
-        "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15])
-        : "memory");
-}
-__device__ __forceinline__ void tmem_ld16(uint32_t addr, uint32_t (&r)[16]) {
-    asm volatile(
-        "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
-        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
-          "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
-        : "r"(addr)
-        : "memory");
-}
-__device__ __forceinline__ void tmem_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
-__device__ __forceinline__ void tmem_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
-
-__device__ __forceinline__ void cluster_arrive() { asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory"); }
-__device__ __forceinline__ void cluster_wait() { asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory"); }
-// optional phase trace of CTA (0,0,0): armed by writing MMF_TRACE_MAGIC into workspace word 1
-constexpr int MMF_TRACE_MAGIC = 0x7ace;
-__device__ __forceinline__ void trace_mark(long long* trace, int slot) {
-    if (trace) trace[slot] = clock64();
-}
-
-// K-major operand tile in shared memory, 128-byte swizzle: rows of 128 bytes, 8-row groups 1024 B apart.
-__device__ __forceinline__ uint64_t make_b_desc(uint32_t smem_addr) {
-    uint64_t d = 0;
-    d |= (uint64_t)((smem_addr & 0x3FFFFu) >> 4);   // start address
-    d |= (uint64_t)1 << 16;                          // leading-dim byte offset (unused for swizzled K-major)
-    d |= (uint64_t)(1024 >> 4) << 32;                // stride-dim byte offset: next 8-row group
-    d |= (uint64_t)1 << 46;                          // descriptor version (sm_100)
-    d |= (uint64_t)2 << 61;                          // SWIZZLE_128B
-    return d;
-}
-
-// barrier table: index ranges inside one uint64 array
+// ---------------------------------------------------
 constexpr int BAR_B_FULL = 0, BAR_B_EMPTY = BAR_B_FULL + MAX_SB, BAR_W_FULL = BAR_B_EMPTY + MAX_SB,
               BAR_W_EMPTY = BAR_W_FULL + MAX_SW, BAR_A_FULL = BAR_W_EMPTY + MAX_SW, BAR_A_EMPTY = BAR_A_FULL + MAX_SA,
               BAR_ACC = BAR_A_EMPTY + MAX_SA, NUM_BARS = BAR_ACC + 1;
@@ -349,7 +223,50 @@ bitlinear_mma_kernel(const __grid_constant__ CUtensorMap q_map, BitLinearArgs a,
             uint32_t started = 0;     // MMAs issued so far, saturating at nacc: the first use of an accumulator overwrites
             const uint32_t nacc = (uint32_t)p.nacc, NTc = (uint32_t)p.NT;
             bool live = true;
-            for (int i = 0; i < nstages && live; ++i, bq.next(), aq.next()) {
+            int i = 0;
+            long long* mtrace = (a.ws && a.ws[1] == MMF_TRACE_MAGIC && (blockIdx.x | blockIdx.y | blockIdx.z) == 0)
+                                    ? reinterpret_cast<long long*>(a.ws + 8) : nullptr;
+            if (p.wt == 1 && nacc == 1) {
+                // lean path (one weight tile, one accumulator, whole 128-K stages): the issuing thread is a
+                // serial instruction stream, so every instruction here costs tensor-pipe time
+                const int nfull = min(nstages, p.KC / 2 - stage0);
+                const uint32_t d_addr = tmem_base;
+                const uint32_t b_lo0 = (uint32_t)b_desc0, b_hi = (uint32_t)(b_desc0 >> 32);
+                uint32_t accum = 0;
+                for (; i < nfull; ++i, bq.next(), aq.next()) {
+                    if (!mbar_wait(&bars[BAR_B_FULL + bq.slot], bq.ph, abort_flag)) { live = false; break; }
+                    if (!mbar_wait(&bars[BAR_A_FULL + aq.slot], aq.ph, abort_flag)) { live = false; break; }
+                    tc_fence_after();
+                    if (mtrace && i < 10) mtrace[8 + i] = clock64();
+                    uint32_t a_addr = tmem_a + aq.slot * 32;
+                    uint32_t b_lo = b_lo0 + (uint32_t)bq.slot * b_desc_step;
+                    asm volatile(
+                        "{\n\t.reg .pred p;\n\t.reg .b64 d0, d1, d2, d3;\n\t"
+                        "setp.ne.b32 p, %4, 0;\n\t"
+                        "mov.b64 d0, {%1, %3};\n\t"
+                        "add.u32 %1, %1, 2;\n\t"
+                        "mov.b64 d1, {%1, %3};\n\t"
+                        "add.u32 %1, %1, 2;\n\t"
+                        "mov.b64 d2, {%1, %3};\n\t"
+                        "add.u32 %1, %1, 2;\n\t"
+                        "mov.b64 d3, {%1, %3};\n\t"
+                        "tcgen05.mma.cta_group::1.kind::i8 [%2], [%0], d0, %5, p;\n\t"
+                        "add.u32 %0, %0, 8;\n\t"
+                        "tcgen05.mma.cta_group::1.kind::i8 [%2], [%0], d1, %5, 1;\n\t"
+                        "add.u32 %0, %0, 8;\n\t"
+                        "tcgen05.mma.cta_group::1.kind::i8 [%2], [%0], d2, %5, 1;\n\t"
+                        "add.u32 %0, %0, 8;\n\t"
+                        "tcgen05.mma.cta_group::1.kind::i8 [%2], [%0], d3, %5, 1;\n\t}"
+                        : "+r"(a_addr), "+r"(b_lo)
+                        : "r"(d_addr), "r"(b_hi), "r"(accum), "r"(p.idesc)
+                        : "memory");
+                    accum = 1;
+                    tc_commit(&bars[BAR_A_EMPTY + aq.slot]);
+                    tc_commit(&bars[BAR_B_EMPTY + bq.slot]);
+                }
+                started = accum ? nacc : 0;
+            }
+            for (; i < nstages && live; ++i, bq.next(), aq.next()) {
                 if (!mbar_wait(&bars[BAR_B_FULL + bq.slot], bq.ph, abort_flag)) break;
                 const uint64_t bd = b_desc0 + (uint64_t)(bq.slot * b_desc_step);
                 const int nmma = min(2, p.KC - (stage0 + i) * 2) * 2;
@@ -402,6 +319,7 @@ bitlinear_mma_kernel(const __grid_constant__ CUtensorMap q_map, BitLinearArgs a,
             wv[0] = *reinterpret_cast<const uint4*>(wsrc);
             wv[1] = nch > 1 ? *reinterpret_cast<const uint4*>(wsrc + MMF_TILE_ROWS * 16) : wv[0];
             mbar_arrive(&bars[BAR_W_EMPTY + ws]);             // the packed bytes are in registers now
+            if (trace && i < 10) trace[18 + i] = clock64();
             ok = __all_sync(0xffffffffu, mbar_wait(&bars[BAR_A_EMPTY + as], aq.ph ^ 1, abort_flag));
             if (!ok) break;   // uniform per warp: the .sync.aligned tcgen05 ops below need the whole warp
 #pragma unroll
@@ -419,6 +337,7 @@ bitlinear_mma_kernel(const __grid_constant__ CUtensorMap q_map, BitLinearArgs a,
             tmem_wait_st();
             tc_fence_before();
             mbar_arrive(&bars[BAR_A_FULL + as]);
+            if (trace && i < 10) trace[19 + i] = clock64();
             if (dual) { w.next(); aq.next(); } else { w.next2(); aq.next2(); }
         }
         trace_mark(trace, 3);
@@ -542,26 +461,10 @@ bitlinear_mma_kernel(const __grid_constant__ CUtensorMap q_map, BitLinearArgs a,
     if (warp == WARP_MMA) tmem_dealloc(tmem_base, (uint32_t)p.tmem_cols);
 }
 
-typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
-                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
-                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-
-EncodeTiledFn get_encode_tiled() {
-    static EncodeTiledFn fn = []() -> EncodeTiledFn {
-        void* ptr = nullptr;
-        cudaDriverEntryPointQueryResult qres;
-        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &qres) != cudaSuccess ||
-            qres != cudaDriverEntryPointSuccess)
-            return nullptr;
-        return reinterpret_cast<EncodeTiledFn>(ptr);
-    }();
-    return fn;
-}
-
 }  // namespace
 
 // tuning overrides (0 = automatic), see mmf_tuning()
-static int g_force_ksplit = 0, g_force_nt = 0, g_force_deep = 0, g_force_wt = 0, g_force_sb = 0, g_force_sa = 0, g_force_sw = 0;
+static int g_force_ksplit = 0, g_force_nt = 0, g_force_deep = 0, g_force_wt = 0, g_force_sb = 0, g_force_sa = 0, g_force_sw = 0, g_force_persistent = 0;
 
 extern "C" int mmf_tuning(int knob, int value) {
     switch (knob) {
@@ -572,6 +475,7 @@ extern "C" int mmf_tuning(int knob, int value) {
         case MMF_TUNE_B_STAGES: g_force_sb = value; return MMF_OK;
         case MMF_TUNE_A_STAGES: g_force_sa = value; return MMF_OK;
         case MMF_TUNE_W_STAGES: g_force_sw = value; return MMF_OK;
+        case MMF_TUNE_PERSISTENT: g_force_persistent = value; return MMF_OK;
         default: return mmf_set_error(MMF_ERR_BAD_ARG, "mmf_tuning: unknown knob %d", knob);
     }
 }
@@ -648,7 +552,7 @@ bool choose_config(const BitLinearArgs& a, MmaParams& best, size_t& best_smem) {
                     smem = 1024 + (size_t)p.SB * NT * 128 + (size_t)p.SW * W_STAGE_BYTES + (ks > 1 ? (size_t)NT * MMF_TILE_ROWS * 4 : 0);
                     occ = (smem <= 110 * 1024 && cols <= 256) ? 2 : 1;
                 }
-                if (smem > 227 * 1024) continue;
+                if (smem + 4096 > 227 * 1024) continue;   // the kernel's static shared memory comes on top
                 const int64_t ctas = (int64_t)((n_tiles + p.wt - 1) / p.wt) * m_tiles * ks;
                 const int64_t waves = (ctas + 148 * occ - 1) / (148 * occ);
                 // fitted to measured phase times (us): per 128-K stage 4 MMAs of >= 88 cycles each (130 at 256 token
@@ -667,6 +571,13 @@ bool choose_config(const BitLinearArgs& a, MmaParams& best, size_t& best_smem) {
 }  // namespace
 
 int bitlinear_mma_launch(const BitLinearArgs& a, cudaStream_t st) {
+    {
+        // many token rows: the persistent kernel (256-token tiles, one CTA per SM) once it has a full wave of work
+        const int64_t n_work = (int64_t)((a.N + MMF_TILE_ROWS - 1) / MMF_TILE_ROWS) * ((a.M + 255) / 256);
+        const bool tuned = g_force_ksplit || g_force_nt || g_force_deep || g_force_wt || g_force_sb || g_force_sa || g_force_sw;
+        if (g_force_persistent == 1 ? a.M > 128 : (g_force_persistent == 0 && !tuned && a.M >= 512 && n_work >= 148))
+            return bitlinear_mma_prefill_launch(a, st);
+    }
     MmaParams p;
     size_t smem = 0;
     MMF_REQUIRE(choose_config(a, p, smem), MMF_ERR_BAD_SHAPE, "mmf_bitlinear(mma): no kernel configuration fits M=%d N=%d K=%d", a.M,
@@ -675,7 +586,7 @@ int bitlinear_mma_launch(const BitLinearArgs& a, cudaStream_t st) {
     // instruction descriptor: D=S32, A=S8 (TMEM), B=S8 (smem, K-major), M=128, N=NT
     p.idesc = (2u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(p.NT >> 3) << 17) | ((uint32_t)(128 >> 4) << 24);
 
-    EncodeTiledFn encode = get_encode_tiled();
+    MmfEncodeTiledFn encode = mmf_encode_tiled();
     MMF_REQUIRE(encode != nullptr, MMF_ERR_CUDA, "mmf_bitlinear(mma): cuTensorMapEncodeTiled is not available from the driver");
     CUtensorMap q_map;
     const cuuint64_t gdim[2] = {(cuuint64_t)a.K, (cuuint64_t)a.groups * (cuuint64_t)a.M};

@@ -21,8 +21,10 @@ int mmf_set_error(int code, const char* fmt, ...);
 #define MMF_CUDA(...)                                                                   \
     do {                                                                                \
         cudaError_t e__ = (__VA_ARGS__);                                                \
-        if (e__ != cudaSuccess)                                                         \
+        if (e__ != cudaSuccess) {                                                       \
+            (void)cudaGetLastError(); /* do not leave the error for a later launch check */ \
             return mmf_set_error(MMF_ERR_CUDA, "%s failed: %s", #__VA_ARGS__, cudaGetErrorString(e__)); \
+        }                                                                               \
     } while (0)
 
 #define MMF_LAUNCH_CHECK(name)                                                          \

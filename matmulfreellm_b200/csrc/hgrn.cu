@@ -1,34 +1,110 @@
 // HGRN recurrence h_t = f_t * h_{t-1} + x_t as an HBM-bound streaming scan.
 //
-// Work decomposition: one CTA owns 64 channels of one sequence and one chunk of the time
-// axis; eight threads per channel each scan an eighth of a 64-timestep stage and are stitched
-// together through shared memory (fp32 state throughout).  [64 timesteps x 64
-// channels] tiles of x and g are staged in shared memory through a 4-deep cp.async ring
-// (about 70-100 KB in flight per CTA) and the outputs leave through a shared-memory tile as
-// 16-byte stores, so every access to HBM is a full sector and x, g, o are each touched
-// once (8 B per element for bf16 x/o and fp32 g).
+// Work decomposition: one CTA owns 64 channels of one sequence and one chunk of the time axis.
+// [64 timesteps x 64 channels] tiles of x and g arrive in shared memory by tiled TMA (one elected
+// thread issues them, a 3-deep ring of mbarrier-tracked stages) and the output tile leaves by a TMA
+// store from a double-buffered shared-memory tile, so no thread spends instructions on addressing
+// or copying global memory and x, g, o are each touched exactly once (8 B per element for bf16 x/o
+// and an fp32 gate).  Inside a stage warp `sub` scans timesteps [8*sub, 8*sub+8) of all 64 channels
+// from a zero state — lane = channel pair, packed 2-element shared-memory accesses — and the eight
+// sub-chunk aggregates (gate product, local end state) meet in shared memory: every thread folds the
+// ones before it and the carry of the previous stage into its carry-in and fixes its eight states
+// up, h_t = h_local_t + prod_t * carry (fp32 throughout).
 //
 // When B*D/64 CTAs would leave most SMs idle the time axis is split into NT chunks
 // ("chunked parallel scan"): pass 1 reduces every chunk but the last to its aggregate
 // (prod f, local end state), pass 2 lets each chunk fold the aggregates before it into its
 // carry-in and scans.  Pass 1 re-reads x and g, so it is only used when it buys occupancy.
 #include "common.cuh"
+#include "tensor_map.cuh"
 
 namespace {
 
-constexpr int HG_BD = 64;      // channels per CTA
-constexpr int HG_SUB = 8;      // threads per channel: each scans an eighth of a stage's timesteps
-constexpr int HG_THREADS = HG_BD * HG_SUB;
-constexpr int HG_TS = 64;      // timesteps per stage
-constexpr int HG_STAGES = 4;  // cp.async ring depth
+constexpr int HG_BD = 64;       // channels per CTA
+constexpr int HG_TS = 64;       // timesteps per stage
+constexpr int HG_SUB = 8;       // sub-chunks (warps) per stage
+constexpr int HG_SUBT = HG_TS / HG_SUB;   // timesteps per thread and stage
+constexpr int HG_THREADS = (HG_BD / 2) * HG_SUB;
+constexpr int HG_STAGES = 3;    // TMA ring depth
+constexpr long long HG_WAIT_LIMIT = 2000000000ll;   // clock cycles (about a second) before a wait gives up
 
-__device__ __forceinline__ void cp_async16(void* smem, const void* gmem) {
-    const uint32_t s = (uint32_t)__cvta_generic_to_shared(smem);
-    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"(s), "l"(gmem) : "memory");
+__device__ int g_hgrn_wait_failed = 0;   // set when a bounded wait on a TMA stage gave up
+
+__device__ __forceinline__ uint32_t hg_smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ void hg_mbar_init(uint64_t* bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(hg_smem_u32(bar)), "r"(count) : "memory");
 }
-__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::: "memory"); }
-template <int N> __device__ __forceinline__ void cp_async_wait() {
-    asm volatile("cp.async.wait_group %0;\n" ::"n"(N) : "memory");
+__device__ __forceinline__ void hg_mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(hg_smem_u32(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool hg_mbar_try(uint64_t* bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred P1;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 P1, [%1], %2;\n\t"
+        "selp.b32 %0, 1, 0, P1;\n\t}"
+        : "=r"(ok)
+        : "r"(hg_smem_u32(bar)), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+// bounded: returns false (and raises *abort_flag) if the phase does not complete within HG_WAIT_LIMIT cycles
+__device__ __forceinline__ bool hg_mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag) {
+#pragma unroll 1
+    for (int i = 0; i < 64; ++i)
+        if (hg_mbar_try(bar, parity)) return true;
+    const long long t0 = clock64();
+#pragma unroll 1
+    for (;;) {
+#pragma unroll 1
+        for (int i = 0; i < 32; ++i)
+            if (hg_mbar_try(bar, parity)) return true;
+        if (*abort_flag) return false;
+        if (clock64() - t0 > HG_WAIT_LIMIT) {
+            *abort_flag = 1;
+            return false;
+        }
+    }
+}
+__device__ __forceinline__ void hg_tma_load_3d(void* dst, const CUtensorMap* map, uint64_t* bar, int x, int y, int z) {
+    asm volatile(
+        "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
+        ::"r"(hg_smem_u32(dst)), "l"(map), "r"(hg_smem_u32(bar)), "r"(x), "r"(y), "r"(z)
+        : "memory");
+}
+__device__ __forceinline__ void hg_tma_store_3d(const CUtensorMap* map, const void* src, int x, int y, int z) {
+    asm volatile("cp.async.bulk.tensor.3d.global.shared::cta.bulk_group [%0, {%2, %3, %4}], [%1];"
+                 ::"l"(map), "r"(hg_smem_u32(src)), "r"(x), "r"(y), "r"(z)
+                 : "memory");
+}
+__device__ __forceinline__ void hg_bulk_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+template <int N> __device__ __forceinline__ void hg_bulk_wait_read() {
+    asm volatile("cp.async.bulk.wait_group.read %0;" ::"n"(N) : "memory");
+}
+__device__ __forceinline__ void hg_bulk_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
+__device__ __forceinline__ void hg_fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+
+// two adjacent elements <-> float2
+__device__ __forceinline__ float2 ld2(const float* p) { return *reinterpret_cast<const float2*>(p); }
+__device__ __forceinline__ float2 ld2(const __nv_bfloat16* p) {
+    return __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(p));
+}
+__device__ __forceinline__ float2 ld2(const __half* p) { return __half22float2(*reinterpret_cast<const __half2*>(p)); }
+__device__ __forceinline__ void st2(float* p, float a, float b) { *reinterpret_cast<float2*>(p) = make_float2(a, b); }
+__device__ __forceinline__ void st2(__nv_bfloat16* p, float a, float b) {
+    *reinterpret_cast<__nv_bfloat162*>(p) = __floats2bfloat162_rn(a, b);
+}
+__device__ __forceinline__ void st2(__half* p, float a, float b) { *reinterpret_cast<__half2*>(p) = __floats2half2_rn(a, b); }
+
+// exp(v) for v <= 0 (a log forget gate): ex2.approx of the rounded product plus a first-order correction with
+// the product's rounding residual, so that the relative error stays at the 2^-22 of the approximation itself
+__device__ __forceinline__ float exp_gate(float v) {
+    const float L2E = 1.4426950408889634f;
+    const float t = __fmul_rn(v, L2E);
+    const float e = __fmaf_rn(v, L2E, -t);
+    float p;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(p) : "f"(t));
+    return __fmaf_rn(__fmul_rn(p, 0.6931471805599453f), e, p);
 }
 
 template <typename T> __device__ __forceinline__ float load_state(const void* p, int64_t i) {
@@ -58,162 +134,203 @@ constexpr int HG_RAW = 2;     // x, g are the raw i/f projection outputs (HGRNBi
                               //   f = round(sigmoid(g)); with a lower bound lb: f = round(lb + round(round(1-lb)*f))
                               //   x = round(silu(x_raw) * round(1-f));  every round() is to the activation dtype TX
 
+// raw (x, g) of one element -> (x_t, f_t) of the recurrence
+template <typename TX, int MODE>
+__device__ __forceinline__ void gate_transform(float& xv, float& f, bool has_lb, float lbv, float oml) {
+    if (MODE == HG_LOG) f = exp_gate(f);
+    if (MODE == HG_RAW) {
+        f = round_to<TX>(sigmoidf_(f));
+        if (has_lb) f = round_to<TX>(__fadd_rn(lbv, round_to<TX>(__fmul_rn(oml, f))));
+        xv = round_to<TX>(silu_mul(xv, round_to<TX>(__fsub_rn(1.0f, f))));
+    }
+}
+
 // AGG = true : pass 1, chunks 0..NT-2 -> aggregates (no o written)
 // AGG = false: pass 2 (or the only pass when NT == 1) -> o, ht
-// x and g rows may be strided (ld_x, ld_g elements); o is [B,T,D] contiguous.
-//
-// A CTA has 512 threads for its 64 channels: thread (channel, sub) scans 8 of the 64 timesteps of a stage
-// from a zero state, keeping the local states and the running gate products in registers; the eight
-// sub-chunk aggregates of a channel meet in shared memory, each thread folds the ones before it (and the
-// carry of the previous stage) into its carry-in and fixes its eight states up: h_t = h_local_t + prod_t * carry.
-// Channel-parallel alone would leave 3-4 warps per SM, which cannot hide the latency of the scan loop.
+// Tensor maps: x, g, o as [B][T][D] with box [1][64][64]; rows past T read as zero and are not stored, channels
+// past D likewise.  chunk_len is a multiple of 64, so only the last stage of the last chunk can be partial.
 template <typename TX, typename TG, int MODE, bool AGG>
 __global__ void __launch_bounds__(HG_THREADS)
-hgrn_scan_kernel(const TX* __restrict__ x, int64_t ld_x, const TG* __restrict__ g, int64_t ld_g,
-                 const TX* __restrict__ lb, const void* __restrict__ h0, void* __restrict__ ht,
-                 int state_dt, TX* __restrict__ o, int T, int D, int NT, int chunk_len, HgrnWs ws) {
+hgrn_scan_kernel(const __grid_constant__ CUtensorMap x_map, const __grid_constant__ CUtensorMap g_map,
+                 const __grid_constant__ CUtensorMap o_map, const TX* __restrict__ lb, const void* __restrict__ h0,
+                 void* __restrict__ ht, int state_dt, int T, int D, int NT, int chunk_len, HgrnWs ws) {
     pdl_trigger();
-    pdl_wait();
-    extern __shared__ __align__(16) uint8_t smem_raw[];
-    constexpr int XB = HG_TS * HG_BD * sizeof(TX);  // bytes of one x stage
+    extern __shared__ uint8_t smem_dyn[];
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_dyn) + 127) & ~uintptr_t(127));
+    constexpr int XB = HG_TS * HG_BD * sizeof(TX);  // bytes of one x stage (= one output tile)
     constexpr int GB = HG_TS * HG_BD * sizeof(TG);
-    TX* sx = reinterpret_cast<TX*>(smem_raw);
-    TG* sg = reinterpret_cast<TG*>(smem_raw + HG_STAGES * XB);
-    TX* so = reinterpret_cast<TX*>(smem_raw + HG_STAGES * (XB + GB));
+    TX* sx = reinterpret_cast<TX*>(smem);
+    TG* sg = reinterpret_cast<TG*>(smem + HG_STAGES * XB);
+    TX* so = reinterpret_cast<TX*>(smem + HG_STAGES * (XB + GB));       // two output tiles
     __shared__ float s_agg_a[HG_SUB][HG_BD], s_agg_h[HG_SUB][HG_BD];
     __shared__ float s_carry[2][HG_BD];          // carry of the previous stage, double-buffered by stage parity
+    __shared__ __align__(8) uint64_t s_full[HG_STAGES];
+    __shared__ int s_abort;
 
     const int d0 = blockIdx.x * HG_BD;
     const int c = blockIdx.y;
-    const int64_t b = blockIdx.z;
+    const int b = blockIdx.z;
     const int tid = threadIdx.x;
-    const int lc = tid & (HG_BD - 1);            // channel inside the block
-    const int sub = tid / HG_BD;                 // which quarter of a stage's timesteps
+    const int lc = (tid & 31) * 2;               // first of this thread's two channels inside the block
+    const int sub = tid >> 5;                    // warp = sub-chunk of the stage
     const int ch = d0 + lc;
-    const bool ch_ok = ch < D;
+    const bool ch_ok = ch < D;                   // D is even: both channels of the pair are in or out together
     const int t_begin = c * chunk_len;
-    const int t_end = min(T, t_begin + chunk_len);
-    const int nsteps = t_end - t_begin;
-    const int nstage = (nsteps + HG_TS - 1) / HG_TS;
-    const TX* xb = x + (b * T + t_begin) * ld_x + d0;
-    const TG* gb = g + (b * T + t_begin) * ld_g + d0;
-    TX* ob = AGG ? nullptr : o + (b * T + t_begin) * (int64_t)D + d0;
+    const int nsteps = min(T, t_begin + chunk_len) - t_begin;            // <= 0: an empty chunk (identity)
+    const int nstage = nsteps > 0 ? (nsteps + HG_TS - 1) / HG_TS : 0;
+    volatile int* abort_flag = &s_abort;
 
-    constexpr int XV = 16 / sizeof(TX), GV = 16 / sizeof(TG);   // channels per 16-byte piece
-    constexpr int XP = HG_BD / XV, GP = HG_BD / GV;             // pieces per tile row
+    if (tid == 0) {
+        for (int i = 0; i < HG_STAGES; ++i) hg_mbar_init(&s_full[i], 1);
+        s_abort = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    __syncthreads();
+    pdl_wait();                                  // x and g are the preceding kernel's output
 
-    auto issue = [&](int s) {
+    auto issue = [&](int s) {                    // thread 0 only
         if (s < nstage) {
             const int buf = s % HG_STAGES;
-            const int rows = min(HG_TS, nsteps - s * HG_TS);
-            for (int p = tid; p < rows * XP; p += HG_THREADS) {
-                const int r = p / XP, pc = (p % XP) * XV;
-                if (d0 + pc < D) cp_async16(sx + (buf * HG_TS + r) * HG_BD + pc, xb + (int64_t)(s * HG_TS + r) * ld_x + pc);
-            }
-            for (int p = tid; p < rows * GP; p += HG_THREADS) {
-                const int r = p / GP, pc = (p % GP) * GV;
-                if (d0 + pc < D) cp_async16(sg + (buf * HG_TS + r) * HG_BD + pc, gb + (int64_t)(s * HG_TS + r) * ld_g + pc);
-            }
+            hg_mbar_expect_tx(&s_full[buf], (uint32_t)(XB + GB));
+            hg_tma_load_3d(sx + buf * HG_TS * HG_BD, &x_map, &s_full[buf], d0, t_begin + s * HG_TS, b);
+            hg_tma_load_3d(sg + buf * HG_TS * HG_BD, &g_map, &s_full[buf], d0, t_begin + s * HG_TS, b);
         }
-        cp_async_commit();  // always commit so that group counting stays uniform
     };
-
-#pragma unroll
-    for (int s = 0; s < HG_STAGES - 1; ++s) issue(s);
+    if (tid == 0)
+        for (int s = 0; s < HG_STAGES; ++s) issue(s);
 
     const bool has_lb = MODE == HG_RAW && lb != nullptr && ch_ok;
-    float lbv = 0.0f, oml = 1.0f;
+    float2 lbv = make_float2(0.0f, 0.0f), oml = make_float2(1.0f, 1.0f);
     if (has_lb) {
-        lbv = to_f32(lb[ch]);
-        oml = round_to<TX>(__fsub_rn(1.0f, lbv));
+        lbv = ld2(lb + ch);
+        oml.x = round_to<TX>(__fsub_rn(1.0f, lbv.x));
+        oml.y = round_to<TX>(__fsub_rn(1.0f, lbv.y));
     }
     // carry into the first stage
     if (sub == 0) {
-        float h = 0.0f;
+        float hc[2] = {0.0f, 0.0f};
         if (!AGG && ch_ok) {
-            if (NT == 1) {
-                if (h0) h = load_state_dt(h0, b * D + ch, state_dt);
-            } else {
-                h = ws.h0c[b * D + ch];
-                for (int j = 0; j < c; ++j) {
-                    const int64_t i = (b * NT + j) * (int64_t)D + ch;
-                    h = fmaf(ws.agg_a[i], h, ws.agg_h[i]);
+#pragma unroll
+            for (int k = 0; k < 2; ++k) {
+                const int64_t sidx = (int64_t)b * D + ch + k;
+                if (NT == 1) {
+                    if (h0) hc[k] = load_state_dt(h0, sidx, state_dt);
+                } else {
+                    float h = ws.h0c[sidx];
+                    for (int j = 0; j < c; ++j) {
+                        const int64_t i = ((int64_t)b * NT + j) * (int64_t)D + ch + k;
+                        h = fmaf(ws.agg_a[i], h, ws.agg_h[i]);
+                    }
+                    hc[k] = h;
                 }
             }
         }
-        s_carry[0][lc] = h;
-        if (AGG && c == 0 && ch_ok) ws.h0c[b * D + ch] = h0 ? load_state_dt(h0, b * D + ch, state_dt) : 0.0f;
+        s_carry[0][lc] = hc[0];
+        s_carry[0][lc + 1] = hc[1];
+        if (AGG && c == 0 && ch_ok) {
+#pragma unroll
+            for (int k = 0; k < 2; ++k)
+                ws.h0c[(int64_t)b * D + ch + k] = h0 ? load_state_dt(h0, (int64_t)b * D + ch + k, state_dt) : 0.0f;
+        }
     }
-    float a_run = 1.0f;   // AGG: product of all gates of this chunk
+    float2 a_run = make_float2(1.0f, 1.0f);   // AGG: product of all gates of this chunk
 
     for (int s = 0; s < nstage; ++s) {
-        cp_async_wait<HG_STAGES - 2>();
-        __syncthreads();                          // stage s has landed; s_carry[s&1] and `so` are free to use
         const int buf = s % HG_STAGES;
+        hg_mbar_wait(&s_full[buf], (uint32_t)((s / HG_STAGES) & 1), abort_flag);
         const int rows = min(HG_TS, nsteps - s * HG_TS);
-        constexpr int SUBT = HG_TS / HG_SUB;      // timesteps per thread
-        float hl[SUBT], ap[SUBT];
+        float2 hl[HG_SUBT], ap[HG_SUBT];
         {
-            const TX* px = sx + (buf * HG_TS + sub * SUBT) * HG_BD + lc;
-            const TG* pg = sg + (buf * HG_TS + sub * SUBT) * HG_BD + lc;
-            float h = 0.0f, a = 1.0f;
+            const TX* px = sx + (buf * HG_TS + sub * HG_SUBT) * HG_BD + lc;
+            const TG* pg = sg + (buf * HG_TS + sub * HG_SUBT) * HG_BD + lc;
+            float2 h = make_float2(0.0f, 0.0f), a = make_float2(1.0f, 1.0f);
+            if (rows == HG_TS) {
 #pragma unroll
-            for (int j = 0; j < SUBT; ++j) {
-                float xv = 0.0f, f = 1.0f;        // steps past the end of the sequence are the identity
-                if (ch_ok && sub * SUBT + j < rows) {
-                    xv = to_f32(px[j * HG_BD]);
-                    f = to_f32(pg[j * HG_BD]);
-                    if (MODE == HG_LOG) f = expf(f);
-                    if (MODE == HG_RAW) {
-                        f = round_to<TX>(sigmoidf_(f));
-                        if (has_lb) f = round_to<TX>(__fadd_rn(lbv, round_to<TX>(__fmul_rn(oml, f))));
-                        xv = round_to<TX>(silu_mul(xv, round_to<TX>(__fsub_rn(1.0f, f))));
-                    }
+                for (int j = 0; j < HG_SUBT; ++j) {
+                    float2 xv = ld2(px + j * HG_BD), f = ld2(pg + j * HG_BD);
+                    gate_transform<TX, MODE>(xv.x, f.x, has_lb, lbv.x, oml.x);
+                    gate_transform<TX, MODE>(xv.y, f.y, has_lb, lbv.y, oml.y);
+                    h.x = fmaf(f.x, h.x, xv.x); h.y = fmaf(f.y, h.y, xv.y);
+                    a.x *= f.x; a.y *= f.y;
+                    hl[j] = h; ap[j] = a;
                 }
-                h = fmaf(f, h, xv);
-                a *= f;
-                hl[j] = h;
-                ap[j] = a;
+            } else {
+#pragma unroll
+                for (int j = 0; j < HG_SUBT; ++j) {
+                    float2 xv = ld2(px + j * HG_BD), f = ld2(pg + j * HG_BD);
+                    gate_transform<TX, MODE>(xv.x, f.x, has_lb, lbv.x, oml.x);
+                    gate_transform<TX, MODE>(xv.y, f.y, has_lb, lbv.y, oml.y);
+                    if (sub * HG_SUBT + j >= rows) {   // steps past the end of the sequence are the identity
+                        xv = make_float2(0.0f, 0.0f);
+                        f = make_float2(1.0f, 1.0f);
+                    }
+                    h.x = fmaf(f.x, h.x, xv.x); h.y = fmaf(f.y, h.y, xv.y);
+                    a.x *= f.x; a.y *= f.y;
+                    hl[j] = h; ap[j] = a;
+                }
             }
-            s_agg_a[sub][lc] = a;
-            s_agg_h[sub][lc] = h;
+            *reinterpret_cast<float2*>(&s_agg_a[sub][lc]) = a;
+            *reinterpret_cast<float2*>(&s_agg_h[sub][lc]) = h;
         }
-        __syncthreads();
+        // the output tile written two stages ago must have been read by its TMA store before it is reused
+        if (!AGG && tid == 0) hg_bulk_wait_read<1>();
+        __syncthreads();                          // aggregates visible; all reads of stage buffer `buf` are done
+        if (*abort_flag) break;                   // uniform: written before the barrier
+        if (tid == 0) issue(s + HG_STAGES);       // refill the stage just consumed
         // carry-in of this thread's sub-chunk: previous stage's carry folded through the sub-chunks before it
-        float cin = s_carry[s & 1][lc];
+        float2 cin = *reinterpret_cast<const float2*>(&s_carry[s & 1][lc]);
 #pragma unroll
-        for (int q = 0; q < HG_SUB; ++q)
-            if (q < sub) cin = fmaf(s_agg_a[q][lc], cin, s_agg_h[q][lc]);
-        if (AGG) {
-#pragma unroll
-            for (int q = 0; q < HG_SUB; ++q) a_run *= s_agg_a[q][lc];
-        } else {
-#pragma unroll
-            for (int j = 0; j < SUBT; ++j) so[(sub * SUBT + j) * HG_BD + lc] = from_f32<TX>(fmaf(ap[j], cin, hl[j]));
-        }
-        if (sub == HG_SUB - 1) s_carry[(s + 1) & 1][lc] = fmaf(ap[SUBT - 1], cin, hl[SUBT - 1]);
-        if (!AGG) {
-            __syncthreads();
-            for (int p = tid; p < rows * XP; p += HG_THREADS) {
-                const int r = p / XP, pc = (p % XP) * XV;
-                if (d0 + pc < D)
-                    *reinterpret_cast<uint4*>(ob + (int64_t)(s * HG_TS + r) * D + pc) =
-                        *reinterpret_cast<const uint4*>(so + r * HG_BD + pc);
+        for (int q = 0; q < HG_SUB - 1; ++q) {
+            if (q < sub) {                        // warp-uniform
+                const float2 qa = *reinterpret_cast<const float2*>(&s_agg_a[q][lc]);
+                const float2 qh = *reinterpret_cast<const float2*>(&s_agg_h[q][lc]);
+                cin.x = fmaf(qa.x, cin.x, qh.x);
+                cin.y = fmaf(qa.y, cin.y, qh.y);
             }
         }
-        issue(s + HG_STAGES - 1);
+        if (AGG) {
+            if (sub == 0) {
+#pragma unroll
+                for (int q = 0; q < HG_SUB; ++q) {
+                    const float2 qa = *reinterpret_cast<const float2*>(&s_agg_a[q][lc]);
+                    a_run.x *= qa.x; a_run.y *= qa.y;
+                }
+            }
+        } else {
+            TX* po = so + ((s & 1) * HG_TS + sub * HG_SUBT) * HG_BD + lc;
+#pragma unroll
+            for (int j = 0; j < HG_SUBT; ++j)
+                st2(po + j * HG_BD, fmaf(ap[j].x, cin.x, hl[j].x), fmaf(ap[j].y, cin.y, hl[j].y));
+            hg_fence_async_smem();                // generic-proxy writes -> visible to the TMA store
+        }
+        if (sub == HG_SUB - 1) {
+            s_carry[(s + 1) & 1][lc] = fmaf(ap[HG_SUBT - 1].x, cin.x, hl[HG_SUBT - 1].x);
+            s_carry[(s + 1) & 1][lc + 1] = fmaf(ap[HG_SUBT - 1].y, cin.y, hl[HG_SUBT - 1].y);
+        }
+        __syncthreads();                          // output tile and next carry complete; aggregates may be overwritten
+        if (!AGG && tid == 0) {
+            hg_tma_store_3d(&o_map, so + (s & 1) * HG_TS * HG_BD, d0, t_begin + s * HG_TS, b);
+            hg_bulk_commit();
+        }
     }
-    cp_async_wait<0>();
+    if (!AGG && tid == 0) hg_bulk_wait_all();     // shared memory must outlive the stores that read it
     __syncthreads();
+    if (*abort_flag) {
+        if (tid == 0) atomicExch(&g_hgrn_wait_failed, 1);
+        return;
+    }
 
     if (ch_ok && sub == 0) {
-        const float h_end = s_carry[nstage & 1][lc];
-        if (AGG) {
-            const int64_t i = (b * NT + c) * (int64_t)D + ch;
-            ws.agg_a[i] = a_run;
-            ws.agg_h[i] = h_end;
-        } else if (ht && c == NT - 1) {
-            store_state_dt(ht, b * D + ch, state_dt, h_end);
+#pragma unroll
+        for (int k = 0; k < 2; ++k) {
+            const float h_end = s_carry[nstage & 1][lc + k];
+            if (AGG) {
+                const int64_t i = ((int64_t)b * NT + c) * (int64_t)D + ch + k;
+                ws.agg_a[i] = k ? a_run.y : a_run.x;
+                ws.agg_h[i] = h_end;
+            } else if (ht && c == NT - 1) {
+                store_state_dt(ht, (int64_t)b * D + ch + k, state_dt, h_end);
+            }
         }
     }
 }
@@ -229,27 +346,49 @@ int hgrn_num_chunks(int64_t B, int64_t T, int64_t D) {
 
 template <typename TX, typename TG>
 size_t hgrn_smem_bytes() {
-    return (size_t)HG_STAGES * HG_TS * HG_BD * (sizeof(TX) + sizeof(TG)) + (size_t)HG_TS * HG_BD * sizeof(TX);
+    return (size_t)HG_STAGES * HG_TS * HG_BD * (sizeof(TX) + sizeof(TG)) + (size_t)2 * HG_TS * HG_BD * sizeof(TX) + 128;
+}
+
+// [B][T][D] view with row pitch `ld` elements (batch pitch T*ld), box = one [64 timesteps x 64 channels] tile
+int hgrn_make_map(CUtensorMap* map, const void* base, int es, int64_t ld, int64_t B, int64_t T, int64_t D, const char* who) {
+    MmfEncodeTiledFn encode = mmf_encode_tiled();
+    MMF_REQUIRE(encode != nullptr, MMF_ERR_CUDA, "%s: cuTensorMapEncodeTiled is not available from the driver", who);
+    const cuuint64_t gdim[3] = {(cuuint64_t)D, (cuuint64_t)T, (cuuint64_t)B};
+    const cuuint64_t gstride[2] = {(cuuint64_t)(ld * es), (cuuint64_t)(T * ld * es)};
+    const cuuint32_t box[3] = {(cuuint32_t)HG_BD, (cuuint32_t)HG_TS, 1u};
+    const cuuint32_t estr[3] = {1u, 1u, 1u};
+    const CUresult cr = encode(map, es == 2 ? CU_TENSOR_MAP_DATA_TYPE_UINT16 : CU_TENSOR_MAP_DATA_TYPE_UINT32, 3,
+                               const_cast<void*>(base), gdim, gstride, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                               CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                               CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    MMF_REQUIRE(cr == CUDA_SUCCESS, MMF_ERR_CUDA, "%s: cuTensorMapEncodeTiled failed (%d)", who, (int)cr);
+    return MMF_OK;
 }
 
 template <typename TX, typename TG, int MODE>
 int hgrn_launch(const void* x, int64_t ld_x, const void* g, int64_t ld_g, const void* lb, const void* h0, void* ht,
                 int state_dt, void* o, int64_t B, int64_t T, int64_t D, int NT, HgrnWs ws, cudaStream_t st) {
     const size_t smem = hgrn_smem_bytes<TX, TG>();
-    const int chunk_len = (int)((T + NT - 1) / NT);
+    // chunks start on stage boundaries so that every chunk but the last consists of whole stages
+    const int chunk_len = (int)(((T + NT - 1) / NT + HG_TS - 1) / HG_TS * HG_TS);
+    CUtensorMap x_map, g_map, o_map;
+    int rc = hgrn_make_map(&x_map, x, (int)sizeof(TX), ld_x, B, T, D, "mmf_hgrn");
+    if (rc == MMF_OK) rc = hgrn_make_map(&g_map, g, (int)sizeof(TG), ld_g, B, T, D, "mmf_hgrn");
+    if (rc == MMF_OK) rc = hgrn_make_map(&o_map, o, (int)sizeof(TX), D, B, T, D, "mmf_hgrn");
+    if (rc != MMF_OK) return rc;
     const dim3 grid((unsigned)((D + HG_BD - 1) / HG_BD), (unsigned)NT, (unsigned)B);
     if (NT > 1) {
         auto k1 = hgrn_scan_kernel<TX, TG, MODE, true>;
         MMF_CUDA(cudaFuncSetAttribute(k1, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
         const dim3 grid1(grid.x, (unsigned)(NT - 1), grid.z);
-        MMF_CUDA(mmf_launch_pdl(k1, grid1, dim3(HG_THREADS), smem, st, (const TX*)x, ld_x, (const TG*)g, ld_g, (const TX*)lb, h0,
-                                (void*)nullptr, state_dt, (TX*)nullptr, (int)T, (int)D, NT, chunk_len, ws));
+        MMF_CUDA(mmf_launch_pdl(k1, grid1, dim3(HG_THREADS), smem, st, x_map, g_map, o_map, (const TX*)lb, h0,
+                                (void*)nullptr, state_dt, (int)T, (int)D, NT, chunk_len, ws));
         MMF_LAUNCH_CHECK("hgrn_scan_kernel<aggregate>");
     }
     auto k2 = hgrn_scan_kernel<TX, TG, MODE, false>;
     MMF_CUDA(cudaFuncSetAttribute(k2, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    MMF_CUDA(mmf_launch_pdl(k2, grid, dim3(HG_THREADS), smem, st, (const TX*)x, ld_x, (const TG*)g, ld_g, (const TX*)lb, h0, ht,
-                            state_dt, (TX*)o, (int)T, (int)D, NT, chunk_len, ws));
+    MMF_CUDA(mmf_launch_pdl(k2, grid, dim3(HG_THREADS), smem, st, x_map, g_map, o_map, (const TX*)lb, h0, ht, state_dt,
+                            (int)T, (int)D, NT, chunk_len, ws));
     MMF_LAUNCH_CHECK("hgrn_scan_kernel<scan>");
     return MMF_OK;
 }
@@ -330,4 +469,10 @@ extern "C" int mmf_hgrn_gated(const void* i_raw, const void* f_raw, int64_t ld, 
                                          (cudaStream_t)stream);
     });
     return rc;
+}
+
+extern "C" int mmf_hgrn_status(int* failed_host) {
+    MMF_REQUIRE(failed_host, MMF_ERR_BAD_ARG, "mmf_hgrn_status: null pointer");
+    MMF_CUDA(cudaMemcpyFromSymbol(failed_host, g_hgrn_wait_failed, sizeof(int)));
+    return MMF_OK;
 }

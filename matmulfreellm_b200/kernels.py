@@ -8,6 +8,8 @@ from __future__ import annotations
 from dataclasses import dataclass
 from typing import Optional, Sequence, Tuple
 
+import ctypes
+
 import torch
 
 from . import _lib
@@ -156,6 +158,10 @@ def _workspace(device: torch.device, nbytes: int) -> torch.Tensor:
 def check_status() -> None:
     """Synchronise and raise if any BitLinear kernel reported a device-side wait that gave up (status word
     at the start of the split-K workspace).  Costs a device sync; meant for tests and debugging."""
+    failed = ctypes.c_int(0)
+    _lib.call("mmf_hgrn_status", ctypes.addressof(failed))
+    if failed.value:
+        raise _lib.MMFreeError("mmf_hgrn_scan", -7, "a scan kernel gave up waiting for a TMA stage")
     for key, ws in list(_ws_cache.items()):
         torch.cuda.synchronize(ws.device)
         status = int(ws[:4].view(torch.int32).item())

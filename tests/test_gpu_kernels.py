@@ -185,6 +185,43 @@ def test_bitlinear_matches_reference_output(K, golden):
         assert np.quantile(d, 0.5) <= 2e-6 * np.abs(ref).max() and d.max() <= 5e-3 * np.abs(ref).max()
 
 
+def test_bitlinear_persistent_kernel(K):
+    """The persistent large-M tensor-core kernel (256-token tiles, work list per CTA), forced on for shapes with a
+    ragged last token tile, a ragged last weight tile and a trailing 64-wide K stage: bit-exact accumulators and
+    outputs in all three dtypes against the CUDA-core kernel; then a grouped (3 x norm weight) call."""
+    from matmulfreellm_b200 import _lib
+    lib = _lib.load()
+    try:
+        for (M, Kd, N) in [(300, 704, 384), (700, 2048, 512), (1024, 2560, 200), (129, 256, 128)]:
+            x, w, _ = O.bitlinear_case(M, Kd, N, seed=M)
+            pw = K.pack_weight(dev(w))
+            q, dq, rs = K.act_quant(dev(x), None, 1e-6)
+            lib.mmf_tuning(7, 2)
+            ref, acc_ref = K.bitlinear(q, dq, rs, pw, torch.float32, kernel=K.KERNEL_GEMV, return_acc=True)
+            lib.mmf_tuning(7, 1)
+            out, acc = K.bitlinear(q, dq, rs, pw, torch.float32, kernel=K.KERNEL_MMA, return_acc=True)
+            K.check_status()
+            assert torch.equal(acc, acc_ref) and torch.equal(out, ref), (M, Kd, N)
+            for dt in (torch.bfloat16, torch.float16):
+                assert torch.equal(K.bitlinear(q, dq, rs, pw, dt, kernel=K.KERNEL_MMA), ref.to(dt)), (M, Kd, N, dt)
+        M, Kdim, N = 260, 256, 256
+        x, _, _ = O.bitlinear_case(M, Kdim, N, seed=3)
+        g = torch.Generator().manual_seed(11)
+        ws = [torch.randn(N, Kdim, generator=g) * 0.02 for _ in range(3)]
+        nws = [1.0 + 0.1 * torch.randn(Kdim, generator=g) for _ in range(3)]
+        pw = K.stack_packed([K.pack_weight(dev(w)) for w in ws])
+        qs = [K.act_quant(dev(x), dev(nw), 1e-6) for nw in nws]
+        q = torch.cat([t[0] for t in qs]); dq = torch.cat([t[1] for t in qs]); rs = torch.cat([t[2] for t in qs])
+        out = K.bitlinear(q, dq, rs, pw, torch.float32, kernel=K.KERNEL_MMA)
+        K.check_status()
+        for gi in range(3):
+            codes, mean = O.ternary_codes(ws[gi])
+            ref = O.bitlinear_int(x, nws[gi], codes, mean, 1e-6)[0]
+            assert torch.equal(out[:, gi * N:(gi + 1) * N].cpu(), ref)
+    finally:
+        lib.mmf_tuning(7, 0)
+
+
 def test_bitlinear_large_m_properties(K):
     """BASELINE-size M: rows are independent, so a slice of a 4096-row call equals the same rows run alone,
     and the first rows match the oracle."""
@@ -465,10 +502,10 @@ def test_bitlinear_mma_configurations_agree(K):
                         assert e.code == -2
                         continue
                     finally:
-                        for kk in range(4):
+                        for kk in range(8):
                             lib.mmf_tuning(kk, 0)
                     K.check_status()
                     assert torch.equal(acc, acc_ref) and torch.equal(out, ref), (M, Kd, N, knob, v)
     finally:
-        for kk in range(4):
+        for kk in range(8):
             lib.mmf_tuning(kk, 0)
