@@ -190,7 +190,8 @@ int mmf_int8_mma_peak(int n_tokens, int iters, int* status_dev, double* tops_hos
 #define MMF_TUNE_B_STAGES 4   /* activation-tile ring depth (128 K per stage)                  */
 #define MMF_TUNE_A_STAGES 5   /* unpacked-weight stages held in tensor memory (even)           */
 #define MMF_TUNE_W_STAGES 6   /* packed-weight ring depth (even)                               */
-#define MMF_TUNE_PERSISTENT 7 /* persistent large-M kernel: 1 = whenever M > 128, 2 = never     */
+#define MMF_TUNE_PERSISTENT 7 /* persistent large-M kernel: 1 = whenever M > 128, 2 = never, 10+v = its compiled shape v (1..4) whenever M > 128 */
+#define MMF_TUNE_PROBE_COMMITS 8 /* mmf_int8_mma_peak: tcgen05.commit instructions issued per 4 MMAs */
 int mmf_tuning(int knob, int value);
 
 /* ------------------------------------------------------------------------------------

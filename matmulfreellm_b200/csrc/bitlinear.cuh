@@ -28,7 +28,8 @@ constexpr int MMF_SPLITK_MAX_M = 256;
 
 int bitlinear_gemv_launch(const BitLinearArgs& a, cudaStream_t st, bool force_split_k);
 int bitlinear_mma_launch(const BitLinearArgs& a, cudaStream_t st);
-int bitlinear_mma_prefill_launch(const BitLinearArgs& a, cudaStream_t st);   // persistent variant for many token rows
+int bitlinear_mma_prefill_launch(const BitLinearArgs& a, cudaStream_t st, int variant);   // persistent kernel for many token rows
+int bitlinear_mma_prefill_tile(const BitLinearArgs& a, int variant);                       // its token tile
 
 // out = acc * (dq * w_scale), the one place the dequantising epilogue is defined
 __device__ __forceinline__ float bitlinear_dequant(int32_t acc, float dq, float w_scale) {

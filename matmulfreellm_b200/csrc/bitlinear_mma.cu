@@ -466,6 +466,8 @@ bitlinear_mma_kernel(const __grid_constant__ CUtensorMap q_map, BitLinearArgs a,
 // tuning overrides (0 = automatic), see mmf_tuning()
 static int g_force_ksplit = 0, g_force_nt = 0, g_force_deep = 0, g_force_wt = 0, g_force_sb = 0, g_force_sa = 0, g_force_sw = 0, g_force_persistent = 0;
 
+extern int g_probe_commits;
+
 extern "C" int mmf_tuning(int knob, int value) {
     switch (knob) {
         case MMF_TUNE_KSPLIT: g_force_ksplit = value; return MMF_OK;
@@ -476,6 +478,7 @@ extern "C" int mmf_tuning(int knob, int value) {
         case MMF_TUNE_A_STAGES: g_force_sa = value; return MMF_OK;
         case MMF_TUNE_W_STAGES: g_force_sw = value; return MMF_OK;
         case MMF_TUNE_PERSISTENT: g_force_persistent = value; return MMF_OK;
+        case MMF_TUNE_PROBE_COMMITS: g_probe_commits = value; return MMF_OK;
         default: return mmf_set_error(MMF_ERR_BAD_ARG, "mmf_tuning: unknown knob %d", knob);
     }
 }
@@ -572,11 +575,15 @@ bool choose_config(const BitLinearArgs& a, MmaParams& best, size_t& best_smem) {
 
 int bitlinear_mma_launch(const BitLinearArgs& a, cudaStream_t st) {
     {
-        // many token rows: the persistent kernel (256-token tiles, one CTA per SM) once it has a full wave of work
-        const int64_t n_work = (int64_t)((a.N + MMF_TILE_ROWS - 1) / MMF_TILE_ROWS) * ((a.M + 255) / 256);
+        // many token rows: the persistent kernel (one CTA per SM) once it has a full wave of work;
+        // knob values >= 10 select experimental variant (value - 10) and force it for every M > 128
+        const int variant = g_force_persistent >= 10 ? g_force_persistent - 10 : 0;
+        const int nt = bitlinear_mma_prefill_tile(a, variant);
+        const int64_t n_work = (int64_t)((a.N + MMF_TILE_ROWS - 1) / MMF_TILE_ROWS) * ((a.M + nt - 1) / nt);
         const bool tuned = g_force_ksplit || g_force_nt || g_force_deep || g_force_wt || g_force_sb || g_force_sa || g_force_sw;
-        if (g_force_persistent == 1 ? a.M > 128 : (g_force_persistent == 0 && !tuned && a.M >= 512 && n_work >= 148))
-            return bitlinear_mma_prefill_launch(a, st);
+        if ((g_force_persistent == 1 || g_force_persistent >= 10) ? a.M > 128
+                                                                   : (g_force_persistent == 0 && !tuned && a.M >= 512 && n_work >= 148))
+            return bitlinear_mma_prefill_launch(a, st, variant);
     }
     MmaParams p;
     size_t smem = 0;

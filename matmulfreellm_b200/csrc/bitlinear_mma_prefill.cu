@@ -4,8 +4,17 @@
 // stream expanded in registers and written straight into tensor memory (A-from-TMEM), int8 activation
 // codes fetched by tiled TMA with the 128-byte swizzle — but organised for throughput instead of latency:
 //
-//  * 256 token columns per tile: one MMA then occupies the tensor pipe for its full 130 cycles, which
-//    also gives the single issuing thread the largest budget per instruction;
+//  * the single thread that issues the MMAs is a serial instruction stream in which one tcgen05.mma costs
+//    about 67 cycles and one tcgen05.commit about 90 (measured), so a stage of four MMAs must not carry
+//    more than one commit and one barrier wait: the unpacked-A ring (TMEM) and the activation ring (shared
+//    memory) have the same depth and advance together, one "full" barrier per stage collects the 128
+//    arrivals of an unpack group plus the TMA transaction bytes, one "empty" barrier (a single commit)
+//    hands both buffers back;
+//  * two tile shapes: 192 token columns with TWO accumulators (2 x 192 + 4 x 32 A-stage columns = all 512
+//    TMEM columns) — the MMAs of the next work item run while the epilogue drains the previous
+//    accumulator; and, for long K, 256 token columns with one accumulator and rings six deep — each MMA
+//    then fills the tensor pipe for 133 cycles, which hides the issue cost completely, and the exposed
+//    epilogue is amortised over many stages;
 //  * every CTA walks a list of (weight tile, token tile) work items, weight tile fastest, so that the
 //    CTAs running at the same time share a few activation tiles in L2; barriers, TMEM and the three
 //    rings (packed weights, unpacked A stages, activation tiles) are set up once and keep streaming
@@ -15,35 +24,53 @@
 //    per-token code sum (weights are stored +1 biased), dequantise and store; the accumulator is handed
 //    back to the MMA warp as soon as its last chunk sits in registers.
 //
-// Warp roles (608 threads): 0-7 unpack (two groups of four that alternate 128-K stages), 8-15 epilogue
-// (TMEM lane quarter = warp % 4, column half = (warp - 8) / 4), 16 packed-weight producer, 17 activation
-// producer, 18 TMEM owner + MMA issuer.  Every wait is bounded and reports through the status word.
+// Warp roles: 4 x GROUPS unpack warps (groups of four take 128-K stages in turn), then 8 epilogue warps (TMEM
+// lane quarter = warp % 4, column half by warp), then the packed-weight producer, the activation producer and
+// the TMEM owner + MMA issuer.  Every wait is bounded and reports through the status word.
 #include "bitlinear.cuh"
 #include "tcgen05.cuh"
 #include "tensor_map.cuh"
 
 namespace {
 
-constexpr int PF_NT = 256;                 // token columns per tile
-constexpr int PF_UNPACK_WARPS = 8, PF_EPI_WARPS = 8;
-constexpr int PF_WARP_W = 16, PF_WARP_B = 17, PF_WARP_MMA = 18;
-constexpr int PF_THREADS = 19 * 32;
-constexpr int PF_SA = 8;                   // unpacked A stages in TMEM (32 columns each, after the 256 accumulator columns)
-constexpr int PF_SB = 5;                   // activation stages (32 KB each)
-constexpr int PF_SW = 8;                   // packed-weight stages (4 KB each)
-constexpr int PF_B_STAGE = PF_NT * 128;
-constexpr int PF_W_STAGE = 2 * MMF_TILE_ROWS * 16;
-constexpr int PF_SMEM = 1024 + PF_SB * PF_B_STAGE + PF_SW * PF_W_STAGE;
-
-constexpr int PB_B_FULL = 0, PB_B_EMPTY = PB_B_FULL + PF_SB, PB_W_FULL = PB_B_EMPTY + PF_SB, PB_W_EMPTY = PB_W_FULL + PF_SW,
-              PB_A_FULL = PB_W_EMPTY + PF_SW, PB_A_EMPTY = PB_A_FULL + PF_SA, PB_ACC_FULL = PB_A_EMPTY + PF_SA,
-              PB_ACC_EMPTY = PB_ACC_FULL + 1, PB_COUNT = PB_ACC_EMPTY + 1;
-
-__device__ __forceinline__ uint32_t pf_bar_count(int i) {
-    if (i >= PB_W_EMPTY && i < PB_A_EMPTY) return 128u;   // the 128 threads of one unpack group
-    if (i == PB_ACC_EMPTY) return (uint32_t)PF_EPI_WARPS;
-    return 1u;
-}
+// Compile-time shape of one variant of the kernel.
+template <int NT_, int GROUPS_, int SA_, int SB_, int SW_, bool DOUBLE_, bool MERGED_, bool STAGE_OUT_>
+struct PfCfg {
+    static constexpr int NT = NT_;                   // token columns per tile
+    static constexpr int GROUPS = GROUPS_;           // unpack groups of four warps that take 128-K stages in turn
+    static constexpr int SA = SA_;                   // unpacked A stages in TMEM (32 columns each, after the accumulators)
+    static constexpr int SB = SB_;                   // activation stages (NT * 128 bytes each)
+    static constexpr int SW = SW_;                   // packed-weight stages (4 KB each)
+    static constexpr int NACC = DOUBLE_ ? 2 : 1;     // accumulators: with two, MMAs of the next item overlap the epilogue
+    // MERGED: the A ring and the activation ring advance together (same depth, same slot), so one "full" barrier
+    // (128 unpack arrivals + the TMA producer's expect_tx) and one "empty" barrier serve a stage: the issuing
+    // thread then executes one wait and one tcgen05.commit per stage instead of two of each
+    static constexpr bool MERGED = MERGED_;
+    static constexpr int UNPACK_WARPS = 4 * GROUPS, EPI_WARPS = 8;
+    static constexpr int WARP_W = UNPACK_WARPS + EPI_WARPS, WARP_B = WARP_W + 1, WARP_MMA = WARP_W + 2;
+    static constexpr int THREADS = (WARP_MMA + 1) * 32;
+    static constexpr int B_STAGE = NT * 128;
+    static constexpr int W_STAGE = 2 * MMF_TILE_ROWS * 16;
+    // STAGE_OUT: 2-byte outputs leave through a [NT][128] shared-memory tile and one TMA store per work item
+    static constexpr bool STAGE_OUT = STAGE_OUT_;
+    static constexpr int OUT_STAGE = STAGE_OUT ? NT * MMF_TILE_ROWS * 2 : 0;
+    static constexpr int SMEM = 1024 + SB * B_STAGE + SW * W_STAGE + OUT_STAGE;
+    static constexpr int B_FULL = 0, B_EMPTY = B_FULL + SB, W_FULL = B_EMPTY + SB, W_EMPTY = W_FULL + SW,
+                         A_FULL = W_EMPTY + SW, A_EMPTY = A_FULL + SA, ACC_FULL = A_EMPTY + SA, ACC_EMPTY = ACC_FULL + 2,
+                         BAR_COUNT = ACC_EMPTY + 2;
+    static_assert(NACC * NT + SA * 32 <= 512, "accumulators and the A ring must fit tensor memory");
+    static_assert(!MERGED || SA == SB, "merged rings have one depth");
+    __host__ __device__ static constexpr int b_full(int slot) { return (MERGED ? A_FULL : B_FULL) + slot; }
+    __host__ __device__ static constexpr int b_empty(int slot) { return (MERGED ? A_EMPTY : B_EMPTY) + slot; }
+    static_assert(NT % 32 == 0 && NT <= 256, "token tile");
+    static_assert(SMEM + 5 * 1024 <= 227 * 1024, "shared memory (dynamic + static) per CTA");
+    __device__ static uint32_t bar_count(int i) {
+        if (MERGED && i >= A_FULL && i < A_EMPTY) return 129u;   // one unpack group + the activation producer
+        if (i >= W_EMPTY && i < A_EMPTY) return 128u;   // the 128 threads of one unpack group
+        if (i >= ACC_EMPTY) return (uint32_t)EPI_WARPS;
+        return 1u;
+    }
+};
 
 struct PfParams {
     int KC;            // K / 64
@@ -51,6 +78,7 @@ struct PfParams {
     int group_tiles;   // weight tiles per group
     int m_tiles;       // token tiles
     int n_work;        // n_tiles * m_tiles
+    int tma_out;       // outputs go through the shared-memory tile and out_map (2-byte dtype, 16-byte aligned rows)
     uint32_t idesc;
 };
 
@@ -86,88 +114,99 @@ __device__ __forceinline__ void pf_store_chunk(const BitLinearArgs& a, const uin
     }
 }
 
-__global__ void __launch_bounds__(PF_THREADS, 1)
-bitlinear_mma_prefill_kernel(const __grid_constant__ CUtensorMap q_map, BitLinearArgs a, PfParams p) {
+template <typename C>
+__global__ void __launch_bounds__(C::THREADS, 1)
+bitlinear_mma_prefill_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant__ CUtensorMap out_map,
+                             BitLinearArgs a, PfParams p) {
     extern __shared__ uint8_t smem_raw[];
     uint8_t* base = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     uint8_t* b_ring = base;
-    uint8_t* w_ring = base + PF_SB * PF_B_STAGE;
+    uint8_t* w_ring = base + C::SB * C::B_STAGE;
 
-    __shared__ __align__(8) uint64_t bars[PB_COUNT];
+    __shared__ __align__(8) uint64_t bars[C::BAR_COUNT];
     __shared__ uint32_t s_tmem_base;
     __shared__ int s_abort;
-    __shared__ __align__(16) float s_scale[2][PF_NT];   // dq[m] * w_scale per token column, double-buffered by work item
-    __shared__ __align__(16) int s_rs[2][PF_NT];        // code sum per token column
+    __shared__ __align__(16) float s_scale[2][C::NT];   // dq[m] * w_scale per token column, double-buffered by work item
+    __shared__ __align__(16) int s_rs[2][C::NT];        // code sum per token column
 
     const int tid = threadIdx.x;
     const int warp = tid >> 5, lane = tid & 31;
     pdl_trigger();
 
-    if (tid < PB_COUNT) mbar_init(&bars[tid], pf_bar_count(tid));
-    if (tid == PB_COUNT) s_abort = 0;
-    if (warp == PF_WARP_MMA) tmem_alloc(&s_tmem_base, 512u);
+    if (tid < C::BAR_COUNT) mbar_init(&bars[tid], C::bar_count(tid));
+    if (tid == C::BAR_COUNT) s_abort = 0;
+    if (warp == C::WARP_MMA) tmem_alloc(&s_tmem_base, 512u);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = s_tmem_base;
-    const uint32_t tmem_a = tmem_base + PF_NT;
+    const uint32_t tmem_a = tmem_base + C::NACC * C::NT;
     volatile int* abort_flag = &s_abort;
     const int S = (p.KC + 1) / 2;              // 128-K stages per work item
     const int first = blockIdx.x, step = gridDim.x;
+    // optional phase trace of CTA 0 (armed by MMF_TRACE_MAGIC in workspace word 1): 28 clock64 slots in the header
+    long long* trace = (lane == 0 && blockIdx.x == 0 && a.ws && a.ws[1] == MMF_TRACE_MAGIC)
+                           ? reinterpret_cast<long long*>(a.ws + 8) : nullptr;
+    if (tid == 0) trace_mark(trace, 0);
 
-    if (warp == PF_WARP_W) {
+    if (warp == C::WARP_W) {
         // ------------------------------------------------------------ packed weights (bulk TMA); independent of the
         // preceding kernel, so the stream starts before the grid dependency wait
         if (elect_one()) {
-            PfRing w{0, 0, PF_SW};
+            PfRing w{0, 0, C::SW};
             bool live = true;
             for (int wk = first; wk < p.n_work && live; wk += step) {
                 const int tile = wk % p.n_tiles;
                 const uint8_t* src = reinterpret_cast<const uint8_t*>(a.packed) + (int64_t)tile * p.KC * (MMF_TILE_ROWS * 16);
                 for (int i = 0; i < S; ++i, w.next()) {
                     const uint32_t bytes = (uint32_t)min(2, p.KC - i * 2) * (MMF_TILE_ROWS * 16);
-                    if (!mbar_wait(&bars[PB_W_EMPTY + w.slot], w.ph ^ 1, abort_flag)) { live = false; break; }
-                    mbar_expect_tx(&bars[PB_W_FULL + w.slot], bytes);
-                    bulk_load_1d(w_ring + w.slot * PF_W_STAGE, src + (int64_t)i * PF_W_STAGE, bytes, &bars[PB_W_FULL + w.slot]);
+                    if (!mbar_wait(&bars[C::W_EMPTY + w.slot], w.ph ^ 1, abort_flag)) { live = false; break; }
+                    mbar_expect_tx(&bars[C::W_FULL + w.slot], bytes);
+                    bulk_load_1d(w_ring + w.slot * C::W_STAGE, src + (int64_t)i * C::W_STAGE, bytes, &bars[C::W_FULL + w.slot]);
                 }
             }
         }
-    } else if (warp == PF_WARP_B) {
+    } else if (warp == C::WARP_B) {
         // ------------------------------------------------------------ activation tiles (TMA, 128-byte swizzle)
         pdl_wait();
         if (elect_one()) {
-            PfRing bq{0, 0, PF_SB};
+            PfRing bq{0, 0, C::SB};
             bool live = true;
             for (int wk = first; wk < p.n_work && live; wk += step) {
                 const int tile = wk % p.n_tiles, mt = wk / p.n_tiles;
-                const int y = (tile / p.group_tiles) * a.M + mt * PF_NT;
+                const int y = (tile / p.group_tiles) * a.M + mt * C::NT;
                 for (int i = 0; i < S; ++i, bq.next()) {
-                    if (!mbar_wait(&bars[PB_B_EMPTY + bq.slot], bq.ph ^ 1, abort_flag)) { live = false; break; }
-                    mbar_expect_tx(&bars[PB_B_FULL + bq.slot], (uint32_t)PF_B_STAGE);
-                    tma_load_2d(b_ring + bq.slot * PF_B_STAGE, &q_map, &bars[PB_B_FULL + bq.slot], i * 128, y);
+                    if (!mbar_wait(&bars[C::b_empty(bq.slot)], bq.ph ^ 1, abort_flag)) { live = false; break; }
+                    mbar_expect_tx(&bars[C::b_full(bq.slot)], (uint32_t)C::B_STAGE);
+                    tma_load_2d(b_ring + bq.slot * C::B_STAGE, &q_map, &bars[C::b_full(bq.slot)], i * 128, y);
                 }
             }
         }
-    } else if (warp == PF_WARP_MMA) {
+    } else if (warp == C::WARP_MMA) {
         // ------------------------------------------------------------ MMA issue: a serial instruction stream, kept short
         if (elect_one()) {
-            PfRing bq{0, 0, PF_SB}, aq{0, 0, PF_SA};
+            PfRing bq{0, 0, C::SB}, aq{0, 0, C::SA};
             const uint64_t b_desc0 = make_b_desc(smem_u32(b_ring));
             const uint32_t b_lo0 = (uint32_t)b_desc0, b_hi = (uint32_t)(b_desc0 >> 32);
-            const uint32_t b_desc_step = (uint32_t)PF_B_STAGE >> 4;
+            const uint32_t b_desc_step = (uint32_t)C::B_STAGE >> 4;
             const int nfull = p.KC / 2;          // whole 128-K stages; a trailing 64-K stage issues two MMAs
             bool live = true;
             int it = 0;
             for (int wk = first; wk < p.n_work && live; wk += step, ++it) {
-                // the epilogue must have drained the accumulator of the previous work item
-                if (!mbar_wait(&bars[PB_ACC_EMPTY], (uint32_t)((it & 1) ^ 1), abort_flag)) break;
+                // the epilogue must have drained this accumulator (used two work items ago)
+                const int ab = C::NACC == 2 ? (it & 1) : 0;              // accumulator of this work item
+                if (!mbar_wait(&bars[C::ACC_EMPTY + ab], (uint32_t)(((it / C::NACC) & 1) ^ 1), abort_flag)) break;
                 tc_fence_after();
+                const uint32_t d_addr = tmem_base + (uint32_t)ab * C::NT;
+                if (it >= 1 && it < 5) trace_mark(trace, 1 + (it - 1) * 3);
+                
                 uint32_t accum = 0;
                 for (int i = 0; i < S; ++i, bq.next(), aq.next()) {
-                    if (!mbar_wait(&bars[PB_B_FULL + bq.slot], bq.ph, abort_flag)) { live = false; break; }
-                    if (!mbar_wait(&bars[PB_A_FULL + aq.slot], aq.ph, abort_flag)) { live = false; break; }
+                    if (!C::MERGED && !mbar_wait(&bars[C::B_FULL + bq.slot], bq.ph, abort_flag)) { live = false; break; }
+                    if (!mbar_wait(&bars[C::A_FULL + aq.slot], aq.ph, abort_flag)) { live = false; break; }
                     tc_fence_after();
+                    if (i == 0 && it >= 1 && it < 5) trace_mark(trace, 2 + (it - 1) * 3);
                     uint32_t a_addr = tmem_a + aq.slot * 32;
                     uint32_t b_lo = b_lo0 + (uint32_t)bq.slot * b_desc_step;
                     if (i < nfull) {
@@ -189,42 +228,44 @@ bitlinear_mma_prefill_kernel(const __grid_constant__ CUtensorMap q_map, BitLinea
                             "add.u32 %0, %0, 8;\n\t"
                             "tcgen05.mma.cta_group::1.kind::i8 [%2], [%0], d3, %5, 1;\n\t}"
                             : "+r"(a_addr), "+r"(b_lo)
-                            : "r"(tmem_base), "r"(b_hi), "r"(accum), "r"(p.idesc)
+                            : "r"(d_addr), "r"(b_hi), "r"(accum), "r"(p.idesc)
                             : "memory");
                     } else {
                         const uint64_t bd = ((uint64_t)b_hi << 32) | b_lo;
-                        mma_i8_ts(tmem_base, a_addr, bd, p.idesc, accum);
-                        mma_i8_ts(tmem_base, a_addr + 8, bd + 2, p.idesc, 1u);
+                        mma_i8_ts(d_addr, a_addr, bd, p.idesc, accum);
+                        mma_i8_ts(d_addr, a_addr + 8, bd + 2, p.idesc, 1u);
                     }
                     accum = 1;
-                    tc_commit(&bars[PB_A_EMPTY + aq.slot]);   // frees the A stage when these MMAs retire
-                    tc_commit(&bars[PB_B_EMPTY + bq.slot]);
+                    tc_commit(&bars[C::A_EMPTY + aq.slot]);   // frees the A stage (and the activation stage) when these MMAs retire
+                    if (!C::MERGED) tc_commit(&bars[C::B_EMPTY + bq.slot]);
                 }
-                if (live) tc_commit(&bars[PB_ACC_FULL]);
+                if (live) tc_commit(&bars[C::ACC_FULL + ab]);
+                if (it >= 1 && it < 5) trace_mark(trace, 3 + (it - 1) * 3);
+                
             }
         }
-    } else if (warp < PF_UNPACK_WARPS) {
+    } else if (warp < C::UNPACK_WARPS) {
         // ------------------------------------------------------------ unpack: lane <-> TMEM lane <-> weight row
         const int qd = warp & 3, gp = warp >> 2;
         const int row = qd * 32 + lane;
         const uint32_t lane_addr = (uint32_t)(qd * 32) << 16;
-        PfRing w{0, 0, PF_SW}, aq{0, 0, PF_SA};
-        if (gp) { w.next(); aq.next(); }
+        PfRing w{0, 0, C::SW}, aq{0, 0, C::SA};
+        for (int k = 0; k < gp; ++k) { w.next(); aq.next(); }
         int sg = gp;            // next global stage (counted across work items) this group expands
         int tile_base = 0;      // global index of the current work item's first stage
         bool ok = true;
         for (int wk = first; wk < p.n_work && ok; wk += step, tile_base += S) {
-            for (; sg < tile_base + S; sg += 2) {
+            for (; sg < tile_base + S; sg += C::GROUPS) {
                 const int i = sg - tile_base;
-                ok = __all_sync(0xffffffffu, mbar_wait(&bars[PB_W_FULL + w.slot], w.ph, abort_flag));   // warp-uniform
+                ok = __all_sync(0xffffffffu, mbar_wait(&bars[C::W_FULL + w.slot], w.ph, abort_flag));   // warp-uniform
                 if (!ok) break;
                 const int nch = min(2, p.KC - i * 2);
-                const uint8_t* wsrc = w_ring + w.slot * PF_W_STAGE + row * 16;
+                const uint8_t* wsrc = w_ring + w.slot * C::W_STAGE + row * 16;
                 uint4 wv[2];
                 wv[0] = *reinterpret_cast<const uint4*>(wsrc);
                 wv[1] = nch > 1 ? *reinterpret_cast<const uint4*>(wsrc + MMF_TILE_ROWS * 16) : wv[0];
-                mbar_arrive(&bars[PB_W_EMPTY + w.slot]);          // the packed bytes are in registers now
-                ok = __all_sync(0xffffffffu, mbar_wait(&bars[PB_A_EMPTY + aq.slot], aq.ph ^ 1, abort_flag));
+                mbar_arrive(&bars[C::W_EMPTY + w.slot]);          // the packed bytes are in registers now
+                ok = __all_sync(0xffffffffu, mbar_wait(&bars[C::A_EMPTY + aq.slot], aq.ph ^ 1, abort_flag));
                 if (!ok) break;   // uniform per warp: the .sync.aligned tcgen05 ops below need the whole warp
                 tc_fence_after();
 #pragma unroll
@@ -241,55 +282,85 @@ bitlinear_mma_prefill_kernel(const __grid_constant__ CUtensorMap q_map, BitLinea
                 }
                 tmem_wait_st();
                 tc_fence_before();
-                mbar_arrive(&bars[PB_A_FULL + aq.slot]);
-                w.next(); w.next();
-                aq.next(); aq.next();
+                mbar_arrive(&bars[C::A_FULL + aq.slot]);
+#pragma unroll
+                for (int k = 0; k < C::GROUPS; ++k) { w.next(); aq.next(); }
             }
+            
         }
     } else {
         // ------------------------------------------------------------ epilogue: TMEM -> registers -> global memory
-        const int ew = warp - PF_UNPACK_WARPS;
+        const int ew = warp - C::UNPACK_WARPS;
         const int lq = ew & 3, hf = ew >> 2;
         const uint32_t lane_addr = (uint32_t)(lq * 32) << 16;
-        const int col0 = hf * (PF_NT / 2);
-        const int eidx = ew * 32 + lane;              // 0..255: the token column whose constants this thread stages
+        const int col0 = hf * (C::NT / 2);
+        const int eidx = ew * 32 + lane;              // the token column (< NT) whose constants this thread stages
+        uint16_t* ostage = reinterpret_cast<uint16_t*>(w_ring + C::SW * C::W_STAGE);   // [NT][128] output tile (STAGE_OUT)
+        const bool staged = C::STAGE_OUT && p.tma_out;
+        const int nl = lq * 32 + lane;                // weight row inside the tile
         pdl_wait();                                   // dq / rowsum come from the preceding kernel
         bool ok = true;
         int it = 0;
         for (int wk = first; wk < p.n_work && ok; wk += step, ++it) {
             const int tile = wk % p.n_tiles, mt = wk / p.n_tiles;
             const int g = tile / p.group_tiles;
-            const int m0 = mt * PF_NT;
+            const int m0 = mt * C::NT;
             float* sc = s_scale[it & 1];
             int* rs = s_rs[it & 1];
-            {
+            if (eidx < C::NT) {
                 const int m = m0 + eidx;
                 const bool in = m < a.M;
                 sc[eidx] = in ? __fmul_rn(a.dq[(int64_t)g * a.M + m], a.w_scale[g]) : 0.0f;
                 rs[eidx] = in ? a.rowsum[(int64_t)g * a.M + m] : 0;
             }
-            asm volatile("bar.sync 1, %0;" ::"n"(PF_EPI_WARPS * 32) : "memory");   // the 8 epilogue warps only
-            ok = __all_sync(0xffffffffu, mbar_wait(&bars[PB_ACC_FULL], (uint32_t)(it & 1), abort_flag));
+            // the TMA store of the previous work item must have read the output tile before it is overwritten
+            if (staged && ew == 0 && lane == 0) bulk_wait_read<0>();
+            asm volatile("bar.sync 1, %0;" ::"n"(C::EPI_WARPS * 32) : "memory");   // the 8 epilogue warps only
+            const int ab = C::NACC == 2 ? (it & 1) : 0;
+            ok = mbar_wait_warp<true>(&bars[C::ACC_FULL + ab], (uint32_t)((it / C::NACC) & 1), abort_flag);
             if (!ok) break;
             tc_fence_after();
+            if (ew == 0 && it < 4) trace_mark(trace, 13 + it * 3);
             const int n = tile * MMF_TILE_ROWS + lq * 32 + lane;
             const bool n_ok = n < a.N;
-            const int mvalid = min(PF_NT / 2, a.M - m0 - col0);    // valid token columns in this warp's half (may be <= 0)
+            const int mvalid = min(C::NT / 2, a.M - m0 - col0);    // valid token columns in this warp's half (may be <= 0)
             uint32_t v[2][16];
-            tmem_ld16(tmem_base + lane_addr + col0, v[0]);
+            const uint32_t acc_addr = tmem_base + (uint32_t)ab * C::NT + lane_addr + col0;
+            tmem_ld16(acc_addr, v[0]);
 #pragma unroll
-            for (int c = 0; c < PF_NT / 32; ++c) {
+            for (int c = 0; c < C::NT / 32; ++c) {
                 tmem_wait_ld();
-                if (c + 1 < PF_NT / 32) {
-                    tmem_ld16(tmem_base + lane_addr + col0 + (c + 1) * 16, v[(c + 1) & 1]);
+                if (c + 1 < C::NT / 32) {
+                    tmem_ld16(acc_addr + (c + 1) * 16, v[(c + 1) & 1]);
                 } else {
                     // the whole accumulator half is in registers: hand it back to the MMA warp
                     tc_fence_before();
                     __syncwarp();
-                    if (lane == 0) mbar_arrive(&bars[PB_ACC_EMPTY]);
+                    if (lane == 0) mbar_arrive(&bars[C::ACC_EMPTY + ab]);
+                    if (ew == 0 && it < 4) trace_mark(trace, 14 + it * 3);
                 }
                 const int ncols = mvalid - c * 16;
-                if (n_ok && ncols > 0) {
+                if (staged) {
+                    // columns past M carry zero constants and rows past N garbage: the TMA store clips both
+                    const int cc = col0 + c * 16;
+                    uint16_t* po = ostage + cc * MMF_TILE_ROWS + nl;
+#pragma unroll
+                    for (int j4 = 0; j4 < 4; ++j4) {
+                        const int4 r4 = *reinterpret_cast<const int4*>(rs + cc + j4 * 4);
+                        const float4 s4 = *reinterpret_cast<const float4*>(sc + cc + j4 * 4);
+                        const int rr[4] = {r4.x, r4.y, r4.z, r4.w};
+                        const float ss[4] = {s4.x, s4.y, s4.z, s4.w};
+#pragma unroll
+                        for (int j = 0; j < 4; ++j) {
+                            const float f = __fmul_rn((float)((int32_t)v[c & 1][j4 * 4 + j] - rr[j]), ss[j]);
+                            po[(j4 * 4 + j) * MMF_TILE_ROWS] =
+                                a.out_dtype == MMF_BF16 ? __bfloat16_as_ushort(__float2bfloat16_rn(f)) : __half_as_ushort(__float2half_rn(f));
+                        }
+                    }
+                    if (a.acc_out && n_ok)
+                        for (int j = 0; j < 16 && j < ncols; ++j)
+                            a.acc_out[(int64_t)(m0 + cc + j) * a.N + n] = (int32_t)v[c & 1][j] - rs[cc + j];
+                } else if (n_ok && ncols > 0) {
                     const int cc = col0 + c * 16;
                     if (a.acc_out) {
                         for (int j = 0; j < 16 && j < ncols; ++j)
@@ -300,7 +371,17 @@ bitlinear_mma_prefill_kernel(const __grid_constant__ CUtensorMap q_map, BitLinea
                     else pf_store_chunk<float>(a, v[c & 1], rs + cc, sc + cc, m0 + cc, n, ncols);
                 }
             }
+            if (ew == 0 && it < 4) trace_mark(trace, 15 + it * 3);
+            if (staged) {
+                fence_async_smem();
+                asm volatile("bar.sync 1, %0;" ::"n"(C::EPI_WARPS * 32) : "memory");
+                if (ew == 0 && lane == 0) {
+                    tma_store_2d(&out_map, ostage, tile * MMF_TILE_ROWS, m0);
+                    bulk_commit();
+                }
+            }
         }
+        if (staged && ew == 0 && lane == 0) bulk_wait_all();   // shared memory must outlive the last store
     }
 
     // teardown: everyone meets, TMEM goes back; on the error path give copies in flight time to land first
@@ -310,51 +391,93 @@ bitlinear_mma_prefill_kernel(const __grid_constant__ CUtensorMap q_map, BitLinea
     }
     tc_fence_before();
     __syncthreads();
-    if (warp == PF_WARP_MMA) tmem_dealloc(tmem_base, 512u);
+    if (warp == C::WARP_MMA) tmem_dealloc(tmem_base, 512u);
 }
 
-}  // namespace
-
-// Launch the persistent kernel (large M).  Same argument contract as bitlinear_mma_launch.
-int bitlinear_mma_prefill_launch(const BitLinearArgs& a, cudaStream_t st) {
+template <typename C>
+int pf_launch(const BitLinearArgs& a, cudaStream_t st) {
     PfParams p;
     p.KC = a.K / MMF_TILE_K;
     p.n_tiles = (a.N + MMF_TILE_ROWS - 1) / MMF_TILE_ROWS;
     p.group_tiles = p.n_tiles / a.groups;
-    p.m_tiles = (a.M + PF_NT - 1) / PF_NT;
+    p.m_tiles = (a.M + C::NT - 1) / C::NT;
     const int64_t n_work = (int64_t)p.n_tiles * p.m_tiles;
     MMF_REQUIRE(n_work < (1ll << 31), MMF_ERR_BAD_SHAPE, "mmf_bitlinear(mma): problem too large");
     p.n_work = (int)n_work;
-    // instruction descriptor: D=S32, A=S8 (TMEM), B=S8 (smem, K-major), M=128, N=256
-    p.idesc = (2u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(PF_NT >> 3) << 17) | ((uint32_t)(128 >> 4) << 24);
+    // instruction descriptor: D=S32, A=S8 (TMEM), B=S8 (smem, K-major), M=128, N=NT
+    p.idesc = (2u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(C::NT >> 3) << 17) | ((uint32_t)(128 >> 4) << 24);
 
     MmfEncodeTiledFn encode = mmf_encode_tiled();
     MMF_REQUIRE(encode != nullptr, MMF_ERR_CUDA, "mmf_bitlinear(mma): cuTensorMapEncodeTiled is not available from the driver");
     CUtensorMap q_map;
     const cuuint64_t gdim[2] = {(cuuint64_t)a.K, (cuuint64_t)a.groups * (cuuint64_t)a.M};
     const cuuint64_t gstride[1] = {(cuuint64_t)a.K};
-    const cuuint32_t box[2] = {128u, (cuuint32_t)PF_NT};
+    const cuuint32_t box[2] = {128u, (cuuint32_t)C::NT};
     const cuuint32_t estr[2] = {1u, 1u};
     const CUresult cr = encode(&q_map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<int8_t*>(a.q), gdim, gstride, box, estr,
                                CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
                                CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     MMF_REQUIRE(cr == CUDA_SUCCESS, MMF_ERR_CUDA, "mmf_bitlinear(mma): cuTensorMapEncodeTiled failed (%d)", (int)cr);
 
+    // output map for the staged epilogue: [M][N] rows of ld_out elements, box = one [NT tokens x 128 rows] tile
+    CUtensorMap out_map = q_map;
+    p.tma_out = 0;
+    if (C::STAGE_OUT && a.out_dtype != MMF_F32 && mmf_aligned(a.out, 16) && (a.ld_out * 2) % 16 == 0) {
+        const cuuint64_t odim[2] = {(cuuint64_t)a.N, (cuuint64_t)a.M};
+        const cuuint64_t ostride[1] = {(cuuint64_t)a.ld_out * 2};
+        const cuuint32_t obox[2] = {(cuuint32_t)MMF_TILE_ROWS, (cuuint32_t)C::NT};
+        const CUresult cr2 = encode(&out_map, CU_TENSOR_MAP_DATA_TYPE_UINT16, 2, a.out, odim, ostride, obox, estr,
+                                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+        MMF_REQUIRE(cr2 == CUDA_SUCCESS, MMF_ERR_CUDA, "mmf_bitlinear(mma): cuTensorMapEncodeTiled (output) failed (%d)", (int)cr2);
+        p.tma_out = 1;
+    }
+
     int dev = 0, sms = 0;
     MMF_CUDA(cudaGetDevice(&dev));
     MMF_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
-    MMF_CUDA(cudaFuncSetAttribute(bitlinear_mma_prefill_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, PF_SMEM));
+    auto kernel = bitlinear_mma_prefill_kernel<C>;
+    MMF_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM));
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3((unsigned)(p.n_work < sms ? p.n_work : sms));
-    cfg.blockDim = dim3(PF_THREADS);
-    cfg.dynamicSmemBytes = PF_SMEM;
+    cfg.blockDim = dim3(C::THREADS);
+    cfg.dynamicSmemBytes = C::SMEM;
     cfg.stream = st;
     cudaLaunchAttribute attr[1];
     attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
-    MMF_CUDA(cudaLaunchKernelEx(&cfg, bitlinear_mma_prefill_kernel, q_map, a, p));
+    MMF_CUDA(cudaLaunchKernelEx(&cfg, kernel, q_map, out_map, a, p));
     MMF_LAUNCH_CHECK("bitlinear_mma_prefill_kernel");
     return MMF_OK;
+}
+
+// Compiled shapes.  1: long K — 256-token tile, one accumulator, rings six deep (the main loop is bound by the tensor
+// pipe and the exposed epilogue is amortised over many stages).  2: 192-token tile, two accumulators, rings four deep
+// (the epilogue of one work item overlaps the main loop of the next).  3: as 2 with the TMA-store epilogue.  4: as 1
+// with separate A / activation rings (two waits and two commits per stage), kept for comparison.
+using PfLongK = PfCfg<256, 2, 6, 6, 6, false, true, false>;
+using PfOverlap = PfCfg<192, 3, 4, 4, 8, true, true, false>;
+using PfOverlapTma = PfCfg<192, 3, 4, 4, 8, true, true, true>;
+using PfSeparate = PfCfg<256, 2, 8, 5, 8, false, false, false>;
+
+int pf_pick(const BitLinearArgs& a, int variant) { return variant ? variant : (a.K >= 4096 ? 1 : 2); }
+
+}  // namespace
+
+int bitlinear_mma_prefill_tile(const BitLinearArgs& a, int variant) {
+    const int v = pf_pick(a, variant);
+    return v == 2 || v == 3 ? 192 : 256;
+}
+
+// Launch the persistent kernel (large M).  Same argument contract as bitlinear_mma_launch; `variant` selects one
+// of the compiled shapes (0 = by problem shape).
+int bitlinear_mma_prefill_launch(const BitLinearArgs& a, cudaStream_t st, int variant) {
+    switch (pf_pick(a, variant)) {
+        case 1: return pf_launch<PfLongK>(a, st);
+        case 3: return pf_launch<PfOverlapTma>(a, st);
+        case 4: return pf_launch<PfSeparate>(a, st);
+        default: return pf_launch<PfOverlap>(a, st);
+    }
 }

@@ -8,13 +8,24 @@ namespace {
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
 
 __global__ void __launch_bounds__(128)
-int8_mma_peak_kernel(int n_tokens, int iters, int* status) {
+int8_mma_peak_kernel(int n_tokens, int iters, int* status, int commits) {
     extern __shared__ uint8_t smem_raw[];
     __shared__ __align__(8) uint64_t bar;
+    __shared__ __align__(8) uint64_t scratch_bar[2];   // target of the extra commits of the issue-cost experiment
     __shared__ uint32_t s_tmem;
     uint8_t* base = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-    for (int i = threadIdx.x; i < (n_tokens * 128) / 4; i += blockDim.x) reinterpret_cast<uint32_t*>(base)[i] = 0x01010101u;
-    if (threadIdx.x == 0) asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(smem_u32(&bar)) : "memory");
+    // pseudo-random operand bytes: constant operands toggle few wires and let the GPU hold a clock that no real
+    // contraction reaches under the power cap
+    for (int i = threadIdx.x; i < (n_tokens * 128) / 4; i += blockDim.x) {
+        uint32_t h = (uint32_t)i * 2654435761u + blockIdx.x * 40503u;
+        h ^= h >> 15; h *= 2246822519u; h ^= h >> 13;
+        reinterpret_cast<uint32_t*>(base)[i] = h;
+    }
+    if (threadIdx.x == 0) {
+        asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(smem_u32(&bar)) : "memory");
+        asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(smem_u32(&scratch_bar[0])) : "memory");
+        asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(smem_u32(&scratch_bar[1])) : "memory");
+    }
     if (threadIdx.x < 32) {
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], 512;" ::"r"(smem_u32(&s_tmem)) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
@@ -24,6 +35,27 @@ int8_mma_peak_kernel(int n_tokens, int iters, int* status) {
     __syncthreads();
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     const uint32_t tmem = s_tmem;
+    {   // A operand: 64 columns (8 K-steps of 32 bytes) of pseudo-random int8 for each of the 128 lanes
+        const uint32_t lane_addr = (uint32_t)((threadIdx.x >> 5) * 32) << 16;
+        for (int c = 0; c < 4; ++c) {
+            uint32_t r[16];
+#pragma unroll
+            for (int j = 0; j < 16; ++j) {
+                uint32_t h = (threadIdx.x * 64u + c * 16u + j) * 2654435761u + blockIdx.x * 7919u;
+                h ^= h >> 15; h *= 2246822519u; h ^= h >> 13;
+                r[j] = h;
+            }
+            asm volatile(
+                "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16};"
+                ::"r"(tmem + lane_addr + 256 + c * 16), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]),
+                "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15])
+                : "memory");
+        }
+        asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+        asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+        __syncthreads();
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    }
     if (threadIdx.x == 0) {
         // shared-memory descriptor of a K-major, 128-byte-swizzled tile; instruction descriptor S32 += S8 x S8
         uint64_t bd = 0;
@@ -42,6 +74,12 @@ int8_mma_peak_kernel(int n_tokens, int iters, int* status) {
                 "tcgen05.mma.cta_group::1.kind::i8 [%0], [%1], %2, %3, {%5, %5, %5, %5}, p;\n\t}"
                 ::"r"(tmem), "r"(a_addr), "l"(b), "r"(idesc), "r"(i > 0 ? 1u : 0u), "r"(0u)
                 : "memory");
+            // issue-cost experiment: `commits` tcgen05.commit instructions after every fourth MMA, as a pipelined
+            // kernel issues them to release its operand stages
+            if ((i & 3) == 3)
+                for (int c = 0; c < commits; ++c)
+                    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];"
+                                 ::"r"(smem_u32(&scratch_bar[c & 1])) : "memory");
         }
         asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(&bar)) : "memory");
         const long long t0 = clock64();
@@ -59,10 +97,12 @@ int8_mma_peak_kernel(int n_tokens, int iters, int* status) {
 
 }  // namespace
 
+int g_probe_commits = 0;   // mmf_tuning(MMF_TUNE_PROBE_COMMITS, n)
+
 extern "C" int mmf_int8_mma_peak(int n_tokens, int iters, int* status_dev, double* tops_host) {
     MMF_REQUIRE(status_dev && tops_host, MMF_ERR_BAD_ARG, "mmf_int8_mma_peak: null pointer");
-    MMF_REQUIRE(n_tokens >= 16 && n_tokens <= 256 && n_tokens % 16 == 0 && iters > 0 && iters <= (1 << 22), MMF_ERR_BAD_SHAPE,
-                "mmf_int8_mma_peak: n_tokens must be a multiple of 16 in [16,256], iters in (0, 4M]");
+    MMF_REQUIRE(n_tokens >= 16 && n_tokens <= 256 && n_tokens % 16 == 0 && iters > 0 && iters <= (1 << 25), MMF_ERR_BAD_SHAPE,
+                "mmf_int8_mma_peak: n_tokens must be a multiple of 16 in [16,256], iters in (0, 32M]");
     int dev = 0, sms = 0;
     MMF_CUDA(cudaGetDevice(&dev));
     MMF_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
@@ -73,9 +113,9 @@ extern "C" int mmf_int8_mma_peak(int n_tokens, int iters, int* status_dev, doubl
     MMF_CUDA(cudaEventCreate(&e1));
     MMF_CUDA(cudaMemset(status_dev, 0, sizeof(int)));
     // 150 KB of shared memory per CTA keeps it at one CTA per SM (each allocates all of tensor memory)
-    int8_mma_peak_kernel<<<sms, 128, 150 * 1024>>>(n_tokens, 64, status_dev);     // warm-up
+    int8_mma_peak_kernel<<<sms, 128, 150 * 1024>>>(n_tokens, 64, status_dev, g_probe_commits);     // warm-up
     MMF_CUDA(cudaEventRecord(e0));
-    int8_mma_peak_kernel<<<sms, 128, 150 * 1024>>>(n_tokens, iters, status_dev);
+    int8_mma_peak_kernel<<<sms, 128, 150 * 1024>>>(n_tokens, iters, status_dev, g_probe_commits);
     MMF_CUDA(cudaEventRecord(e1));
     MMF_CUDA(cudaEventSynchronize(e1));
     MMF_LAUNCH_CHECK("int8_mma_peak_kernel");

@@ -55,6 +55,43 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volati
     }
 }
 
+// Wait of a role that is not on the critical path (a producer ahead of its consumers, unpack warps with a full
+// ring): polls with a short sleep in between so that it does not take issue slots from the warps that are.
+__device__ __forceinline__ bool mbar_wait_relaxed(uint64_t* bar, uint32_t parity, volatile int* abort_flag) {
+#pragma unroll 1
+    for (int i = 0; i < 4; ++i)
+        if (mbar_try(bar, parity)) return true;
+    const long long t0 = clock64();
+#pragma unroll 1
+    for (;;) {
+#pragma unroll 1
+        for (int i = 0; i < 32; ++i) {
+            if (mbar_try(bar, parity)) return true;
+            __nanosleep(40);
+        }
+        if (*abort_flag) return false;
+        if (clock64() - t0 > WAIT_LIMIT_CYCLES) {
+            *abort_flag = 1;
+            return false;
+        }
+    }
+}
+// Whole-warp wait: lane 0 polls (with or without sleeping between polls), then every lane observes the completed phase itself (its own acquire).
+template <bool RELAXED>
+__device__ __forceinline__ bool mbar_wait_warp(uint64_t* bar, uint32_t parity, volatile int* abort_flag) {
+    int ok = 1;
+    if ((threadIdx.x & 31) == 0)
+        ok = (RELAXED ? mbar_wait_relaxed(bar, parity, abort_flag) : mbar_wait(bar, parity, abort_flag)) ? 1 : 0;
+    ok = __shfl_sync(0xffffffffu, ok, 0);
+    if (ok) {
+        int tries = 0;
+        while (!mbar_try(bar, parity) && ++tries < 100000) {}
+        ok = __all_sync(0xffffffffu, tries < 100000) ? 1 : 0;
+        if (!ok) *abort_flag = 1;
+    }
+    return ok != 0;
+}
+
 __device__ __forceinline__ bool elect_one() {
     uint32_t pred;
     asm volatile(
@@ -76,6 +113,21 @@ __device__ __forceinline__ void bulk_load_1d(void* dst, const void* src, uint32_
                  ::"r"(smem_u32(dst)), "l"(src), "r"(bytes), "r"(smem_u32(bar))
                  : "memory");
 }
+
+// shared memory -> global memory (tiled TMA store); completion is tracked per thread in bulk groups
+__device__ __forceinline__ void tma_store_2d(const CUtensorMap* map, const void* src, int x, int y) {
+    asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];"
+                 ::"l"(map), "r"(smem_u32(src)), "r"(x), "r"(y)
+                 : "memory");
+}
+__device__ __forceinline__ void bulk_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+// all but the newest N bulk groups of this thread have finished READING their shared-memory source
+template <int N> __device__ __forceinline__ void bulk_wait_read() {
+    asm volatile("cp.async.bulk.wait_group.read %0;" ::"n"(N) : "memory");
+}
+__device__ __forceinline__ void bulk_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
+// make generic-proxy writes to shared memory visible to the async proxy (TMA)
+__device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
 
 __device__ __forceinline__ void tmem_alloc(uint32_t* slot, uint32_t cols) {
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(slot)), "r"(cols) : "memory");

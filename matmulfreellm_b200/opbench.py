@@ -93,8 +93,12 @@ def rowwise(a):
 
 
 def int8peak(a):
-    print(json.dumps({"op": "int8_mma_peak", "tops_n256": K.int8_mma_peak_tops(256, 200000),
-                      "tops_n128": K.int8_mma_peak_tops(128, 200000), "tops_n32": K.int8_mma_peak_tops(32, 200000)}))
+    """Bare tcgen05.mma kind::i8 issue loop with pseudo-random operands: a burst of about 7 ms (the GPU holds its
+    maximum clock) and a loop of about 3 s (the clock settles under the power cap)."""
+    print(json.dumps({"op": "int8_mma_peak", "tops_n256_burst": K.int8_mma_peak_tops(256, 200000),
+                      "tops_n256_sustained": K.int8_mma_peak_tops(256, 24000000),
+                      "tops_n192_burst": K.int8_mma_peak_tops(192, 200000), "tops_n128_burst": K.int8_mma_peak_tops(128, 200000),
+                      "tops_n32_burst": K.int8_mma_peak_tops(32, 200000)}))
 
 
 def main():

@@ -186,24 +186,29 @@ def test_bitlinear_matches_reference_output(K, golden):
 
 
 def test_bitlinear_persistent_kernel(K):
-    """The persistent large-M tensor-core kernel (256-token tiles, work list per CTA), forced on for shapes with a
-    ragged last token tile, a ragged last weight tile and a trailing 64-wide K stage: bit-exact accumulators and
-    outputs in all three dtypes against the CUDA-core kernel; then a grouped (3 x norm weight) call."""
+    """The persistent large-M tensor-core kernel, forced on (knob 7 = 1: shape chosen by the library; 11..14: each
+    compiled shape — 256-token tile with one accumulator, 192-token tile with two accumulators, the same with the
+    TMA-store epilogue, separate rings) for problems with a ragged last token tile, a ragged last weight tile and a
+    trailing 64-wide K stage: bit-exact accumulators and outputs in all three dtypes against the CUDA-core kernel;
+    then a grouped (3 x norm weight) call."""
     from matmulfreellm_b200 import _lib
     lib = _lib.load()
     try:
-        for (M, Kd, N) in [(300, 704, 384), (700, 2048, 512), (1024, 2560, 200), (129, 256, 128)]:
+        for (M, Kd, N) in [(300, 704, 384), (700, 2048, 512), (1024, 2560, 200), (129, 256, 128), (520, 4096, 256)]:
             x, w, _ = O.bitlinear_case(M, Kd, N, seed=M)
             pw = K.pack_weight(dev(w))
             q, dq, rs = K.act_quant(dev(x), None, 1e-6)
             lib.mmf_tuning(7, 2)
             ref, acc_ref = K.bitlinear(q, dq, rs, pw, torch.float32, kernel=K.KERNEL_GEMV, return_acc=True)
-            lib.mmf_tuning(7, 1)
-            out, acc = K.bitlinear(q, dq, rs, pw, torch.float32, kernel=K.KERNEL_MMA, return_acc=True)
-            K.check_status()
-            assert torch.equal(acc, acc_ref) and torch.equal(out, ref), (M, Kd, N)
-            for dt in (torch.bfloat16, torch.float16):
-                assert torch.equal(K.bitlinear(q, dq, rs, pw, dt, kernel=K.KERNEL_MMA), ref.to(dt)), (M, Kd, N, dt)
+            for knob in (1, 11, 12, 13, 14):
+                lib.mmf_tuning(7, knob)
+                out, acc = K.bitlinear(q, dq, rs, pw, torch.float32, kernel=K.KERNEL_MMA, return_acc=True)
+                K.check_status()
+                assert torch.equal(acc, acc_ref) and torch.equal(out, ref), (M, Kd, N, knob)
+                for dt in (torch.bfloat16, torch.float16):
+                    assert torch.equal(K.bitlinear(q, dq, rs, pw, dt, kernel=K.KERNEL_MMA), ref.to(dt)), (M, Kd, N, knob, dt)
+                    got, acc2 = K.bitlinear(q, dq, rs, pw, dt, kernel=K.KERNEL_MMA, return_acc=True)
+                    assert torch.equal(got, ref.to(dt)) and torch.equal(acc2, acc_ref), (M, Kd, N, knob, dt)
         M, Kdim, N = 260, 256, 256
         x, _, _ = O.bitlinear_case(M, Kdim, N, seed=3)
         g = torch.Generator().manual_seed(11)
@@ -212,12 +217,15 @@ def test_bitlinear_persistent_kernel(K):
         pw = K.stack_packed([K.pack_weight(dev(w)) for w in ws])
         qs = [K.act_quant(dev(x), dev(nw), 1e-6) for nw in nws]
         q = torch.cat([t[0] for t in qs]); dq = torch.cat([t[1] for t in qs]); rs = torch.cat([t[2] for t in qs])
-        out = K.bitlinear(q, dq, rs, pw, torch.float32, kernel=K.KERNEL_MMA)
-        K.check_status()
-        for gi in range(3):
-            codes, mean = O.ternary_codes(ws[gi])
-            ref = O.bitlinear_int(x, nws[gi], codes, mean, 1e-6)[0]
-            assert torch.equal(out[:, gi * N:(gi + 1) * N].cpu(), ref)
+        for knob in (11, 12, 13):
+            lib.mmf_tuning(7, knob)
+            for dt in (torch.float32, torch.bfloat16):
+                out = K.bitlinear(q, dq, rs, pw, dt, kernel=K.KERNEL_MMA)
+                K.check_status()
+                for gi in range(3):
+                    codes, mean = O.ternary_codes(ws[gi])
+                    ref = O.bitlinear_int(x, nws[gi], codes, mean, 1e-6)[0]
+                    assert torch.equal(out[:, gi * N:(gi + 1) * N].cpu(), ref.to(dt)), (knob, dt, gi)
     finally:
         lib.mmf_tuning(7, 0)
 
