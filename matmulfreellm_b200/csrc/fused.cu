@@ -27,7 +27,7 @@ constexpr int FW = FT / 32;    // warps
 constexpr int PER = 32;        // row values a thread can hold -> D <= FT * PER = 8192
 constexpr int MAX_D = FT * PER;
 
-// One-sync block reductions: warp shuffle, lane 0 parks the partial in a slot that is used once per kernel,
+// One-sync block reductions: warp shuffle, lane 0 parks the partial in a slot that is used once per row,
 // one barrier, then every thread folds the FW partials in a fixed order.
 template <int K>
 __device__ __forceinline__ void block_sum_d(double (&v)[K], double* slot /* K*FW */) {
@@ -84,7 +84,7 @@ __device__ __forceinline__ void block_sum_i(int (&v)[K], int* slot) {
     }
 }
 
-struct RedScratch {       // each member is written once per kernel -> no barrier needed to recycle it
+struct RedScratch {       // each member is written once per row and at least two barriers lie between two uses -> no extra barrier
     double d0[3 * FW], d1[3 * FW];
     float f0[3 * FW];
     int i0[3 * FW];
@@ -178,46 +178,48 @@ prenorm_quant_kernel(PrenormArgs a) {
     pdl_wait();
     __syncthreads();
 
-    const int64_t m = blockIdx.x;
-    const T* xr = reinterpret_cast<const T*>(a.x) + m * a.ld_x;
-    const T* rr = a.res ? reinterpret_cast<const T*>(a.res) + m * a.ld_res : nullptr;
-    T* ro = a.res_out ? reinterpret_cast<T*>(a.res_out) + m * (int64_t)D : nullptr;
-    float v[PER];
-    double ss[1] = {0.0};
-    ROW_FOREACH(V, D, it, c) {
-        float x[V];
-        load16<T>(xr + c, x);
-        if (rr) {
-            float r[V];
-            load16<T>(rr + c, r);
-#pragma unroll
-            for (int i = 0; i < V; ++i) x[i] = __fadd_rn(x[i], r[i]);
+    // a CTA takes rows blockIdx.x, blockIdx.x + gridDim.x, ...: with many rows the staged norm weights are reused
+    for (int64_t m = blockIdx.x; m < a.M; m += gridDim.x) {
+        const T* xr = reinterpret_cast<const T*>(a.x) + m * a.ld_x;
+        const T* rr = a.res ? reinterpret_cast<const T*>(a.res) + m * a.ld_res : nullptr;
+        T* ro = a.res_out ? reinterpret_cast<T*>(a.res_out) + m * (int64_t)D : nullptr;
+        float v[PER];
+        double ss[1] = {0.0};
+        ROW_FOREACH(V, D, it, c) {
+            float x[V];
+            load16<T>(xr + c, x);
+            if (rr) {
+                float r[V];
+                load16<T>(rr + c, r);
+    #pragma unroll
+                for (int i = 0; i < V; ++i) x[i] = __fadd_rn(x[i], r[i]);
+            }
+            if (ro) store16<T>(ro + c, x);
+    #pragma unroll
+            for (int i = 0; i < V; ++i) {
+                if (a.round_sum_first) x[i] = round_to<T>(x[i]);
+                v[it * V + i] = x[i];
+                ss[0] += (double)x[i] * (double)x[i];
+            }
         }
-        if (ro) store16<T>(ro + c, x);
-#pragma unroll
-        for (int i = 0; i < V; ++i) {
-            if (a.round_sum_first) x[i] = round_to<T>(x[i]);
-            v[it * V + i] = x[i];
-            ss[0] += (double)x[i] * (double)x[i];
+        block_sum_d<1>(ss, red.d0);
+        const float rstd1 = rstd_from_sumsq(ss[0], D, a.eps_norm);
+        T* yo = a.y_out ? reinterpret_cast<T*>(a.y_out) + m * (int64_t)D : nullptr;
+        double ss2 = 0.0;
+        ROW_FOREACH(V, D, it, c) {
+            float o[V];
+    #pragma unroll
+            for (int i = 0; i < V; ++i) {
+                const float t = round_to<T>(__fmul_rn(__fmul_rn(v[it * V + i], rstd1), sw[c + i]));
+                o[i] = t;
+                v[it * V + i] = t;
+                ss2 += (double)t * (double)t;
+            }
+            if (yo) store16<T>(yo + c, o);
         }
+        if (a.G == 3) bitlinear_prologue<V, 3>(v, D, ss2, a.eps_bl, sw + D, a.q, a.dq, a.rowsum, a.M, m, red);
+        else if (a.G == 1) bitlinear_prologue<V, 1>(v, D, ss2, a.eps_bl, sw + D, a.q, a.dq, a.rowsum, a.M, m, red);
     }
-    block_sum_d<1>(ss, red.d0);
-    const float rstd1 = rstd_from_sumsq(ss[0], D, a.eps_norm);
-    T* yo = a.y_out ? reinterpret_cast<T*>(a.y_out) + m * (int64_t)D : nullptr;
-    double ss2 = 0.0;
-    ROW_FOREACH(V, D, it, c) {
-        float o[V];
-#pragma unroll
-        for (int i = 0; i < V; ++i) {
-            const float t = round_to<T>(__fmul_rn(__fmul_rn(v[it * V + i], rstd1), sw[c + i]));
-            o[i] = t;
-            v[it * V + i] = t;
-            ss2 += (double)t * (double)t;
-        }
-        if (yo) store16<T>(yo + c, o);
-    }
-    if (a.G == 3) bitlinear_prologue<V, 3>(v, D, ss2, a.eps_bl, sw + D, a.q, a.dq, a.rowsum, a.M, m, red);
-    else if (a.G == 1) bitlinear_prologue<V, 1>(v, D, ss2, a.eps_bl, sw + D, a.q, a.dq, a.rowsum, a.M, m, red);
 }
 
 // y = round_T( ((g*rstd)*w) * o * sigmoid(o) ), then BitLinear prologue.  `ov` holds the gate row o in registers.
@@ -256,23 +258,25 @@ gatenorm_quant_kernel(const T* __restrict__ gx, int64_t ld_g, const T* __restric
     stage_weights(sw + D, nw, D);
     pdl_wait();
     __syncthreads();
-    const int64_t m = blockIdx.x;
-    const T* gr = gx + m * ld_g;
-    const T* orow = o + m * ld_o;
-    float gv[PER], ov[PER];
-    double ss = 0.0;
-    ROW_FOREACH(V, D, it, c) {
-        float a[V], b[V];
-        load16<T>(gr + c, a);
-        load16<T>(orow + c, b);
-#pragma unroll
-        for (int i = 0; i < V; ++i) {
-            gv[it * V + i] = a[i];
-            ov[it * V + i] = b[i];
-            ss += (double)a[i] * (double)a[i];
+    // a CTA takes rows blockIdx.x, blockIdx.x + gridDim.x, ...: with many rows the staged norm weights are reused
+    for (int64_t m = blockIdx.x; m < M; m += gridDim.x) {
+        const T* gr = gx + m * ld_g;
+        const T* orow = o + m * ld_o;
+        float gv[PER], ov[PER];
+        double ss = 0.0;
+        ROW_FOREACH(V, D, it, c) {
+            float a[V], b[V];
+            load16<T>(gr + c, a);
+            load16<T>(orow + c, b);
+    #pragma unroll
+            for (int i = 0; i < V; ++i) {
+                gv[it * V + i] = a[i];
+                ov[it * V + i] = b[i];
+                ss += (double)a[i] * (double)a[i];
+            }
         }
+        gatenorm_tail<T, V>(gv, ov, ss, D, eps_g, eps_bl, sw, q, dq, rowsum, M, m, red);
     }
-    gatenorm_tail<T, V>(gv, ov, ss, D, eps_g, eps_bl, sw, q, dq, rowsum, M, m, red);
 }
 
 // Single-token step of the token mixer for row b (mmfreelm/layers/hgrn_bit.py:113-140 with T = 1):
@@ -344,23 +348,25 @@ swiglu_quant_kernel(const T* __restrict__ gate, const T* __restrict__ up, int64_
     stage_weights(sw, nw, D);
     pdl_wait();
     __syncthreads();
-    const int64_t m = blockIdx.x;
-    const T* gr = gate + m * ld;
-    const T* ur = up + m * ld;
-    float v[PER];
-    double ss = 0.0;
-    ROW_FOREACH(V, D, it, c) {
-        float gv[V], uv[V];
-        load16<T>(gr + c, gv);
-        load16<T>(ur + c, uv);
-#pragma unroll
-        for (int i = 0; i < V; ++i) {
-            const float t = round_to<T>(silu_mul(gv[i], uv[i]));
-            v[it * V + i] = t;
-            ss += (double)t * (double)t;
+    // a CTA takes rows blockIdx.x, blockIdx.x + gridDim.x, ...: with many rows the staged norm weights are reused
+    for (int64_t m = blockIdx.x; m < M; m += gridDim.x) {
+        const T* gr = gate + m * ld;
+        const T* ur = up + m * ld;
+        float v[PER];
+        double ss = 0.0;
+        ROW_FOREACH(V, D, it, c) {
+            float gv[V], uv[V];
+            load16<T>(gr + c, gv);
+            load16<T>(ur + c, uv);
+    #pragma unroll
+            for (int i = 0; i < V; ++i) {
+                const float t = round_to<T>(silu_mul(gv[i], uv[i]));
+                v[it * V + i] = t;
+                ss += (double)t * (double)t;
+            }
         }
+        bitlinear_prologue<V, 1>(v, D, ss, eps_bl, sw, q, dq, rowsum, M, m, red);
     }
-    bitlinear_prologue<V, 1>(v, D, ss, eps_bl, sw, q, dq, rowsum, M, m, red);
 }
 
 }  // namespace
@@ -372,6 +378,9 @@ swiglu_quant_kernel(const T* __restrict__ gate, const T* __restrict__ up, int64_
     MMF_REQUIRE(mmf_dtype_ok(dtype), MMF_ERR_BAD_ARG, name ": unknown dtype %d", dtype);                             \
     MMF_REQUIRE(M >= 0 && (D) > 0 && (D) <= MAX_D && (D) % 16 == 0, MMF_ERR_BAD_SHAPE,                               \
                 name ": need 0 < D <= 8192 and D %% 16 == 0 (D=%lld)", (long long)(D));
+
+// one CTA per row up to eight CTAs per SM; beyond that the CTAs loop over rows
+static inline unsigned row_grid(int64_t M) { return (unsigned)(M < 148 * 8 ? M : 148 * 8); }
 
 #define FUSED_SMEM_ATTR(kernel, smem) \
     if ((smem) > 48 * 1024) MMF_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)(smem)))
@@ -398,7 +407,7 @@ extern "C" int mmf_prenorm_quant(const void* x, int64_t ld_x, const void* residu
     const size_t smem = (size_t)(1 + groups) * D * sizeof(float);
     MMF_DISPATCH(dtype, T, {
         FUSED_SMEM_ATTR(prenorm_quant_kernel<T>, smem);
-        MMF_CUDA(mmf_launch_pdl(prenorm_quant_kernel<T>, dim3((unsigned)M), dim3(FT), smem, (cudaStream_t)stream, a));
+        MMF_CUDA(mmf_launch_pdl(prenorm_quant_kernel<T>, dim3(row_grid(M)), dim3(FT), smem, (cudaStream_t)stream, a));
     });
     MMF_LAUNCH_CHECK("prenorm_quant_kernel");
     return MMF_OK;
@@ -417,7 +426,7 @@ extern "C" int mmf_gatenorm_quant(const void* g, int64_t ld_g, const void* o, in
     const size_t smem = (size_t)2 * D * sizeof(float);
     MMF_DISPATCH(dtype, T, {
         FUSED_SMEM_ATTR(gatenorm_quant_kernel<T>, smem);
-        MMF_CUDA(mmf_launch_pdl(gatenorm_quant_kernel<T>, dim3((unsigned)M), dim3(FT), smem, (cudaStream_t)stream, (const T*)g, ld_g,
+        MMF_CUDA(mmf_launch_pdl(gatenorm_quant_kernel<T>, dim3(row_grid(M)), dim3(FT), smem, (cudaStream_t)stream, (const T*)g, ld_g,
                                 (const T*)o, ld_o, gnorm_w, eps_g, nw, eps_bl, q, dq, rowsum, M, (int)D));
     });
     MMF_LAUNCH_CHECK("gatenorm_quant_kernel");
@@ -456,7 +465,7 @@ extern "C" int mmf_swiglu_quant(const void* gate, const void* up, int64_t ld, in
     const size_t smem = (size_t)D * sizeof(float);
     MMF_DISPATCH(dtype, T, {
         FUSED_SMEM_ATTR(swiglu_quant_kernel<T>, smem);
-        MMF_CUDA(mmf_launch_pdl(swiglu_quant_kernel<T>, dim3((unsigned)M), dim3(FT), smem, (cudaStream_t)stream, (const T*)gate,
+        MMF_CUDA(mmf_launch_pdl(swiglu_quant_kernel<T>, dim3(row_grid(M)), dim3(FT), smem, (cudaStream_t)stream, (const T*)gate,
                                 (const T*)up, ld, nw, eps_bl, q, dq, rowsum, M, (int)D));
     });
     MMF_LAUNCH_CHECK("swiglu_quant_kernel");

@@ -4,6 +4,7 @@
     python -m matmulfreellm_b200.opbench hgrn --B 8 --T 2048 --D 2048 [--gate log|linear]
     python -m matmulfreellm_b200.opbench rowwise --M 4096 --D 2048
     python -m matmulfreellm_b200.opbench int8peak
+    python -m matmulfreellm_b200.opbench prefill --batch 16 --seq 2048 --layers 2
 
 Each prints one JSON line: device time per call (CUDA events, after 3 warm-ups) and the achieved GB/s of
 algorithmic bytes and/or TOP/s.  Inputs are seeded synthetic data; every repetition of `bitlinear` uses a
@@ -101,6 +102,30 @@ def int8peak(a):
                       "tops_n32_burst": K.int8_mma_peak_tops(32, 200000)}))
 
 
+def prefill(a):
+    """Prompt pass of a random-init HGRNBit with the 1.3B layer shapes (hidden 2048, intermediate 5632, vocab 32000) and
+    `--layers` blocks through the fused chain; last-position logits only."""
+    from .models import HGRNBitConfig, HGRNBitForCausalLM
+    from .ops.fusedbitnet import BitLinear
+    dev = torch.device("cuda")
+    cfg = HGRNBitConfig(vocab_size=32000, hidden_size=2048, num_hidden_layers=a.layers, intermediate_size=5632)
+    with torch.device(dev):
+        model = HGRNBitForCausalLM(cfg).eval()
+    g = torch.Generator(device=dev).manual_seed(1234)
+    with torch.no_grad():
+        for m in model.modules():
+            if isinstance(m, BitLinear):
+                m.weight.normal_(0.0, 0.02, generator=g)
+        model.model.embeddings.weight.normal_(0.0, 0.02, generator=g)
+    model.pack_weights()
+    model = model.to(torch.bfloat16)
+    ids = torch.randint(0, 32000, (a.batch, a.seq), device=dev, generator=g)
+    with torch.no_grad():
+        t = _time(lambda: model(input_ids=ids, use_cache=True, last_token_only=True), a.iters)
+    print(json.dumps({"op": "prefill", "batch": a.batch, "seq": a.seq, "layers": a.layers, "ms": t * 1e3,
+                      "tokens_per_s_per_layer_block": a.batch * a.seq / t * a.layers}))
+
+
 def main():
     ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
     sub = ap.add_subparsers(dest="op", required=True)
@@ -115,8 +140,11 @@ def main():
     r = sub.add_parser("rowwise")
     r.add_argument("--M", type=int, default=4096); r.add_argument("--D", type=int, default=2048); r.add_argument("--iters", type=int, default=10)
     sub.add_parser("int8peak")
+    pf = sub.add_parser("prefill")
+    pf.add_argument("--batch", type=int, default=16); pf.add_argument("--seq", type=int, default=2048)
+    pf.add_argument("--layers", type=int, default=2); pf.add_argument("--iters", type=int, default=2)
     a = ap.parse_args()
-    {"bitlinear": bitlinear, "hgrn": hgrn, "rowwise": rowwise, "int8peak": int8peak}[a.op](a)
+    {"bitlinear": bitlinear, "hgrn": hgrn, "rowwise": rowwise, "int8peak": int8peak, "prefill": prefill}[a.op](a)
 
 
 if __name__ == "__main__":
