@@ -88,6 +88,13 @@ template <> __device__ __forceinline__ __half from_f32<__half>(float v) { return
 // value of v after a round trip through T (models an intermediate tensor of dtype T)
 template <typename T> __device__ __forceinline__ float round_to(float v) { return to_f32(from_f32<T>(v)); }
 
+// int8 activation code clamp(rint(p), -128, 127) for |p| < 2^22 without conversion instructions: adding 1.5 * 2^23
+// leaves the round-to-nearest-even integer in the low mantissa bits of the sum (same result as rintf + cast)
+__device__ __forceinline__ int quant_code(float p) {
+    const int iv = __float_as_int(__fadd_rn(p, 12582912.0f)) - 0x4B400000;
+    return max(-128, min(127, iv));
+}
+
 // 16-byte vector of T: 4 floats or 8 halves
 template <typename T> struct Vec16 { static constexpr int N = 16 / sizeof(T); T v[N]; };
 

@@ -24,8 +24,10 @@ namespace {
 
 constexpr int FT = 256;        // threads per row CTA
 constexpr int FW = FT / 32;    // warps
-constexpr int PER = 32;        // row values a thread can hold -> D <= FT * PER = 8192
-constexpr int MAX_D = FT * PER;
+constexpr int MAX_PER = 32;    // most row values a thread can hold -> D <= FT * MAX_PER = 8192
+constexpr int MAX_D = FT * MAX_PER;
+// Kernels are compiled for P = 8, 16 and 32 row values per thread (D <= 2048, 4096, 8192): the row lives in
+// registers, so the smaller instantiations leave room for more resident CTAs.
 
 // One-sync block reductions: warp shuffle, lane 0 parks the partial in a slot that is used once per row,
 // one barrier, then every thread folds the FW partials in a fixed order.
@@ -99,14 +101,14 @@ __device__ __forceinline__ void stage_weights(float* dst, const float* src, int 
     }
 }
 
-// iterate over the 16-byte vectors of a row held as v[PER]: vector `it` of this thread starts at column c
+// iterate over the 16-byte vectors of a row held as v[P] (P: the enclosing template parameter): vector `it` of this thread starts at column c
 #define ROW_FOREACH(V, D, it, c) \
-    _Pragma("unroll") for (int it = 0, c = threadIdx.x * (V); it < PER / (V); ++it, c += FT * (V)) if (c < (D))
+    _Pragma("unroll") for (int it = 0, c = threadIdx.x * (V); it < P / (V); ++it, c += FT * (V)) if (c < (D))
 
 // BitLinear prologue on a register-resident row `v` (values already in T precision): shared sum of squares
 // `ss`, then per projection g: y = (v*rstd)*nw_g, absmax -> scale -> int8 codes, dq, rowsum.
-template <int V, int G>
-__device__ __forceinline__ void bitlinear_prologue(const float (&v)[PER], int D, double ss, float eps, const float* snw /* smem [G][D] */,
+template <int V, int G, int P>
+__device__ __forceinline__ void bitlinear_prologue(const float (&v)[P], int D, double ss, float eps, const float* snw /* smem [G][D] */,
                                                    int8_t* q, float* dq, int32_t* rowsum, int64_t M, int64_t m, RedScratch& red) {
     double s1[1] = {ss};
     block_sum_d<1>(s1, red.d1);
@@ -135,9 +137,7 @@ __device__ __forceinline__ void bitlinear_prologue(const float (&v)[PER], int D,
 #pragma unroll
             for (int i = 0; i < V; ++i) {
                 const float y = __fmul_rn(__fmul_rn(v[it * V + i], rstd), snw[g * D + c + i]);
-                float r = rintf(__fmul_rn(y, s));
-                r = fminf(fmaxf(r, -128.0f), 127.0f);
-                const int iv = (int)r;
+                const int iv = quant_code(__fmul_rn(y, s));
                 codes[i] = (int8_t)iv;
                 lsum[g] += iv;
             }
@@ -165,7 +165,7 @@ struct PrenormArgs {
     int round_sum_first;                   // 1: the reference added x+residual as a tensor op (rounded to T) before norm
 };
 
-template <typename T>
+template <typename T, int P>
 __global__ void __launch_bounds__(FT)
 prenorm_quant_kernel(PrenormArgs a) {
     extern __shared__ __align__(16) float sw[];   // [1 + G][D]: block norm weight, then the BitLinear norm weights
@@ -183,7 +183,7 @@ prenorm_quant_kernel(PrenormArgs a) {
         const T* xr = reinterpret_cast<const T*>(a.x) + m * a.ld_x;
         const T* rr = a.res ? reinterpret_cast<const T*>(a.res) + m * a.ld_res : nullptr;
         T* ro = a.res_out ? reinterpret_cast<T*>(a.res_out) + m * (int64_t)D : nullptr;
-        float v[PER];
+        float v[P];
         double ss[1] = {0.0};
         ROW_FOREACH(V, D, it, c) {
             float x[V];
@@ -217,14 +217,14 @@ prenorm_quant_kernel(PrenormArgs a) {
             }
             if (yo) store16<T>(yo + c, o);
         }
-        if (a.G == 3) bitlinear_prologue<V, 3>(v, D, ss2, a.eps_bl, sw + D, a.q, a.dq, a.rowsum, a.M, m, red);
-        else if (a.G == 1) bitlinear_prologue<V, 1>(v, D, ss2, a.eps_bl, sw + D, a.q, a.dq, a.rowsum, a.M, m, red);
+        if (a.G == 3) bitlinear_prologue<V, 3, P>(v, D, ss2, a.eps_bl, sw + D, a.q, a.dq, a.rowsum, a.M, m, red);
+        else if (a.G == 1) bitlinear_prologue<V, 1, P>(v, D, ss2, a.eps_bl, sw + D, a.q, a.dq, a.rowsum, a.M, m, red);
     }
 }
 
 // y = round_T( ((g*rstd)*w) * o * sigmoid(o) ), then BitLinear prologue.  `ov` holds the gate row o in registers.
-template <typename T, int V>
-__device__ __forceinline__ void gatenorm_tail(float (&gv)[PER], const float (&ov)[PER], double ssg, int D, float eps_g, float eps_bl,
+template <typename T, int V, int P>
+__device__ __forceinline__ void gatenorm_tail(float (&gv)[P], const float (&ov)[P], double ssg, int D, float eps_g, float eps_bl,
                                               const float* sw /* [2][D]: g_norm weight, BitLinear norm weight */, int8_t* q, float* dq,
                                               int32_t* rowsum, int64_t M, int64_t m, RedScratch& red) {
     double s0[1] = {ssg};
@@ -242,10 +242,10 @@ __device__ __forceinline__ void gatenorm_tail(float (&gv)[PER], const float (&ov
             ss2 += (double)t * (double)t;
         }
     }
-    bitlinear_prologue<V, 1>(gv, D, ss2, eps_bl, sw + D, q, dq, rowsum, M, m, red);
+    bitlinear_prologue<V, 1, P>(gv, D, ss2, eps_bl, sw + D, q, dq, rowsum, M, m, red);
 }
 
-template <typename T>
+template <typename T, int P>
 __global__ void __launch_bounds__(FT)
 gatenorm_quant_kernel(const T* __restrict__ gx, int64_t ld_g, const T* __restrict__ o, int64_t ld_o,
                       const float* __restrict__ gw, float eps_g, const float* __restrict__ nw, float eps_bl,
@@ -262,7 +262,7 @@ gatenorm_quant_kernel(const T* __restrict__ gx, int64_t ld_g, const T* __restric
     for (int64_t m = blockIdx.x; m < M; m += gridDim.x) {
         const T* gr = gx + m * ld_g;
         const T* orow = o + m * ld_o;
-        float gv[PER], ov[PER];
+        float gv[P], ov[P];
         double ss = 0.0;
         ROW_FOREACH(V, D, it, c) {
             float a[V], b[V];
@@ -275,14 +275,14 @@ gatenorm_quant_kernel(const T* __restrict__ gx, int64_t ld_g, const T* __restric
                 ss += (double)a[i] * (double)a[i];
             }
         }
-        gatenorm_tail<T, V>(gv, ov, ss, D, eps_g, eps_bl, sw, q, dq, rowsum, M, m, red);
+        gatenorm_tail<T, V, P>(gv, ov, ss, D, eps_g, eps_bl, sw, q, dq, rowsum, M, m, red);
     }
 }
 
 // Single-token step of the token mixer for row b (mmfreelm/layers/hgrn_bit.py:113-140 with T = 1):
 //   f = round(sigmoid(f_raw)); with lb: f = round(lb + round(round(1-lb)*f));  x = round(silu(i_raw)*round(1-f))
 //   h = f*h + x  (fp32 state, updated in place);  o = round(h);  then gatenorm_quant(g_raw, o).
-template <typename T>
+template <typename T, int P>
 __global__ void __launch_bounds__(FT)
 decode_mix_kernel(const T* __restrict__ ifg, int64_t ld, const T* __restrict__ lb, float* __restrict__ state,
                   const float* __restrict__ gw, float eps_g, const float* __restrict__ nw, float eps_bl,
@@ -302,7 +302,7 @@ decode_mix_kernel(const T* __restrict__ ifg, int64_t ld, const T* __restrict__ l
     const T* fr = ir + D;
     const T* gr = ir + 2 * D;
     float* st = state + m * (int64_t)D;
-    float gv[PER], ov[PER];
+    float gv[P], ov[P];
     double ss = 0.0;
     ROW_FOREACH(V, D, it, c) {
         float iv[V], fv[V], g8[V];
@@ -333,11 +333,11 @@ decode_mix_kernel(const T* __restrict__ ifg, int64_t ld, const T* __restrict__ l
             ss += (double)g8[i] * (double)g8[i];
         }
     }
-    gatenorm_tail<T, V>(gv, ov, ss, D, eps_g, eps_bl, sw, q, dq, rowsum, M, m, red);
+    gatenorm_tail<T, V, P>(gv, ov, ss, D, eps_g, eps_bl, sw, q, dq, rowsum, M, m, red);
 }
 
 // z = round_T(silu(gate)*up), then BitLinear prologue.  gate/up are the two halves of a [M, 2D] tensor.
-template <typename T>
+template <typename T, int P>
 __global__ void __launch_bounds__(FT)
 swiglu_quant_kernel(const T* __restrict__ gate, const T* __restrict__ up, int64_t ld, const float* __restrict__ nw,
                     float eps_bl, int8_t* __restrict__ q, float* __restrict__ dq, int32_t* __restrict__ rowsum, int64_t M, int D) {
@@ -352,7 +352,7 @@ swiglu_quant_kernel(const T* __restrict__ gate, const T* __restrict__ up, int64_
     for (int64_t m = blockIdx.x; m < M; m += gridDim.x) {
         const T* gr = gate + m * ld;
         const T* ur = up + m * ld;
-        float v[PER];
+        float v[P];
         double ss = 0.0;
         ROW_FOREACH(V, D, it, c) {
             float gv[V], uv[V];
@@ -365,7 +365,7 @@ swiglu_quant_kernel(const T* __restrict__ gate, const T* __restrict__ up, int64_
                 ss += (double)t * (double)t;
             }
         }
-        bitlinear_prologue<V, 1>(v, D, ss, eps_bl, sw, q, dq, rowsum, M, m, red);
+        bitlinear_prologue<V, 1, P>(v, D, ss, eps_bl, sw, q, dq, rowsum, M, m, red);
     }
 }
 
@@ -381,6 +381,12 @@ swiglu_quant_kernel(const T* __restrict__ gate, const T* __restrict__ up, int64_
 
 // one CTA per row up to eight CTAs per SM; beyond that the CTAs loop over rows
 static inline unsigned row_grid(int64_t M) { return (unsigned)(M < 148 * 8 ? M : 148 * 8); }
+
+// Run `...` with `P` (row values per thread) bound to the smallest compiled size that holds a row of D values.
+#define FUSED_DISPATCH_P(D, P, ...)                                   \
+    if ((D) <= FT * 8) { constexpr int P = 8; __VA_ARGS__; }          \
+    else if ((D) <= FT * 16) { constexpr int P = 16; __VA_ARGS__; }   \
+    else { constexpr int P = 32; __VA_ARGS__; }
 
 #define FUSED_SMEM_ATTR(kernel, smem) \
     if ((smem) > 48 * 1024) MMF_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)(smem)))
@@ -406,8 +412,10 @@ extern "C" int mmf_prenorm_quant(const void* x, int64_t ld_x, const void* residu
     a.q = q; a.dq = dq; a.rowsum = rowsum; a.M = M; a.D = (int)D; a.G = groups; a.round_sum_first = round_sum_first;
     const size_t smem = (size_t)(1 + groups) * D * sizeof(float);
     MMF_DISPATCH(dtype, T, {
-        FUSED_SMEM_ATTR(prenorm_quant_kernel<T>, smem);
-        MMF_CUDA(mmf_launch_pdl(prenorm_quant_kernel<T>, dim3(row_grid(M)), dim3(FT), smem, (cudaStream_t)stream, a));
+        FUSED_DISPATCH_P(D, P, {
+            FUSED_SMEM_ATTR((prenorm_quant_kernel<T, P>), smem);
+            MMF_CUDA(mmf_launch_pdl(prenorm_quant_kernel<T, P>, dim3(row_grid(M)), dim3(FT), smem, (cudaStream_t)stream, a));
+        });
     });
     MMF_LAUNCH_CHECK("prenorm_quant_kernel");
     return MMF_OK;
@@ -425,9 +433,11 @@ extern "C" int mmf_gatenorm_quant(const void* g, int64_t ld_g, const void* o, in
     if (M == 0) return MMF_OK;
     const size_t smem = (size_t)2 * D * sizeof(float);
     MMF_DISPATCH(dtype, T, {
-        FUSED_SMEM_ATTR(gatenorm_quant_kernel<T>, smem);
-        MMF_CUDA(mmf_launch_pdl(gatenorm_quant_kernel<T>, dim3(row_grid(M)), dim3(FT), smem, (cudaStream_t)stream, (const T*)g, ld_g,
-                                (const T*)o, ld_o, gnorm_w, eps_g, nw, eps_bl, q, dq, rowsum, M, (int)D));
+        FUSED_DISPATCH_P(D, P, {
+            FUSED_SMEM_ATTR((gatenorm_quant_kernel<T, P>), smem);
+            MMF_CUDA(mmf_launch_pdl(gatenorm_quant_kernel<T, P>, dim3(row_grid(M)), dim3(FT), smem, (cudaStream_t)stream, (const T*)g,
+                                    ld_g, (const T*)o, ld_o, gnorm_w, eps_g, nw, eps_bl, q, dq, rowsum, M, (int)D));
+        });
     });
     MMF_LAUNCH_CHECK("gatenorm_quant_kernel");
     return MMF_OK;
@@ -446,9 +456,11 @@ extern "C" int mmf_decode_mix(const void* ifg, int64_t ld, int dtype, const void
     if (M == 0) return MMF_OK;
     const size_t smem = (size_t)3 * D * sizeof(float);
     MMF_DISPATCH(dtype, T, {
-        FUSED_SMEM_ATTR(decode_mix_kernel<T>, smem);
-        MMF_CUDA(mmf_launch_pdl(decode_mix_kernel<T>, dim3((unsigned)M), dim3(FT), smem, (cudaStream_t)stream, (const T*)ifg, ld,
-                                (const T*)lower_bound, state, gnorm_w, eps_g, nw, eps_bl, q, dq, rowsum, M, (int)D));
+        FUSED_DISPATCH_P(D, P, {
+            FUSED_SMEM_ATTR((decode_mix_kernel<T, P>), smem);
+            MMF_CUDA(mmf_launch_pdl(decode_mix_kernel<T, P>, dim3((unsigned)M), dim3(FT), smem, (cudaStream_t)stream, (const T*)ifg, ld,
+                                    (const T*)lower_bound, state, gnorm_w, eps_g, nw, eps_bl, q, dq, rowsum, M, (int)D));
+        });
     });
     MMF_LAUNCH_CHECK("decode_mix_kernel");
     return MMF_OK;
@@ -464,9 +476,11 @@ extern "C" int mmf_swiglu_quant(const void* gate, const void* up, int64_t ld, in
     if (M == 0) return MMF_OK;
     const size_t smem = (size_t)D * sizeof(float);
     MMF_DISPATCH(dtype, T, {
-        FUSED_SMEM_ATTR(swiglu_quant_kernel<T>, smem);
-        MMF_CUDA(mmf_launch_pdl(swiglu_quant_kernel<T>, dim3(row_grid(M)), dim3(FT), smem, (cudaStream_t)stream, (const T*)gate,
-                                (const T*)up, ld, nw, eps_bl, q, dq, rowsum, M, (int)D));
+        FUSED_DISPATCH_P(D, P, {
+            FUSED_SMEM_ATTR((swiglu_quant_kernel<T, P>), smem);
+            MMF_CUDA(mmf_launch_pdl(swiglu_quant_kernel<T, P>, dim3(row_grid(M)), dim3(FT), smem, (cudaStream_t)stream, (const T*)gate,
+                                    (const T*)up, ld, nw, eps_bl, q, dq, rowsum, M, (int)D));
+        });
     });
     MMF_LAUNCH_CHECK("swiglu_quant_kernel");
     return MMF_OK;

@@ -82,9 +82,7 @@ act_quant_kernel(const T* __restrict__ x, int64_t ld_x, const float* __restrict_
         int8_t codes[V];
 #pragma unroll
         for (int i = 0; i < V; ++i) {
-            float r = rintf(__fmul_rn(row[c + i], s));
-            r = fminf(fmaxf(r, -128.0f), 127.0f);
-            const int iv = (int)r;
+            const int iv = quant_code(__fmul_rn(row[c + i], s));
             codes[i] = (int8_t)iv;
             lsum += iv;
         }
