@@ -262,7 +262,8 @@ int mmf_gatenorm_quant(const void* g, int64_t ld_g, const void* o, int64_t ld_o,
 /* Single-token (decode) step of the token mixer in one kernel: for each of M sequences, the gate math
  * and state update of mmf_hgrn_gated with T = 1 (state fp32 [M, D], updated in place) followed by
  * mmf_gatenorm_quant on the same row.  ifg: [M, ld] rows holding the i | f | g projections as three
- * consecutive D-wide slabs (ld >= 3*D).
+ * consecutive D-wide slabs (ld >= 3*D).  lower_bound, gnorm_w and nw are read before the kernel synchronises with
+ * the launches preceding it on the stream: they must be complete when those launches are enqueued (model constants).
  * Replaces: mmfreelm/layers/hgrn_bit.py:113-140 for a one-token forward. */
 int mmf_decode_mix(const void* ifg, int64_t ld, int dtype, const void* lower_bound, float* state,
                    const float* gnorm_w, float eps_g, const float* nw, float eps_bl, int8_t* q, float* dq,

@@ -50,6 +50,7 @@ struct MmaParams {
     int wt;              // weight tiles (128 rows each) one CTA multiplies against each activation stage: 1 or 2
     int nacc;            // independent accumulators (NT columns each) that consecutive MMAs rotate through
     int SA, SB, SW;      // ring depths: unpacked-A stages in TMEM, activation stages, packed-weight stages
+    int merged;          // SA == SB and both rings share one full / one empty barrier per stage (one wait, one commit)
     uint32_t idesc;
 };
 
@@ -58,7 +59,9 @@ constexpr int BAR_B_FULL = 0, BAR_B_EMPTY = BAR_B_FULL + MAX_SB, BAR_W_FULL = BA
               BAR_W_EMPTY = BAR_W_FULL + MAX_SW, BAR_A_FULL = BAR_W_EMPTY + MAX_SW, BAR_A_EMPTY = BAR_A_FULL + MAX_SA,
               BAR_ACC = BAR_A_EMPTY + MAX_SA, NUM_BARS = BAR_ACC + 1;
 
-__device__ __forceinline__ uint32_t bar_count(int i) {
+__device__ __forceinline__ uint32_t bar_count(int i, int merged) {
+    // merged rings: a stage's "full" barrier also takes the activation producer's expect_tx arrival
+    if (merged && i >= BAR_A_FULL && i < BAR_A_EMPTY) return 129u;
     // arrivals per phase: the 128 threads of one unpack group for "weights consumed" and "A stage written",
     // one (producer's expect_tx arrive or a tcgen05.commit) for everything else
     return (i >= BAR_W_EMPTY && i < BAR_A_EMPTY) ? 128u : 1u;
@@ -159,7 +162,7 @@ bitlinear_mma_kernel(const __grid_constant__ CUtensorMap q_map, BitLinearArgs a,
     const int nstages = min(p.stages_per_cta, total_stages - stage0);   // >= 1 by construction
 
     static_assert(NUM_BARS <= MM_THREADS, "one thread initialises one barrier");
-    if (tid < NUM_BARS) mbar_init(&bars[tid], bar_count(tid));
+    if (tid < NUM_BARS) mbar_init(&bars[tid], bar_count(tid, p.merged));
     if (tid == NUM_BARS) s_abort = 0;
     if (warp == WARP_MMA) tmem_alloc(&s_tmem_base, (uint32_t)p.tmem_cols);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -205,9 +208,11 @@ bitlinear_mma_kernel(const __grid_constant__ CUtensorMap q_map, BitLinearArgs a,
             Ring bq{0, 0, SB};
             const int y = g * a.M + m0;
             for (int i = 0; i < nstages; ++i, bq.next()) {
-                if (!mbar_wait(&bars[BAR_B_EMPTY + bq.slot], bq.ph ^ 1, abort_flag)) break;
-                mbar_expect_tx(&bars[BAR_B_FULL + bq.slot], (uint32_t)b_stage_bytes);
-                tma_load_2d(b_ring + bq.slot * b_stage_bytes, &q_map, &bars[BAR_B_FULL + bq.slot], (stage0 + i) * 128, y);
+                uint64_t* empty = &bars[(p.merged ? BAR_A_EMPTY : BAR_B_EMPTY) + bq.slot];
+                uint64_t* full = &bars[(p.merged ? BAR_A_FULL : BAR_B_FULL) + bq.slot];
+                if (!mbar_wait(empty, bq.ph ^ 1, abort_flag)) break;
+                mbar_expect_tx(full, (uint32_t)b_stage_bytes);
+                tma_load_2d(b_ring + bq.slot * b_stage_bytes, &q_map, full, (stage0 + i) * 128, y);
             }
         }
     } else if (warp == WARP_MMA) {
@@ -226,48 +231,53 @@ bitlinear_mma_kernel(const __grid_constant__ CUtensorMap q_map, BitLinearArgs a,
             int i = 0;
             long long* mtrace = (a.ws && a.ws[1] == MMF_TRACE_MAGIC && (blockIdx.x | blockIdx.y | blockIdx.z) == 0)
                                     ? reinterpret_cast<long long*>(a.ws + 8) : nullptr;
-            if (p.wt == 1 && nacc == 1) {
-                // lean path (one weight tile, one accumulator, whole 128-K stages): the issuing thread is a
-                // serial instruction stream, so every instruction here costs tensor-pipe time
+            if (p.wt == 1 && (nacc == 1 || nacc == 2 || nacc == 4)) {
+                // lean path (one weight tile, whole 128-K stages): the issuing thread is a serial instruction
+                // stream, so every instruction here costs tensor-pipe time.  MMA k of a stage goes to accumulator
+                // k % nacc (nacc = 1, 2 or 4); only the first use of an accumulator overwrites it.
                 const int nfull = min(nstages, p.KC / 2 - stage0);
-                const uint32_t d_addr = tmem_base;
+                const uint32_t dk1 = tmem_base + (1u % nacc) * NTc, dk2 = tmem_base + (2u % nacc) * NTc,
+                               dk3 = tmem_base + (3u % nacc) * NTc;
                 const uint32_t b_lo0 = (uint32_t)b_desc0, b_hi = (uint32_t)(b_desc0 >> 32);
-                uint32_t accum = 0;
+                uint32_t f0 = 0, f1 = nacc > 1 ? 0u : 1u, f2 = nacc > 2 ? 0u : 1u, f3 = nacc > 3 ? 0u : 1u;
                 for (; i < nfull; ++i, bq.next(), aq.next()) {
-                    if (!mbar_wait(&bars[BAR_B_FULL + bq.slot], bq.ph, abort_flag)) { live = false; break; }
+                    if (!p.merged && !mbar_wait(&bars[BAR_B_FULL + bq.slot], bq.ph, abort_flag)) { live = false; break; }
                     if (!mbar_wait(&bars[BAR_A_FULL + aq.slot], aq.ph, abort_flag)) { live = false; break; }
                     tc_fence_after();
                     if (mtrace && i < 10) mtrace[8 + i] = clock64();
                     uint32_t a_addr = tmem_a + aq.slot * 32;
                     uint32_t b_lo = b_lo0 + (uint32_t)bq.slot * b_desc_step;
                     asm volatile(
-                        "{\n\t.reg .pred p;\n\t.reg .b64 d0, d1, d2, d3;\n\t"
-                        "setp.ne.b32 p, %4, 0;\n\t"
-                        "mov.b64 d0, {%1, %3};\n\t"
+                        "{\n\t.reg .pred p0, p1, p2, p3;\n\t.reg .b64 d0, d1, d2, d3;\n\t"
+                        "setp.ne.b32 p0, %7, 0;\n\t"
+                        "setp.ne.b32 p1, %8, 0;\n\t"
+                        "setp.ne.b32 p2, %9, 0;\n\t"
+                        "setp.ne.b32 p3, %10, 0;\n\t"
+                        "mov.b64 d0, {%1, %6};\n\t"
                         "add.u32 %1, %1, 2;\n\t"
-                        "mov.b64 d1, {%1, %3};\n\t"
+                        "mov.b64 d1, {%1, %6};\n\t"
                         "add.u32 %1, %1, 2;\n\t"
-                        "mov.b64 d2, {%1, %3};\n\t"
+                        "mov.b64 d2, {%1, %6};\n\t"
                         "add.u32 %1, %1, 2;\n\t"
-                        "mov.b64 d3, {%1, %3};\n\t"
-                        "tcgen05.mma.cta_group::1.kind::i8 [%2], [%0], d0, %5, p;\n\t"
+                        "mov.b64 d3, {%1, %6};\n\t"
+                        "tcgen05.mma.cta_group::1.kind::i8 [%2], [%0], d0, %11, p0;\n\t"
                         "add.u32 %0, %0, 8;\n\t"
-                        "tcgen05.mma.cta_group::1.kind::i8 [%2], [%0], d1, %5, 1;\n\t"
+                        "tcgen05.mma.cta_group::1.kind::i8 [%3], [%0], d1, %11, p1;\n\t"
                         "add.u32 %0, %0, 8;\n\t"
-                        "tcgen05.mma.cta_group::1.kind::i8 [%2], [%0], d2, %5, 1;\n\t"
+                        "tcgen05.mma.cta_group::1.kind::i8 [%4], [%0], d2, %11, p2;\n\t"
                         "add.u32 %0, %0, 8;\n\t"
-                        "tcgen05.mma.cta_group::1.kind::i8 [%2], [%0], d3, %5, 1;\n\t}"
+                        "tcgen05.mma.cta_group::1.kind::i8 [%5], [%0], d3, %11, p3;\n\t}"
                         : "+r"(a_addr), "+r"(b_lo)
-                        : "r"(d_addr), "r"(b_hi), "r"(accum), "r"(p.idesc)
+                        : "r"(tmem_base), "r"(dk1), "r"(dk2), "r"(dk3), "r"(b_hi), "r"(f0), "r"(f1), "r"(f2), "r"(f3), "r"(p.idesc)
                         : "memory");
-                    accum = 1;
+                    f0 = f1 = f2 = f3 = 1;
                     tc_commit(&bars[BAR_A_EMPTY + aq.slot]);
-                    tc_commit(&bars[BAR_B_EMPTY + bq.slot]);
+                    if (!p.merged) tc_commit(&bars[BAR_B_EMPTY + bq.slot]);
                 }
-                started = accum ? nacc : 0;
+                started = f0 ? nacc : 0;
             }
             for (; i < nstages && live; ++i, bq.next(), aq.next()) {
-                if (!mbar_wait(&bars[BAR_B_FULL + bq.slot], bq.ph, abort_flag)) break;
+                if (!p.merged && !mbar_wait(&bars[BAR_B_FULL + bq.slot], bq.ph, abort_flag)) break;
                 const uint64_t bd = b_desc0 + (uint64_t)(bq.slot * b_desc_step);
                 const int nmma = min(2, p.KC - (stage0 + i) * 2) * 2;
                 for (int t = 0; t < ntile; ++t) {
@@ -292,7 +302,7 @@ bitlinear_mma_kernel(const __grid_constant__ CUtensorMap q_map, BitLinearArgs a,
                     }
                     tc_commit(&bars[BAR_A_EMPTY + slot]);   // frees the A stage when these MMAs retire
                 }
-                tc_commit(&bars[BAR_B_EMPTY + bq.slot]);
+                if (!p.merged) tc_commit(&bars[BAR_B_EMPTY + bq.slot]);
             }
             tc_commit(&bars[BAR_ACC]);
         }
@@ -555,6 +565,7 @@ bool choose_config(const BitLinearArgs& a, MmaParams& best, size_t& best_smem) {
                     smem = 1024 + (size_t)p.SB * NT * 128 + (size_t)p.SW * W_STAGE_BYTES + (ks > 1 ? (size_t)NT * MMF_TILE_ROWS * 4 : 0);
                     occ = (smem <= 110 * 1024 && cols <= 256) ? 2 : 1;
                 }
+                p.merged = (mode == 0 && p.SA == p.SB) ? 1 : 0;
                 if (smem + 4096 > 227 * 1024) continue;   // the kernel's static shared memory comes on top
                 const int64_t ctas = (int64_t)((n_tiles + p.wt - 1) / p.wt) * m_tiles * ks;
                 const int64_t waves = (ctas + 148 * occ - 1) / (148 * occ);

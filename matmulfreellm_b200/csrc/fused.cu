@@ -293,9 +293,11 @@ decode_mix_kernel(const T* __restrict__ ifg, int64_t ld, const T* __restrict__ l
     pdl_trigger();
     stage_weights(sw, gw, D);
     stage_weights(sw + D, nw, D);
-    pdl_wait();     // the lower bounds are computed by a preceding kernel of the same forward pass
+    // the lower bounds are constants of the model like the norm weights (derived from parameters only): they are
+    // staged before the grid-dependency wait and must not be written by the kernels launched just before this one
     if (lb)
         for (int i = threadIdx.x; i < D; i += FT) sw[2 * D + i] = to_f32(lb[i]);
+    pdl_wait();
     __syncthreads();
     const int64_t m = blockIdx.x;
     const T* ir = ifg + m * ld;
