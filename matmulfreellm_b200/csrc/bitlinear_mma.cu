@@ -568,12 +568,16 @@ bool choose_config(const BitLinearArgs& a, MmaParams& best, size_t& best_smem) {
                 p.merged = (mode == 0 && p.SA == p.SB) ? 1 : 0;
                 if (smem + 4096 > 227 * 1024) continue;   // the kernel's static shared memory comes on top
                 const int64_t ctas = (int64_t)((n_tiles + p.wt - 1) / p.wt) * m_tiles * ks;
+                // Latency model in microseconds.  Inside a decode step the kernel starts while its predecessor
+                // still runs and fills its rings with weights before the activations exist, so what counts is the
+                // path after the dependency wait: fixed set-up / TMA round trip / epilogue, 0.24 us per 128-K stage
+                // (0.30 at 256 token columns), and for a K split the cluster barriers and the push reduction.  More
+                // split than a stand-alone launch would want wins there (measured on the whole step).  Clusters of
+                // 8 with more than 32 token columns no longer fit side by side (measured +6 us).
                 const int64_t waves = (ctas + 148 * occ - 1) / (148 * occ);
-                // fitted to measured phase times (us): per 128-K stage 4 MMAs of >= 88 cycles each (130 at 256 token
-                // columns) plus issue overhead; fixed launch/set-up/first-TMA latency; epilogue; cluster reduction
                 const double t_stage = mode == 2 ? 0.90 : NT > 128 ? 0.30 : 0.24;   // (two tiles per CTA measured slower: kept for experiments)
                 double t = 2.5 + stages * t_stage + 0.5 + p.wt * NT * 0.012;
-                if (ks > 1) t += 1.5 + NT * 0.012;
+                if (ks > 1) t += 1.5 + NT * 0.012 + (ks == 8 && NT > 32 ? 6.0 : 0.0);
                 const double cost = waves * t;
                 if (cost < best_cost) { best_cost = cost; best = p; best_smem = smem; found = true; }
             }
