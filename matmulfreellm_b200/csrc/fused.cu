@@ -101,6 +101,16 @@ __device__ __forceinline__ void stage_weights(float* dst, const float* src, int 
     }
 }
 
+// V consecutive staged weights (16-byte aligned: columns start at multiples of V, D is a multiple of 16) as vector loads
+template <int V>
+__device__ __forceinline__ void lds_weights(const float* p, float (&w)[V]) {
+#pragma unroll
+    for (int i = 0; i < V; i += 4) {
+        const float4 t = *reinterpret_cast<const float4*>(p + i);
+        w[i] = t.x; w[i + 1] = t.y; w[i + 2] = t.z; w[i + 3] = t.w;
+    }
+}
+
 // iterate over the 16-byte vectors of a row held as v[P] (P: the enclosing template parameter): vector `it` of this thread starts at column c
 #define ROW_FOREACH(V, D, it, c) \
     _Pragma("unroll") for (int it = 0, c = threadIdx.x * (V); it < P / (V); ++it, c += FT * (V)) if (c < (D))
@@ -118,10 +128,11 @@ __device__ __forceinline__ void bitlinear_prologue(const float (&v)[P], int D, d
     for (int g = 0; g < G; ++g) amax[g] = 0.0f;
     ROW_FOREACH(V, D, it, c) {
 #pragma unroll
-        for (int i = 0; i < V; ++i) {
-            const float y = __fmul_rn(v[it * V + i], rstd);
+        for (int g = 0; g < G; ++g) {
+            float w[V];
+            lds_weights<V>(snw + g * D + c, w);
 #pragma unroll
-            for (int g = 0; g < G; ++g) amax[g] = fmaxf(amax[g], fabsf(__fmul_rn(y, snw[g * D + c + i])));
+            for (int i = 0; i < V; ++i) amax[g] = fmaxf(amax[g], fabsf(__fmul_rn(__fmul_rn(v[it * V + i], rstd), w[i])));
         }
     }
     block_max_f<G>(amax, red.f0);
@@ -134,9 +145,11 @@ __device__ __forceinline__ void bitlinear_prologue(const float (&v)[P], int D, d
         lsum[g] = 0;
         ROW_FOREACH(V, D, it, c) {
             int8_t codes[V];
+            float w[V];
+            lds_weights<V>(snw + g * D + c, w);
 #pragma unroll
             for (int i = 0; i < V; ++i) {
-                const float y = __fmul_rn(__fmul_rn(v[it * V + i], rstd), snw[g * D + c + i]);
+                const float y = __fmul_rn(__fmul_rn(v[it * V + i], rstd), w[i]);
                 const int iv = quant_code(__fmul_rn(y, s));
                 codes[i] = (int8_t)iv;
                 lsum[g] += iv;
@@ -207,10 +220,11 @@ prenorm_quant_kernel(PrenormArgs a) {
         T* yo = a.y_out ? reinterpret_cast<T*>(a.y_out) + m * (int64_t)D : nullptr;
         double ss2 = 0.0;
         ROW_FOREACH(V, D, it, c) {
-            float o[V];
-    #pragma unroll
+            float o[V], w[V];
+            lds_weights<V>(sw + c, w);
+#pragma unroll
             for (int i = 0; i < V; ++i) {
-                const float t = round_to<T>(__fmul_rn(__fmul_rn(v[it * V + i], rstd1), sw[c + i]));
+                const float t = round_to<T>(__fmul_rn(__fmul_rn(v[it * V + i], rstd1), w[i]));
                 o[i] = t;
                 v[it * V + i] = t;
                 ss2 += (double)t * (double)t;
@@ -232,10 +246,12 @@ __device__ __forceinline__ void gatenorm_tail(float (&gv)[P], const float (&ov)[
     const float rstd = rstd_from_sumsq(s0[0], D, eps_g);
     double ss2 = 0.0;
     ROW_FOREACH(V, D, it, c) {
+        float w[V];
+        lds_weights<V>(sw + c, w);
 #pragma unroll
         for (int i = 0; i < V; ++i) {
             const float o = ov[it * V + i];
-            float t = __fmul_rn(__fmul_rn(gv[it * V + i], rstd), sw[c + i]);
+            float t = __fmul_rn(__fmul_rn(gv[it * V + i], rstd), w[i]);
             t = __fmul_rn(t, o);
             t = round_to<T>(__fmul_rn(t, sigmoidf_(o)));
             gv[it * V + i] = t;

@@ -446,6 +446,40 @@ def test_gatenorm_and_swiglu_quant(K, dtype):
     _codes_close(q, dq, q_ref, dq_ref, exact=False)
 
 
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
+@pytest.mark.parametrize("D", [704, 2048, 2560, 5632])
+def test_fused_row_kernels_many_rows(K, dtype, D):
+    """With more rows than resident CTAs the fused row kernels loop over rows.  Rows are independent, so a 1500-row
+    call must reproduce, bit for bit, the same rows run in two small one-CTA-per-row calls (the shape checked against
+    the oracle above)."""
+    g = torch.Generator().manual_seed(D)
+    M = 1500
+    x = dev((torch.randn(M, D, generator=g) * 2).to(dtype))
+    res = dev(torch.randn(M, D, generator=g).to(dtype))
+    nw = dev(1.0 + 0.1 * torch.randn(D, generator=g))
+    bl = [dev(1.0 + 0.1 * torch.randn(D, generator=g)) for _ in range(3)]
+    parts = [slice(0, 700), slice(700, M)]
+
+    def check(fn, n_groups):
+        big = fn(slice(0, M))
+        small = [fn(sl) for sl in parts]
+        for k, t in enumerate(big):
+            if t is None:
+                continue
+            if n_groups > 1 and t.shape[0] == n_groups * M:       # group-major codes / scales
+                t = t.view(n_groups, M, *t.shape[1:])
+                ref = torch.cat([sm[k].view(n_groups, -1, *t.shape[2:]) for sm in small], dim=1)
+            else:
+                ref = torch.cat([sm[k] for sm in small], dim=0)
+            assert torch.equal(t, ref), (k, D, dtype)
+
+    check(lambda sl: K.prenorm_quant(x[sl], res[sl], nw, 1e-6, bl, 1e-6, False, want_residual_out=True, want_y=True), 3)
+    check(lambda sl: K.prenorm_quant(x[sl], None, nw, 1e-6, [bl[0]], 1e-6, True), 1)
+    check(lambda sl: K.gatenorm_quant(x[sl], res[sl], nw, 1e-6, bl[1], 1e-6), 1)
+    gu = dev(torch.randn(M, 2 * D, generator=g).to(dtype))
+    check(lambda sl: K.swiglu_quant(gu[sl], bl[2], 1e-6), 1)
+
+
 @pytest.mark.parametrize("dtype,tol", [(torch.bfloat16, 1e-2), (torch.float32, 1e-4)])
 @pytest.mark.parametrize("B,T,D", [(3, 1, 256), (2, 70, 128), (1, 1024, 64)])
 def test_hgrn_gated_vs_oracle(K, dtype, tol, B, T, D):
