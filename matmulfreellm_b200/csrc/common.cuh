@@ -186,8 +186,21 @@ __device__ __forceinline__ float rstd_from_sumsq(double sumsq, int64_t K, float 
     const float mean = (float)(sumsq / (double)K);
     return __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(mean, eps)));
 }
+// e^-x and the reciprocal through the special-function unit (ex2.approx, rcp.approx: relative error about 2^-22 each).
+// The results feed values that are rounded to the activation dtype right away, or compared at 1e-4, so the two extra
+// units in the last place are invisible there, and each call is 6 instructions instead of more than 20.
+__device__ __forceinline__ float exp_neg(float x) {
+    float p;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(p) : "f"(__fmul_rn(x, -1.4426950408889634f)));
+    return p;
+}
+__device__ __forceinline__ float rcp_fast(float x) {
+    float r;
+    asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(x));
+    return r;
+}
 __device__ __forceinline__ float silu_mul(float x, float y) {
     // float(x) * float(y) / (1.0f + exp(-float(x)))
-    return __fdiv_rn(__fmul_rn(x, y), __fadd_rn(1.0f, expf(-x)));
+    return __fmul_rn(__fmul_rn(x, y), rcp_fast(__fadd_rn(1.0f, exp_neg(x))));
 }
-__device__ __forceinline__ float sigmoidf_(float x) { return __fdiv_rn(1.0f, __fadd_rn(1.0f, expf(-x))); }
+__device__ __forceinline__ float sigmoidf_(float x) { return rcp_fast(__fadd_rn(1.0f, exp_neg(x))); }
