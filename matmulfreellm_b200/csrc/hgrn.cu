@@ -335,6 +335,40 @@ hgrn_scan_kernel(const __grid_constant__ CUtensorMap x_map, const __grid_constan
     }
 }
 
+// T = 1 (a decode step outside the fused chain): one thread per channel pair, h = f * h0 + x, o = h, state written back.
+template <typename TX, typename TG, int MODE>
+__global__ void __launch_bounds__(256)
+hgrn_step_kernel(const TX* __restrict__ x, int64_t ld_x, const TG* __restrict__ g, int64_t ld_g, const TX* __restrict__ lb,
+                 const void* __restrict__ h0, void* __restrict__ ht, int state_dt, TX* __restrict__ o, int64_t B, int D) {
+    pdl_trigger();
+    pdl_wait();
+    const int64_t idx = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) * 2;
+    if (idx >= B * D) return;
+    const int64_t b = idx / D;
+    const int ch = (int)(idx - b * D);
+    float2 xv = ld2(x + b * ld_x + ch), f = ld2(g + b * ld_g + ch);
+    const bool has_lb = MODE == HG_RAW && lb != nullptr;
+    float2 lbv = make_float2(0.0f, 0.0f), oml = make_float2(1.0f, 1.0f);
+    if (has_lb) {
+        lbv = ld2(lb + ch);
+        oml.x = round_to<TX>(__fsub_rn(1.0f, lbv.x));
+        oml.y = round_to<TX>(__fsub_rn(1.0f, lbv.y));
+    }
+    gate_transform<TX, MODE>(xv.x, f.x, has_lb, lbv.x, oml.x);
+    gate_transform<TX, MODE>(xv.y, f.y, has_lb, lbv.y, oml.y);
+    float h0x = 0.0f, h0y = 0.0f;
+    if (h0) {
+        h0x = load_state_dt(h0, idx, state_dt);
+        h0y = load_state_dt(h0, idx + 1, state_dt);
+    }
+    const float hx = fmaf(f.x, h0x, xv.x), hy = fmaf(f.y, h0y, xv.y);
+    st2(o + idx, hx, hy);
+    if (ht) {
+        store_state_dt(ht, idx, state_dt, hx);
+        store_state_dt(ht, idx + 1, state_dt, hy);
+    }
+}
+
 // number of time chunks: split only while it at least doubles the number of busy SMs and each
 // chunk keeps >= 256 timesteps
 int hgrn_num_chunks(int64_t B, int64_t T, int64_t D) {
@@ -368,6 +402,13 @@ int hgrn_make_map(CUtensorMap* map, const void* base, int es, int64_t ld, int64_
 template <typename TX, typename TG, int MODE>
 int hgrn_launch(const void* x, int64_t ld_x, const void* g, int64_t ld_g, const void* lb, const void* h0, void* ht,
                 int state_dt, void* o, int64_t B, int64_t T, int64_t D, int NT, HgrnWs ws, cudaStream_t st) {
+    if (T == 1) {   // a single step: no tiles, no scan
+        const int64_t pairs = B * D / 2;
+        MMF_CUDA(mmf_launch_pdl(hgrn_step_kernel<TX, TG, MODE>, dim3((unsigned)((pairs + 255) / 256)), dim3(256), 0, st, (const TX*)x,
+                                ld_x, (const TG*)g, ld_g, (const TX*)lb, h0, ht, state_dt, (TX*)o, B, (int)D));
+        MMF_LAUNCH_CHECK("hgrn_step_kernel");
+        return MMF_OK;
+    }
     const size_t smem = hgrn_smem_bytes<TX, TG>();
     // chunks start on stage boundaries so that every chunk but the last consists of whole stages
     const int chunk_len = (int)(((T + NT - 1) / NT + HG_TS - 1) / HG_TS * HG_TS);

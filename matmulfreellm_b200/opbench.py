@@ -5,6 +5,7 @@
     python -m matmulfreellm_b200.opbench rowwise --M 4096 --D 2048
     python -m matmulfreellm_b200.opbench int8peak
     python -m matmulfreellm_b200.opbench prefill --batch 16 --seq 2048 --layers 2
+    python -m matmulfreellm_b200.opbench sweep          (the BitLinear op sweep: 5 token counts x 4 layer shapes)
 
 Each prints one JSON line: device time per call (CUDA events, after 3 warm-ups) and the achieved GB/s of
 algorithmic bytes and/or TOP/s.  Inputs are seeded synthetic data; every repetition of `bitlinear` uses a
@@ -76,8 +77,19 @@ def hgrn(a):
     glog = torch.nn.functional.logsigmoid(torch.randn(a.B, a.T, a.D, device=dev, generator=g))
     x = ((1 - glog.exp()) * torch.nn.functional.silu(torch.randn(a.B, a.T, a.D, device=dev, generator=g))).bfloat16()
     gate = glog if a.gate == "log" else glog.exp()
-    t = _time(lambda: K.hgrn_scan(x, gate, None, True, gate_is_log=a.gate == "log", state_dtype=torch.float32), a.iters)
-    nbytes = 8.0 * x.numel()
+    h0 = torch.zeros(a.B, a.D, device=dev)
+    fn = lambda: K.hgrn_scan(x, gate, h0, True, gate_is_log=a.gate == "log", state_dtype=torch.float32)
+    if getattr(a, "graph", 0):     # small problems: device time without host launch cost
+        fn()
+        torch.cuda.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            for _ in range(a.graph):
+                fn()
+        t = _time(graph.replay, a.iters) / a.graph
+    else:
+        t = _time(fn, a.iters)
+    nbytes = 8.0 * x.numel() + (8.0 * a.B * a.D if a.T == 1 else 0.0)     # a single step also reads and writes the state
     print(json.dumps({"op": "hgrn_scan", "B": a.B, "T": a.T, "D": a.D, "us": t * 1e6, "algorithmic_bytes": nbytes,
                       "gb_per_s": nbytes / t / 1e9}))
 
@@ -126,6 +138,26 @@ def prefill(a):
                       "tokens_per_s_per_layer_block": a.batch * a.seq / t * a.layers}))
 
 
+def sweep(a):
+    """FusedBitLinear op sweep: M in {1,16,256,4096,16384} x (K,N) in {(2048,2048),(2048,11264),(5632,2048),(2560,2560)}.
+    Small M: 24 launches over 24 distinct weight buffers (more than L2 in total for the larger shapes) replayed from one
+    CUDA graph, so the figure is device time per launch with the weights streamed from HBM; the launches in the graph
+    overlap their prologues (programmatic dependent launch), as they do inside a decode step."""
+    class Args:
+        pass
+    for (Kd, N) in ((2048, 2048), (2048, 11264), (5632, 2048), (2560, 2560)):
+        for M in (1, 16, 256, 4096, 16384):
+            b = Args()
+            b.M, b.K, b.N, b.kernel, b.iters = M, Kd, N, "auto", 5
+            b.buffers, b.graph = (24, 24) if M <= 256 else (1, 0)
+            bitlinear(b)
+    for (B, T) in ((8, 2048), (8, 8192), (256, 1)):
+        h = Args()
+        h.B, h.T, h.D, h.gate, h.iters = B, T, 2048, "log", 10
+        h.graph = 20 if T == 1 else 0
+        hgrn(h)
+
+
 def main():
     ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
     sub = ap.add_subparsers(dest="op", required=True)
@@ -137,14 +169,16 @@ def main():
     h = sub.add_parser("hgrn")
     h.add_argument("--B", type=int, default=8); h.add_argument("--T", type=int, default=2048)
     h.add_argument("--D", type=int, default=2048); h.add_argument("--gate", default="log"); h.add_argument("--iters", type=int, default=10)
+    h.add_argument("--graph", type=int, default=0)
     r = sub.add_parser("rowwise")
     r.add_argument("--M", type=int, default=4096); r.add_argument("--D", type=int, default=2048); r.add_argument("--iters", type=int, default=10)
     sub.add_parser("int8peak")
+    sub.add_parser("sweep")
     pf = sub.add_parser("prefill")
     pf.add_argument("--batch", type=int, default=16); pf.add_argument("--seq", type=int, default=2048)
     pf.add_argument("--layers", type=int, default=2); pf.add_argument("--iters", type=int, default=2)
     a = ap.parse_args()
-    {"bitlinear": bitlinear, "hgrn": hgrn, "rowwise": rowwise, "int8peak": int8peak, "prefill": prefill}[a.op](a)
+    {"bitlinear": bitlinear, "hgrn": hgrn, "rowwise": rowwise, "int8peak": int8peak, "prefill": prefill, "sweep": sweep}[a.op](a)
 
 
 if __name__ == "__main__":
