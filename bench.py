@@ -187,10 +187,10 @@ def run_reference(args):
 # ----------------------------------------------------------------------------------------------------------
 # GPU arm
 # ----------------------------------------------------------------------------------------------------------
-def build_model(args, device, dtype=torch.bfloat16):
+def build_model(args, device, dtype=torch.bfloat16, spec=None):
     from matmulfreellm_b200.models import HGRNBitConfig, HGRNBitForCausalLM
     from matmulfreellm_b200.ops.fusedbitnet import BitLinear
-    cfg = HGRNBitConfig(**{**MODEL, "num_hidden_layers": args.layers})
+    cfg = HGRNBitConfig(**(spec or {**MODEL, "num_hidden_layers": args.layers}))
     with torch.device(device):
         model = HGRNBitForCausalLM(cfg).eval()
     g = torch.Generator(device=device).manual_seed(1234)       # same weights on every rank
@@ -297,6 +297,7 @@ def run_ours(args):
         "whole_step_frac": probe.packed_bytes / (ms * 1e-3) / 1e9 / peak,
     }
 
+    kernels_per_step, packed_mb = dec.kernels_per_step, probe.packed_bytes / 1e6
     extras = {}
     if not args.no_extras and rank == 0 and world == 1:
         for b in (1, 256):
@@ -354,6 +355,20 @@ def run_ours(args):
             hg[f"B8_T{T}_D2048"] = {"us": t * 1e3, "gb_per_s": gbs, "frac_of_hbm_peak": gbs / peak_gbs}
             del x, g
         extras["hgrn_scan"] = hg
+        # the 2.7B shapes (32 blocks, hidden 2560, intermediate 6912) at the per-GPU batch of the 8-GPU throughput
+        # configuration (512 sequences / 8)
+        del dec, probe, model
+        torch.cuda.empty_cache()
+        big = build_model(args, device, spec=dict(vocab_size=32000, hidden_size=2560, num_hidden_layers=32, intermediate_size=6912))
+        d = GreedyDecoder(big, 64)
+        d.prefill(torch.randint(0, MODEL["vocab_size"], (64, 16), generator=gen).to(device))
+        for _ in range(3):
+            d.step()
+        torch.cuda.synchronize()
+        m = device_time_ms(d.step, 16, stream)
+        extras["hgrnbit_2.7b_decode_batch64_tokens_per_s"] = 64 / (m * 1e-3)
+        extras["hgrnbit_2.7b_decode_batch64_ms_per_step"] = m
+        del d, big
 
     cpu = None
     if rank == 0 and world == 1 and not args.skip_cpu:
@@ -369,11 +384,11 @@ def run_ours(args):
             "config": {"workload": workload_name(args), "per_gpu_batch": B, "global_batch": world * B,
                        "parallelism": f"batch-sharded x{world}, no data-path collective",
                        "l2_policy": "inputs larger than L2: one step streams %.0f MB of packed weights (L2 = 126 MB)"
-                                    % (probe.packed_bytes / 1e6)},
+                                    % packed_mb},
             "e2e": {"value": world * B / (e2e_ms * 1e-3), "unit": "tokens/s", "ms_per_step": e2e_ms,
                     "h2d_bytes_per_step": B * 8, "d2h_bytes_per_step": B * 8},
-            "gpu_launches": dec.kernels_per_step * args.steps,
-            "kernels_per_step": dec.kernels_per_step,
+            "gpu_launches": kernels_per_step * args.steps,
+            "kernels_per_step": kernels_per_step,
             "roofline": roofline, "cpu_baseline": cpu, "clocks": clocks.summary(), "extras": extras,
         }
         print(json.dumps(line), flush=True)
