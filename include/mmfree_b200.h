@@ -226,6 +226,13 @@ int mmf_hgrn_gated(const void* i_raw, const void* f_raw, int64_t ld, int dtype,
                    const void* lower_bound, float* state, void* o, int64_t B, int64_t T, int64_t D,
                    void* workspace, int64_t workspace_bytes, void* stream);
 
+/* mmf_hgrn_gated with a padding mask: mask is uint8 [B, T] (device), 1 = token, 0 = padding; at a masked position
+ * the input x_t is replaced by zero (the forget gate still applies), mask == NULL means no padding.
+ * Replaces: `i = i.mul_(attention_mask.unsqueeze(-1))`, mmfreelm/layers/hgrn_bit.py:119-120, fused into the scan. */
+int mmf_hgrn_gated_masked(const void* i_raw, const void* f_raw, int64_t ld, int dtype,
+                          const void* lower_bound, const uint8_t* mask, float* state, void* o, int64_t B,
+                          int64_t T, int64_t D, void* workspace, int64_t workspace_bytes, void* stream);
+
 /* Error reporting of the scan kernels (no counterpart in the reference): the kernels wait for their TMA
  * stages with a bounded spin; *failed_host becomes 1 if any launch of this process ever gave up on such a
  * wait (its outputs are then undefined).  Synchronises with the device. */

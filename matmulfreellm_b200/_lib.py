@@ -46,6 +46,8 @@ PROTOTYPES = {
     "mmf_hgrn_status": (c_int, [c_void_p]),
     "mmf_hgrn_gated": (c_int, [c_void_p, c_void_p, c_int64, c_int, c_void_p, c_void_p, c_void_p, c_int64, c_int64,
                                c_int64, c_void_p, c_int64, c_void_p]),
+    "mmf_hgrn_gated_masked": (c_int, [c_void_p, c_void_p, c_int64, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int64,
+                                      c_int64, c_int64, c_void_p, c_int64, c_void_p]),
     "mmf_prenorm_quant": (c_int, [c_void_p, c_int64, c_void_p, c_int64, c_int, c_int, c_void_p, c_float, c_void_p,
                                   c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_float, c_void_p, c_void_p, c_void_p,
                                   c_int64, c_int64, c_void_p]),

@@ -152,8 +152,9 @@ __device__ __forceinline__ void gate_transform(float& xv, float& f, bool has_lb,
 template <typename TX, typename TG, int MODE, bool AGG>
 __global__ void __launch_bounds__(HG_THREADS)
 hgrn_scan_kernel(const __grid_constant__ CUtensorMap x_map, const __grid_constant__ CUtensorMap g_map,
-                 const __grid_constant__ CUtensorMap o_map, const TX* __restrict__ lb, const void* __restrict__ h0,
-                 void* __restrict__ ht, int state_dt, int T, int D, int NT, int chunk_len, HgrnWs ws) {
+                 const __grid_constant__ CUtensorMap o_map, const TX* __restrict__ lb, const uint8_t* __restrict__ mask,
+                 const void* __restrict__ h0, void* __restrict__ ht, int state_dt, int T, int D, int NT, int chunk_len,
+                 HgrnWs ws) {
     pdl_trigger();
     extern __shared__ uint8_t smem_dyn[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_dyn) + 127) & ~uintptr_t(127));
@@ -244,12 +245,15 @@ hgrn_scan_kernel(const __grid_constant__ CUtensorMap x_map, const __grid_constan
             const TX* px = sx + (buf * HG_TS + sub * HG_SUBT) * HG_BD + lc;
             const TG* pg = sg + (buf * HG_TS + sub * HG_SUBT) * HG_BD + lc;
             float2 h = make_float2(0.0f, 0.0f), a = make_float2(1.0f, 1.0f);
+            // padding mask of the sequence (attention layer only): a masked position contributes no input
+            const uint8_t* pm = mask ? mask + (int64_t)b * T + t_begin + s * HG_TS + sub * HG_SUBT : nullptr;
             if (rows == HG_TS) {
 #pragma unroll
                 for (int j = 0; j < HG_SUBT; ++j) {
                     float2 xv = ld2(px + j * HG_BD), f = ld2(pg + j * HG_BD);
                     gate_transform<TX, MODE>(xv.x, f.x, has_lb, lbv.x, oml.x);
                     gate_transform<TX, MODE>(xv.y, f.y, has_lb, lbv.y, oml.y);
+                    if (pm && !pm[j]) xv = make_float2(0.0f, 0.0f);
                     h.x = fmaf(f.x, h.x, xv.x); h.y = fmaf(f.y, h.y, xv.y);
                     a.x *= f.x; a.y *= f.y;
                     hl[j] = h; ap[j] = a;
@@ -263,6 +267,8 @@ hgrn_scan_kernel(const __grid_constant__ CUtensorMap x_map, const __grid_constan
                     if (sub * HG_SUBT + j >= rows) {   // steps past the end of the sequence are the identity
                         xv = make_float2(0.0f, 0.0f);
                         f = make_float2(1.0f, 1.0f);
+                    } else if (pm && !pm[j]) {
+                        xv = make_float2(0.0f, 0.0f);
                     }
                     h.x = fmaf(f.x, h.x, xv.x); h.y = fmaf(f.y, h.y, xv.y);
                     a.x *= f.x; a.y *= f.y;
@@ -339,7 +345,8 @@ hgrn_scan_kernel(const __grid_constant__ CUtensorMap x_map, const __grid_constan
 template <typename TX, typename TG, int MODE>
 __global__ void __launch_bounds__(256)
 hgrn_step_kernel(const TX* __restrict__ x, int64_t ld_x, const TG* __restrict__ g, int64_t ld_g, const TX* __restrict__ lb,
-                 const void* __restrict__ h0, void* __restrict__ ht, int state_dt, TX* __restrict__ o, int64_t B, int D) {
+                 const uint8_t* __restrict__ mask, const void* __restrict__ h0, void* __restrict__ ht, int state_dt,
+                 TX* __restrict__ o, int64_t B, int D) {
     pdl_trigger();
     pdl_wait();
     const int64_t idx = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) * 2;
@@ -356,6 +363,7 @@ hgrn_step_kernel(const TX* __restrict__ x, int64_t ld_x, const TG* __restrict__ 
     }
     gate_transform<TX, MODE>(xv.x, f.x, has_lb, lbv.x, oml.x);
     gate_transform<TX, MODE>(xv.y, f.y, has_lb, lbv.y, oml.y);
+    if (mask && !mask[b]) xv = make_float2(0.0f, 0.0f);
     float h0x = 0.0f, h0y = 0.0f;
     if (h0) {
         h0x = load_state_dt(h0, idx, state_dt);
@@ -400,12 +408,12 @@ int hgrn_make_map(CUtensorMap* map, const void* base, int es, int64_t ld, int64_
 }
 
 template <typename TX, typename TG, int MODE>
-int hgrn_launch(const void* x, int64_t ld_x, const void* g, int64_t ld_g, const void* lb, const void* h0, void* ht,
-                int state_dt, void* o, int64_t B, int64_t T, int64_t D, int NT, HgrnWs ws, cudaStream_t st) {
+int hgrn_launch(const void* x, int64_t ld_x, const void* g, int64_t ld_g, const void* lb, const uint8_t* mask, const void* h0,
+                void* ht, int state_dt, void* o, int64_t B, int64_t T, int64_t D, int NT, HgrnWs ws, cudaStream_t st) {
     if (T == 1) {   // a single step: no tiles, no scan
         const int64_t pairs = B * D / 2;
         MMF_CUDA(mmf_launch_pdl(hgrn_step_kernel<TX, TG, MODE>, dim3((unsigned)((pairs + 255) / 256)), dim3(256), 0, st, (const TX*)x,
-                                ld_x, (const TG*)g, ld_g, (const TX*)lb, h0, ht, state_dt, (TX*)o, B, (int)D));
+                                ld_x, (const TG*)g, ld_g, (const TX*)lb, mask, h0, ht, state_dt, (TX*)o, B, (int)D));
         MMF_LAUNCH_CHECK("hgrn_step_kernel");
         return MMF_OK;
     }
@@ -422,13 +430,13 @@ int hgrn_launch(const void* x, int64_t ld_x, const void* g, int64_t ld_g, const 
         auto k1 = hgrn_scan_kernel<TX, TG, MODE, true>;
         MMF_CUDA(cudaFuncSetAttribute(k1, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
         const dim3 grid1(grid.x, (unsigned)(NT - 1), grid.z);
-        MMF_CUDA(mmf_launch_pdl(k1, grid1, dim3(HG_THREADS), smem, st, x_map, g_map, o_map, (const TX*)lb, h0,
+        MMF_CUDA(mmf_launch_pdl(k1, grid1, dim3(HG_THREADS), smem, st, x_map, g_map, o_map, (const TX*)lb, mask, h0,
                                 (void*)nullptr, state_dt, (int)T, (int)D, NT, chunk_len, ws));
         MMF_LAUNCH_CHECK("hgrn_scan_kernel<aggregate>");
     }
     auto k2 = hgrn_scan_kernel<TX, TG, MODE, false>;
     MMF_CUDA(cudaFuncSetAttribute(k2, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    MMF_CUDA(mmf_launch_pdl(k2, grid, dim3(HG_THREADS), smem, st, x_map, g_map, o_map, (const TX*)lb, h0, ht, state_dt,
+    MMF_CUDA(mmf_launch_pdl(k2, grid, dim3(HG_THREADS), smem, st, x_map, g_map, o_map, (const TX*)lb, mask, h0, ht, state_dt,
                             (int)T, (int)D, NT, chunk_len, ws));
     MMF_LAUNCH_CHECK("hgrn_scan_kernel<scan>");
     return MMF_OK;
@@ -477,8 +485,8 @@ extern "C" int mmf_hgrn_scan(const void* x, int x_dtype, const void* g, int g_dt
     cudaStream_t st = (cudaStream_t)stream;
     int rc = MMF_OK;
 #define HG_GO(TX, TG)                                                                                                  \
-    rc = gate_is_log ? hgrn_launch<TX, TG, HG_LOG>(x, D, g, D, nullptr, h0, ht, state_dtype, o, B, T, D, NT, ws, st)     \
-                     : hgrn_launch<TX, TG, HG_LINEAR>(x, D, g, D, nullptr, h0, ht, state_dtype, o, B, T, D, NT, ws, st)
+    rc = gate_is_log ? hgrn_launch<TX, TG, HG_LOG>(x, D, g, D, nullptr, nullptr, h0, ht, state_dtype, o, B, T, D, NT, ws, st)     \
+                     : hgrn_launch<TX, TG, HG_LINEAR>(x, D, g, D, nullptr, nullptr, h0, ht, state_dtype, o, B, T, D, NT, ws, st)
     if (x_dtype == MMF_F32 && g_dtype == MMF_F32) { HG_GO(float, float); }
     else if (x_dtype == MMF_BF16 && g_dtype == MMF_BF16) { HG_GO(__nv_bfloat16, __nv_bfloat16); }
     else if (x_dtype == MMF_BF16 && g_dtype == MMF_F32) { HG_GO(__nv_bfloat16, float); }
@@ -489,9 +497,9 @@ extern "C" int mmf_hgrn_scan(const void* x, int x_dtype, const void* g, int g_dt
     return rc;
 }
 
-extern "C" int mmf_hgrn_gated(const void* i_raw, const void* f_raw, int64_t ld, int dtype, const void* lower_bound,
-                              float* state, void* o, int64_t B, int64_t T, int64_t D, void* workspace,
-                              int64_t workspace_bytes, void* stream) {
+extern "C" int mmf_hgrn_gated_masked(const void* i_raw, const void* f_raw, int64_t ld, int dtype, const void* lower_bound,
+                                     const uint8_t* mask, float* state, void* o, int64_t B, int64_t T, int64_t D,
+                                     void* workspace, int64_t workspace_bytes, void* stream) {
     MMF_REQUIRE(i_raw && f_raw && state && o, MMF_ERR_BAD_ARG, "mmf_hgrn_gated: null pointer");
     MMF_REQUIRE(mmf_dtype_ok(dtype), MMF_ERR_BAD_ARG, "mmf_hgrn_gated: unknown dtype %d", dtype);
     MMF_REQUIRE(B >= 0 && B < 65536 && T >= 0 && T < (1ll << 31) && D > 0 && D < (1ll << 31) && D % 8 == 0 && ld >= D,
@@ -506,10 +514,16 @@ extern "C" int mmf_hgrn_gated(const void* i_raw, const void* f_raw, int64_t ld, 
     if (rc0 != MMF_OK) return rc0;
     int rc = MMF_OK;
     MMF_DISPATCH(dtype, Ty, {
-        rc = hgrn_launch<Ty, Ty, HG_RAW>(i_raw, ld, f_raw, ld, lower_bound, state, state, MMF_F32, o, B, T, D, NT, ws,
+        rc = hgrn_launch<Ty, Ty, HG_RAW>(i_raw, ld, f_raw, ld, lower_bound, mask, state, state, MMF_F32, o, B, T, D, NT, ws,
                                          (cudaStream_t)stream);
     });
     return rc;
+}
+
+extern "C" int mmf_hgrn_gated(const void* i_raw, const void* f_raw, int64_t ld, int dtype, const void* lower_bound,
+                              float* state, void* o, int64_t B, int64_t T, int64_t D, void* workspace,
+                              int64_t workspace_bytes, void* stream) {
+    return mmf_hgrn_gated_masked(i_raw, f_raw, ld, dtype, lower_bound, nullptr, state, o, B, T, D, workspace, workspace_bytes, stream);
 }
 
 extern "C" int mmf_hgrn_status(int* failed_host) {

@@ -151,8 +151,10 @@ class FusedRunner:
 
     @torch.no_grad()
     def forward(self, input_ids, inputs_embeds, states, last_only: bool, want_logits: bool = True,
-                want_hidden: bool = False):
-        """states: list of fp32 [B, ..., h]-shaped tensors advanced in place.  Returns (logits | None, hidden | None)."""
+                want_hidden: bool = False, attention_mask=None):
+        """states: list of fp32 [B, ..., h]-shaped tensors advanced in place.  attention_mask: optional [B, T], zero at
+        (left-)padding positions — their input to the recurrence is dropped, as the reference's attention layer does
+        (layers/hgrn_bit.py:119-120); only used for T > 1.  Returns (logits | None, hidden | None)."""
         model = self.lm.model
         if inputs_embeds is None:
             x = kernels.embedding(model.embeddings.weight, input_ids)
@@ -162,6 +164,9 @@ class FusedRunner:
         M = B * T
         x = x.reshape(M, h)
         lbs = self.lower_bounds
+        mask = None
+        if attention_mask is not None and T > 1:
+            mask = (attention_mask.to(x.device) != 0).to(torch.uint8).contiguous()
         stream, z = x, None                      # residual stream, last block's MLP output
         for i, L in enumerate(self.layers):
             if i == 0:
@@ -175,7 +180,7 @@ class FusedRunner:
                 q, dq, rs = kernels.decode_mix(ifg.view(M, 3 * h), lb, states[i].view(B, h), L["gnorm_w"], L["gnorm_eps"],
                                                L["o_nw"], L["eps_bl"])
             else:
-                o = kernels.hgrn_gated(ifg[:, :, :h], ifg[:, :, h:2 * h], lb, states[i].view(B, h))
+                o = kernels.hgrn_gated(ifg[:, :, :h], ifg[:, :, h:2 * h], lb, states[i].view(B, h), mask=mask)
                 q, dq, rs = kernels.gatenorm_quant(ifg.view(M, 3 * h)[:, 2 * h:], o.view(M, h), L["gnorm_w"], L["gnorm_eps"],
                                                    L["o_nw"], L["eps_bl"])
             attn_out = kernels.bitlinear(q, dq, rs, L["o"], self.dtype)

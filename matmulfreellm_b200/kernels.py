@@ -236,10 +236,10 @@ def hgrn_scan(x: torch.Tensor, g: torch.Tensor, initial_state: Optional[torch.Te
 
 
 def hgrn_gated(i_raw: torch.Tensor, f_raw: torch.Tensor, lower_bound: Optional[torch.Tensor], state: torch.Tensor,
-               out: Optional[torch.Tensor] = None) -> torch.Tensor:
+               out: Optional[torch.Tensor] = None, mask: Optional[torch.Tensor] = None) -> torch.Tensor:
     """Gated recurrence from the raw i/f projections: i_raw, f_raw are [B,T,D] views with unit inner stride
     and a common row stride (e.g. column slabs of one [B,T,3D] tensor); `state` fp32 [B,D] is advanced in
-    place; returns o [B,T,D]."""
+    place; returns o [B,T,D].  `mask`: optional uint8 [B,T], 0 at padding positions (their input is dropped)."""
     _need_cuda(i_raw, f_raw, state, lower_bound)
     B, T, D = i_raw.shape
     ld = i_raw.stride(1)
@@ -254,8 +254,10 @@ def hgrn_gated(i_raw: torch.Tensor, f_raw: torch.Tensor, lower_bound: Optional[t
     o = out if out is not None else torch.empty(B, T, D, dtype=i_raw.dtype, device=i_raw.device)
     nbytes = _lib.load().mmf_hgrn_workspace_bytes(B, T, D)
     ws = torch.empty(nbytes, dtype=torch.uint8, device=i_raw.device) if nbytes else None
-    _lib.call("mmf_hgrn_gated", i_raw.data_ptr(), f_raw.data_ptr(), ld, _code(i_raw.dtype), _ptr(lower_bound),
-              state.data_ptr(), o.data_ptr(), B, T, D, _ptr(ws), nbytes, _stream())
+    if mask is not None and (mask.dtype != torch.uint8 or mask.shape != (B, T) or not mask.is_contiguous() or not mask.is_cuda):
+        raise ValueError("mask must be a contiguous uint8 CUDA tensor [B, T]")
+    _lib.call("mmf_hgrn_gated_masked", i_raw.data_ptr(), f_raw.data_ptr(), ld, _code(i_raw.dtype), _ptr(lower_bound),
+              _ptr(mask), state.data_ptr(), o.data_ptr(), B, T, D, _ptr(ws), nbytes, _stream())
     return o
 
 

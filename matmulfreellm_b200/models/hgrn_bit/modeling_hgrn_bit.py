@@ -234,7 +234,8 @@ class HGRNBitForCausalLM(HGRNBitPreTrainedModel):
         if use_cache is None:
             use_cache = self.config.use_cache if not self.training else False
         if self._can_fuse(input_ids, inputs_embeds, attention_mask, output_hidden_states):
-            logits, cache = self._forward_fused(input_ids, inputs_embeds, past_key_values, use_cache, last_token_only)
+            logits, cache = self._forward_fused(input_ids, inputs_embeds, past_key_values, use_cache, last_token_only,
+                                                attention_mask)
             if not return_dict:
                 return tuple(x for x in (logits, cache) if x is not None)
             return CausalLMOutputWithPast(loss=None, logits=logits, past_key_values=cache, hidden_states=None,
@@ -263,11 +264,12 @@ class HGRNBitForCausalLM(HGRNBitPreTrainedModel):
         if self.config.expand_ratio != 1 or self.config.hidden_size % 16 or self.config.intermediate_size is not None \
                 and self.config.intermediate_size % 16:
             return False
-        if attention_mask is not None and not bool(attention_mask.all()):   # left padding: module path
-            return False
+        ref = input_ids if input_ids is not None else inputs_embeds
+        if attention_mask is not None and ref.shape[1] == 1 and not bool(attention_mask.all()):
+            return False   # a masked single token: module path (the fused decode step has no mask input)
         return True
 
-    def _forward_fused(self, input_ids, inputs_embeds, past_key_values, use_cache, last_token_only):
+    def _forward_fused(self, input_ids, inputs_embeds, past_key_values, use_cache, last_token_only, attention_mask=None):
         from ...engine import fused_runner
         ref = input_ids if input_ids is not None else inputs_embeds
         B = ref.shape[0]
@@ -281,7 +283,8 @@ class HGRNBitForCausalLM(HGRNBitPreTrainedModel):
         else:
             cache = RecurrentCache.from_legacy_cache([layer.attn.init_state(B) for layer in layers])
         states = [cache.states[i][-1] for i in range(len(layers))]
-        logits, _ = fused_runner(self).forward(input_ids, inputs_embeds, states, last_token_only)
+        logits, _ = fused_runner(self).forward(input_ids, inputs_embeds, states, last_token_only,
+                                               attention_mask=attention_mask)
         if use_cache and past_key_values is not None and len(layers):
             cache._seen_tokens += ref.shape[1]
         return logits, (cache.to_legacy_cache() if use_cache else None)

@@ -446,6 +446,32 @@ def test_gatenorm_and_swiglu_quant(K, dtype):
     _codes_close(q, dq, q_ref, dq_ref, exact=False)
 
 
+@pytest.mark.parametrize("dtype,tol", [(torch.bfloat16, 1e-2), (torch.float32, 1e-4)])
+@pytest.mark.parametrize("B,T,D", [(3, 1, 256), (2, 70, 128), (2, 200, 64)])
+def test_hgrn_gated_with_padding_mask(K, dtype, tol, B, T, D):
+    """Left padding: at masked positions the input gate is zeroed (layers/hgrn_bit.py:119-120), fused into the scan."""
+    g = torch.Generator().manual_seed(B * 1000 + T)
+    ifg = torch.randn(B, T, 3 * D, generator=g).to(dtype)
+    h0 = torch.randn(B, D, generator=g)
+    mask = torch.ones(B, T, dtype=torch.uint8)
+    for b in range(B):
+        mask[b, : (b * 37) % max(T // 2, 1) if T > 1 else b % 2] = 0
+    f = ifg[..., D:2 * D].sigmoid()
+    i = O.swiglu_ref(ifg[..., :D], 1 - f) * mask.unsqueeze(-1).to(dtype)
+    o_ref, ht_ref = O.naive_recurrent_hgrn(i.unsqueeze(1), f.unsqueeze(1), h0.unsqueeze(1), True)
+    state = dev(h0.clone())
+    d_ifg = dev(ifg)
+    o = K.hgrn_gated(d_ifg[..., :D], d_ifg[..., D:2 * D], None, state, mask=dev(mask))
+    so = o_ref.float().abs().max().item()
+    assert (o.cpu().float() - o_ref.squeeze(1).float()).abs().max().item() <= tol * so
+    assert (state.cpu() - ht_ref.squeeze(1)).abs().max().item() <= max(tol, 1e-4) * ht_ref.abs().max().item()
+    # an all-ones mask changes nothing
+    s1, s2 = dev(h0.clone()), dev(h0.clone())
+    o1 = K.hgrn_gated(d_ifg[..., :D], d_ifg[..., D:2 * D], None, s1, mask=dev(torch.ones(B, T, dtype=torch.uint8)))
+    o2 = K.hgrn_gated(d_ifg[..., :D], d_ifg[..., D:2 * D], None, s2)
+    assert torch.equal(o1, o2) and torch.equal(s1, s2)
+
+
 @pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
 @pytest.mark.parametrize("D", [704, 2048, 2560, 5632])
 def test_fused_row_kernels_many_rows(K, dtype, D):

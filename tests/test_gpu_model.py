@@ -246,6 +246,29 @@ def test_long_prompt_uses_persistent_kernel_with_identical_results(mm):
     kernels.check_status()
 
 
+def test_left_padded_prompt_fused_equals_module_path(mm):
+    """A left-padded batch (attention_mask with leading zeros) runs through the fused chain with the mask applied
+    inside the scan; the module-by-module path applies it as the reference does (i.mul_(mask))."""
+    cfg = tiny_cfg()
+    sd = O.random_weights(cfg, seed=21)
+    ids = torch.randint(0, 32000, (3, 48), generator=torch.Generator().manual_seed(22)).cuda()
+    mask = torch.ones(3, 48, dtype=torch.long, device="cuda")
+    mask[0, :5] = 0
+    mask[2, :17] = 0
+    for dtype, typical, worst in ((torch.float32, 1e-6, 2e-2), (torch.bfloat16, 4e-3, 1e-1)):
+        model = build_gpu_model(sd, cfg, dtype)
+        fused = model(ids, attention_mask=mask, use_cache=True)
+        model.fuse = False
+        plain = model(ids, attention_mask=mask, use_cache=True)
+        del model.fuse
+        _close_up_to_code_flips(fused.logits.float().cpu().numpy(), plain.logits.float().cpu().numpy(), typical, worst)
+        for a, b in zip(fused.past_key_values, plain.past_key_values):
+            _close_up_to_code_flips(a[0].cpu().numpy(), b[0].cpu().numpy(), typical, worst)
+        # and the mask matters: without it the padded rows give different states
+        nomask = model(ids, use_cache=True)
+        assert not torch.equal(nomask.past_key_values[0][0][2], fused.past_key_values[0][0][2])
+
+
 def test_generate_api(mm):
     cfg = tiny_cfg()
     sd = O.random_weights(cfg, seed=1)
