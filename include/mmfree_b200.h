@@ -311,6 +311,15 @@ int mmf_swiglu(const void* x, int64_t ld_x, const void* y, int64_t ld_y, void* o
 int mmf_argmax_rows(const void* logits, int dtype, int64_t ld, int64_t M, int64_t V,
                     int64_t* idx, void* stream);
 
+/* Nucleus sampling helper: idx[m] = one token drawn from softmax(logits[m, 0:V] / temperature) restricted to the
+ * smallest set of most probable tokens whose mass reaches top_p (top_p >= 1: no restriction; tokens tied with the
+ * least probable kept one are all kept), using the caller's uniform number uniforms[m] in [0, 1): the first kept
+ * token, in index order, at which the running kept mass exceeds uniforms[m] * (kept mass).  Deterministic.
+ * Replaces: the sampling step of model.generate(..., do_sample=True, top_p=0.4, temperature=0.6) in the reference's
+ * generate.py:11 (transformers' TemperatureLogitsWarper + TopPLogitsWarper + multinomial). */
+int mmf_sample_top_p(const void* logits, int dtype, int64_t ld, float temperature, float top_p,
+                     const float* uniforms, int64_t* idx, int64_t M, int64_t V, void* stream);
+
 /* out[m, :] = table[ids[m], :].  Replaces: nn.Embedding lookup, modeling_hgrn_bit.py:211-213. */
 int mmf_embedding(const void* table, int dtype, int64_t V, int64_t D, const int64_t* ids,
                   void* out, int64_t M, void* stream);

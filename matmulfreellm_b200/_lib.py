@@ -64,6 +64,7 @@ PROTOTYPES = {
     "mmf_swiglu": (c_int, [c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_int64, c_int, c_int64, c_int64,
                            c_void_p]),
     "mmf_argmax_rows": (c_int, [c_void_p, c_int, c_int64, c_int64, c_int64, c_void_p, c_void_p]),
+    "mmf_sample_top_p": (c_int, [c_void_p, c_int, c_int64, c_float, c_float, c_void_p, c_void_p, c_int64, c_int64, c_void_p]),
     "mmf_embedding": (c_int, [c_void_p, c_int, c_int64, c_int64, c_void_p, c_void_p, c_int64, c_void_p]),
 }
 

@@ -260,6 +260,85 @@ argmax_kernel(const T* __restrict__ logits, int64_t ld, int V, int64_t* __restri
     }
 }
 
+// Nucleus (top-p) sampling of one token per row, deterministic given one uniform number per row:
+//   p_i = softmax(logits_i / temperature); keep the smallest set of most probable tokens whose mass reaches top_p
+//   (all tokens with p_i >= tau, tau found by bisection on the float bit pattern; tokens tied at tau are all kept);
+//   the sample is the first kept token, in index order, at which the running kept mass exceeds u * (kept mass).
+// Sums are accumulated in fp64 in a fixed order, so the result does not depend on scheduling.
+template <typename T>
+__global__ void __launch_bounds__(256)
+sample_top_p_kernel(const T* __restrict__ logits, int64_t ld, int V, float inv_temp, float top_p,
+                    const float* __restrict__ uniforms, int64_t* __restrict__ out) {
+    pdl_trigger();
+    pdl_wait();
+    __shared__ double red[40];
+    __shared__ float redf[40];
+    __shared__ double s_part[256];
+    __shared__ int s_found;
+    const T* r = logits + blockIdx.x * ld;
+    const int chunk = (V + 255) / 256;
+    const int c0 = min(V, (int)threadIdx.x * chunk), c1 = min(V, c0 + chunk);   // this thread's contiguous tokens
+    float mx = -INFINITY;
+    for (int c = c0; c < c1; ++c) mx = fmaxf(mx, __fmul_rn(to_f32(r[c]), inv_temp));
+    mx = warp_max(mx);
+    if ((threadIdx.x & 31) == 0) redf[threadIdx.x >> 5] = mx;
+    __syncthreads();
+#pragma unroll
+    for (int w = 0; w < 8; ++w) mx = fmaxf(mx, redf[w]);
+    auto prob = [&](int c) { return expf(__fsub_rn(__fmul_rn(to_f32(r[c]), inv_temp), mx)); };
+    auto mass_ge = [&](float tau) {          // total probability (unnormalised) of the tokens with p >= tau
+        double acc = 0.0;
+        for (int c = c0; c < c1; ++c) {
+            const float p = prob(c);
+            if (p >= tau) acc += (double)p;
+        }
+        return block_sum(acc, red);
+    };
+    const double total = mass_ge(0.0f);
+    const double want = (double)top_p * total;
+    uint32_t lo = 0u, hi = __float_as_uint(1.0f) + 1u;    // mass_ge(lo) >= want > mass_ge(hi)  (p <= 1 everywhere)
+    while (hi - lo > 1u) {
+        const uint32_t mid = lo + (hi - lo) / 2u;
+        if (mass_ge(__uint_as_float(mid)) >= want) lo = mid; else hi = mid;
+    }
+    const float tau = __uint_as_float(lo);
+    // kept mass per thread, then an exclusive prefix in thread order (= token order)
+    double part = 0.0;
+    for (int c = c0; c < c1; ++c) {
+        const float p = prob(c);
+        if (p >= tau) part += (double)p;
+    }
+    s_part[threadIdx.x] = part;
+    if (threadIdx.x == 0) s_found = 0x7fffffff;
+    __syncthreads();
+    double before = 0.0, kept = 0.0;
+    for (int t = 0; t < 256; ++t) {
+        if (t == (int)threadIdx.x) before = kept;
+        kept += s_part[t];
+    }
+    const double target = (double)uniforms[blockIdx.x] * kept;
+    if (part > 0.0 && target >= before && target < before + part) {
+        double run = before;
+        for (int c = c0; c < c1; ++c) {
+            const float p = prob(c);
+            if (p >= tau) {
+                run += (double)p;
+                if (run > target) { atomicMin(&s_found, c); break; }
+            }
+        }
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        // rounding may leave the last interval open at its end: fall back to the last kept token
+        int found = s_found;
+        if (found == 0x7fffffff) {
+            for (int c = V - 1; c >= 0; --c)
+                if (prob(c) >= tau) { found = c; break; }
+        }
+        out[blockIdx.x] = found == 0x7fffffff ? 0 : found;
+    }
+}
+
 __global__ void __launch_bounds__(128)
 embedding_kernel(const uint8_t* __restrict__ table, int64_t V, int64_t row_bytes,
                  const int64_t* __restrict__ ids, uint8_t* __restrict__ out, int vec16) {
@@ -424,5 +503,21 @@ extern "C" int mmf_embedding(const void* table, int dtype, int64_t V, int64_t D,
     MMF_CUDA(mmf_launch_pdl(embedding_kernel, dim3((unsigned)M), dim3(128), 0, (cudaStream_t)stream, (const uint8_t*)table, V, row_bytes, ids,
                                                                     (uint8_t*)out, vec16));
     MMF_LAUNCH_CHECK("embedding_kernel");
+    return MMF_OK;
+}
+
+extern "C" int mmf_sample_top_p(const void* logits, int dtype, int64_t ld, float temperature, float top_p, const float* uniforms,
+                                int64_t* idx, int64_t M, int64_t V, void* stream) {
+    MMF_REQUIRE(logits && uniforms && idx, MMF_ERR_BAD_ARG, "mmf_sample_top_p: null pointer");
+    MMF_REQUIRE(mmf_dtype_ok(dtype), MMF_ERR_BAD_ARG, "mmf_sample_top_p: unknown dtype %d", dtype);
+    MMF_REQUIRE(M >= 0 && V > 0 && V < (1ll << 31) && ld >= V, MMF_ERR_BAD_SHAPE, "mmf_sample_top_p: bad sizes");
+    MMF_REQUIRE(temperature > 0.0f && top_p >= 0.0f, MMF_ERR_BAD_ARG, "mmf_sample_top_p: need temperature > 0 and top_p >= 0");
+    if (M == 0) return MMF_OK;
+    const float inv_temp = 1.0f / temperature;
+    MMF_DISPATCH(dtype, T, {
+        MMF_CUDA(mmf_launch_pdl(sample_top_p_kernel<T>, dim3((unsigned)M), dim3(256), 0, (cudaStream_t)stream, (const T*)logits, ld, (int)V,
+                                inv_temp, top_p < 1.0f ? top_p : 1.0f, uniforms, idx));
+    });
+    MMF_LAUNCH_CHECK("sample_top_p_kernel");
     return MMF_OK;
 }

@@ -422,6 +422,22 @@ def argmax_rows(logits: torch.Tensor) -> torch.Tensor:
     return idx.reshape(logits.shape[:-1])
 
 
+def sample_top_p(logits: torch.Tensor, temperature: float, top_p: float, uniforms: torch.Tensor) -> torch.Tensor:
+    """One token per row from softmax(logits / temperature) restricted to its top-p nucleus, using the caller's uniform
+    numbers (float32 in [0, 1), one per row): deterministic for given inputs.  Returns int64 indices."""
+    _need_cuda(logits, uniforms)
+    l2 = logits.reshape(-1, logits.shape[-1])
+    if l2.stride(1) != 1:
+        l2 = l2.contiguous()
+    if uniforms.dtype != torch.float32 or uniforms.numel() != l2.shape[0] or not uniforms.is_contiguous():
+        raise ValueError("uniforms must be contiguous float32 with one value per row")
+    idx = torch.empty(l2.shape[0], dtype=torch.int64, device=logits.device)
+    if l2.shape[0]:
+        _lib.call("mmf_sample_top_p", l2.data_ptr(), _code(l2.dtype), l2.stride(0), float(temperature), float(top_p),
+                  uniforms.data_ptr(), idx.data_ptr(), l2.shape[0], l2.shape[1], _stream())
+    return idx.reshape(logits.shape[:-1])
+
+
 def embedding(table: torch.Tensor, ids: torch.Tensor) -> torch.Tensor:
     _need_cuda(table, ids)
     if ids.dtype != torch.int64:

@@ -291,22 +291,33 @@ class HGRNBitForCausalLM(HGRNBitPreTrainedModel):
 
     @torch.no_grad()
     def generate(self, input_ids: torch.LongTensor, max_new_tokens: int = 20, max_length: Optional[int] = None,
-                 do_sample: bool = False, eos_token_id: Optional[int] = None, **kwargs) -> torch.LongTensor:
-        """Greedy decoding: prefill once, then one cached single-token forward per new token.
+                 do_sample: bool = False, eos_token_id: Optional[int] = None, top_p: float = 1.0, temperature: float = 1.0,
+                 generator: Optional[torch.Generator] = None, attention_mask: Optional[torch.Tensor] = None,
+                 **kwargs) -> torch.LongTensor:
+        """Prefill once, then one cached single-token forward per new token; greedy, or with `do_sample=True` nucleus
+        sampling (temperature, then top-p, as `generate.py:11` of the reference asks of transformers).
 
         The reference defers to transformers' GenerationMixin (:311-324), which current transformers releases
-        no longer provide to this class; this loop covers the deterministic strategy.  Returns
-        [B, prompt + new] token ids like GenerationMixin.generate."""
-        if do_sample:
-            raise NotImplementedError("only greedy decoding (do_sample=False) is implemented")
+        no longer provide to this class.  Sampling draws one uniform number per sequence and step from `generator`
+        (a CUDA generator; the default one if None) and is deterministic given those.  `attention_mask` marks
+        left padding of the prompt.  Returns [B, prompt + new] token ids like GenerationMixin.generate."""
+        if kwargs.get("num_beams", 1) != 1 or kwargs.get("top_k"):
+            raise NotImplementedError("only greedy decoding and temperature / top-p sampling are implemented")
+
+        def pick(logits):
+            if not do_sample:
+                return kernels.argmax_rows(logits)
+            u = torch.rand(logits.shape[0], device=logits.device, dtype=torch.float32, generator=generator)
+            return kernels.sample_top_p(logits, temperature, top_p, u)
+
         if max_length is not None:
             max_new_tokens = max(0, max_length - input_ids.shape[1])
-        out = self(input_ids=input_ids, use_cache=True, last_token_only=True)
+        out = self(input_ids=input_ids, attention_mask=attention_mask, use_cache=True, last_token_only=True)
         cache = RecurrentCache.from_legacy_cache(out.past_key_values, input_ids.shape[1])
         tokens = [input_ids]
         finished = torch.zeros(input_ids.shape[0], dtype=torch.bool, device=input_ids.device)
         for step in range(max_new_tokens):
-            nxt = kernels.argmax_rows(out.logits[:, -1])
+            nxt = pick(out.logits[:, -1])
             if eos_token_id is not None:
                 nxt = torch.where(finished, torch.full_like(nxt, eos_token_id), nxt)
                 finished |= nxt == eos_token_id

@@ -360,3 +360,38 @@ def hgrn_case(B: int, T: int, D: int, seed: int = 0, dtype=torch.bfloat16):
     g_log = F.logsigmoid(torch.randn(B, 1, T, D, generator=g))
     x = ((1 - torch.exp(g_log)) * F.silu(torch.randn(B, 1, T, D, generator=g))).to(dtype)
     return x, g_log
+
+def sample_top_p_ref(logits, temperature: float, top_p: float, uniforms):
+    """Nucleus sampling with caller-supplied uniform numbers, restating what the reference asks of transformers in
+    generate.py:11 (`do_sample=True, top_p=..., temperature=...`): logits / temperature -> softmax -> keep the
+    smallest set of most probable tokens whose mass reaches top_p (ties with the least probable kept token kept) ->
+    draw by inverse CDF in token order: the first kept token whose running kept mass exceeds u * kept mass.
+    Returns (tokens int64 [M], margin [M]) where margin is the distance of u * kept mass to the nearest CDF step and
+    of top_p to the nearest nucleus step, relative to the total mass (rows with a tiny margin are ill-conditioned)."""
+    import numpy as np
+    z = np.asarray(logits, dtype=np.float32) * np.float32(1.0 / temperature)
+    p = np.exp((z - z.max(-1, keepdims=True)).astype(np.float32)).astype(np.float64)
+    out = np.zeros(p.shape[0], dtype=np.int64)
+    margin = np.zeros(p.shape[0])
+    for m in range(p.shape[0]):
+        row = p[m]
+        total = row.sum()
+        order = np.argsort(-row, kind="stable")
+        csum = np.cumsum(row[order])
+        want = min(top_p, 1.0) * total
+        k = int(np.searchsorted(csum, want, side="left"))          # first position with csum >= want
+        k = min(k, len(row) - 1)
+        tau = row[order[k]]
+        kept = row >= tau
+        kp = np.where(kept, row, 0.0)
+        c = np.cumsum(kp)
+        target = float(uniforms[m]) * c[-1]
+        idx = int(np.searchsorted(c, target, side="right"))        # first index with c > target
+        idx = min(idx, len(row) - 1)
+        while not kept[idx]:
+            idx += 1
+        out[m] = idx
+        steps = c[kept]
+        nucleus = np.abs(csum[:-1] - want).min() if top_p < 1.0 and len(row) > 1 else np.inf   # top_p >= 1 keeps everything
+        margin[m] = min(np.abs(steps - target).min(), nucleus) / total
+    return out, margin

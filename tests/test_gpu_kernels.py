@@ -577,3 +577,26 @@ def test_bitlinear_mma_configurations_agree(K):
     finally:
         for kk in range(8):
             lib.mmf_tuning(kk, 0)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("temperature,top_p", [(1.0, 1.0), (0.6, 0.4), (2.0, 0.9), (1.0, 0.0)])
+def test_sample_top_p_vs_oracle(K, dtype, temperature, top_p):
+    """Temperature + nucleus sampling with supplied uniform numbers equals the oracle's inverse-CDF draw on every row
+    whose draw is not within 2e-6 (of the total mass) of a CDF step — there the last bits of the exponentials decide."""
+    g = torch.Generator().manual_seed(int(temperature * 10 + top_p * 100))
+    M, V = 48, 32000
+    logits = (torch.randn(M, V, generator=g) * 3).to(dtype)
+    logits[0, 5:9] = logits[0].max() + 1          # a tie among the most probable tokens
+    u = torch.rand(M, generator=g)
+    u[1] = 0.0
+    ref, margin = O.sample_top_p_ref(logits.float().numpy(), temperature, top_p, u.numpy())
+    got = K.sample_top_p(dev(logits), temperature, top_p, dev(u)).cpu().numpy()
+    safe = margin > 2e-6
+    assert safe.mean() > 0.5 and np.array_equal(got[safe], ref[safe])
+    if top_p == 0.0:                              # degenerates to arg-max (one of the tied maxima, chosen by u)
+        lf = logits.float()
+        assert torch.equal(lf[torch.arange(M), torch.from_numpy(got)], lf.max(-1).values)
+    # same inputs, same tokens
+    again = K.sample_top_p(dev(logits), temperature, top_p, dev(u)).cpu().numpy()
+    assert np.array_equal(got, again)

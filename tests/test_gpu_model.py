@@ -282,4 +282,12 @@ def test_generate_api(mm):
     with pytest.raises(ValueError):
         model.model()
     with pytest.raises(NotImplementedError):
-        model.generate(ids, do_sample=True)
+        model.generate(ids, num_beams=4)
+    # sampling: reproducible from the generator's seed (top_p -> 0 picks among the tied maxima: kernel-level test)
+    g1 = torch.Generator(device="cuda").manual_seed(7)
+    g2 = torch.Generator(device="cuda").manual_seed(7)
+    s1 = model.generate(ids, max_new_tokens=6, do_sample=True, top_p=0.4, temperature=0.6, generator=g1)
+    s2 = model.generate(ids, max_new_tokens=6, do_sample=True, top_p=0.4, temperature=0.6, generator=g2)
+    assert s1.shape == (3, 11) and torch.equal(s1, s2) and torch.equal(s1[:, :5], ids)
+    s0 = model.generate(ids, max_new_tokens=4, do_sample=True, top_p=0.0, generator=g1)
+    assert s0.shape == a.shape and torch.equal(s0[:, :5], ids)
