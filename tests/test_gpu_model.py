@@ -291,3 +291,33 @@ def test_generate_api(mm):
     assert s1.shape == (3, 11) and torch.equal(s1, s2) and torch.equal(s1[:, :5], ids)
     s0 = model.generate(ids, max_new_tokens=4, do_sample=True, top_p=0.0, generator=g1)
     assert s0.shape == a.shape and torch.equal(s0[:, :5], ids)
+
+
+def test_packed_checkpoint_round_trip(mm, tmp_path):
+    """save_packed -> load_packed: the loaded model never holds a latent weight, serves the same packed bytes and
+    produces identical logits and tokens; the bytes in the file are the oracle's packing of the oracle's ternary codes."""
+    from matmulfreellm_b200 import checkpoint
+    cfg = tiny_cfg()
+    sd = O.random_weights(cfg, seed=31)
+    sd["model.lower_bounds"] = 0.3 * torch.randn(2, 256, generator=torch.Generator().manual_seed(4))
+    model = build_gpu_model(sd, cfg, torch.bfloat16)
+    path = str(tmp_path / "tiny.mmfpack.npz")
+    info = checkpoint.save_packed(model, path)
+    n_ternary = sum(v.numel() for k, v in sd.items() if k.endswith("_proj.weight") or k == "lm_head.weight")
+    assert info["bitlinear"] == 2 * 6 + 1
+    assert info["bytes"] < n_ternary // 4 + 2 * 32000 * 256 + 300_000      # 2 bits per weight + the bf16 embedding table
+    # file contents against the oracle (host only)
+    _, manifest, z = checkpoint.read_packed(path)
+    name = "model.layers.1.mlp.gate_proj"
+    codes, mean = O.ternary_codes(sd[name + ".weight"])
+    assert np.array_equal(z[name + ".packed"].view(np.uint32), O.pack_ternary(codes).reshape(-1))
+    assert z[name + ".scale"][0] == np.float32(mean) and manifest["bitlinear"][name] == [1408, 256]
+    # load and compare
+    loaded = checkpoint.load_packed(path, "cuda")
+    assert all(m.weight.numel() == 0 for m in loaded.modules() if type(m).__name__ in ("BitLinear", "FusedBitLinear"))
+    ids = torch.randint(0, 32000, (2, 24), generator=torch.Generator().manual_seed(5)).cuda()
+    a, b = model(ids, use_cache=True), loaded(ids, use_cache=True)
+    assert torch.equal(a.logits, b.logits)
+    for x, y in zip(a.past_key_values, b.past_key_values):
+        assert torch.equal(x[0], y[0])
+    assert torch.equal(model.generate(ids, max_new_tokens=8), loaded.generate(ids, max_new_tokens=8))
