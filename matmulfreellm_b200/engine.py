@@ -17,15 +17,16 @@ class GreedyDecoder:
 
     `prefill(prompt)` runs the prompt once and seeds the static cache and the first token; each `step()`
     replays the captured graph: it reads `self.ids` [B,1], advances every layer's recurrent state in place,
-    writes the next token to `self.next` [B] and feeds it back into `self.ids`.
+    writes the next token to `self.next` [B], which is the same buffer as `self.ids`.
     """
 
     def __init__(self, model, batch_size: int, use_graph: bool = True):
         self.model, self.B = model, batch_size
         dev = next(model.parameters()).device
         self.device = dev
-        self.ids = torch.zeros(batch_size, 1, dtype=torch.int64, device=dev)
+        # `next` [B] and `ids` [B,1] are two views of one buffer: the arg-max of a step writes the next step's input
         self.next = torch.zeros(batch_size, dtype=torch.int64, device=dev)
+        self.ids = self.next.view(batch_size, 1)
         self.cache = RecurrentCache.from_legacy_cache(
             [layer.attn.init_state(batch_size) for layer in model.model.layers])
         self.graph: Optional[torch.cuda.CUDAGraph] = None
@@ -34,9 +35,7 @@ class GreedyDecoder:
 
     def _step_eager(self):
         out = self.model(input_ids=self.ids, past_key_values=self.cache, use_cache=True)
-        nxt = kernels.argmax_rows(out.logits[:, -1])
-        self.next.copy_(nxt)
-        self.ids.copy_(nxt[:, None])
+        kernels.argmax_rows(out.logits[:, -1], out=self.next)
 
     def _capture(self):
         saved = [tuple(s.clone() for s in layer) for layer in self.cache.states]
@@ -69,9 +68,7 @@ class GreedyDecoder:
         for layer, new in zip(self.cache.states, out.past_key_values):
             for dst, src in zip(layer, new):
                 dst.copy_(src)
-        nxt = kernels.argmax_rows(out.logits[:, -1])
-        self.next.copy_(nxt)
-        self.ids.copy_(nxt[:, None])
+        kernels.argmax_rows(out.logits[:, -1], out=self.next)
         return self.next
 
     @torch.no_grad()

@@ -411,15 +411,22 @@ def swiglu(x: torch.Tensor, y: torch.Tensor) -> torch.Tensor:
     return out.view(shape)
 
 
-def argmax_rows(logits: torch.Tensor) -> torch.Tensor:
+def argmax_rows(logits: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """First index of the maximum of every row; `out`: optional contiguous int64 tensor with one element per row."""
     _need_cuda(logits)
     l2 = logits.reshape(-1, logits.shape[-1])
     if l2.stride(1) != 1:
         l2 = l2.contiguous()
-    idx = torch.empty(l2.shape[0], dtype=torch.int64, device=logits.device)
-    _lib.call("mmf_argmax_rows", l2.data_ptr(), _code(l2.dtype), l2.stride(0), l2.shape[0], l2.shape[1],
-              idx.data_ptr(), _stream())
-    return idx.reshape(logits.shape[:-1])
+    if out is None:
+        idx = torch.empty(l2.shape[0], dtype=torch.int64, device=logits.device)
+    else:
+        if out.dtype != torch.int64 or out.numel() != l2.shape[0] or not out.is_contiguous() or out.device != logits.device:
+            raise ValueError("bad `out` tensor")
+        idx = out
+    if l2.shape[0]:
+        _lib.call("mmf_argmax_rows", l2.data_ptr(), _code(l2.dtype), l2.stride(0), l2.shape[0], l2.shape[1],
+                  idx.data_ptr(), _stream())
+    return idx if out is not None else idx.reshape(logits.shape[:-1])
 
 
 def sample_top_p(logits: torch.Tensor, temperature: float, top_p: float, uniforms: torch.Tensor) -> torch.Tensor:
