@@ -68,6 +68,15 @@ __device__ __forceinline__ uint32_t bar_count(int i, int merged) {
 }
 
 
+// address of this CTA's shared-memory location `my_smem_addr` in CTA `peer_rank` of the cluster
+__device__ __forceinline__ uint32_t peer_addr(const void* my_smem_addr, uint32_t peer_rank) {
+    uint32_t remote;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(smem_u32(my_smem_addr)), "r"(peer_rank));
+    return remote;
+}
+__device__ __forceinline__ void st_cluster_b32(uint32_t cluster_addr, uint32_t v) {
+    asm volatile("st.shared::cluster.b32 [%0], %1;" ::"r"(cluster_addr), "r"(v) : "memory");
+}
 __device__ __forceinline__ void st_peer_v4(void* my_smem_addr, uint32_t peer_rank, const int4& v) {
     uint32_t remote;
     asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(smem_u32(my_smem_addr)), "r"(peer_rank));
@@ -363,6 +372,7 @@ bitlinear_mma_kernel(const __grid_constant__ CUtensorMap q_map, BitLinearArgs a,
         ok = __all_sync(0xffffffffu, ok && mbar_wait(&bars[BAR_ACC], 0, abort_flag));
         tc_fence_after();
         trace_mark(trace, 4);
+        if (p.ksplit > 1) cluster_wait();                 // barrier #1 (arrived at kernel start): every CTA of the cluster is running
         if (ok) {
             const int ngroups = p.NT >> 4;
             if (dual) {
@@ -379,6 +389,7 @@ bitlinear_mma_kernel(const __grid_constant__ CUtensorMap q_map, BitLinearArgs a,
             } else {
                 const int total_mma = (min(p.KC, (stage0 + nstages) * 2) - stage0 * 2) * 2;   // MMAs this CTA issued
                 const int nused = min(p.nacc, total_mma);                                      // accumulators that hold data
+                const int per = p.NT / p.ksplit;                  // K split: token columns each CTA of the cluster finishes
                 for (int gi = gp; gi < ngroups; gi += 2) {        // groups of 16 columns, alternating between the warp groups
                     uint32_t v0[16], v1[16];
                     tmem_ld16(tmem_base + lane_addr + gi * 16, v0);
@@ -389,12 +400,27 @@ bitlinear_mma_kernel(const __grid_constant__ CUtensorMap q_map, BitLinearArgs a,
                         for (int j = 0; j < 16; ++j) v0[j] += v1[j];
                     }
                     tmem_wait_ld();
+                    if (p.ksplit == 1) {
 #pragma unroll
-                    for (int j = 0; j < 16; ++j) stg[(gi * 16 + j) * MMF_TILE_ROWS + row] = (int32_t)v0[j];
+                        for (int j = 0; j < 16; ++j) stg[(gi * 16 + j) * MMF_TILE_ROWS + row] = (int32_t)v0[j];
+                    } else {
+                        // straight from registers into the landing zone of the CTA that finishes the column, slot
+                        // [my rank] (the own columns included): part[rank][column in the owner's slice][row]
+                        int o = (gi * 16) / per, cl = gi * 16 - o * per;
+                        uint32_t dst = peer_addr(part + ((int64_t)ks * per) * MMF_TILE_ROWS + row, (uint32_t)o);
+#pragma unroll
+                        for (int j = 0; j < 16; ++j) {
+                            st_cluster_b32(dst + (uint32_t)(cl * MMF_TILE_ROWS * 4), v0[j]);
+                            if (++cl == per) {
+                                cl = 0;
+                                if (++o < p.ksplit) dst = peer_addr(part + ((int64_t)ks * per) * MMF_TILE_ROWS + row, (uint32_t)o);
+                            }
+                        }
+                    }
                 }
             }
         }
-        asm volatile("bar.sync 1, %0;" ::"n"(UNPACK_THREADS) : "memory");   // the 8 epilogue warps only
+        if (p.ksplit == 1) asm volatile("bar.sync 1, %0;" ::"n"(UNPACK_THREADS) : "memory");   // the 8 epilogue warps only
         trace_mark(trace, 5);
 
         // ---- phase B: 16 threads per token column, 8 consecutive weight rows each
@@ -417,17 +443,6 @@ bitlinear_mma_kernel(const __grid_constant__ CUtensorMap q_map, BitLinearArgs a,
             }
         } else {
             const int per = p.NT / p.ksplit;                  // token columns each CTA of the cluster finishes
-            cluster_wait();                                   // barrier #1: every CTA of the cluster is running
-            if (ok) {
-                // push the columns owned by peer o into its landing zone, slot [my rank]
-                const int vecs = per * (MMF_TILE_ROWS / 4);   // int4 pieces per slice
-                for (int o = 0; o < p.ksplit; ++o) {
-                    if (o == ks) continue;
-                    const int4* src = reinterpret_cast<const int4*>(stg + o * per * MMF_TILE_ROWS);
-                    int4* dst = reinterpret_cast<int4*>(part + ks * per * MMF_TILE_ROWS);
-                    for (int idx = tid; idx < vecs; idx += UNPACK_THREADS) st_peer_v4(dst + idx, (uint32_t)o, src[idx]);
-                }
-            }
             cluster_arrive();                                 // barrier #2 orders all pushes before the owners' reads
             cluster_wait();
             trace_mark(trace, 6);
@@ -436,12 +451,10 @@ bitlinear_mma_kernel(const __grid_constant__ CUtensorMap q_map, BitLinearArgs a,
                     const int c = ks * per + cl;
                     const int m = m0 + c;
                     if (m >= a.M) break;
-                    const int4 x0 = *reinterpret_cast<const int4*>(stg + c * MMF_TILE_ROWS + n8);
-                    const int4 x1 = *reinterpret_cast<const int4*>(stg + c * MMF_TILE_ROWS + n8 + 4);
-                    int32_t acc[8] = {x0.x, x0.y, x0.z, x0.w, x1.x, x1.y, x1.z, x1.w};
+                    int32_t acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
 #pragma unroll
                     for (int peer = 0; peer < 8; ++peer) {
-                        if (peer < p.ksplit && peer != ks) {
+                        if (peer < p.ksplit) {
                             const int4 y0 = *reinterpret_cast<const int4*>(part + (peer * per + cl) * MMF_TILE_ROWS + n8);
                             const int4 y1 = *reinterpret_cast<const int4*>(part + (peer * per + cl) * MMF_TILE_ROWS + n8 + 4);
                             acc[0] += y0.x; acc[1] += y0.y; acc[2] += y0.z; acc[3] += y0.w;
@@ -577,7 +590,7 @@ bool choose_config(const BitLinearArgs& a, MmaParams& best, size_t& best_smem) {
                 const int64_t waves = (ctas + 148 * occ - 1) / (148 * occ);
                 const double t_stage = mode == 2 ? 0.90 : NT > 128 ? 0.30 : 0.24;   // (two tiles per CTA measured slower: kept for experiments)
                 double t = 2.5 + stages * t_stage + 0.5 + p.wt * NT * 0.012;
-                if (ks > 1) t += 1.5 + NT * 0.012 + (ks == 8 && NT > 32 ? 6.0 : 0.0);
+                if (ks > 1) t += 0.75 + 0.22 * ks + NT * 0.012 + (ks == 8 && NT > 32 ? 6.0 : 0.0);   // measured: 1.2 / 1.6 / 2.5 us at 2 / 4 / 8
                 const double cost = waves * t;
                 if (cost < best_cost) { best_cost = cost; best = p; best_smem = smem; found = true; }
             }
