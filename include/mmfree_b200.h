@@ -192,6 +192,7 @@ int mmf_int8_mma_peak(int n_tokens, int iters, int* status_dev, double* tops_hos
 #define MMF_TUNE_W_STAGES 6   /* packed-weight ring depth (even)                               */
 #define MMF_TUNE_PERSISTENT 7 /* persistent large-M kernel: 1 = whenever M > 128, 2 = never, 10+v = its compiled shape v (1..4) whenever M > 128 */
 #define MMF_TUNE_PROBE_COMMITS 8 /* mmf_int8_mma_peak: tcgen05.commit instructions issued per 4 MMAs */
+#define MMF_TUNE_ACCUMULATORS 9 /* accumulators consecutive MMAs rotate through at few token columns: 1, 2 or 4 */
 int mmf_tuning(int knob, int value);
 
 /* ------------------------------------------------------------------------------------

@@ -487,7 +487,7 @@ bitlinear_mma_kernel(const __grid_constant__ CUtensorMap q_map, BitLinearArgs a,
 }  // namespace
 
 // tuning overrides (0 = automatic), see mmf_tuning()
-static int g_force_ksplit = 0, g_force_nt = 0, g_force_deep = 0, g_force_wt = 0, g_force_sb = 0, g_force_sa = 0, g_force_sw = 0, g_force_persistent = 0;
+static int g_force_ksplit = 0, g_force_nt = 0, g_force_deep = 0, g_force_wt = 0, g_force_sb = 0, g_force_sa = 0, g_force_sw = 0, g_force_persistent = 0, g_force_nacc = 0;
 
 extern int g_probe_commits;
 
@@ -502,6 +502,7 @@ extern "C" int mmf_tuning(int knob, int value) {
         case MMF_TUNE_W_STAGES: g_force_sw = value; return MMF_OK;
         case MMF_TUNE_PERSISTENT: g_force_persistent = value; return MMF_OK;
         case MMF_TUNE_PROBE_COMMITS: g_probe_commits = value; return MMF_OK;
+        case MMF_TUNE_ACCUMULATORS: g_force_nacc = value; return MMF_OK;
         default: return mmf_set_error(MMF_ERR_BAD_ARG, "mmf_tuning: unknown knob %d", knob);
     }
 }
@@ -565,7 +566,10 @@ bool choose_config(const BitLinearArgs& a, MmaParams& best, size_t& best_smem) {
                     occ = 1;
                 } else {
                     p.SA = 4; p.SB = 4; p.SW = NT >= 128 ? 8 : 12;   // 8 keeps a 128-token tile under half an SM's shared memory
-                    p.nacc = NT >= 128 ? 1 : (128 / NT < 4 ? 128 / NT : 4);
+                    // one accumulator: the issuing thread needs about 67 cycles per MMA, which already exceeds the pipe time of a
+                    // dependent small-N MMA, and every extra accumulator is one more TMEM read round trip in the epilogue
+                    p.nacc = 1;
+                    if (g_force_nacc && g_force_nacc * NT <= 128) p.nacc = g_force_nacc;
                     if (g_force_sb) p.SB = g_force_sb < MAX_SB ? g_force_sb : MAX_SB;
                     if (g_force_sa) p.SA = (g_force_sa < MAX_SA ? g_force_sa : MAX_SA) & ~1;   // the two unpack groups alternate slots
                     if (g_force_sw) p.SW = (g_force_sw < MAX_SW ? g_force_sw : MAX_SW) & ~1;
