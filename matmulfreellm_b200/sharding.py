@@ -69,3 +69,42 @@ def generate_sharded(model, input_ids: torch.Tensor, max_new_tokens: int, group:
     else:
         out = input_ids.new_empty((0, input_ids.shape[1] + max_new_tokens))
     return gather_batch(out, B, group)
+
+
+def _self_check() -> None:
+    """`python -m torch.distributed.run --nproc-per-node N -m matmulfreellm_b200.sharding`: a small random-init model,
+    a ragged batch sharded over the N GPUs and gathered with NCCL, compared on every rank with the same batch decoded
+    on that rank alone.  Prints one JSON line on rank 0."""
+    import json
+    import os
+
+    from .models import HGRNBitConfig, HGRNBitForCausalLM
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    device = torch.device("cuda", local)
+    if "RANK" in os.environ:
+        dist.init_process_group("nccl", device_id=device)
+    world = dist.get_world_size() if dist.is_initialized() else 1
+    torch.manual_seed(0)                                   # same weights on every rank
+    cfg = HGRNBitConfig(vocab_size=32000, hidden_size=256, num_hidden_layers=2, intermediate_size=704)
+    model = HGRNBitForCausalLM(cfg).eval().to(device)
+    model.pack_weights()
+    model = model.bfloat16()
+    B = 2 * world + 1                                      # ragged: one rank gets an extra sequence
+    ids = torch.randint(0, 32000, (B, 12), generator=torch.Generator().manual_seed(1)).to(device)
+    sharded = generate_sharded(model, ids, 16)
+    alone = model.generate(ids, max_new_tokens=16)
+    ok = torch.tensor([int(torch.equal(sharded, alone))], device=device)
+    if dist.is_initialized():
+        dist.all_reduce(ok, op=dist.ReduceOp.MIN)
+    if (dist.get_rank() if dist.is_initialized() else 0) == 0:
+        print(json.dumps({"check": "generate_sharded == single-GPU generate", "world": world, "batch": B,
+                          "shape": list(sharded.shape), "ok": bool(ok.item())}), flush=True)
+    if dist.is_initialized():
+        dist.destroy_process_group()
+    if not ok.item():
+        raise SystemExit(1)
+
+
+if __name__ == "__main__":
+    _self_check()
