@@ -19,9 +19,10 @@
 //
 // Weights are stored biased (+1); sum_k (t+1)*x = acc + rowsum(x) and the epilogue subtracts the
 // per-token code sum.  For few tokens the K range is split over the CTAs of a thread-block cluster
-// (2, 4 or 8) to fill the GPU; each CTA parks its partial int32 tile in its own shared memory and,
-// after a cluster barrier, reduces its share of the token columns over its peers' tiles through
-// distributed shared memory (integer adds: deterministic) and dequantises them.
+// (2, 4 or 8) to fill the GPU; each CTA owns a share of the token columns, writes the partial int32
+// sums of every other share from its registers straight into the owner's shared memory (distributed
+// shared memory stores) and, after one cluster barrier, adds up the slots it received (integer adds:
+// deterministic) and dequantises them.
 #include <cuda.h>
 
 #include "bitlinear.cuh"
