@@ -88,11 +88,48 @@ template <> __device__ __forceinline__ __half from_f32<__half>(float v) { return
 // value of v after a round trip through T (models an intermediate tensor of dtype T)
 template <typename T> __device__ __forceinline__ float round_to(float v) { return to_f32(from_f32<T>(v)); }
 
+// Two values rounded to T in place with one packed conversion; returns the two T values as 32 bits (a in the low
+// half), which a caller that also stores them can write out without converting again.  No-op for T = float.
+template <typename T> __device__ __forceinline__ uint32_t round_pair(float& a, float& b);
+template <> __device__ __forceinline__ uint32_t round_pair<float>(float&, float&) { return 0u; }
+template <> __device__ __forceinline__ uint32_t round_pair<__nv_bfloat16>(float& a, float& b) {
+    const __nv_bfloat162 p = __floats2bfloat162_rn(a, b);
+    const uint32_t u = *reinterpret_cast<const uint32_t*>(&p);
+    a = __uint_as_float(u << 16);
+    b = __uint_as_float(u & 0xffff0000u);
+    return u;
+}
+template <> __device__ __forceinline__ uint32_t round_pair<__half>(float& a, float& b) {
+    const __half2 p = __floats2half2_rn(a, b);
+    const float2 f = __half22float2(p);
+    a = f.x;
+    b = f.y;
+    return *reinterpret_cast<const uint32_t*>(&p);
+}
+// V values (one 16-byte vector of T) rounded to T in place; `bits` receives the packed T values (16-bit T only)
+template <typename T, int V>
+__device__ __forceinline__ void round_vec(float (&x)[V], uint32_t (&bits)[V / 2]) {
+#pragma unroll
+    for (int i = 0; i < V; i += 2) bits[i / 2] = round_pair<T>(x[i], x[i + 1]);
+}
+// store a vector that round_vec has rounded: the packed bits for a 16-bit T, the values themselves for float
+template <typename T, int V>
+__device__ __forceinline__ void store_rounded(T* p, const float (&x)[V], const uint32_t (&bits)[V / 2]) {
+    if constexpr (sizeof(T) == 2) *reinterpret_cast<uint4*>(p) = make_uint4(bits[0], bits[1], bits[2], bits[3]);
+    else *reinterpret_cast<float4*>(p) = make_float4(x[0], x[1], x[2], x[3]);
+}
+
 // int8 activation code clamp(rint(p), -128, 127) for |p| < 2^22 without conversion instructions: adding 1.5 * 2^23
 // leaves the round-to-nearest-even integer in the low mantissa bits of the sum (same result as rintf + cast)
 __device__ __forceinline__ int quant_code(float p) {
     const int iv = __float_as_int(__fadd_rn(p, 12582912.0f)) - 0x4B400000;
     return max(-128, min(127, iv));
+}
+
+// the same code plus 0x4B400000 (whose low byte is zero): the low byte of the result IS the int8 code, which is all a
+// caller that packs bytes needs — one instruction less than quant_code
+__device__ __forceinline__ int quant_code_biased(float p) {
+    return max(0x4B400000 - 128, min(0x4B400000 + 127, __float_as_int(__fadd_rn(p, 12582912.0f))));
 }
 
 // 16-byte vector of T: 4 floats or 8 halves

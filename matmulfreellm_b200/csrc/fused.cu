@@ -32,7 +32,7 @@ constexpr int MAX_D = FT * MAX_PER;
 // One-sync block reductions: warp shuffle, lane 0 parks the partial in a slot that is used once per row,
 // one barrier, then every thread folds the FW partials in a fixed order.
 template <int K>
-__device__ __forceinline__ void block_sum_d(double (&v)[K], double* slot /* K*FW */) {
+__device__ __forceinline__ void block_sum_d(double (&v)[K], double* slot /* K*FW, 16-byte aligned */) {
     const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
 #pragma unroll
     for (int k = 0; k < K; ++k) v[k] = warp_sum(v[k]);
@@ -45,15 +45,21 @@ __device__ __forceinline__ void block_sum_d(double (&v)[K], double* slot /* K*FW
     for (int k = 0; k < K; ++k) {
         double t = 0.0;
 #pragma unroll
-        for (int w = 0; w < FW; ++w) t += slot[k * FW + w];
+        for (int w = 0; w < FW; w += 2) {
+            const double2 p = *reinterpret_cast<const double2*>(slot + k * FW + w);
+            t += p.x;
+            t += p.y;
+        }
         v[k] = t;
     }
 }
+// maximum of non-negative, non-NaN floats: their bit patterns order like unsigned integers, so one warp-wide
+// integer reduction instruction replaces five shuffle + max rounds
 template <int K>
 __device__ __forceinline__ void block_max_f(float (&v)[K], float* slot) {
     const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
 #pragma unroll
-    for (int k = 0; k < K; ++k) v[k] = warp_max(v[k]);
+    for (int k = 0; k < K; ++k) v[k] = __uint_as_float(__reduce_max_sync(0xffffffffu, __float_as_uint(v[k])));
     if (lane == 0) {
 #pragma unroll
         for (int k = 0; k < K; ++k) slot[k * FW + wid] = v[k];
@@ -63,30 +69,39 @@ __device__ __forceinline__ void block_max_f(float (&v)[K], float* slot) {
     for (int k = 0; k < K; ++k) {
         float t = 0.0f;
 #pragma unroll
-        for (int w = 0; w < FW; ++w) t = fmaxf(t, slot[k * FW + w]);
+        for (int w = 0; w < FW; w += 4) {
+            const float4 p = *reinterpret_cast<const float4*>(slot + k * FW + w);
+            t = fmaxf(fmaxf(t, p.x), fmaxf(p.y, fmaxf(p.z, p.w)));
+        }
         v[k] = t;
     }
 }
+// block-wide integer sums; only thread 0 receives them (it is the one that writes them out)
 template <int K>
-__device__ __forceinline__ void block_sum_i(int (&v)[K], int* slot) {
+__device__ __forceinline__ void block_sum_i_t0(int (&v)[K], int* slot) {
     const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
 #pragma unroll
-    for (int k = 0; k < K; ++k) v[k] = warp_sum(v[k]);
+    for (int k = 0; k < K; ++k) v[k] = __reduce_add_sync(0xffffffffu, v[k]);
     if (lane == 0) {
 #pragma unroll
         for (int k = 0; k < K; ++k) slot[k * FW + wid] = v[k];
     }
     __syncthreads();
+    if (threadIdx.x == 0) {
 #pragma unroll
-    for (int k = 0; k < K; ++k) {
-        int t = 0;
+        for (int k = 0; k < K; ++k) {
+            int t = 0;
 #pragma unroll
-        for (int w = 0; w < FW; ++w) t += slot[k * FW + w];
-        v[k] = t;
+            for (int w = 0; w < FW; w += 4) {
+                const int4 p = *reinterpret_cast<const int4*>(slot + k * FW + w);
+                t += (p.x + p.y) + (p.z + p.w);
+            }
+            v[k] = t;
+        }
     }
 }
 
-struct RedScratch {       // each member is written once per row and at least two barriers lie between two uses -> no extra barrier
+struct __align__(16) RedScratch {       // each member is written once per row and at least two barriers lie between two uses -> no extra barrier
     double d0[3 * FW], d1[3 * FW];
     float f0[3 * FW];
     int i0[3 * FW];
@@ -118,7 +133,7 @@ __device__ __forceinline__ void lds_weights(const float* p, float (&w)[V]) {
 // BitLinear prologue on a register-resident row `v` (values already in T precision): shared sum of squares
 // `ss`, then per projection g: y = (v*rstd)*nw_g, absmax -> scale -> int8 codes, dq, rowsum.
 template <int V, int G, int P>
-__device__ __forceinline__ void bitlinear_prologue(const float (&v)[P], int D, double ss, float eps, const float* snw /* smem [G][D] */,
+__device__ __forceinline__ void bitlinear_prologue(float (&v)[P], int D, double ss, float eps, const float* snw /* smem [G][D] */,
                                                    int8_t* q, float* dq, int32_t* rowsum, int64_t M, int64_t m, RedScratch& red) {
     double s1[1] = {ss};
     block_sum_d<1>(s1, red.d1);
@@ -128,11 +143,17 @@ __device__ __forceinline__ void bitlinear_prologue(const float (&v)[P], int D, d
     for (int g = 0; g < G; ++g) amax[g] = 0.0f;
     ROW_FOREACH(V, D, it, c) {
 #pragma unroll
+        for (int i = 0; i < V; ++i) v[it * V + i] = __fmul_rn(v[it * V + i], rstd);   // the row is kept normalised from here on
+#pragma unroll
         for (int g = 0; g < G; ++g) {
             float w[V];
             lds_weights<V>(snw + g * D + c, w);
 #pragma unroll
-            for (int i = 0; i < V; ++i) amax[g] = fmaxf(amax[g], fabsf(__fmul_rn(__fmul_rn(v[it * V + i], rstd), w[i])));
+            for (int i = 0; i < V; ++i) {
+                const float y = __fmul_rn(v[it * V + i], w[i]);
+                if constexpr (G == 1) v[it * V + i] = y;    // a single projection: keep y itself for the second pass
+                amax[g] = fmaxf(amax[g], fabsf(y));
+            }
         }
     }
     block_max_f<G>(amax, red.f0);
@@ -144,22 +165,28 @@ __device__ __forceinline__ void bitlinear_prologue(const float (&v)[P], int D, d
         int8_t* qr = q + ((int64_t)g * M + m) * D;
         lsum[g] = 0;
         ROW_FOREACH(V, D, it, c) {
-            int8_t codes[V];
+            uint32_t words[V / 4];
             float w[V];
-            lds_weights<V>(snw + g * D + c, w);
+            if constexpr (G > 1) lds_weights<V>(snw + g * D + c, w);
 #pragma unroll
-            for (int i = 0; i < V; ++i) {
-                const float y = __fmul_rn(__fmul_rn(v[it * V + i], rstd), w[i]);
-                const int iv = quant_code(__fmul_rn(y, s));
-                codes[i] = (int8_t)iv;
-                lsum[g] += iv;
+            for (int i = 0; i < V; i += 4) {
+                int iv[4];
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    const float y = G == 1 ? v[it * V + i + j] : __fmul_rn(v[it * V + i + j], w[i + j]);
+                    iv[j] = quant_code_biased(__fmul_rn(y, s));
+                }
+                // low bytes of the four codes -> one word; its signed byte sum joins the row's code sum in one instruction
+                const uint32_t word = __byte_perm(__byte_perm(iv[0], iv[1], 0x0040), __byte_perm(iv[2], iv[3], 0x0040), 0x5410);
+                words[i / 4] = word;
+                lsum[g] = __dp4a((int)word, 0x01010101, lsum[g]);
             }
-            if constexpr (V == 8) *reinterpret_cast<uint2*>(qr + c) = *reinterpret_cast<const uint2*>(codes);
-            else *reinterpret_cast<uint32_t*>(qr + c) = *reinterpret_cast<const uint32_t*>(codes);
+            if constexpr (V == 8) *reinterpret_cast<uint2*>(qr + c) = make_uint2(words[0], words[1]);
+            else *reinterpret_cast<uint32_t*>(qr + c) = words[0];
         }
         if (threadIdx.x == 0) dq[(int64_t)g * M + m] = __fdiv_rn(a, 127.0f);
     }
-    block_sum_i<G>(lsum, red.i0);
+    block_sum_i_t0<G>(lsum, red.i0);
     if (threadIdx.x == 0) {
 #pragma unroll
         for (int g = 0; g < G; ++g) rowsum[(int64_t)g * M + m] = lsum[g];
@@ -207,10 +234,20 @@ prenorm_quant_kernel(PrenormArgs a) {
     #pragma unroll
                 for (int i = 0; i < V; ++i) x[i] = __fadd_rn(x[i], r[i]);
             }
-            if (ro) store16<T>(ro + c, x);
+            if (ro || a.round_sum_first) {
+                float xr_[V];
+                uint32_t bits[V / 2];
+    #pragma unroll
+                for (int i = 0; i < V; ++i) xr_[i] = x[i];
+                round_vec<T, V>(xr_, bits);
+                if (ro) store_rounded<T, V>(ro + c, xr_, bits);
+                if (a.round_sum_first) {
+    #pragma unroll
+                    for (int i = 0; i < V; ++i) x[i] = xr_[i];
+                }
+            }
     #pragma unroll
             for (int i = 0; i < V; ++i) {
-                if (a.round_sum_first) x[i] = round_to<T>(x[i]);
                 v[it * V + i] = x[i];
                 ss[0] += (double)x[i] * (double)x[i];
             }
@@ -221,15 +258,17 @@ prenorm_quant_kernel(PrenormArgs a) {
         double ss2 = 0.0;
         ROW_FOREACH(V, D, it, c) {
             float o[V], w[V];
+            uint32_t bits[V / 2];
             lds_weights<V>(sw + c, w);
 #pragma unroll
+            for (int i = 0; i < V; ++i) o[i] = __fmul_rn(__fmul_rn(v[it * V + i], rstd1), w[i]);
+            round_vec<T, V>(o, bits);
+#pragma unroll
             for (int i = 0; i < V; ++i) {
-                const float t = round_to<T>(__fmul_rn(__fmul_rn(v[it * V + i], rstd1), w[i]));
-                o[i] = t;
-                v[it * V + i] = t;
-                ss2 += (double)t * (double)t;
+                v[it * V + i] = o[i];
+                ss2 += (double)o[i] * (double)o[i];
             }
-            if (yo) store16<T>(yo + c, o);
+            if (yo) store_rounded<T, V>(yo + c, o, bits);
         }
         if (a.G == 3) bitlinear_prologue<V, 3, P>(v, D, ss2, a.eps_bl, sw + D, a.q, a.dq, a.rowsum, a.M, m, red);
         else if (a.G == 1) bitlinear_prologue<V, 1, P>(v, D, ss2, a.eps_bl, sw + D, a.q, a.dq, a.rowsum, a.M, m, red);
@@ -246,16 +285,19 @@ __device__ __forceinline__ void gatenorm_tail(float (&gv)[P], const float (&ov)[
     const float rstd = rstd_from_sumsq(s0[0], D, eps_g);
     double ss2 = 0.0;
     ROW_FOREACH(V, D, it, c) {
-        float w[V];
+        float w[V], t[V];
+        uint32_t bits[V / 2];
         lds_weights<V>(sw + c, w);
 #pragma unroll
         for (int i = 0; i < V; ++i) {
             const float o = ov[it * V + i];
-            float t = __fmul_rn(__fmul_rn(gv[it * V + i], rstd), w[i]);
-            t = __fmul_rn(t, o);
-            t = round_to<T>(__fmul_rn(t, sigmoidf_(o)));
-            gv[it * V + i] = t;
-            ss2 += (double)t * (double)t;
+            t[i] = __fmul_rn(__fmul_rn(__fmul_rn(__fmul_rn(gv[it * V + i], rstd), w[i]), o), sigmoidf_(o));
+        }
+        round_vec<T, V>(t, bits);
+#pragma unroll
+        for (int i = 0; i < V; ++i) {
+            gv[it * V + i] = t[i];
+            ss2 += (double)t[i] * (double)t[i];
         }
     }
     bitlinear_prologue<V, 1, P>(gv, D, ss2, eps_bl, sw + D, q, dq, rowsum, M, m, red);
@@ -377,10 +419,13 @@ swiglu_quant_kernel(const T* __restrict__ gate, const T* __restrict__ up, int64_
             load16<T>(gr + c, gv);
             load16<T>(ur + c, uv);
     #pragma unroll
+            for (int i = 0; i < V; ++i) gv[i] = silu_mul(gv[i], uv[i]);
+            uint32_t bits[V / 2];
+            round_vec<T, V>(gv, bits);
+    #pragma unroll
             for (int i = 0; i < V; ++i) {
-                const float t = round_to<T>(silu_mul(gv[i], uv[i]));
-                v[it * V + i] = t;
-                ss += (double)t * (double)t;
+                v[it * V + i] = gv[i];
+                ss += (double)gv[i] * (double)gv[i];
             }
         }
         bitlinear_prologue<V, 1, P>(v, D, ss, eps_bl, sw, q, dq, rowsum, M, m, red);
@@ -397,8 +442,29 @@ swiglu_quant_kernel(const T* __restrict__ gate, const T* __restrict__ up, int64_
     MMF_REQUIRE(M >= 0 && (D) > 0 && (D) <= MAX_D && (D) % 16 == 0, MMF_ERR_BAD_SHAPE,                               \
                 name ": need 0 < D <= 8192 and D %% 16 == 0 (D=%lld)", (long long)(D));
 
-// one CTA per row up to eight CTAs per SM; beyond that the CTAs loop over rows
-static inline unsigned row_grid(int64_t M) { return (unsigned)(M < 148 * 8 ? M : 148 * 8); }
+// CTAs of `kernel` (FT threads, `smem` dynamic bytes) that fit on one SM at a time; asked of the runtime once per
+// (kernel, smem) and remembered per host thread
+static int resident_ctas(const void* kernel, size_t smem) {
+    struct Entry { const void* k; size_t s; int occ; };
+    thread_local Entry cache[24];
+    thread_local int n = 0;
+    for (int i = 0; i < n; ++i)
+        if (cache[i].k == kernel && cache[i].s == smem) return cache[i].occ;
+    int occ = 0;
+    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ, kernel, FT, smem) != cudaSuccess || occ < 1) {
+        (void)cudaGetLastError();
+        occ = 4;
+    }
+    if (n < 24) cache[n++] = Entry{kernel, smem, occ};
+    return occ;
+}
+// one CTA per row while all of them are resident at once; beyond that exactly one resident set of CTAs, which loop
+// over the rows (a partial second wave would leave SMs idle at the end)
+template <typename Kern>
+static inline unsigned row_grid(Kern kernel, size_t smem, int64_t M) {
+    const int64_t cap = (int64_t)148 * resident_ctas(reinterpret_cast<const void*>(kernel), smem);
+    return (unsigned)(M < cap ? M : cap);
+}
 
 // Run `...` with `P` (row values per thread) bound to the smallest compiled size that holds a row of D values.
 #define FUSED_DISPATCH_P(D, P, ...)                                   \
@@ -432,7 +498,7 @@ extern "C" int mmf_prenorm_quant(const void* x, int64_t ld_x, const void* residu
     MMF_DISPATCH(dtype, T, {
         FUSED_DISPATCH_P(D, P, {
             FUSED_SMEM_ATTR((prenorm_quant_kernel<T, P>), smem);
-            MMF_CUDA(mmf_launch_pdl(prenorm_quant_kernel<T, P>, dim3(row_grid(M)), dim3(FT), smem, (cudaStream_t)stream, a));
+            MMF_CUDA(mmf_launch_pdl(prenorm_quant_kernel<T, P>, dim3(row_grid(prenorm_quant_kernel<T, P>, smem, M)), dim3(FT), smem, (cudaStream_t)stream, a));
         });
     });
     MMF_LAUNCH_CHECK("prenorm_quant_kernel");
@@ -453,7 +519,7 @@ extern "C" int mmf_gatenorm_quant(const void* g, int64_t ld_g, const void* o, in
     MMF_DISPATCH(dtype, T, {
         FUSED_DISPATCH_P(D, P, {
             FUSED_SMEM_ATTR((gatenorm_quant_kernel<T, P>), smem);
-            MMF_CUDA(mmf_launch_pdl(gatenorm_quant_kernel<T, P>, dim3(row_grid(M)), dim3(FT), smem, (cudaStream_t)stream, (const T*)g,
+            MMF_CUDA(mmf_launch_pdl(gatenorm_quant_kernel<T, P>, dim3(row_grid(gatenorm_quant_kernel<T, P>, smem, M)), dim3(FT), smem, (cudaStream_t)stream, (const T*)g,
                                     ld_g, (const T*)o, ld_o, gnorm_w, eps_g, nw, eps_bl, q, dq, rowsum, M, (int)D));
         });
     });
@@ -496,7 +562,7 @@ extern "C" int mmf_swiglu_quant(const void* gate, const void* up, int64_t ld, in
     MMF_DISPATCH(dtype, T, {
         FUSED_DISPATCH_P(D, P, {
             FUSED_SMEM_ATTR((swiglu_quant_kernel<T, P>), smem);
-            MMF_CUDA(mmf_launch_pdl(swiglu_quant_kernel<T, P>, dim3(row_grid(M)), dim3(FT), smem, (cudaStream_t)stream, (const T*)gate,
+            MMF_CUDA(mmf_launch_pdl(swiglu_quant_kernel<T, P>, dim3(row_grid(swiglu_quant_kernel<T, P>, smem, M)), dim3(FT), smem, (cudaStream_t)stream, (const T*)gate,
                                     (const T*)up, ld, nw, eps_bl, q, dq, rowsum, M, (int)D));
         });
     });

@@ -134,14 +134,24 @@ constexpr int HG_RAW = 2;     // x, g are the raw i/f projection outputs (HGRNBi
                               //   f = round(sigmoid(g)); with a lower bound lb: f = round(lb + round(round(1-lb)*f))
                               //   x = round(silu(x_raw) * round(1-f));  every round() is to the activation dtype TX
 
-// raw (x, g) of one element -> (x_t, f_t) of the recurrence
+// raw (x, g) of a channel pair -> (x_t, f_t) of the recurrence; in raw mode every rounding converts both channels
+// with one packed instruction
 template <typename TX, int MODE>
-__device__ __forceinline__ void gate_transform(float& xv, float& f, bool has_lb, float lbv, float oml) {
-    if (MODE == HG_LOG) f = exp_gate(f);
+__device__ __forceinline__ void gate_transform2(float2& xv, float2& f, bool has_lb, float2 lbv, float2 oml) {
+    if (MODE == HG_LOG) { f.x = exp_gate(f.x); f.y = exp_gate(f.y); }
     if (MODE == HG_RAW) {
-        f = round_to<TX>(sigmoidf_(f));
-        if (has_lb) f = round_to<TX>(__fadd_rn(lbv, round_to<TX>(__fmul_rn(oml, f))));
-        xv = round_to<TX>(silu_mul(xv, round_to<TX>(__fsub_rn(1.0f, f))));
+        f.x = sigmoidf_(f.x); f.y = sigmoidf_(f.y);
+        round_pair<TX>(f.x, f.y);
+        if (has_lb) {
+            f.x = __fmul_rn(oml.x, f.x); f.y = __fmul_rn(oml.y, f.y);
+            round_pair<TX>(f.x, f.y);
+            f.x = __fadd_rn(lbv.x, f.x); f.y = __fadd_rn(lbv.y, f.y);
+            round_pair<TX>(f.x, f.y);
+        }
+        float2 omf = make_float2(__fsub_rn(1.0f, f.x), __fsub_rn(1.0f, f.y));
+        round_pair<TX>(omf.x, omf.y);
+        xv.x = silu_mul(xv.x, omf.x); xv.y = silu_mul(xv.y, omf.y);
+        round_pair<TX>(xv.x, xv.y);
     }
 }
 
@@ -251,8 +261,7 @@ hgrn_scan_kernel(const __grid_constant__ CUtensorMap x_map, const __grid_constan
 #pragma unroll
                 for (int j = 0; j < HG_SUBT; ++j) {
                     float2 xv = ld2(px + j * HG_BD), f = ld2(pg + j * HG_BD);
-                    gate_transform<TX, MODE>(xv.x, f.x, has_lb, lbv.x, oml.x);
-                    gate_transform<TX, MODE>(xv.y, f.y, has_lb, lbv.y, oml.y);
+                    gate_transform2<TX, MODE>(xv, f, has_lb, lbv, oml);
                     if (pm && !pm[j]) xv = make_float2(0.0f, 0.0f);
                     h.x = fmaf(f.x, h.x, xv.x); h.y = fmaf(f.y, h.y, xv.y);
                     a.x *= f.x; a.y *= f.y;
@@ -262,8 +271,7 @@ hgrn_scan_kernel(const __grid_constant__ CUtensorMap x_map, const __grid_constan
 #pragma unroll
                 for (int j = 0; j < HG_SUBT; ++j) {
                     float2 xv = ld2(px + j * HG_BD), f = ld2(pg + j * HG_BD);
-                    gate_transform<TX, MODE>(xv.x, f.x, has_lb, lbv.x, oml.x);
-                    gate_transform<TX, MODE>(xv.y, f.y, has_lb, lbv.y, oml.y);
+                    gate_transform2<TX, MODE>(xv, f, has_lb, lbv, oml);
                     if (sub * HG_SUBT + j >= rows) {   // steps past the end of the sequence are the identity
                         xv = make_float2(0.0f, 0.0f);
                         f = make_float2(1.0f, 1.0f);
@@ -361,8 +369,7 @@ hgrn_step_kernel(const TX* __restrict__ x, int64_t ld_x, const TG* __restrict__ 
         oml.x = round_to<TX>(__fsub_rn(1.0f, lbv.x));
         oml.y = round_to<TX>(__fsub_rn(1.0f, lbv.y));
     }
-    gate_transform<TX, MODE>(xv.x, f.x, has_lb, lbv.x, oml.x);
-    gate_transform<TX, MODE>(xv.y, f.y, has_lb, lbv.y, oml.y);
+    gate_transform2<TX, MODE>(xv, f, has_lb, lbv, oml);
     if (mask && !mask[b]) xv = make_float2(0.0f, 0.0f);
     float h0x = 0.0f, h0y = 0.0f;
     if (h0) {
