@@ -141,18 +141,28 @@ __device__ __forceinline__ void bitlinear_prologue(float (&v)[P], int D, double 
     float amax[G];
 #pragma unroll
     for (int g = 0; g < G; ++g) amax[g] = 0.0f;
+    // fp32 multiplies and adds below are issued two at a time (packed f32x2 instructions: each half is the same IEEE
+    // round-to-nearest operation as the scalar instruction)
+    const float2 rstd2 = make_float2(rstd, rstd);
     ROW_FOREACH(V, D, it, c) {
 #pragma unroll
-        for (int i = 0; i < V; ++i) v[it * V + i] = __fmul_rn(v[it * V + i], rstd);   // the row is kept normalised from here on
+        for (int i = 0; i < V; i += 2) {   // the row is kept normalised from here on
+            const float2 t = __fmul2_rn(make_float2(v[it * V + i], v[it * V + i + 1]), rstd2);
+            v[it * V + i] = t.x;
+            v[it * V + i + 1] = t.y;
+        }
 #pragma unroll
         for (int g = 0; g < G; ++g) {
             float w[V];
             lds_weights<V>(snw + g * D + c, w);
 #pragma unroll
-            for (int i = 0; i < V; ++i) {
-                const float y = __fmul_rn(v[it * V + i], w[i]);
-                if constexpr (G == 1) v[it * V + i] = y;    // a single projection: keep y itself for the second pass
-                amax[g] = fmaxf(amax[g], fabsf(y));
+            for (int i = 0; i < V; i += 2) {
+                const float2 y = __fmul2_rn(make_float2(v[it * V + i], v[it * V + i + 1]), make_float2(w[i], w[i + 1]));
+                if constexpr (G == 1) {   // a single projection: keep y itself for the second pass
+                    v[it * V + i] = y.x;
+                    v[it * V + i + 1] = y.y;
+                }
+                amax[g] = fmaxf(amax[g], fmaxf(fabsf(y.x), fabsf(y.y)));
             }
         }
     }
@@ -162,6 +172,7 @@ __device__ __forceinline__ void bitlinear_prologue(float (&v)[P], int D, double 
     for (int g = 0; g < G; ++g) {
         const float a = fmaxf(amax[g], 1e-5f);
         const float s = __fdiv_rn(127.0f, a);
+        const float2 s2 = make_float2(s, s);
         int8_t* qr = q + ((int64_t)g * M + m) * D;
         lsum[g] = 0;
         ROW_FOREACH(V, D, it, c) {
@@ -172,9 +183,14 @@ __device__ __forceinline__ void bitlinear_prologue(float (&v)[P], int D, double 
             for (int i = 0; i < V; i += 4) {
                 int iv[4];
 #pragma unroll
-                for (int j = 0; j < 4; ++j) {
-                    const float y = G == 1 ? v[it * V + i + j] : __fmul_rn(v[it * V + i + j], w[i + j]);
-                    iv[j] = quant_code_biased(__fmul_rn(y, s));
+                for (int j = 0; j < 4; j += 2) {
+                    float2 y = make_float2(v[it * V + i + j], v[it * V + i + j + 1]);
+                    if constexpr (G > 1) y = __fmul2_rn(y, make_float2(w[i + j], w[i + j + 1]));
+                    // |y * s| <= 127 * (1 + 2^-23) because a >= |y|: the rounded code needs no clamp.  Adding 1.5 * 2^23
+                    // leaves the code, rounded to nearest even, in the low byte of the sum.
+                    const float2 r = __fadd2_rn(__fmul2_rn(y, s2), make_float2(12582912.0f, 12582912.0f));
+                    iv[j] = __float_as_int(r.x);
+                    iv[j + 1] = __float_as_int(r.y);
                 }
                 // low bytes of the four codes -> one word; its signed byte sum joins the row's code sum in one instruction
                 const uint32_t word = __byte_perm(__byte_perm(iv[0], iv[1], 0x0040), __byte_perm(iv[2], iv[3], 0x0040), 0x5410);
