@@ -126,12 +126,6 @@ __device__ __forceinline__ int quant_code(float p) {
     return max(-128, min(127, iv));
 }
 
-// the same code plus 0x4B400000 (whose low byte is zero): the low byte of the result IS the int8 code, which is all a
-// caller that packs bytes needs — one instruction less than quant_code
-__device__ __forceinline__ int quant_code_biased(float p) {
-    return max(0x4B400000 - 128, min(0x4B400000 + 127, __float_as_int(__fadd_rn(p, 12582912.0f))));
-}
-
 // 16-byte vector of T: 4 floats or 8 halves
 template <typename T> struct Vec16 { static constexpr int N = 16 / sizeof(T); T v[N]; };
 
@@ -241,3 +235,15 @@ __device__ __forceinline__ float silu_mul(float x, float y) {
     return __fmul_rn(__fmul_rn(x, y), rcp_fast(__fadd_rn(1.0f, exp_neg(x))));
 }
 __device__ __forceinline__ float sigmoidf_(float x) { return rcp_fast(__fadd_rn(1.0f, exp_neg(x))); }
+// the same on two values at once: the multiplies and adds are packed f32x2 instructions (each half is the scalar IEEE
+// operation), the special-function calls stay per value.  No packed multiply here feeds an add directly (such a pair
+// can be merged into a fused multiply-add, which rounds once instead of twice).
+__device__ __forceinline__ float2 sigmoid2(float2 x) {
+    const float2 t = __fmul2_rn(x, make_float2(-1.4426950408889634f, -1.4426950408889634f));
+    float2 e;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e.x) : "f"(t.x));
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e.y) : "f"(t.y));
+    const float2 d = __fadd2_rn(make_float2(1.0f, 1.0f), e);
+    return make_float2(rcp_fast(d.x), rcp_fast(d.y));
+}
+__device__ __forceinline__ float2 silu_mul2(float2 x, float2 y) { return __fmul2_rn(__fmul2_rn(x, y), sigmoid2(x)); }

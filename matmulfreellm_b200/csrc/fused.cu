@@ -141,8 +141,8 @@ __device__ __forceinline__ void bitlinear_prologue(float (&v)[P], int D, double 
     float amax[G];
 #pragma unroll
     for (int g = 0; g < G; ++g) amax[g] = 0.0f;
-    // fp32 multiplies and adds below are issued two at a time (packed f32x2 instructions: each half is the same IEEE
-    // round-to-nearest operation as the scalar instruction)
+    // independent fp32 multiplies below are issued two at a time (packed f32x2 instructions: each half is the same
+    // IEEE round-to-nearest operation as the scalar instruction); a multiply whose result feeds an add is never packed
     const float2 rstd2 = make_float2(rstd, rstd);
     ROW_FOREACH(V, D, it, c) {
 #pragma unroll
@@ -172,7 +172,6 @@ __device__ __forceinline__ void bitlinear_prologue(float (&v)[P], int D, double 
     for (int g = 0; g < G; ++g) {
         const float a = fmaxf(amax[g], 1e-5f);
         const float s = __fdiv_rn(127.0f, a);
-        const float2 s2 = make_float2(s, s);
         int8_t* qr = q + ((int64_t)g * M + m) * D;
         lsum[g] = 0;
         ROW_FOREACH(V, D, it, c) {
@@ -187,10 +186,11 @@ __device__ __forceinline__ void bitlinear_prologue(float (&v)[P], int D, double 
                     float2 y = make_float2(v[it * V + i + j], v[it * V + i + j + 1]);
                     if constexpr (G > 1) y = __fmul2_rn(y, make_float2(w[i + j], w[i + j + 1]));
                     // |y * s| <= 127 * (1 + 2^-23) because a >= |y|: the rounded code needs no clamp.  Adding 1.5 * 2^23
-                    // leaves the code, rounded to nearest even, in the low byte of the sum.
-                    const float2 r = __fadd2_rn(__fmul2_rn(y, s2), make_float2(12582912.0f, 12582912.0f));
-                    iv[j] = __float_as_int(r.x);
-                    iv[j + 1] = __float_as_int(r.y);
+                    // leaves the code, rounded to nearest even, in the low byte of the sum.  These two steps stay scalar:
+                    // a packed multiply followed by a packed add can be merged into one fused multiply-add, which would
+                    // round the exact product instead of the rounded one.
+                    iv[j] = __float_as_int(__fadd_rn(__fmul_rn(y.x, s), 12582912.0f));
+                    iv[j + 1] = __float_as_int(__fadd_rn(__fmul_rn(y.y, s), 12582912.0f));
                 }
                 // low bytes of the four codes -> one word; its signed byte sum joins the row's code sum in one instruction
                 const uint32_t word = __byte_perm(__byte_perm(iv[0], iv[1], 0x0040), __byte_perm(iv[2], iv[3], 0x0040), 0x5410);
@@ -248,7 +248,11 @@ prenorm_quant_kernel(PrenormArgs a) {
                 float r[V];
                 load16<T>(rr + c, r);
     #pragma unroll
-                for (int i = 0; i < V; ++i) x[i] = __fadd_rn(x[i], r[i]);
+                for (int i = 0; i < V; i += 2) {
+                    const float2 t = __fadd2_rn(make_float2(x[i], x[i + 1]), make_float2(r[i], r[i + 1]));
+                    x[i] = t.x;
+                    x[i + 1] = t.y;
+                }
             }
             if (ro || a.round_sum_first) {
                 float xr_[V];
@@ -277,7 +281,12 @@ prenorm_quant_kernel(PrenormArgs a) {
             uint32_t bits[V / 2];
             lds_weights<V>(sw + c, w);
 #pragma unroll
-            for (int i = 0; i < V; ++i) o[i] = __fmul_rn(__fmul_rn(v[it * V + i], rstd1), w[i]);
+            for (int i = 0; i < V; i += 2) {
+                const float2 t = __fmul2_rn(__fmul2_rn(make_float2(v[it * V + i], v[it * V + i + 1]), make_float2(rstd1, rstd1)),
+                                            make_float2(w[i], w[i + 1]));
+                o[i] = t.x;
+                o[i + 1] = t.y;
+            }
             round_vec<T, V>(o, bits);
 #pragma unroll
             for (int i = 0; i < V; ++i) {
@@ -305,9 +314,13 @@ __device__ __forceinline__ void gatenorm_tail(float (&gv)[P], const float (&ov)[
         uint32_t bits[V / 2];
         lds_weights<V>(sw + c, w);
 #pragma unroll
-        for (int i = 0; i < V; ++i) {
-            const float o = ov[it * V + i];
-            t[i] = __fmul_rn(__fmul_rn(__fmul_rn(__fmul_rn(gv[it * V + i], rstd), w[i]), o), sigmoidf_(o));
+        for (int i = 0; i < V; i += 2) {
+            const float2 o = make_float2(ov[it * V + i], ov[it * V + i + 1]);
+            float2 y = __fmul2_rn(__fmul2_rn(make_float2(gv[it * V + i], gv[it * V + i + 1]), make_float2(rstd, rstd)),
+                                  make_float2(w[i], w[i + 1]));
+            y = __fmul2_rn(__fmul2_rn(y, o), sigmoid2(o));
+            t[i] = y.x;
+            t[i + 1] = y.y;
         }
         round_vec<T, V>(t, bits);
 #pragma unroll
@@ -435,7 +448,11 @@ swiglu_quant_kernel(const T* __restrict__ gate, const T* __restrict__ up, int64_
             load16<T>(gr + c, gv);
             load16<T>(ur + c, uv);
     #pragma unroll
-            for (int i = 0; i < V; ++i) gv[i] = silu_mul(gv[i], uv[i]);
+            for (int i = 0; i < V; i += 2) {
+                const float2 t = silu_mul2(make_float2(gv[i], gv[i + 1]), make_float2(uv[i], uv[i + 1]));
+                gv[i] = t.x;
+                gv[i + 1] = t.y;
+            }
             uint32_t bits[V / 2];
             round_vec<T, V>(gv, bits);
     #pragma unroll

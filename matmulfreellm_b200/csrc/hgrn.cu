@@ -140,17 +140,19 @@ template <typename TX, int MODE>
 __device__ __forceinline__ void gate_transform2(float2& xv, float2& f, bool has_lb, float2 lbv, float2 oml) {
     if (MODE == HG_LOG) { f.x = exp_gate(f.x); f.y = exp_gate(f.y); }
     if (MODE == HG_RAW) {
-        f.x = sigmoidf_(f.x); f.y = sigmoidf_(f.y);
+        f = sigmoid2(f);
         round_pair<TX>(f.x, f.y);
         if (has_lb) {
+            // scalar on purpose: a packed multiply feeding a packed add can be merged into a fused multiply-add, and
+            // for a float activation dtype no rounding step separates the two
             f.x = __fmul_rn(oml.x, f.x); f.y = __fmul_rn(oml.y, f.y);
             round_pair<TX>(f.x, f.y);
             f.x = __fadd_rn(lbv.x, f.x); f.y = __fadd_rn(lbv.y, f.y);
             round_pair<TX>(f.x, f.y);
         }
-        float2 omf = make_float2(__fsub_rn(1.0f, f.x), __fsub_rn(1.0f, f.y));
+        float2 omf = __fadd2_rn(make_float2(1.0f, 1.0f), make_float2(-f.x, -f.y));   // 1 - f (the negation is exact)
         round_pair<TX>(omf.x, omf.y);
-        xv.x = silu_mul(xv.x, omf.x); xv.y = silu_mul(xv.y, omf.y);
+        xv = silu_mul2(xv, omf);
         round_pair<TX>(xv.x, xv.y);
     }
 }
@@ -263,8 +265,8 @@ hgrn_scan_kernel(const __grid_constant__ CUtensorMap x_map, const __grid_constan
                     float2 xv = ld2(px + j * HG_BD), f = ld2(pg + j * HG_BD);
                     gate_transform2<TX, MODE>(xv, f, has_lb, lbv, oml);
                     if (pm && !pm[j]) xv = make_float2(0.0f, 0.0f);
-                    h.x = fmaf(f.x, h.x, xv.x); h.y = fmaf(f.y, h.y, xv.y);
-                    a.x *= f.x; a.y *= f.y;
+                    h = __ffma2_rn(f, h, xv);      // both channels in one packed f32x2 instruction
+                    a = __fmul2_rn(a, f);
                     hl[j] = h; ap[j] = a;
                 }
             } else {
@@ -278,8 +280,8 @@ hgrn_scan_kernel(const __grid_constant__ CUtensorMap x_map, const __grid_constan
                     } else if (pm && !pm[j]) {
                         xv = make_float2(0.0f, 0.0f);
                     }
-                    h.x = fmaf(f.x, h.x, xv.x); h.y = fmaf(f.y, h.y, xv.y);
-                    a.x *= f.x; a.y *= f.y;
+                    h = __ffma2_rn(f, h, xv);      // both channels in one packed f32x2 instruction
+                    a = __fmul2_rn(a, f);
                     hl[j] = h; ap[j] = a;
                 }
             }
@@ -298,8 +300,7 @@ hgrn_scan_kernel(const __grid_constant__ CUtensorMap x_map, const __grid_constan
             if (q < sub) {                        // warp-uniform
                 const float2 qa = *reinterpret_cast<const float2*>(&s_agg_a[q][lc]);
                 const float2 qh = *reinterpret_cast<const float2*>(&s_agg_h[q][lc]);
-                cin.x = fmaf(qa.x, cin.x, qh.x);
-                cin.y = fmaf(qa.y, cin.y, qh.y);
+                cin = __ffma2_rn(qa, cin, qh);
             }
         }
         if (AGG) {
@@ -313,8 +314,10 @@ hgrn_scan_kernel(const __grid_constant__ CUtensorMap x_map, const __grid_constan
         } else {
             TX* po = so + ((s & 1) * HG_TS + sub * HG_SUBT) * HG_BD + lc;
 #pragma unroll
-            for (int j = 0; j < HG_SUBT; ++j)
-                st2(po + j * HG_BD, fmaf(ap[j].x, cin.x, hl[j].x), fmaf(ap[j].y, cin.y, hl[j].y));
+            for (int j = 0; j < HG_SUBT; ++j) {
+                const float2 o2 = __ffma2_rn(ap[j], cin, hl[j]);
+                st2(po + j * HG_BD, o2.x, o2.y);
+            }
             hg_fence_async_smem();                // generic-proxy writes -> visible to the TMA store
         }
         if (sub == HG_SUB - 1) {
