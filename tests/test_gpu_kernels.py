@@ -473,6 +473,24 @@ def test_hgrn_gated_with_padding_mask(K, dtype, tol, B, T, D):
 
 
 @pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
+def test_prenorm_quant_codes_exact_at_scale(K, dtype):
+    """6 million codes against the oracle.  A product that is rounded once instead of twice (a multiply merged with the
+    add that follows it) changes about one code in 260 000, which the small cases above cannot see."""
+    g = torch.Generator().manual_seed(77)
+    M, D = 1024, 2048
+    x = (torch.randn(M, D, generator=g) * 2).to(dtype)
+    nw = 1.0 + 0.1 * torch.randn(D, generator=g)
+    bl = [1.0 + 0.1 * torch.randn(D, generator=g) for _ in range(3)]
+    q, dq, rs, _, y = K.prenorm_quant(dev(x), None, dev(nw), 1e-6, [dev(b) for b in bl], 1e-6, False, want_y=True)
+    y = y.cpu()
+    for gi in range(3):
+        q_ref, dq_ref, rs_ref = O.act_codes(y, bl[gi], 1e-6)
+        assert np.array_equal(q[gi * M:(gi + 1) * M].cpu().numpy(), q_ref)
+        assert np.array_equal(dq[gi * M:(gi + 1) * M].cpu().numpy(), dq_ref)
+        assert np.array_equal(rs[gi * M:(gi + 1) * M].cpu().numpy(), rs_ref)
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
 @pytest.mark.parametrize("D", [704, 2048, 2560, 5632])
 def test_fused_row_kernels_many_rows(K, dtype, D):
     """With more rows than resident CTAs the fused row kernels loop over rows.  Rows are independent, so a 1500-row
