@@ -126,6 +126,13 @@ __device__ __forceinline__ void lds_weights(const float* p, float (&w)[V]) {
     }
 }
 
+// asynchronous 16-byte copy global -> shared memory (no register staging) and its group bookkeeping
+__device__ __forceinline__ void cp_async16(void* smem, const void* gmem) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"((uint32_t)__cvta_generic_to_shared(smem)), "l"(gmem) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+__device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wait_group 0;" ::: "memory"); }
+
 // iterate over the 16-byte vectors of a row held as v[P] (P: the enclosing template parameter): vector `it` of this thread starts at column c
 #define ROW_FOREACH(V, D, it, c) \
     _Pragma("unroll") for (int it = 0, c = threadIdx.x * (V); it < P / (V); ++it, c += FT * (V)) if (c < (D))
@@ -221,8 +228,8 @@ struct PrenormArgs {
     int round_sum_first;                   // 1: the reference added x+residual as a tensor op (rounded to T) before norm
 };
 
-template <typename T, int P>
-__global__ void __launch_bounds__(FT)
+template <typename T, int P, int LAT>
+__global__ void __launch_bounds__(FT, LAT)
 prenorm_quant_kernel(PrenormArgs a) {
     extern __shared__ __align__(16) float sw[];   // [1 + G][D]: block norm weight, then the BitLinear norm weights
     __shared__ RedScratch red;
@@ -234,10 +241,23 @@ prenorm_quant_kernel(PrenormArgs a) {
     pdl_wait();
     __syncthreads();
 
+    // Row loop (LAT = 0): the CTA's next row travels global -> shared memory by cp.async while the current one is
+    // processed (thread-private 16-byte slots: no barrier, only the thread's own wait)
+    T* sx = reinterpret_cast<T*>(sw + (1 + a.G) * D);   // [D] x row, [D] residual row (LAT = 0 only)
+    T* sr = sx + D;
+    auto fetch = [&](int64_t row) {
+        ROW_FOREACH(V, D, it, c) {
+            cp_async16(sx + c, reinterpret_cast<const T*>(a.x) + row * a.ld_x + c);
+            if (a.res) cp_async16(sr + c, reinterpret_cast<const T*>(a.res) + row * a.ld_res + c);
+        }
+        cp_async_commit();
+    };
+    if (LAT == 0 && blockIdx.x < a.M) fetch(blockIdx.x);
     // a CTA takes rows blockIdx.x, blockIdx.x + gridDim.x, ...: with many rows the staged norm weights are reused
     for (int64_t m = blockIdx.x; m < a.M; m += gridDim.x) {
-        const T* xr = reinterpret_cast<const T*>(a.x) + m * a.ld_x;
-        const T* rr = a.res ? reinterpret_cast<const T*>(a.res) + m * a.ld_res : nullptr;
+        const T* xr = LAT == 0 ? sx : reinterpret_cast<const T*>(a.x) + m * a.ld_x;
+        const T* rr = a.res ? (LAT == 0 ? sr : reinterpret_cast<const T*>(a.res) + m * a.ld_res) : nullptr;
+        if (LAT == 0) cp_async_wait_all();
         T* ro = a.res_out ? reinterpret_cast<T*>(a.res_out) + m * (int64_t)D : nullptr;
         float v[P];
         double ss[1] = {0.0};
@@ -272,6 +292,7 @@ prenorm_quant_kernel(PrenormArgs a) {
                 ss[0] += (double)x[i] * (double)x[i];
             }
         }
+        if (LAT == 0 && m + gridDim.x < a.M) fetch(m + gridDim.x);   // this thread's slots have just been read
         block_sum_d<1>(ss, red.d0);
         const float rstd1 = rstd_from_sumsq(ss[0], D, a.eps_norm);
         T* yo = a.y_out ? reinterpret_cast<T*>(a.y_out) + m * (int64_t)D : nullptr;
@@ -332,8 +353,8 @@ __device__ __forceinline__ void gatenorm_tail(float (&gv)[P], const float (&ov)[
     bitlinear_prologue<V, 1, P>(gv, D, ss2, eps_bl, sw + D, q, dq, rowsum, M, m, red);
 }
 
-template <typename T, int P>
-__global__ void __launch_bounds__(FT)
+template <typename T, int P, int LAT>
+__global__ void __launch_bounds__(FT, LAT)
 gatenorm_quant_kernel(const T* __restrict__ gx, int64_t ld_g, const T* __restrict__ o, int64_t ld_o,
                       const float* __restrict__ gw, float eps_g, const float* __restrict__ nw, float eps_bl,
                       int8_t* __restrict__ q, float* __restrict__ dq, int32_t* __restrict__ rowsum, int64_t M, int D) {
@@ -345,10 +366,22 @@ gatenorm_quant_kernel(const T* __restrict__ gx, int64_t ld_g, const T* __restric
     stage_weights(sw + D, nw, D);
     pdl_wait();
     __syncthreads();
+    // Row loop (LAT = 0): next row by cp.async into thread-private slots, as in prenorm_quant_kernel
+    T* sg = reinterpret_cast<T*>(sw + 2 * D);   // [D] g row, [D] o row (LAT = 0 only)
+    T* so = sg + D;
+    auto fetch = [&](int64_t row) {
+        ROW_FOREACH(V, D, it, c) {
+            cp_async16(sg + c, gx + row * ld_g + c);
+            cp_async16(so + c, o + row * ld_o + c);
+        }
+        cp_async_commit();
+    };
+    if (LAT == 0 && blockIdx.x < M) fetch(blockIdx.x);
     // a CTA takes rows blockIdx.x, blockIdx.x + gridDim.x, ...: with many rows the staged norm weights are reused
     for (int64_t m = blockIdx.x; m < M; m += gridDim.x) {
-        const T* gr = gx + m * ld_g;
-        const T* orow = o + m * ld_o;
+        const T* gr = LAT == 0 ? sg : gx + m * ld_g;
+        const T* orow = LAT == 0 ? so : o + m * ld_o;
+        if (LAT == 0) cp_async_wait_all();
         float gv[P], ov[P];
         double ss = 0.0;
         ROW_FOREACH(V, D, it, c) {
@@ -362,6 +395,7 @@ gatenorm_quant_kernel(const T* __restrict__ gx, int64_t ld_g, const T* __restric
                 ss += (double)a[i] * (double)a[i];
             }
         }
+        if (LAT == 0 && m + gridDim.x < M) fetch(m + gridDim.x);   // this thread's slots have just been read
         gatenorm_tail<T, V, P>(gv, ov, ss, D, eps_g, eps_bl, sw, q, dq, rowsum, M, m, red);
     }
 }
@@ -369,8 +403,8 @@ gatenorm_quant_kernel(const T* __restrict__ gx, int64_t ld_g, const T* __restric
 // Single-token step of the token mixer for row b (mmfreelm/layers/hgrn_bit.py:113-140 with T = 1):
 //   f = round(sigmoid(f_raw)); with lb: f = round(lb + round(round(1-lb)*f));  x = round(silu(i_raw)*round(1-f))
 //   h = f*h + x  (fp32 state, updated in place);  o = round(h);  then gatenorm_quant(g_raw, o).
-template <typename T, int P>
-__global__ void __launch_bounds__(FT)
+template <typename T, int P, int LAT>
+__global__ void __launch_bounds__(FT, LAT)
 decode_mix_kernel(const T* __restrict__ ifg, int64_t ld, const T* __restrict__ lb, float* __restrict__ state,
                   const float* __restrict__ gw, float eps_g, const float* __restrict__ nw, float eps_bl,
                   int8_t* __restrict__ q, float* __restrict__ dq, int32_t* __restrict__ rowsum, int64_t M, int D) {
@@ -426,8 +460,8 @@ decode_mix_kernel(const T* __restrict__ ifg, int64_t ld, const T* __restrict__ l
 }
 
 // z = round_T(silu(gate)*up), then BitLinear prologue.  gate/up are the two halves of a [M, 2D] tensor.
-template <typename T, int P>
-__global__ void __launch_bounds__(FT)
+template <typename T, int P, int LAT>
+__global__ void __launch_bounds__(FT, LAT)
 swiglu_quant_kernel(const T* __restrict__ gate, const T* __restrict__ up, int64_t ld, const float* __restrict__ nw,
                     float eps_bl, int8_t* __restrict__ q, float* __restrict__ dq, int32_t* __restrict__ rowsum, int64_t M, int D) {
     extern __shared__ __align__(16) float sw[];
@@ -437,10 +471,24 @@ swiglu_quant_kernel(const T* __restrict__ gate, const T* __restrict__ up, int64_
     stage_weights(sw, nw, D);
     pdl_wait();
     __syncthreads();
+    // Row loop (LAT = 0): the next row of this CTA travels global -> shared memory by cp.async while the current one is
+    // reduced and quantised, so its load latency is hidden without holding it in registers.  Every thread copies and
+    // later reads the same 16-byte slots, so the copies need no barrier, only the thread's own wait.
+    T* sg = reinterpret_cast<T*>(sw + D);   // [D] gate row, [D] up row (LAT = 0 only)
+    T* su = sg + D;
+    auto fetch = [&](int64_t row) {
+        ROW_FOREACH(V, D, it, c) {
+            cp_async16(sg + c, gate + row * ld + c);
+            cp_async16(su + c, up + row * ld + c);
+        }
+        cp_async_commit();
+    };
+    if (LAT == 0 && blockIdx.x < M) fetch(blockIdx.x);
     // a CTA takes rows blockIdx.x, blockIdx.x + gridDim.x, ...: with many rows the staged norm weights are reused
     for (int64_t m = blockIdx.x; m < M; m += gridDim.x) {
-        const T* gr = gate + m * ld;
-        const T* ur = up + m * ld;
+        const T* gr = LAT == 0 ? sg : gate + m * ld;
+        const T* ur = LAT == 0 ? su : up + m * ld;
+        if (LAT == 0) cp_async_wait_all();
         float v[P];
         double ss = 0.0;
         ROW_FOREACH(V, D, it, c) {
@@ -461,6 +509,7 @@ swiglu_quant_kernel(const T* __restrict__ gate, const T* __restrict__ up, int64_
                 ss += (double)gv[i] * (double)gv[i];
             }
         }
+        if (LAT == 0 && m + gridDim.x < M) fetch(m + gridDim.x);   // this thread's slots have just been read
         bitlinear_prologue<V, 1, P>(v, D, ss, eps_bl, sw, q, dq, rowsum, M, m, red);
     }
 }
@@ -505,8 +554,17 @@ static inline unsigned row_grid(Kern kernel, size_t smem, int64_t M) {
     else if ((D) <= FT * 16) { constexpr int P = 16; __VA_ARGS__; }   \
     else { constexpr int P = 32; __VA_ARGS__; }
 
+// Two builds of every kernel.  LAT = 1 (at least one CTA per SM: the compiler may spend registers on overlapping the
+// loads and reductions of a row) for calls whose rows are all resident at once, i.e. decode steps, where the latency of
+// a row is what counts; LAT = 0 (no hint: fewer registers, more resident CTAs) for the row loop over a prompt.
+constexpr int64_t LAT_MAX_ROWS = 296;
+#define FUSED_DISPATCH_LAT(M, LAT, ...)                                \
+    if ((M) <= LAT_MAX_ROWS) { constexpr int LAT = 1; __VA_ARGS__; }   \
+    else { constexpr int LAT = 0; __VA_ARGS__; }
+
+// the 48 KB that need no opt-in include the kernel's static shared memory (reduction scratch)
 #define FUSED_SMEM_ATTR(kernel, smem) \
-    if ((smem) > 48 * 1024) MMF_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)(smem)))
+    if ((smem) + 2048 > 48 * 1024) MMF_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)(smem)))
 
 extern "C" int mmf_prenorm_quant(const void* x, int64_t ld_x, const void* residual, int64_t ld_res, int dtype,
                                  int round_sum_first, const float* norm_w, float eps_norm, void* residual_out,
@@ -527,12 +585,12 @@ extern "C" int mmf_prenorm_quant(const void* x, int64_t ld_x, const void* residu
     a.x = x; a.ld_x = ld_x; a.res = residual; a.ld_res = ld_res; a.res_out = residual_out; a.y_out = y_out;
     a.norm_w = norm_w; a.eps_norm = eps_norm; a.nws[0] = nw0; a.nws[1] = nw1; a.nws[2] = nw2; a.eps_bl = eps_bl;
     a.q = q; a.dq = dq; a.rowsum = rowsum; a.M = M; a.D = (int)D; a.G = groups; a.round_sum_first = round_sum_first;
-    const size_t smem = (size_t)(1 + groups) * D * sizeof(float);
     MMF_DISPATCH(dtype, T, {
-        FUSED_DISPATCH_P(D, P, {
-            FUSED_SMEM_ATTR((prenorm_quant_kernel<T, P>), smem);
-            MMF_CUDA(mmf_launch_pdl(prenorm_quant_kernel<T, P>, dim3(row_grid(prenorm_quant_kernel<T, P>, smem, M)), dim3(FT), smem, (cudaStream_t)stream, a));
-        });
+        FUSED_DISPATCH_P(D, P, { FUSED_DISPATCH_LAT(M, LAT, {
+            const size_t smem = (size_t)(1 + groups) * D * sizeof(float) + (LAT ? 0 : (size_t)2 * D * sizeof(T));   // + row staging
+            FUSED_SMEM_ATTR((prenorm_quant_kernel<T, P, LAT>), smem);
+            MMF_CUDA(mmf_launch_pdl(prenorm_quant_kernel<T, P, LAT>, dim3(row_grid(prenorm_quant_kernel<T, P, LAT>, smem, M)), dim3(FT), smem, (cudaStream_t)stream, a));
+        }); });
     });
     MMF_LAUNCH_CHECK("prenorm_quant_kernel");
     return MMF_OK;
@@ -548,13 +606,13 @@ extern "C" int mmf_gatenorm_quant(const void* g, int64_t ld_g, const void* o, in
                     mmf_aligned(gnorm_w, 16) && mmf_aligned(nw, 16),
                 MMF_ERR_ALIGN, "mmf_gatenorm_quant: rows and norm weights must be 16-byte aligned");
     if (M == 0) return MMF_OK;
-    const size_t smem = (size_t)2 * D * sizeof(float);
     MMF_DISPATCH(dtype, T, {
-        FUSED_DISPATCH_P(D, P, {
-            FUSED_SMEM_ATTR((gatenorm_quant_kernel<T, P>), smem);
-            MMF_CUDA(mmf_launch_pdl(gatenorm_quant_kernel<T, P>, dim3(row_grid(gatenorm_quant_kernel<T, P>, smem, M)), dim3(FT), smem, (cudaStream_t)stream, (const T*)g,
+        FUSED_DISPATCH_P(D, P, { FUSED_DISPATCH_LAT(M, LAT, {
+            const size_t smem = (size_t)2 * D * sizeof(float) + (LAT ? 0 : (size_t)2 * D * sizeof(T));   // + row staging
+            FUSED_SMEM_ATTR((gatenorm_quant_kernel<T, P, LAT>), smem);
+            MMF_CUDA(mmf_launch_pdl(gatenorm_quant_kernel<T, P, LAT>, dim3(row_grid(gatenorm_quant_kernel<T, P, LAT>, smem, M)), dim3(FT), smem, (cudaStream_t)stream, (const T*)g,
                                     ld_g, (const T*)o, ld_o, gnorm_w, eps_g, nw, eps_bl, q, dq, rowsum, M, (int)D));
-        });
+        }); });
     });
     MMF_LAUNCH_CHECK("gatenorm_quant_kernel");
     return MMF_OK;
@@ -573,11 +631,11 @@ extern "C" int mmf_decode_mix(const void* ifg, int64_t ld, int dtype, const void
     if (M == 0) return MMF_OK;
     const size_t smem = (size_t)3 * D * sizeof(float);
     MMF_DISPATCH(dtype, T, {
-        FUSED_DISPATCH_P(D, P, {
-            FUSED_SMEM_ATTR((decode_mix_kernel<T, P>), smem);
-            MMF_CUDA(mmf_launch_pdl(decode_mix_kernel<T, P>, dim3((unsigned)M), dim3(FT), smem, (cudaStream_t)stream, (const T*)ifg, ld,
+        FUSED_DISPATCH_P(D, P, { FUSED_DISPATCH_LAT(M, LAT, {
+            FUSED_SMEM_ATTR((decode_mix_kernel<T, P, LAT>), smem);
+            MMF_CUDA(mmf_launch_pdl(decode_mix_kernel<T, P, LAT>, dim3((unsigned)M), dim3(FT), smem, (cudaStream_t)stream, (const T*)ifg, ld,
                                     (const T*)lower_bound, state, gnorm_w, eps_g, nw, eps_bl, q, dq, rowsum, M, (int)D));
-        });
+        }); });
     });
     MMF_LAUNCH_CHECK("decode_mix_kernel");
     return MMF_OK;
@@ -591,13 +649,13 @@ extern "C" int mmf_swiglu_quant(const void* gate, const void* up, int64_t ld, in
     MMF_REQUIRE(mmf_aligned(gate, 16) && mmf_aligned(up, 16) && mmf_aligned(q, 16) && (ld * es) % 16 == 0 && mmf_aligned(nw, 16),
                 MMF_ERR_ALIGN, "mmf_swiglu_quant: rows and norm weight must be 16-byte aligned");
     if (M == 0) return MMF_OK;
-    const size_t smem = (size_t)D * sizeof(float);
     MMF_DISPATCH(dtype, T, {
-        FUSED_DISPATCH_P(D, P, {
-            FUSED_SMEM_ATTR((swiglu_quant_kernel<T, P>), smem);
-            MMF_CUDA(mmf_launch_pdl(swiglu_quant_kernel<T, P>, dim3(row_grid(swiglu_quant_kernel<T, P>, smem, M)), dim3(FT), smem, (cudaStream_t)stream, (const T*)gate,
+        FUSED_DISPATCH_P(D, P, { FUSED_DISPATCH_LAT(M, LAT, {
+            const size_t smem = (size_t)D * sizeof(float) + (LAT ? 0 : (size_t)2 * D * sizeof(T));   // + row staging in the row loop
+            FUSED_SMEM_ATTR((swiglu_quant_kernel<T, P, LAT>), smem);
+            MMF_CUDA(mmf_launch_pdl(swiglu_quant_kernel<T, P, LAT>, dim3(row_grid(swiglu_quant_kernel<T, P, LAT>, smem, M)), dim3(FT), smem, (cudaStream_t)stream, (const T*)gate,
                                     (const T*)up, ld, nw, eps_bl, q, dq, rowsum, M, (int)D));
-        });
+        }); });
     });
     MMF_LAUNCH_CHECK("swiglu_quant_kernel");
     return MMF_OK;

@@ -493,16 +493,17 @@ def test_prenorm_quant_codes_exact_at_scale(K, dtype):
 @pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
 @pytest.mark.parametrize("D", [704, 2048, 2560, 5632])
 def test_fused_row_kernels_many_rows(K, dtype, D):
-    """With more rows than resident CTAs the fused row kernels loop over rows.  Rows are independent, so a 1500-row
-    call must reproduce, bit for bit, the same rows run in two small one-CTA-per-row calls (the shape checked against
-    the oracle above)."""
+    """With more rows than resident CTAs the fused row kernels run their second build: CTAs loop over rows and fetch
+    the next row into shared memory while they work.  Rows are independent, so a 1500-row call must reproduce, bit for
+    bit, the same rows run in 250-row calls, which take the one-CTA-per-row build that the cases above check against
+    the oracle."""
     g = torch.Generator().manual_seed(D)
     M = 1500
     x = dev((torch.randn(M, D, generator=g) * 2).to(dtype))
     res = dev(torch.randn(M, D, generator=g).to(dtype))
     nw = dev(1.0 + 0.1 * torch.randn(D, generator=g))
     bl = [dev(1.0 + 0.1 * torch.randn(D, generator=g)) for _ in range(3)]
-    parts = [slice(0, 700), slice(700, M)]
+    parts = [slice(i, i + 250) for i in range(0, M, 250)]
 
     def check(fn, n_groups):
         big = fn(slice(0, M))
