@@ -566,7 +566,11 @@ bool choose_config(const BitLinearArgs& a, MmaParams& best, size_t& best_smem) {
                     smem = 1024 + (size_t)p.SB * NT * 128 + (size_t)2 * p.SW * W_STAGE_BYTES;
                     occ = 1;
                 } else {
-                    p.SA = 4; p.SB = 4; p.SW = NT >= 128 ? 8 : 12;   // 8 keeps a 128-token tile under half an SM's shared memory
+                    // ring depths measured on whole decode steps (batch 32 / 64 / 128): six A / activation stages instead of
+                    // four are worth 4 % at 64 token columns and 2.5 % at 128, a 16-deep packed-weight ring (more of the
+                    // weight stream fetched while the preceding kernel still runs) another 5 % at 64 columns but -8 % at 128
+                    p.SA = p.SB = NT <= 128 ? 6 : 4;
+                    p.SW = NT >= 128 ? 8 : NT <= 64 ? 16 : 12;
                     // one accumulator: the issuing thread needs about 67 cycles per MMA, which already exceeds the pipe time of a
                     // dependent small-N MMA, and every extra accumulator is one more TMEM read round trip in the epilogue
                     p.nacc = 1;
