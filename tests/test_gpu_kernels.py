@@ -619,3 +619,29 @@ def test_sample_top_p_vs_oracle(K, dtype, temperature, top_p):
     # same inputs, same tokens
     again = K.sample_top_p(dev(logits), temperature, top_p, dev(u)).cpu().numpy()
     assert np.array_equal(got, again)
+
+
+@pytest.mark.parametrize("gate_is_log", [True, False])
+def test_time_sliced_scan_stitches_to_whole_scan(K, gate_is_log):
+    """The exchange of the sequence-sharded scan, with the ranks emulated one after the other on one GPU: every
+    slice is reduced to (decay, final state), the pairs are folded, slices after the first are run again from their
+    incoming state.  Outputs and the final state must equal the scan over the whole sequence (fp32 state 1e-4)."""
+    from matmulfreellm_b200.seq_sharding import fold_carries, slice_decay
+    g = torch.Generator().manual_seed(31)
+    B, T, D = 2, 3000, 128
+    x = dev(torch.randn(B, T, D, generator=g).to(torch.bfloat16))
+    gl = torch.nn.functional.logsigmoid(torch.randn(B, T, D, generator=g) + 2.0)
+    gate = dev(gl if gate_is_log else gl.exp())
+    h0 = dev(torch.randn(B, D, generator=g))
+    o_ref, h_ref = K.hgrn_scan(x, gate, h0, True, gate_is_log=gate_is_log, state_dtype=torch.float32)
+    cuts = [(0, 1000), (1000, 1001), (1001, 2200), (2200, T)]
+    first = [K.hgrn_scan(x[:, a:b].contiguous(), gate[:, a:b].contiguous(), h0 if i == 0 else None, True,
+                         gate_is_log=gate_is_log, state_dtype=torch.float32) for i, (a, b) in enumerate(cuts)]
+    decay = torch.stack([slice_decay(gate[:, a:b], gate_is_log) for a, b in cuts])
+    carry, last = fold_carries(decay, torch.stack([f[1] for f in first]))
+    outs = [first[0][0]] + [K.hgrn_scan(x[:, a:b].contiguous(), gate[:, a:b].contiguous(), carry[i].contiguous(), True,
+                                        gate_is_log=gate_is_log, state_dtype=torch.float32)[0]
+                            for i, (a, b) in enumerate(cuts) if i > 0]
+    o = torch.cat(outs, dim=1)
+    assert (o.float() - o_ref.float()).abs().max().item() <= 1e-2 * o_ref.float().abs().max().item()
+    assert (last - h_ref).abs().max().item() <= 1e-4 * h_ref.abs().max().item()

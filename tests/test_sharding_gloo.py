@@ -61,3 +61,69 @@ def test_single_process_passthrough():
     t = torch.arange(6).view(3, 2)
     assert gather_batch(t, 3) is t
     assert torch.equal(generate_sharded(_EchoModel(), t, 1), torch.cat([t, t[:, :1]], 1))
+
+
+# ------------------------------------------------------------------------------------------------------------
+# sequence (T) sharding of the recurrence: one (decay, final state) exchange per scan
+# ------------------------------------------------------------------------------------------------------------
+def _cpu_scan(gate_is_log):
+    """h_t = f_t * h_{t-1} + x_t in fp32, as the oracle's naive recurrence; stands in for the CUDA scan kernel."""
+    def scan(x, g, h0):
+        f = g.float().exp() if gate_is_log else g.float()
+        h = torch.zeros(x.shape[0], x.shape[-1]) if h0 is None else h0.float().clone()
+        o = torch.empty(x.shape, dtype=torch.float32)
+        for t in range(x.shape[1]):
+            h = f[:, t] * h + x[:, t].float()
+            o[:, t] = h
+        return o.to(x.dtype), h
+    return scan
+
+
+def _seq_case(gate_is_log, T=53):
+    g = torch.Generator().manual_seed(11)
+    x = torch.randn(2, T, 8, generator=g)
+    gate = torch.nn.functional.logsigmoid(torch.randn(2, T, 8, generator=g) + 1.0)
+    return x, (gate if gate_is_log else gate.exp()), torch.randn(2, 8, generator=g)
+
+
+def _seq_worker(rank, world, port, gate_is_log):
+    from matmulfreellm_b200.seq_sharding import hgrn_scan_seq_sharded
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        x, gate, h0 = _seq_case(gate_is_log)
+        scan = _cpu_scan(gate_is_log)
+        o_ref, h_ref = scan(x, gate, h0)
+        lo, hi = shard_range(x.shape[1], rank, world)            # ragged slices: 53 positions over 2 or 3 ranks
+        o, last = hgrn_scan_seq_sharded(x[:, lo:hi].contiguous(), gate[:, lo:hi].contiguous(), h0, gate_is_log,
+                                        local_scan=scan)
+        assert torch.allclose(o, o_ref[:, lo:hi], rtol=1e-5, atol=1e-5)
+        assert torch.allclose(last, h_ref, rtol=1e-5, atol=1e-5)     # the whole sequence's final state, on every rank
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("world,gate_is_log", [(2, True), (3, True), (2, False)])
+def test_sequence_sharded_scan_matches_whole_scan(world, gate_is_log):
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        port = s.getsockname()[1]
+    mp.spawn(_seq_worker, args=(world, port, gate_is_log), nprocs=world, join=True)
+
+
+def test_fold_carries_and_single_process():
+    from matmulfreellm_b200.seq_sharding import fold_carries, hgrn_scan_seq_sharded, slice_decay
+    x, gate, h0 = _seq_case(True)
+    scan = _cpu_scan(True)
+    o_ref, h_ref = scan(x, gate, h0)
+    # three slices folded by hand
+    cuts = [(0, 20), (20, 21), (21, 53)]
+    decay = torch.stack([slice_decay(gate[:, a:b], True) for a, b in cuts])
+    final = torch.stack([scan(x[:, a:b], gate[:, a:b], h0 if i == 0 else None)[1] for i, (a, b) in enumerate(cuts)])
+    carry, last = fold_carries(decay, final)
+    assert torch.allclose(last, h_ref, rtol=1e-5, atol=1e-5)
+    assert torch.count_nonzero(carry[0]) == 0
+    assert torch.allclose(carry[2], scan(x[:, :21], gate[:, :21], h0)[1], rtol=1e-5, atol=1e-5)
+    # without a process group the call is the plain scan
+    o, last = hgrn_scan_seq_sharded(x, gate, h0, True, local_scan=scan)
+    assert torch.equal(o, o_ref) and torch.equal(last, h_ref)
