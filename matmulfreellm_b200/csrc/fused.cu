@@ -26,7 +26,7 @@ constexpr int FT = 256;        // threads per row CTA
 constexpr int FW = FT / 32;    // warps
 constexpr int MAX_PER = 32;    // most row values a thread can hold -> D <= FT * MAX_PER = 8192
 constexpr int MAX_D = FT * MAX_PER;
-// Kernels are compiled for P = 8, 16 and 32 row values per thread (D <= 2048, 4096, 8192): the row lives in
+// Kernels are compiled for P = 8, 16, 24 and 32 row values per thread (D <= 2048, 4096, 6144, 8192): the row lives in
 // registers, so the smaller instantiations leave room for more resident CTAs.
 
 // One-sync block reductions: warp shuffle, lane 0 parks the partial in a slot that is used once per row,
@@ -552,6 +552,7 @@ static inline unsigned row_grid(Kern kernel, size_t smem, int64_t M) {
 #define FUSED_DISPATCH_P(D, P, ...)                                   \
     if ((D) <= FT * 8) { constexpr int P = 8; __VA_ARGS__; }          \
     else if ((D) <= FT * 16) { constexpr int P = 16; __VA_ARGS__; }   \
+    else if ((D) <= FT * 24) { constexpr int P = 24; __VA_ARGS__; }   \
     else { constexpr int P = 32; __VA_ARGS__; }
 
 // Two builds of every kernel.  LAT = 1 (at least one CTA per SM: the compiler may spend registers on overlapping the
