@@ -491,7 +491,7 @@ def test_prenorm_quant_codes_exact_at_scale(K, dtype):
 
 
 @pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
-@pytest.mark.parametrize("D", [704, 2048, 2560, 5632])
+@pytest.mark.parametrize("D", [704, 2048, 2560, 5632, 6912])
 def test_fused_row_kernels_many_rows(K, dtype, D):
     """With more rows than resident CTAs the fused row kernels run their second build: CTAs loop over rows and fetch
     the next row into shared memory while they work.  Rows are independent, so a 1500-row call must reproduce, bit for
