@@ -143,8 +143,19 @@ class FusedRunner:
 
     @staticmethod
     def fingerprint(lm):
-        """Changes whenever a parameter is replaced, cast or modified in place."""
-        return tuple((p.data_ptr(), p._version, p.dtype) for p in lm.parameters())
+        """Changes whenever a parameter is replaced, cast or modified in place.  Walking the module tree costs about
+        2 ms per call on a 24-block model, so the (parameter dict, name) slots are listed once per model object and
+        only looked up afterwards; a replaced parameter is still seen, because the slot is read anew."""
+        slots = lm.__dict__.get("_fused_param_slots")
+        if slots is None:
+            slots = [(m._parameters, n) for m in lm.modules() for n in m._parameters]
+            object.__setattr__(lm, "_fused_param_slots", slots)
+        out = []
+        for d, n in slots:
+            p = d.get(n)
+            if p is not None:
+                out.append((p.data_ptr(), p._version, p.dtype))
+        return tuple(out)
 
     @torch.no_grad()
     def forward(self, input_ids, inputs_embeds, states, last_only: bool, want_logits: bool = True,
