@@ -151,6 +151,7 @@ def act_quant(x: torch.Tensor, norm_weight: Optional[torch.Tensor], eps: float, 
 
 
 _ws_cache: dict = {}
+_ws_bytes: dict = {}   # (M, N, K) -> mmf_bitlinear_workspace_bytes, a pure function of the shape
 
 
 def _workspace(device: torch.device, nbytes: int) -> torch.Tensor:
@@ -199,7 +200,9 @@ def bitlinear(q: torch.Tensor, dq: torch.Tensor, rowsum: torch.Tensor, pw: Packe
     acc = torch.empty(M, pw.N, dtype=torch.int32, device=q.device) if return_acc else None
     if M == 0:
         return (out, acc) if return_acc else out
-    nbytes = _lib.load().mmf_bitlinear_workspace_bytes(M, pw.N, pw.K)
+    nbytes = _ws_bytes.get((M, pw.N, pw.K))
+    if nbytes is None:
+        nbytes = _ws_bytes[(M, pw.N, pw.K)] = _lib.load().mmf_bitlinear_workspace_bytes(M, pw.N, pw.K)
     ws = _workspace(q.device, nbytes)
     try:
         _lib.call("mmf_bitlinear", q.data_ptr(), dq.data_ptr(), rowsum.data_ptr(), pw.packed.data_ptr(),
