@@ -558,7 +558,11 @@ static inline unsigned row_grid(Kern kernel, size_t smem, int64_t M) {
 // Two builds of every kernel.  LAT = 1 (at least one CTA per SM: the compiler may spend registers on overlapping the
 // loads and reductions of a row) for calls whose rows are all resident at once, i.e. decode steps, where the latency of
 // a row is what counts; LAT = 0 (no hint: fewer registers, more resident CTAs) for the row loop over a prompt.
-constexpr int64_t LAT_MAX_ROWS = 296;
+// Measured on whole decode steps: the register-rich build still wins at 320 - 448 rows (2 - 3 %), equal at 512.
+#ifndef MMF_LAT_MAX_ROWS
+#define MMF_LAT_MAX_ROWS 592
+#endif
+constexpr int64_t LAT_MAX_ROWS = MMF_LAT_MAX_ROWS;
 #define FUSED_DISPATCH_LAT(M, LAT, ...)                                \
     if ((M) <= LAT_MAX_ROWS) { constexpr int LAT = 1; __VA_ARGS__; }   \
     else { constexpr int LAT = 0; __VA_ARGS__; }
