@@ -32,6 +32,10 @@ class GreedyDecoder:
         self.graph: Optional[torch.cuda.CUDAGraph] = None
         self.kernels_per_step = 0
         self._use_graph = use_graph
+        # prompt passes of a repeated length are replayed from a graph as well: an eager pass is about 200 launches
+        # through Python (about 19 us of host time each), which is more than the GPU needs for a short prompt
+        self._prompt_seen: dict = {}       # prompt length -> times seen
+        self._prompt_graphs: dict = {}     # prompt length -> (graph, static ids buffer), at most PROMPT_GRAPHS entries
 
     def _step_eager(self):
         out = self.model(input_ids=self.ids, past_key_values=self.cache, use_cache=True)
@@ -59,16 +63,51 @@ class GreedyDecoder:
                 dst.copy_(src)
         self.ids.copy_(saved_ids)
 
-    @torch.no_grad()
-    def prefill(self, prompt_ids: torch.Tensor) -> torch.Tensor:
-        """Run the prompt [B, T]; returns the first generated token [B] (also left in self.ids / self.next)."""
-        if prompt_ids.shape[0] != self.B:
-            raise ValueError(f"decoder was built for batch {self.B}, got {prompt_ids.shape[0]}")
+    PROMPT_GRAPH_MAX_TOKENS = 8192   # larger prompts are bound by the GPU, and their graphs would pin gigabytes
+    PROMPT_GRAPHS = 4
+
+    def _prefill_eager(self, prompt_ids: torch.Tensor) -> None:
         out = self.model(input_ids=prompt_ids, use_cache=True, last_token_only=True)
         for layer, new in zip(self.cache.states, out.past_key_values):
             for dst, src in zip(layer, new):
                 dst.copy_(src)
         kernels.argmax_rows(out.logits[:, -1], out=self.next)
+
+    def _capture_prompt(self, T: int):
+        ids = torch.zeros(self.B, T, dtype=torch.int64, device=self.device)
+        side = torch.cuda.Stream(device=self.device)
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            self._prefill_eager(ids)               # warm-up outside capture (allocator, workspace of this stream)
+        torch.cuda.current_stream().wait_stream(side)
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph, stream=side):
+            self._prefill_eager(ids)
+        if len(self._prompt_graphs) >= self.PROMPT_GRAPHS:
+            self._prompt_graphs.pop(next(iter(self._prompt_graphs)))
+        self._prompt_graphs[T] = (graph, ids)
+        return graph, ids
+
+    @torch.no_grad()
+    def prefill(self, prompt_ids: torch.Tensor) -> torch.Tensor:
+        """Run the prompt [B, T]; returns the first generated token [B] (also left in self.ids / self.next).  The
+        pass overwrites the recurrent state (a prompt starts from the zero state).  From the second prompt of the same
+        length on, the pass is replayed from a CUDA graph."""
+        if prompt_ids.shape[0] != self.B:
+            raise ValueError(f"decoder was built for batch {self.B}, got {prompt_ids.shape[0]}")
+        T = prompt_ids.shape[1]
+        if self._use_graph and self.B * T <= self.PROMPT_GRAPH_MAX_TOKENS:
+            entry = self._prompt_graphs.get(T)
+            seen = self._prompt_seen.get(T, 0)
+            self._prompt_seen[T] = seen + 1
+            if entry is None and seen >= 1:
+                entry = self._capture_prompt(T)
+            if entry is not None:
+                graph, ids = entry
+                ids.copy_(prompt_ids)
+                graph.replay()
+                return self.next
+        self._prefill_eager(prompt_ids)
         return self.next
 
     @torch.no_grad()

@@ -321,3 +321,29 @@ def test_packed_checkpoint_round_trip(mm, tmp_path):
     for x, y in zip(a.past_key_values, b.past_key_values):
         assert torch.equal(x[0], y[0])
     assert torch.equal(model.generate(ids, max_new_tokens=8), loaded.generate(ids, max_new_tokens=8))
+
+
+def test_decoder_replays_repeated_prompt_lengths_from_a_graph(mm):
+    """GreedyDecoder runs the first prompt of a length eagerly and captures the pass on the second one; every later
+    prompt of that length is a graph replay.  Eager, captured and replayed passes give identical tokens, a prompt starts
+    from the zero state whatever ran before, and other lengths are unaffected."""
+    from matmulfreellm_b200.engine import GreedyDecoder
+    cfg = tiny_cfg()
+    sd = O.random_weights(cfg, seed=3)
+    model = build_gpu_model(sd, cfg, torch.bfloat16)
+    g = torch.Generator().manual_seed(9)
+    prompts = [torch.randint(0, 32000, (3, 12), generator=g).cuda() for _ in range(4)]
+    other = torch.randint(0, 32000, (3, 7), generator=g).cuda()
+    ref = GreedyDecoder(model, 3, use_graph=False)
+    want = [ref.generate(p, 6) for p in prompts]
+    want_other = ref.generate(other, 6)
+    dec = GreedyDecoder(model, 3)
+    got = [dec.generate(prompts[0], 6), dec.generate(prompts[1], 6)]      # eager, then capture + replay
+    assert 12 in dec._prompt_graphs
+    got.append(dec.generate(other, 6))                                     # another length in between (eager)
+    got += [dec.generate(prompts[2], 6), dec.generate(prompts[3], 6)]      # replays
+    assert 7 not in dec._prompt_graphs
+    assert torch.equal(got[0], want[0]) and torch.equal(got[1], want[1])
+    assert torch.equal(got[2], want_other)
+    assert torch.equal(got[3], want[2]) and torch.equal(got[4], want[3])
+    mm.kernels.check_status()
