@@ -111,6 +111,16 @@ class GreedyDecoder:
         return self.next
 
     @torch.no_grad()
+    def seed(self, past_key_values, last_logits: torch.Tensor) -> torch.Tensor:
+        """Take over after a prompt pass made elsewhere (e.g. one with a padding mask): copy its recurrent states
+        into the static cache and pick the first token from its last-position logits [B, V]."""
+        for layer, new in zip(self.cache.states, past_key_values):
+            for dst, src in zip(layer, new):
+                dst.copy_(src)
+        kernels.argmax_rows(last_logits, out=self.next)
+        return self.next
+
+    @torch.no_grad()
     def step(self) -> torch.Tensor:
         """Consume self.ids, produce the next token in self.next (and feed it back). Returns self.next."""
         if not self._use_graph:

@@ -253,6 +253,52 @@ class HGRNBitForCausalLM(HGRNBitPreTrainedModel):
         return CausalLMOutputWithPast(loss=None, logits=logits, past_key_values=outputs.past_key_values,
                                       hidden_states=outputs.hidden_states, attentions=None)
 
+    GREEDY_DECODERS = 2    # decoders (static state + captured step graph) kept per model, one per batch size
+
+    @torch.no_grad()
+    def _generate_greedy_graph(self, input_ids, max_new_tokens, eos_token_id, attention_mask):
+        """Greedy generation with every decode step replayed from a CUDA graph (an eager step is about 200 launches
+        through Python, several times what the GPU needs).  Same tokens as the step-by-step loop of `generate`:
+        sequences are independent, so a finished sequence may keep running; its tokens after the first
+        `eos_token_id` are overwritten with it, and the result is cut where the loop would have stopped."""
+        from ...engine import GreedyDecoder, fused_runner
+        B = input_ids.shape[0]
+        key = fused_runner(self).key
+        decs = self.__dict__.get("_greedy_decoders")
+        if decs is None or decs.get("key") != key:        # weights replaced or repacked: captured graphs are stale
+            decs = {"key": key}
+            object.__setattr__(self, "_greedy_decoders", decs)
+        dec = decs.pop(B, None)
+        if dec is None:
+            dec = GreedyDecoder(self, B)
+            while len(decs) - 1 >= self.GREEDY_DECODERS:
+                decs.pop(next(k for k in decs if k != "key"))
+        decs[B] = dec                                       # most recently used last
+        if attention_mask is None:
+            dec.prefill(input_ids)
+        else:
+            out = self(input_ids=input_ids, attention_mask=attention_mask, use_cache=True, last_token_only=True)
+            dec.seed(out.past_key_values, out.logits[:, -1])
+        toks = torch.empty(B, max_new_tokens, dtype=torch.int64, device=input_ids.device)
+        n = 0
+        while n < max_new_tokens:
+            toks[:, n].copy_(dec.next)
+            n += 1
+            if n == max_new_tokens:
+                break
+            if eos_token_id is not None and n % 16 == 0 and bool((toks[:, :n] == eos_token_id).any(dim=1).all()):
+                break                                       # every sequence has finished (checked every 16 steps)
+            dec.step()
+        toks = toks[:, :n]
+        if eos_token_id is not None:
+            hit = toks == eos_token_id
+            after = (hit.cumsum(dim=1) - hit.to(torch.int64)) > 0          # positions after a sequence's first eos
+            toks = torch.where(after, torch.full_like(toks, eos_token_id), toks)
+            if bool(hit.any(dim=1).all()):                  # the step loop stops once the last sequence emits eos
+                first = torch.where(hit, torch.arange(n, device=toks.device).expand_as(hit), n).min(dim=1).values
+                toks = toks[:, : int(first.max().item()) + 1]
+        return torch.cat([input_ids, toks], dim=1)
+
     # -- fused execution -------------------------------------------------------------------------------------
     fuse = True   # set False to run module by module (same kernels, unfused; used to cross-check the fused chain)
 
@@ -293,14 +339,15 @@ class HGRNBitForCausalLM(HGRNBitPreTrainedModel):
     def generate(self, input_ids: torch.LongTensor, max_new_tokens: int = 20, max_length: Optional[int] = None,
                  do_sample: bool = False, eos_token_id: Optional[int] = None, top_p: float = 1.0, temperature: float = 1.0,
                  generator: Optional[torch.Generator] = None, attention_mask: Optional[torch.Tensor] = None,
-                 **kwargs) -> torch.LongTensor:
+                 use_graph: bool = True, **kwargs) -> torch.LongTensor:
         """Prefill once, then one cached single-token forward per new token; greedy, or with `do_sample=True` nucleus
         sampling (temperature, then top-p, as `generate.py:11` of the reference asks of transformers).
 
         The reference defers to transformers' GenerationMixin (:311-324), which current transformers releases
         no longer provide to this class.  Sampling draws one uniform number per sequence and step from `generator`
         (a CUDA generator; the default one if None) and is deterministic given those.  `attention_mask` marks
-        left padding of the prompt.  Returns [B, prompt + new] token ids like GenerationMixin.generate."""
+        left padding of the prompt.  Greedy decoding replays each step from a CUDA graph (`use_graph=False` runs the
+        same kernels step by step).  Returns [B, prompt + new] token ids like GenerationMixin.generate."""
         if kwargs.get("num_beams", 1) != 1 or kwargs.get("top_k"):
             raise NotImplementedError("only greedy decoding and temperature / top-p sampling are implemented")
 
@@ -312,6 +359,9 @@ class HGRNBitForCausalLM(HGRNBitPreTrainedModel):
 
         if max_length is not None:
             max_new_tokens = max(0, max_length - input_ids.shape[1])
+        if use_graph and not do_sample and max_new_tokens > 0 and input_ids.is_cuda and \
+                self._can_fuse(input_ids, None, attention_mask, None):
+            return self._generate_greedy_graph(input_ids, max_new_tokens, eos_token_id, attention_mask)
         out = self(input_ids=input_ids, attention_mask=attention_mask, use_cache=True, last_token_only=True)
         cache = RecurrentCache.from_legacy_cache(out.past_key_values, input_ids.shape[1])
         tokens = [input_ids]

@@ -347,3 +347,39 @@ def test_decoder_replays_repeated_prompt_lengths_from_a_graph(mm):
     assert torch.equal(got[2], want_other)
     assert torch.equal(got[3], want[2]) and torch.equal(got[4], want[3])
     mm.kernels.check_status()
+
+
+def test_generate_graph_path_equals_step_loop(mm):
+    """`generate` replays greedy decode steps from a CUDA graph; tokens, the handling of eos (finished sequences
+    keep emitting it, the result ends where the last sequence finishes) and left-padded prompts must equal the
+    step-by-step loop, also when batch sizes alternate and after the weights change."""
+    cfg = tiny_cfg()
+    sd = O.random_weights(cfg, seed=4)
+    model = build_gpu_model(sd, cfg, torch.bfloat16)
+    g = torch.Generator().manual_seed(2)
+    ids3 = torch.randint(0, 32000, (3, 9), generator=g).cuda()
+    ids5 = torch.randint(0, 32000, (5, 4), generator=g).cuda()
+    for ids in (ids3, ids5, ids3):
+        want = model.generate(ids, max_new_tokens=40, use_graph=False)
+        got = model.generate(ids, max_new_tokens=40)
+        assert torch.equal(got, want)
+        new = want[:, ids.shape[1]:]
+        # eos choices: a token every sequence emits at some step (cuts the result), one that only one sequence
+        # emits (that sequence is padded with it), one that never appears
+        common = [t for t in new[0].tolist() if all(t in row for row in new.tolist())]
+        for eos in ([common[0]] if common else []) + [int(new[1, 3]), 31999]:
+            a = model.generate(ids, max_new_tokens=40, eos_token_id=eos, use_graph=False)
+            b = model.generate(ids, max_new_tokens=40, eos_token_id=eos)
+            assert torch.equal(a, b), eos
+    assert len([k for k in model._greedy_decoders if k != "key"]) == 2
+    mask = torch.ones(3, 9, dtype=torch.int64, device="cuda")
+    mask[0, :4] = 0
+    mask[2, :1] = 0
+    assert torch.equal(model.generate(ids3, max_new_tokens=12, attention_mask=mask),
+                       model.generate(ids3, max_new_tokens=12, attention_mask=mask, use_graph=False))
+    # new weights: the cached decoders (graphs with the old weight pointers baked in) must not be reused
+    with torch.no_grad():
+        model.model.layers[0].mlp.down_proj.weight.mul_(-1.0)
+    model.pack_weights()
+    assert torch.equal(model.generate(ids3, max_new_tokens=12), model.generate(ids3, max_new_tokens=12, use_graph=False))
+    mm.kernels.check_status()
