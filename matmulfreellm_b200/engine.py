@@ -31,6 +31,7 @@ class GreedyDecoder:
             [layer.attn.init_state(batch_size) for layer in model.model.layers])
         self.graph: Optional[torch.cuda.CUDAGraph] = None
         self.kernels_per_step = 0
+        self.last_logits: Optional[torch.Tensor] = None
         self._use_graph = use_graph
         # prompt passes of a repeated length are replayed from a graph as well: an eager pass is about 200 launches
         # through Python (about 19 us of host time each), which is more than the GPU needs for a short prompt
@@ -39,7 +40,10 @@ class GreedyDecoder:
 
     def _step_eager(self):
         out = self.model(input_ids=self.ids, past_key_values=self.cache, use_cache=True)
-        kernels.argmax_rows(out.logits[:, -1], out=self.next)
+        # [B, V] logits of the step; inside the captured graph this is a fixed buffer that every replay rewrites, so a
+        # caller that samples instead of taking the arg-max reads it after step() and overwrites self.next
+        self.last_logits = out.logits[:, -1]
+        kernels.argmax_rows(self.last_logits, out=self.next)
 
     def _capture(self):
         saved = [tuple(s.clone() for s in layer) for layer in self.cache.states]

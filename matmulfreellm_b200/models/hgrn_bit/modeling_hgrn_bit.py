@@ -256,11 +256,13 @@ class HGRNBitForCausalLM(HGRNBitPreTrainedModel):
     GREEDY_DECODERS = 2    # decoders (static state + captured step graph) kept per model, one per batch size
 
     @torch.no_grad()
-    def _generate_greedy_graph(self, input_ids, max_new_tokens, eos_token_id, attention_mask):
-        """Greedy generation with every decode step replayed from a CUDA graph (an eager step is about 200 launches
+    def _generate_graph(self, input_ids, max_new_tokens, eos_token_id, attention_mask, pick=None):
+        """Generation with every decode step replayed from a CUDA graph (an eager step is about 200 launches
         through Python, several times what the GPU needs).  Same tokens as the step-by-step loop of `generate`:
         sequences are independent, so a finished sequence may keep running; its tokens after the first
-        `eos_token_id` are overwritten with it, and the result is cut where the loop would have stopped."""
+        `eos_token_id` are overwritten with it, and the result is cut where the loop would have stopped.
+        `pick` (sampling) maps the step's logits [B, V] to tokens [B]; None takes the graph's own arg-max.  Sampling
+        draws its random numbers in the same order as the step loop, so both give the same tokens."""
         from ...engine import GreedyDecoder, fused_runner
         B = input_ids.shape[0]
         key = fused_runner(self).key
@@ -274,11 +276,13 @@ class HGRNBitForCausalLM(HGRNBitPreTrainedModel):
             while len(decs) - 1 >= self.GREEDY_DECODERS:
                 decs.pop(next(k for k in decs if k != "key"))
         decs[B] = dec                                       # most recently used last
-        if attention_mask is None:
+        if attention_mask is None and pick is None:
             dec.prefill(input_ids)
         else:
             out = self(input_ids=input_ids, attention_mask=attention_mask, use_cache=True, last_token_only=True)
             dec.seed(out.past_key_values, out.logits[:, -1])
+            if pick is not None:
+                dec.next.copy_(pick(out.logits[:, -1]))
         toks = torch.empty(B, max_new_tokens, dtype=torch.int64, device=input_ids.device)
         n = 0
         while n < max_new_tokens:
@@ -289,6 +293,8 @@ class HGRNBitForCausalLM(HGRNBitPreTrainedModel):
             if eos_token_id is not None and n % 16 == 0 and bool((toks[:, :n] == eos_token_id).any(dim=1).all()):
                 break                                       # every sequence has finished (checked every 16 steps)
             dec.step()
+            if pick is not None:
+                dec.next.copy_(pick(dec.last_logits))
         toks = toks[:, :n]
         if eos_token_id is not None:
             hit = toks == eos_token_id
@@ -359,9 +365,8 @@ class HGRNBitForCausalLM(HGRNBitPreTrainedModel):
 
         if max_length is not None:
             max_new_tokens = max(0, max_length - input_ids.shape[1])
-        if use_graph and not do_sample and max_new_tokens > 0 and input_ids.is_cuda and \
-                self._can_fuse(input_ids, None, attention_mask, None):
-            return self._generate_greedy_graph(input_ids, max_new_tokens, eos_token_id, attention_mask)
+        if use_graph and max_new_tokens > 0 and input_ids.is_cuda and self._can_fuse(input_ids, None, attention_mask, None):
+            return self._generate_graph(input_ids, max_new_tokens, eos_token_id, attention_mask, pick if do_sample else None)
         out = self(input_ids=input_ids, attention_mask=attention_mask, use_cache=True, last_token_only=True)
         cache = RecurrentCache.from_legacy_cache(out.past_key_values, input_ids.shape[1])
         tokens = [input_ids]

@@ -377,6 +377,14 @@ def test_generate_graph_path_equals_step_loop(mm):
     mask[2, :1] = 0
     assert torch.equal(model.generate(ids3, max_new_tokens=12, attention_mask=mask),
                        model.generate(ids3, max_new_tokens=12, attention_mask=mask, use_graph=False))
+    # sampling through the graph decoder draws the same random numbers in the same order as the step loop
+    for eos in (None, int(want[0, -3])):
+        g1 = torch.Generator(device="cuda").manual_seed(11)
+        g2 = torch.Generator(device="cuda").manual_seed(11)
+        a = model.generate(ids3, max_new_tokens=24, do_sample=True, top_p=0.8, temperature=0.9, generator=g1, eos_token_id=eos)
+        b = model.generate(ids3, max_new_tokens=24, do_sample=True, top_p=0.8, temperature=0.9, generator=g2, eos_token_id=eos,
+                           use_graph=False)
+        assert torch.equal(a, b), eos
     # new weights: the cached decoders (graphs with the old weight pointers baked in) must not be reused
     with torch.no_grad():
         model.model.layers[0].mlp.down_proj.weight.mul_(-1.0)
