@@ -118,11 +118,15 @@ int mmf_act_quant(const void* x, int dtype, int64_t ld_x, const float* norm_w, i
  * mmfreelm/ops/fusedbitnet.py:456-458 (cuBLAS fp16/bf16 GEMM in the reference).
  * ------------------------------------------------------------------------------------ */
 
-/* Which kernel mmf_bitlinear runs. AUTO: GEMV below MMF_MMA_MIN_M rows, tcgen05 above. */
+/* Which kernel mmf_bitlinear runs.  AUTO: the decode kernel up to MMF_STREAM_MAX_M token rows (when the codes of
+ * all rows fit in shared memory), tcgen05 above; the CUDA-core GEMV only on request. */
 #define MMF_KERNEL_AUTO 0
-#define MMF_KERNEL_GEMV 1 /* CUDA-core dp4a, weight-streaming, any M (slow for large M) */
-#define MMF_KERNEL_MMA 2  /* tcgen05 kind::i8 tensor-core tiles, weights unpacked into TMEM */
+#define MMF_KERNEL_GEMV 1   /* CUDA-core dp4a, weight-streaming, any M (slow for large M) */
+#define MMF_KERNEL_MMA 2    /* tcgen05 kind::i8 tensor-core tiles, weights unpacked into TMEM */
+#define MMF_KERNEL_STREAM 3 /* decode kernel: one persistent CTA per SM, codes resident in shared memory, weights streamed
+                               by bulk TMA ahead of the grid dependency, mma.sync m16n8k32 per (16 rows x 8 tokens); M <= 64 */
 #define MMF_MMA_MIN_M 5
+#define MMF_STREAM_MAX_M 64
 
 /* Bytes of int32 workspace mmf_bitlinear may need for split-K partial sums (a multiple of
  * 256; includes a 256-byte header whose first word is a status flag — 0, or 1 if a bounded

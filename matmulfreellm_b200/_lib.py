@@ -12,7 +12,7 @@ from pathlib import Path
 LIB_PATH = Path(__file__).resolve().parent / "libmmfree_b200.so"
 
 F32, BF16, F16 = 0, 1, 2
-KERNEL_AUTO, KERNEL_GEMV, KERNEL_MMA = 0, 1, 2
+KERNEL_AUTO, KERNEL_GEMV, KERNEL_MMA, KERNEL_STREAM = 0, 1, 2, 3
 TILE_ROWS, TILE_K = 128, 64
 ABSMEAN_PARTIALS = 1024
 ABI_VERSION = 1

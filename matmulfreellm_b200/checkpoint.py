@@ -115,7 +115,7 @@ def load_packed(path: str, device="cuda"):
             m.weight = nn.Parameter(torch.empty(0, device=device, dtype=dtype), requires_grad=False)
             m._packed = kernels.PackedWeight(torch.from_numpy(z[f"{name}.packed"].copy()).to(device),
                                              torch.from_numpy(z[f"{name}.scale"].copy()).to(device), N, K, 1)
-            m._packed_version = None
+            m._packed_from = None
             m.norm.weight = nn.Parameter(torch.from_numpy(z[f"{name}.norm"].copy()).to(device=device, dtype=dtype),
                                          requires_grad=False)
         params = dict(model.named_parameters())

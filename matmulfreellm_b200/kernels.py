@@ -13,7 +13,7 @@ import ctypes
 import torch
 
 from . import _lib
-from ._lib import BF16, F16, F32, KERNEL_AUTO, KERNEL_GEMV, KERNEL_MMA, TILE_K, TILE_ROWS  # noqa: F401
+from ._lib import BF16, F16, F32, KERNEL_AUTO, KERNEL_GEMV, KERNEL_MMA, KERNEL_STREAM, TILE_K, TILE_ROWS  # noqa: F401
 
 _DT = {torch.float32: F32, torch.bfloat16: BF16, torch.float16: F16}
 
@@ -23,6 +23,12 @@ def _code(dtype: torch.dtype) -> int:
         return _DT[dtype]
     except KeyError:
         raise TypeError(f"unsupported dtype {dtype}; expected float32, bfloat16 or float16") from None
+
+
+# torch.cuda.current_stream() costs about 13 us of host time per call (device-index resolution, a Stream object);
+# the raw handle is available directly, and a prompt pass makes several hundred launches
+_raw_stream = getattr(torch._C, "_cuda_getCurrentRawStream", None)
+_raw_device = getattr(torch._C, "_cuda_getDevice", None)
 
 
 def _need_cuda(*tensors: Optional[torch.Tensor]) -> torch.device:
@@ -37,18 +43,18 @@ def _need_cuda(*tensors: Optional[torch.Tensor]) -> torch.device:
         elif t.device != dev:
             raise RuntimeError(f"tensors on different devices: {dev} and {t.device}")
     assert dev is not None
-    _lib.require_device(dev.index if dev.index is not None else torch.cuda.current_device())
+    # the C entry points launch on the CURRENT device and `_stream()` is the current device's stream: tensors of
+    # another GPU would be handed to a kernel running on this one (a fault, or with peer access silently the wrong GPU)
+    cur = _raw_device() if _raw_device is not None else torch.cuda.current_device()
+    if dev.index is not None and dev.index != cur:
+        raise RuntimeError(f"tensors live on cuda:{dev.index} but the current device is cuda:{cur}; wrap the call in "
+                           f"`with torch.cuda.device({dev.index}):` (the library launches on the current device)")
+    _lib.require_device(cur)
     return dev
 
 
 def _ptr(t: Optional[torch.Tensor]):
     return None if t is None else t.data_ptr()
-
-
-# torch.cuda.current_stream() costs about 13 us of host time per call (device-index resolution, a Stream object);
-# the raw handle is available directly, and a prompt pass makes several hundred launches
-_raw_stream = getattr(torch._C, "_cuda_getCurrentRawStream", None)
-_raw_device = getattr(torch._C, "_cuda_getDevice", None)
 
 
 def _stream() -> int:
@@ -150,18 +156,33 @@ def act_quant(x: torch.Tensor, norm_weight: Optional[torch.Tensor], eps: float, 
     return q, dq, rs
 
 
-_ws_cache: dict = {}
-_ws_bytes: dict = {}   # (M, N, K) -> mmf_bitlinear_workspace_bytes, a pure function of the shape
+_ws_cache: dict = {}     # (device index, raw stream handle) -> current workspace of that stream
+_ws_retired: list = []   # workspaces that were outgrown: never freed, because a captured CUDA graph may still point at them
+_ws_bytes: dict = {}     # (M, N, K) -> mmf_bitlinear_workspace_bytes, a pure function of the shape
 
 
 def _workspace(device: torch.device, nbytes: int) -> torch.Tensor:
-    """Zero-initialised split-K workspace, one per (device, stream); kernels leave it zeroed."""
+    """Zero-initialised split-K workspace, one per (device, stream); kernels leave it zeroed.
+
+    A captured CUDA graph (decode step, prompt pass) bakes in the address of the workspace it was captured with, so a
+    workspace is never released once handed out: when a later call on the same stream needs a larger one, the old
+    buffer is retired (kept alive) and a new one takes its place for new launches."""
     key = (device.index, _stream())
     ws = _ws_cache.get(key)
     if ws is None or ws.numel() < nbytes:
+        if ws is not None:
+            _ws_retired.append(ws)
         ws = torch.zeros(max(nbytes, 1 << 20), dtype=torch.uint8, device=device)
         _ws_cache[key] = ws
     return ws
+
+
+def _rezero_workspaces() -> None:
+    """After a failed launch or a device-side time-out partial sums may be left behind: clear every workspace in place
+    (their addresses stay valid for captured graphs)."""
+    for ws in list(_ws_cache.values()) + _ws_retired:
+        with torch.cuda.device(ws.device):
+            ws.zero_()
 
 
 def check_status() -> None:
@@ -171,11 +192,11 @@ def check_status() -> None:
     _lib.call("mmf_hgrn_status", ctypes.addressof(failed))
     if failed.value:
         raise _lib.MMFreeError("mmf_hgrn_scan", -7, "a scan kernel gave up waiting for a TMA stage")
-    for key, ws in list(_ws_cache.items()):
+    for ws in list(_ws_cache.values()) + _ws_retired:
         torch.cuda.synchronize(ws.device)
         status = int(ws[:4].view(torch.int32).item())
         if status != 0:
-            _ws_cache.pop(key, None)
+            _rezero_workspaces()
             raise _lib.MMFreeError("mmf_bitlinear", -7, f"device-side wait timed out (status word {status})")
 
 
@@ -209,7 +230,7 @@ def bitlinear(q: torch.Tensor, dq: torch.Tensor, rowsum: torch.Tensor, pw: Packe
                   pw.scale.data_ptr(), G, out.data_ptr(), _code(out_dtype), out.stride(0), _ptr(acc), M, pw.N, pw.K,
                   ws.data_ptr(), ws.numel(), kernel, _stream())
     except _lib.MMFreeError:
-        _ws_cache.clear()  # a failed launch may have left partial sums behind
+        _rezero_workspaces()  # a failed launch may have left partial sums behind
         raise
     return (out, acc) if return_acc else out
 

@@ -329,14 +329,18 @@ class HGRNBitForCausalLM(HGRNBitPreTrainedModel):
         if use_cache and past_key_values is not None:
             cache = past_key_values if isinstance(past_key_values, RecurrentCache) \
                 else RecurrentCache.from_legacy_cache(past_key_values)
-            for layer_states in cache.states:
-                if layer_states[-1].dtype != torch.float32:
-                    raise TypeError("recurrent states are kept in float32")
         else:
             cache = RecurrentCache.from_legacy_cache([layer.attn.init_state(B) for layer in layers])
-        states = [cache.states[i][-1] for i in range(len(layers))]
+        # The kernels advance float32 states in place.  A cache built the reference's way holds its states in the
+        # parameter dtype (init_state: param.new_zeros; fused_recurrent_hgrn returns x.dtype): such states are widened
+        # for the pass and written back, rounded to their own dtype, afterwards — the reference's rounding point.
+        given = [cache.states[i][-1] for i in range(len(layers))]
+        states = [s if s.dtype == torch.float32 else s.float() for s in given]
         logits, _ = fused_runner(self).forward(input_ids, inputs_embeds, states, last_token_only,
                                                attention_mask=attention_mask)
+        for dst, src in zip(given, states):
+            if dst is not src:
+                dst.copy_(src)
         if use_cache and past_key_values is not None and len(layers):
             cache._seen_tokens += ref.shape[1]
         return logits, (cache.to_legacy_cache() if use_cache else None)

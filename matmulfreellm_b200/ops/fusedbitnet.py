@@ -42,21 +42,43 @@ class BitLinear(nn.Linear):
         super().__init__(in_features, out_features, bias=bias)
         self.norm = RMSNorm(in_features, eps=1e-8)
         self._packed: Optional[kernels.PackedWeight] = None
-        self._packed_version = None
+        self._packed_from = None    # (parameter object, its _version, its dtype, packed by an explicit call) at pack time
         self._norm_w32: Optional[torch.Tensor] = None
         self._norm_version = None
 
     # -- offline packing -------------------------------------------------------------------------
+    def _pack(self, explicit: bool) -> kernels.PackedWeight:
+        w = self.weight
+        self._packed = kernels.pack_weight(w)
+        self._packed_from = (w, w._version, w.dtype, explicit)
+        return self._packed
+
     def pack_weights(self) -> kernels.PackedWeight:
         """(Re)build the 2-bit packed weight from the current latent weight. Called lazily by forward; call it
         yourself before casting the module to half precision so the codes come from the fp32 weights."""
-        self._packed = kernels.pack_weight(self.weight)
-        self._packed_version = (self.weight._version, self.weight.data_ptr())
-        return self._packed
+        return self._pack(explicit=True)
 
     def packed(self) -> kernels.PackedWeight:
-        if self._packed is None or self._packed.device != self.weight.device:
-            self.pack_weights()
+        """The packed weight that matches the CURRENT latent weight.  The reference re-ternarises on every forward
+        (fusedbitnet.py:456); here the codes are rebuilt whenever the weight was replaced or modified in place
+        (load_state_dict, weight.mul_, re-initialisation) since they were made.  A dtype cast alone (.half(),
+        .bfloat16()) keeps codes that pack_weights() made from the higher-precision weight; codes packed lazily by
+        a forward are rebuilt from the cast weight, which is what the reference would ternarise.  A module loaded
+        from a packed checkpoint has no latent weight (numel 0) and keeps its codes."""
+        w = self.weight
+        if self._packed is None:
+            return self._pack(explicit=False)
+        if w.numel() == 0 or self._packed_from is None:
+            if self._packed.device != w.device:
+                self._packed = kernels.PackedWeight(self._packed.packed.to(w.device), self._packed.scale.to(w.device),
+                                                    self._packed.N, self._packed.K, self._packed.groups)
+            return self._packed
+        src, version, dtype, explicit = self._packed_from
+        if src is not w or w._version != version or (w.dtype != dtype and not explicit):
+            return self._pack(explicit=False)
+        if self._packed.device != w.device:     # the module moved: the codes move with it
+            self._packed = kernels.PackedWeight(self._packed.packed.to(w.device), self._packed.scale.to(w.device),
+                                                self._packed.N, self._packed.K, self._packed.groups)
         return self._packed
 
     def norm_weight_f32(self) -> torch.Tensor:

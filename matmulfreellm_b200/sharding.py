@@ -57,18 +57,37 @@ def gather_batch(local: torch.Tensor, n_total: int, group: Optional[dist.Process
 @torch.no_grad()
 def generate_sharded(model, input_ids: torch.Tensor, max_new_tokens: int, group: Optional[dist.ProcessGroup] = None,
                      **generate_kwargs) -> torch.Tensor:
-    """Greedy-generate for the full batch `input_ids` [B, T] (identical on every rank): each rank decodes its
-    slice with `model.generate`, then one gather returns [B, T + new] on every rank.  Ranks whose slice is
-    empty (B < world) only take part in the gather."""
-    B = input_ids.shape[0]
+    """Generate for the full batch `input_ids` [B, T] (identical on every rank): each rank decodes its slice with
+    `model.generate`, then one gather returns [B, T + new] on every rank.  Ranks whose slice is empty (B < world)
+    only take part in the gather.
+
+    With `eos_token_id`, `generate` ends a slice where its last sequence finished, so the ranks' results differ in
+    width.  A collective needs equal element counts on every rank: each slice is padded with eos to
+    T + max_new_tokens before the gather, and the gathered batch is cut where a single-GPU `generate` of the whole
+    batch would have stopped (one past the step at which the last sequence emitted eos, if every sequence did)."""
+    B, T = input_ids.shape
     world = dist.get_world_size(group) if dist.is_initialized() else 1
     rank = dist.get_rank(group) if dist.is_initialized() else 0
+    eos = generate_kwargs.get("eos_token_id")
     mine = shard_batch(input_ids, rank, world)
+    full_width = T + max_new_tokens
     if mine.shape[0]:
         out = model.generate(mine, max_new_tokens=max_new_tokens, **generate_kwargs)
+        if out.shape[1] < full_width:
+            if eos is None:
+                raise RuntimeError(f"generate returned {out.shape[1]} positions, expected {full_width}")
+            pad = out.new_full((out.shape[0], full_width - out.shape[1]), int(eos))
+            out = torch.cat([out, pad], dim=1)
     else:
-        out = input_ids.new_empty((0, input_ids.shape[1] + max_new_tokens))
-    return gather_batch(out, B, group)
+        out = input_ids.new_empty((0, full_width))
+    full = gather_batch(out, B, group)
+    if eos is not None and B and max_new_tokens:
+        hit = full[:, T:] == int(eos)
+        if bool(hit.any(dim=1).all()):
+            steps = torch.arange(max_new_tokens, device=full.device).expand_as(hit)
+            first = torch.where(hit, steps, torch.full_like(steps, max_new_tokens)).min(dim=1).values
+            full = full[:, : T + int(first.max().item()) + 1]
+    return full
 
 
 def _self_check() -> None:

@@ -361,17 +361,17 @@ def hgrn_case(B: int, T: int, D: int, seed: int = 0, dtype=torch.bfloat16):
     x = ((1 - torch.exp(g_log)) * F.silu(torch.randn(B, 1, T, D, generator=g))).to(dtype)
     return x, g_log
 
-def sample_top_p_ref(logits, temperature: float, top_p: float, uniforms):
-    """Nucleus sampling with caller-supplied uniform numbers, restating what the reference asks of transformers in
-    generate.py:11 (`do_sample=True, top_p=..., temperature=...`): logits / temperature -> softmax -> keep the
-    smallest set of most probable tokens whose mass reaches top_p (ties with the least probable kept token kept) ->
-    draw by inverse CDF in token order: the first kept token whose running kept mass exceeds u * kept mass.
-    Returns (tokens int64 [M], margin [M]) where margin is the distance of u * kept mass to the nearest CDF step and
-    of top_p to the nearest nucleus step, relative to the total mass (rows with a tiny margin are ill-conditioned)."""
-    import numpy as np
+def nucleus_ref(logits, temperature: float, top_p: float):
+    """What the reference's `model.generate(do_sample=True, top_p=..., temperature=...)` (generate.py:11) asks of
+    transformers before it draws: TemperatureLogitsWarper (logits / temperature) then TopPLogitsWarper (keep the most
+    probable tokens up to and including the one at which the kept mass reaches top_p, i.e. drop a token when the mass
+    of the strictly more probable ones is already >= top_p; at least one token stays).  Tokens exactly as probable as
+    the least probable kept one are all kept.  Returns (kept bool [M,V], unnormalised fp64 weights [M,V] of the
+    tempered softmax, boundary margin [M]: distance of top_p from the nearest cumulative-mass step, relative to the
+    total mass).  Pinned against transformers' own warpers in tests/test_oracle_golden.py."""
     z = np.asarray(logits, dtype=np.float32) * np.float32(1.0 / temperature)
     p = np.exp((z - z.max(-1, keepdims=True)).astype(np.float32)).astype(np.float64)
-    out = np.zeros(p.shape[0], dtype=np.int64)
+    kept = np.zeros(p.shape, dtype=bool)
     margin = np.zeros(p.shape[0])
     for m in range(p.shape[0]):
         row = p[m]
@@ -381,17 +381,29 @@ def sample_top_p_ref(logits, temperature: float, top_p: float, uniforms):
         want = min(top_p, 1.0) * total
         k = int(np.searchsorted(csum, want, side="left"))          # first position with csum >= want
         k = min(k, len(row) - 1)
-        tau = row[order[k]]
-        kept = row >= tau
-        kp = np.where(kept, row, 0.0)
-        c = np.cumsum(kp)
+        kept[m] = row >= row[order[k]]
+        margin[m] = (np.abs(csum[:-1] - want).min() / total) if top_p < 1.0 and len(row) > 1 else np.inf
+    return kept, p, margin
+
+
+def sample_top_p_ref(logits, temperature: float, top_p: float, uniforms):
+    """Nucleus sampling with caller-supplied uniform numbers: the kept set and weights of `nucleus_ref`, then a draw
+    by inverse CDF in token order — the first kept token whose running kept mass exceeds u * kept mass (the
+    multinomial draw of transformers' sampling loop, made deterministic by taking the uniform number as an input).
+    Returns (tokens int64 [M], margin [M]) where margin is the distance of u * kept mass to the nearest CDF step and
+    of top_p to the nearest nucleus step, relative to the total mass (rows with a tiny margin are ill-conditioned)."""
+    kept_all, p, nucleus = nucleus_ref(logits, temperature, top_p)
+    out = np.zeros(p.shape[0], dtype=np.int64)
+    margin = np.zeros(p.shape[0])
+    for m in range(p.shape[0]):
+        row, kept = p[m], kept_all[m]
+        total = row.sum()
+        c = np.cumsum(np.where(kept, row, 0.0))
         target = float(uniforms[m]) * c[-1]
         idx = int(np.searchsorted(c, target, side="right"))        # first index with c > target
         idx = min(idx, len(row) - 1)
         while not kept[idx]:
             idx += 1
         out[m] = idx
-        steps = c[kept]
-        nucleus = np.abs(csum[:-1] - want).min() if top_p < 1.0 and len(row) > 1 else np.inf   # top_p >= 1 keeps everything
-        margin[m] = min(np.abs(steps - target).min(), nucleus) / total
+        margin[m] = min(np.abs(c[kept] - target).min() / total, nucleus[m])
     return out, margin

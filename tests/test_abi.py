@@ -79,3 +79,26 @@ def test_cpu_tensors_are_refused():
     from matmulfreellm_b200 import kernels
     with pytest.raises(RuntimeError, match="CUDA tensors only"):
         kernels.rmsnorm(torch.zeros(2, 64), torch.ones(64), 1e-6)
+
+
+def test_kernels_refuse_tensors_of_another_device(monkeypatch):
+    """The C entry points launch on the current CUDA device; tensors that live on another GPU must be refused before
+    anything is launched (checked with stand-in tensor objects: no GPU needed)."""
+    import types
+
+    import pytest
+    import torch
+
+    from matmulfreellm_b200 import _lib, kernels
+    monkeypatch.setattr(kernels, "_raw_device", lambda: 0)
+    monkeypatch.setattr(_lib, "require_device", lambda idx: None)
+    t0 = types.SimpleNamespace(is_cuda=True, device=torch.device("cuda", 0))
+    t1 = types.SimpleNamespace(is_cuda=True, device=torch.device("cuda", 1))
+    cpu = types.SimpleNamespace(is_cuda=False, device=torch.device("cpu"))
+    assert kernels._need_cuda(t0, None, t0) == torch.device("cuda", 0)
+    with pytest.raises(RuntimeError, match="current device is cuda:0"):
+        kernels._need_cuda(t1)
+    with pytest.raises(RuntimeError, match="different devices"):
+        kernels._need_cuda(t0, t1)
+    with pytest.raises(RuntimeError, match="CUDA tensors only"):
+        kernels._need_cuda(cpu)

@@ -1,0 +1,203 @@
+"""Parity at the full benchmark sizes (run with `-m gpu` on a B200).
+
+Every shape whose throughput the bench quotes is compared with the CPU oracle here:
+  * the BitLinear sweep at 4096 and 16384 token rows for all four layer shapes — activation codes of every row,
+    int32 accumulators of 256 sampled rows, an int64 column checksum over all rows, and the bf16 output;
+  * the HGRN recurrence at B = 8, D = 2048, T = 2048 and 8192 in both gate conventions;
+  * a model with the 1.3B layer shapes (hidden 2048, intermediate 5632, vocabulary 32000; two blocks) in bf16:
+    logits and states of a prompt pass, then 64 greedy steps at batch 32 through the CUDA-graph decoder."""
+import numpy as np
+import pytest
+import torch
+
+from oracle import mmfree_oracle as O
+
+pytestmark = pytest.mark.gpu
+
+SHAPES = [(2048, 2048), (2048, 11264), (5632, 2048), (2560, 2560)]
+
+
+@pytest.fixture(scope="module")
+def K():
+    from matmulfreellm_b200 import _lib, kernels
+    assert _lib.LIB_PATH.exists(), "libmmfree_b200.so has not been built"
+    assert torch.cuda.is_available()
+    return kernels
+
+
+def _sample_rows(M: int, tile: int, seed: int) -> np.ndarray:
+    """256 row indices: first and last rows, both sides of every kind of token-tile edge the kernels use
+    (128-, 192- and 256-row tiles), and random rows."""
+    rows = {0, 1, M - 1, M - 2}
+    for t in (128, 192, 256):
+        for e in (t, 2 * t, (M // t) * t, (M // (2 * t)) * t):
+            rows.update(r for r in (e - 1, e, e + 1) if 0 <= r < M)
+    rng = np.random.default_rng(seed)
+    while len(rows) < 256:
+        rows.add(int(rng.integers(0, M)))
+    return np.array(sorted(rows)[:256])
+
+
+@pytest.mark.parametrize("Kdim,N", SHAPES)
+@pytest.mark.parametrize("M", [4096, 16384])
+def test_bitlinear_sweep_large_m_vs_oracle(K, M, Kdim, N):
+    """bf16 activations N(0,1) with 1% outlier channels x20, weights 0.02*N(0,1) ternarised: int8 codes of every row,
+    int32 accumulators (256 sampled rows bit-equal, int64 column sums over all rows), fp32 output of the sampled rows
+    bit-equal, and the bf16 output equal to the rounded fp32 one."""
+    x, w, _ = O.bitlinear_case(M, Kdim, N, seed=M + Kdim + N)
+    codes, mean = O.ternary_codes(w)
+    q_ref, dq_ref, rs_ref = O.act_codes(x, None, 1e-6)
+    pw = K.pack_weight(w.cuda())
+    q, dq, rs = K.act_quant(x.cuda(), None, 1e-6)
+    assert np.array_equal(q.cpu().numpy(), q_ref), "int8 activation codes differ"
+    assert np.array_equal(dq.cpu().numpy(), dq_ref) and np.array_equal(rs.cpu().numpy(), rs_ref)
+    out, acc = K.bitlinear(q, dq, rs, pw, torch.float32, return_acc=True)
+    K.check_status()
+    rows = _sample_rows(M, 128, seed=N)
+    acc_ref = O.bitlinear_acc(q_ref[rows], codes)
+    assert np.array_equal(acc[torch.from_numpy(rows).cuda()].cpu().numpy(), acc_ref), "int32 accumulators differ"
+    out_ref = acc_ref.astype(np.float32) * (dq_ref[rows] * np.float32(mean))[:, None]
+    assert np.array_equal(out[torch.from_numpy(rows).cuda()].cpu().numpy(), out_ref), "dequantised fp32 output differs"
+    # column checksum over ALL rows: sum_m acc[m, n] == codes[n, :] . (sum_m q[m, :]), in int64
+    colsum = q_ref.astype(np.int64).sum(0)
+    assert np.array_equal(acc.sum(0, dtype=torch.int64).cpu().numpy(), codes.astype(np.int64) @ colsum)
+    out_b = K.bitlinear(q, dq, rs, pw, torch.bfloat16)
+    assert torch.equal(out_b, out.to(torch.bfloat16)), "bf16 output is not the rounded fp32 output"
+    K.check_status()
+
+
+@pytest.mark.parametrize("T", [2048, 8192])
+@pytest.mark.parametrize("log", [True, False])
+def test_hgrn_full_size_vs_oracle(K, T, log):
+    """B = 8, D = 2048, bf16 inputs, fp32 log-forget gate (chunk_hgrn convention) or its exponential
+    (fused_recurrent_hgrn convention), zero initial state: outputs rel 1e-2, fp32 final state rel 1e-4, against the
+    CPU restatement of naive_recurrent_hgrn."""
+    x, g_log = O.hgrn_case(8, T, 2048, seed=T, dtype=torch.bfloat16)
+    g = g_log if log else torch.exp(g_log)
+    o_ref, ht_ref = (O.chunk_hgrn_ref if log else O.naive_recurrent_hgrn)(x, g, None, True)
+    o, ht = K.hgrn_scan(x.cuda(), g.cuda(), None, True, gate_is_log=log, state_dtype=torch.float32)
+    K.check_status()
+    so = o_ref.float().abs().max().item()
+    assert (o.cpu().float() - o_ref.float()).abs().max().item() <= 1e-2 * so
+    assert (ht.cpu() - ht_ref).abs().max().item() <= 1e-4 * ht_ref.abs().max().item()
+
+
+def test_hgrn_decode_shape_vs_oracle(K):
+    """Single-step update with B = 256, T = 1: the state is advanced in place."""
+    g = torch.Generator().manual_seed(4)
+    st = torch.randn(256, 1, 2048, generator=g)
+    x1 = torch.randn(256, 1, 1, 2048, generator=g).bfloat16()
+    g1 = torch.rand(256, 1, 1, 2048, generator=g)
+    o_ref, ht_ref = O.naive_recurrent_hgrn(x1, g1, st, True)
+    sd = st.cuda().view(256, 2048).clone()
+    o1, st2 = K.hgrn_scan(x1.cuda().view(256, 1, 2048), g1.cuda().view(256, 1, 2048), sd, True, gate_is_log=False,
+                          state_dtype=torch.float32, final_state_out=sd)
+    assert st2.data_ptr() == sd.data_ptr()
+    assert (sd.cpu() - ht_ref.view(256, 2048)).abs().max().item() <= 1e-4 * ht_ref.abs().max().item()
+    assert (o1.cpu().float().view(-1) - o_ref.float().view(-1)).abs().max().item() <= 1e-2 * o_ref.float().abs().max().item()
+
+
+# ----------------------------------------------------------------------------------------------------------
+# model with the 1.3B layer shapes
+# ----------------------------------------------------------------------------------------------------------
+def _build(sd, cfg, dtype):
+    import matmulfreellm_b200 as pkg
+    pkg.install_as_mmfreelm()
+    from mmfreelm.models import HGRNBitConfig, HGRNBitForCausalLM
+    hf = HGRNBitConfig(vocab_size=cfg.vocab_size, hidden_size=cfg.hidden_size, num_hidden_layers=cfg.num_hidden_layers,
+                       intermediate_size=cfg.intermediate_size, rms_norm_eps=cfg.rms_norm_eps)
+    model = HGRNBitForCausalLM(hf).eval()
+    model.load_state_dict(sd, strict=True)
+    model = model.cuda()
+    model.pack_weights()
+    return model.to(dtype)
+
+
+def greedy_parity(model, oracle, ids, steps, decoder):
+    """Greedy decoding of `model` through `decoder` (a GreedyDecoder) against `oracle`.
+
+    1. The oracle decodes freely and records, per step, its tokens, its top-2 logit margin and its logits.
+    2. Teacher-forced pass: the decoder is fed the ORACLE's tokens and its logits are compared with the oracle's at
+       every step; `err` = the largest logit difference seen in that pass.  Two implementations whose logits differ
+       by at most err can only disagree on an arg-max where the top-2 margin is below 2*err.
+    3. Free-running pass: the decoder's own tokens must equal the oracle's at every step of every sequence up to the
+       first step where the oracle's margin is below 2*err (after such a step the sequence follows another, equally
+       valid path and is not compared further).
+    Returns (fraction of identical tokens, err, smallest margin, number of sequences compared over all steps)."""
+    B = ids.shape[0]
+    logits, states = oracle.forward(ids, last_only=True)
+    ref_tokens, ref_logits, margins = [], [], []
+    for _ in range(steps):
+        last = logits[:, -1].float()
+        top2 = last.topk(2, dim=-1).values
+        margins.append(top2[:, 0] - top2[:, 1])
+        ref_logits.append(last)
+        nxt = last.argmax(-1)
+        ref_tokens.append(nxt)
+        logits, states = oracle.forward(nxt[:, None], states, last_only=True)
+    ref_tokens, margins = torch.stack(ref_tokens, 1), torch.stack(margins, 1)
+
+    # teacher-forced: after the prompt pass the decoder holds the logits of step 0; feeding token t gives step t+1
+    decoder.prefill(ids.cuda())
+    err = 0.0
+    got_logits = _last_logits_after_prefill(model, ids)
+    err = max(err, (got_logits - ref_logits[0]).abs().max().item())
+    for t in range(steps - 1):
+        decoder.ids.copy_(ref_tokens[:, t:t + 1].cuda())
+        decoder.step()
+        err = max(err, (decoder.last_logits.float().cpu() - ref_logits[t + 1]).abs().max().item())
+
+    # free-running
+    first = decoder.prefill(ids.cuda()).clone()
+    toks = [first.cpu()]
+    for _ in range(steps - 1):
+        toks.append(decoder.step().clone().cpu())
+    toks = torch.stack(toks, 1)
+    same = toks == ref_tokens
+    full = 0
+    for b in range(B):
+        ambiguous = torch.nonzero(margins[b] < 2 * err)
+        limit = int(ambiguous[0]) if len(ambiguous) else steps     # tokens up to and excluding this step must agree
+        assert bool(same[b, :limit].all()), (
+            f"sequence {b} left the oracle's path at step {int(torch.nonzero(~same[b])[0])} where the oracle's top-2 margin "
+            f"{margins[b, int(torch.nonzero(~same[b])[0])]:.3e} exceeds twice the measured logit error {err:.3e}")
+        full += int(limit == steps)
+    return same.float().mean().item(), err, margins.min().item(), full
+
+
+def _last_logits_after_prefill(model, ids):
+    return model(ids.cuda(), use_cache=False, last_token_only=True).logits[:, -1].float().cpu()
+
+
+def test_model_with_1p3b_layer_shapes_vs_oracle(K):
+    """Hidden 2048, intermediate 5632, vocabulary 32000, two blocks, bf16 activations, weights N(0, 0.02).
+    (a) prompt pass, batch 4 x 48 tokens: last-position logits and per-block states against the integer oracle;
+    (b) 64 greedy steps at batch 32 through the CUDA-graph decoder: tokens identical to the oracle's wherever the
+        oracle's own top-2 margin exceeds twice the logit error measured in the teacher-forced pass of the same run,
+        that error itself bounded, and most sequences identical over all 64 steps."""
+    from matmulfreellm_b200.engine import GreedyDecoder
+    cfg = O.OracleConfig(vocab_size=32000, hidden_size=2048, num_hidden_layers=2, intermediate_size=5632)
+    sd = O.random_weights(cfg, seed=13)
+    model = _build(sd, cfg, torch.bfloat16)
+    oracle = O.OracleHGRNBit(cfg, sd, dtype=torch.bfloat16, linear="int", bitlinear_eps=1e-6)
+
+    ids = torch.randint(0, 32000, (4, 48), generator=torch.Generator().manual_seed(14))
+    ref_logits, ref_states = oracle.forward(ids, last_only=True)
+    out = model(ids.cuda(), use_cache=True, last_token_only=True)
+    scale = ref_logits.float().abs().max().item()
+    d = (out.logits.float().cpu() - ref_logits.float()).abs()
+    # bf16 logits: one bf16 rounding step is 2^-8 relative; code flips upstream move single entries further
+    assert d.median().item() <= 1e-2 * scale and d.max().item() <= 1e-1 * scale, (d.median().item() / scale, d.max().item() / scale)
+    for s, r in zip(out.past_key_values, ref_states):
+        ds = (s[0].float().cpu() - r).abs()
+        assert ds.median().item() <= 1e-2 * r.abs().max().item() and ds.max().item() <= 1e-1 * r.abs().max().item()
+
+    ids32 = torch.randint(0, 32000, (32, 16), generator=torch.Generator().manual_seed(15))
+    dec = GreedyDecoder(model, 32)
+    frac, err, min_margin, full = greedy_parity(model, oracle, ids32, 64, dec)
+    assert dec.graph is not None, "the decode steps did not run from the CUDA graph"
+    K.check_status()
+    print(f"[1.3B shapes, batch 32, 64 steps] identical tokens {frac:.4f}; teacher-forced logit error {err:.3e} "
+          f"(logit scale {scale:.3f}); smallest oracle top-2 margin {min_margin:.3e}; {full}/32 sequences compared over all steps")
+    assert err <= 1e-1 * scale, "teacher-forced logits drifted beyond the bf16 code-flip bound"
+    assert full >= 16 and frac >= 0.5

@@ -152,6 +152,35 @@ def test_bitlinear_mma_bit_exact(K, M, Kdim, N):
     _bitlinear_check(K, M, Kdim, N, K.KERNEL_MMA)
 
 
+STREAM_CASES = [(1, 256, 128), (1, 2048, 2048), (2, 704, 256), (4, 5632, 2048), (5, 704, 256), (8, 2048, 11264),
+                (16, 2048, 2048), (24, 2560, 2560), (32, 2048, 11264), (32, 5632, 2048), (33, 2048, 384), (64, 2560, 2560),
+                (64, 2048, 200), (17, 2048, 200), (3, 6912, 2560), (32, 6912, 2560), (64, 5632, 2048), (40, 2048, 32000)]
+
+
+@pytest.mark.parametrize("M,Kdim,N", STREAM_CASES)
+def test_bitlinear_stream_bit_exact(K, M, Kdim, N):
+    """The decode kernel (persistent CTAs, resident codes, mma.sync per 16 rows x 8 tokens): every token-tile count
+    1..8, a ragged last slab (N = 200), K with a trailing chunk group (704 = 11 chunks), and problems whose codes do
+    not fit in shared memory at once (32 x 6912, 64 x 5632: run as two launches over token blocks)."""
+    _bitlinear_check(K, M, Kdim, N, K.KERNEL_STREAM)
+
+
+def test_bitlinear_stream_is_the_default_for_decode_batches(K):
+    """AUTO takes the decode kernel up to 64 token rows: identical accumulators and outputs to the forced selection, and
+    strided output rows (ld_out > N) are honoured."""
+    x, w, _ = O.bitlinear_case(32, 2048, 384, seed=5)
+    pw = K.pack_weight(dev(w))
+    q, dq, rs = K.act_quant(dev(x), None, 1e-6)
+    a, acc_a = K.bitlinear(q, dq, rs, pw, torch.bfloat16, return_acc=True)
+    b, acc_b = K.bitlinear(q, dq, rs, pw, torch.bfloat16, kernel=K.KERNEL_STREAM, return_acc=True)
+    c, acc_c = K.bitlinear(q, dq, rs, pw, torch.bfloat16, kernel=K.KERNEL_MMA, return_acc=True)
+    assert torch.equal(a, b) and torch.equal(acc_a, acc_b) and torch.equal(a, c) and torch.equal(acc_a, acc_c)
+    wide = torch.zeros(32, 512, dtype=torch.bfloat16, device="cuda")
+    K.bitlinear(q, dq, rs, pw, torch.bfloat16, kernel=K.KERNEL_STREAM, out=wide[:, 64:448])
+    assert torch.equal(wide[:, 64:448], a) and int(wide[:, :64].abs().sum()) == 0 and int(wide[:, 448:].abs().sum()) == 0
+    K.check_status()
+
+
 @pytest.mark.parametrize("M", [1, 4, 32])
 def test_bitlinear_grouped(K, M):
     """Three projections sharing an input row but not a norm weight, run as one grouped launch."""
@@ -163,11 +192,12 @@ def test_bitlinear_grouped(K, M):
     pw = K.stack_packed([K.pack_weight(dev(w)) for w in ws])
     qs = [K.act_quant(dev(x), dev(nw), 1e-6) for nw in nws]
     q = torch.cat([t[0] for t in qs]); dq = torch.cat([t[1] for t in qs]); rs = torch.cat([t[2] for t in qs])
-    out = K.bitlinear(q, dq, rs, pw, torch.float32)
-    for gi in range(3):
-        codes, mean = O.ternary_codes(ws[gi])
-        ref = O.bitlinear_int(x, nws[gi], codes, mean, 1e-6)[0]
-        assert torch.equal(out[:, gi * N:(gi + 1) * N].cpu(), ref)
+    for kernel in (K.KERNEL_AUTO, K.KERNEL_STREAM, K.KERNEL_GEMV, K.KERNEL_MMA):
+        out = K.bitlinear(q, dq, rs, pw, torch.float32, kernel=kernel)
+        for gi in range(3):
+            codes, mean = O.ternary_codes(ws[gi])
+            ref = O.bitlinear_int(x, nws[gi], codes, mean, 1e-6)[0]
+            assert torch.equal(out[:, gi * N:(gi + 1) * N].cpu(), ref), (kernel, gi)
 
 
 def test_bitlinear_matches_reference_output(K, golden):

@@ -1,6 +1,7 @@
 """Pin the CPU oracle against fixtures produced by running the reference itself
 (tests/golden/make_golden.py).  No GPU needed."""
 import numpy as np
+import pytest
 import torch
 
 from oracle import mmfree_oracle as O
@@ -146,3 +147,47 @@ def test_tiny_model_integer_path_matches_reference(golden):
         if not same[b].all():
             first = int(np.argmin(same[b]))
             assert g["greedy_margins"][b, first] < 5e-3, (b, first, g["greedy_margins"][b, first])
+
+
+@pytest.mark.parametrize("temperature,top_p", [(0.6, 0.4), (1.0, 0.9), (2.0, 0.95), (0.7, 1.0)])
+def test_nucleus_oracle_matches_transformers_warpers(temperature, top_p):
+    """The reference samples through transformers (generate.py:11: do_sample, top_p, temperature).  The oracle's
+    tempered-softmax + top-p restatement is pinned here against the library's own TemperatureLogitsWarper and
+    TopPLogitsWarper on seeded logits: identical kept sets, renormalised probabilities equal to fp32 accuracy, and
+    the inverse-CDF draw over the library's probabilities picks the oracle's token."""
+    from transformers.generation.logits_process import TemperatureLogitsWarper, TopPLogitsWarper
+    g = torch.Generator().manual_seed(int(temperature * 100 + top_p * 1000))
+    M, V = 24, 32000
+    logits = torch.randn(M, V, generator=g) * 3
+    u = torch.rand(M, generator=g).numpy()
+    scores = TemperatureLogitsWarper(temperature)(None, logits.clone())
+    if top_p < 1.0:
+        scores = TopPLogitsWarper(top_p)(None, scores)
+    kept_hf = torch.isfinite(scores).numpy()
+    probs_hf = torch.softmax(scores.double(), -1).numpy()
+    kept, w, margin = O.nucleus_ref(logits.numpy(), temperature, top_p)
+    tok, draw_margin = O.sample_top_p_ref(logits.numpy(), temperature, top_p, u)
+    n_same = 0
+    for m in range(M):
+        # the library takes its cumulative sum in fp32 over up to 32000 terms (error up to ~1e-5 of the mass), so at a
+        # flat boundary its kept set may differ from the fp64 one by tokens whose cumulative mass is that close to top_p
+        diff = np.nonzero(kept[m] != kept_hf[m])[0]
+        if len(diff):
+            order = np.argsort(-w[m], kind="stable")
+            before = np.concatenate([[0.0], np.cumsum(w[m][order])[:-1]])      # mass of the strictly more probable tokens
+            pos = np.empty(V, dtype=np.int64)
+            pos[order] = np.arange(V)
+            total = w[m].sum()
+            assert np.all(np.abs(before[pos[diff]] - top_p * total) <= 2e-5 * total), (m, len(diff))
+        # tempered-softmax weights: renormalised over the library's kept set they are the library's probabilities
+        p = np.where(kept_hf[m], w[m], 0.0)
+        p /= p.sum()
+        assert np.allclose(p, probs_hf[m], rtol=2e-5, atol=1e-12), m
+        if len(diff) == 0:
+            n_same += 1
+            if draw_margin[m] > 1e-6:
+                c = np.cumsum(probs_hf[m])
+                assert int(np.searchsorted(c, u[m] * c[-1], side="right")) == tok[m], m
+    assert n_same >= M // 2          # identical kept sets on most rows (all rows at the reference's 0.6 / 0.4 setting)
+    if (temperature, top_p) == (0.6, 0.4):
+        assert n_same == M

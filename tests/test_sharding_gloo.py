@@ -57,6 +57,44 @@ def test_two_rank_gather_and_generate(n_total):
     mp.spawn(_worker, args=(2, port, n_total), nprocs=2, join=True)
 
 
+class _EosModel:
+    """Stand-in for generate(..., eos_token_id=e): sequence b (identified by its first token) emits eos at step
+    first_token % 7, is padded with eos afterwards, and the result ends where the last LOCAL sequence finished —
+    so two ranks return different widths."""
+
+    def generate(self, ids, max_new_tokens=1, eos_token_id=None):
+        stop = ids[:, 0] % 7
+        steps = torch.arange(max_new_tokens).expand(ids.shape[0], max_new_tokens)
+        toks = torch.where(steps >= stop[:, None], torch.full_like(steps, eos_token_id), 1000 + steps)
+        n = min(int(stop.max().item()) + 1, max_new_tokens)
+        return torch.cat([ids, toks[:, :n]], 1)
+
+
+def _eos_worker(rank, world, port):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        # rank 0's sequences stop at steps 0..2, rank 1's at steps 3..6 -> local widths 3+3 and 3+7
+        full = torch.tensor([[0, 9, 9], [1, 9, 9], [2, 9, 9], [3, 9, 9], [5, 9, 9], [6, 9, 9]])
+        out = generate_sharded(_EosModel(), full, max_new_tokens=12, eos_token_id=77)
+        want = _EosModel().generate(full, max_new_tokens=12, eos_token_id=77)       # the whole batch on one rank
+        assert out.shape == want.shape == (6, 3 + 7) and torch.equal(out, want)
+        # a sequence that never stops within the budget: full width, finished rows padded with eos
+        full2 = torch.tensor([[0, 9, 9], [1, 9, 9], [6, 9, 9], [2, 9, 9]])
+        out2 = generate_sharded(_EosModel(), full2, max_new_tokens=4, eos_token_id=77)
+        want2 = _EosModel().generate(full2, max_new_tokens=4, eos_token_id=77)
+        assert out2.shape == (4, 7) and torch.equal(out2, want2)
+    finally:
+        dist.destroy_process_group()
+
+
+def test_two_rank_generate_with_eos_finishing_at_different_steps():
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        port = s.getsockname()[1]
+    mp.spawn(_eos_worker, args=(2, port), nprocs=2, join=True)
+
+
 def test_single_process_passthrough():
     t = torch.arange(6).view(3, 2)
     assert gather_batch(t, 3) is t
