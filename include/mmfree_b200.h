@@ -29,7 +29,7 @@
 extern "C" {
 #endif
 
-#define MMF_ABI_VERSION 1
+#define MMF_ABI_VERSION 2
 
 /* element types of activation tensors */
 #define MMF_F32 0
@@ -118,15 +118,11 @@ int mmf_act_quant(const void* x, int dtype, int64_t ld_x, const float* norm_w, i
  * mmfreelm/ops/fusedbitnet.py:456-458 (cuBLAS fp16/bf16 GEMM in the reference).
  * ------------------------------------------------------------------------------------ */
 
-/* Which kernel mmf_bitlinear runs.  AUTO: the decode kernel up to MMF_STREAM_MAX_M token rows (when the codes of
- * all rows fit in shared memory), tcgen05 above; the CUDA-core GEMV only on request. */
+/* Which kernel mmf_bitlinear runs. AUTO: GEMV below MMF_MMA_MIN_M rows, tcgen05 above. */
 #define MMF_KERNEL_AUTO 0
-#define MMF_KERNEL_GEMV 1   /* CUDA-core dp4a, weight-streaming, any M (slow for large M) */
-#define MMF_KERNEL_MMA 2    /* tcgen05 kind::i8 tensor-core tiles, weights unpacked into TMEM */
-#define MMF_KERNEL_STREAM 3 /* decode kernel: one persistent CTA per SM, codes resident in shared memory, weights streamed
-                               by bulk TMA ahead of the grid dependency, mma.sync m16n8k32 per (16 rows x 8 tokens); M <= 64 */
+#define MMF_KERNEL_GEMV 1 /* CUDA-core dp4a, weight-streaming, any M (slow for large M) */
+#define MMF_KERNEL_MMA 2  /* tcgen05 kind::i8 tensor-core tiles, weights unpacked into TMEM */
 #define MMF_MMA_MIN_M 5
-#define MMF_STREAM_MAX_M 64
 
 /* Bytes of int32 workspace mmf_bitlinear may need for split-K partial sums (a multiple of
  * 256; includes a 256-byte header whose first word is a status flag — 0, or 1 if a bounded
@@ -149,6 +145,29 @@ int mmf_bitlinear(const int8_t* q, const float* dq, const int32_t* rowsum, const
                   const float* w_scale, int groups, void* out, int out_dtype, int64_t ld_out,
                   int32_t* acc_out, int64_t M, int64_t N, int64_t K, void* workspace,
                   int64_t workspace_bytes, int kernel, void* stream);
+
+/* Slab-major copy of a packed weight for mmf_bitlinear_decode (no counterpart in the reference: a layout choice of
+ * this library).  The tile-major layout of mmf_pack_ternary keeps a 16-row slab as K/64 pieces of 256 bytes that lie
+ * 2 KB apart; the decode kernel fetches whole slabs with one bulk copy each, so it reads a second copy in which slab
+ * s (16 rows) of tile t occupies the (K/64)*256 contiguous bytes at ((t*8 + s) * (K/64)) * 256: chunk c at + c*256,
+ * row r of the slab at + r*16, the 16 bytes themselves unchanged.  `slabs`: mmf_packed_bytes(N, K) bytes. */
+int mmf_repack_slabs(const void* packed, int64_t N, int64_t K, void* slabs, void* stream);
+
+/* 1 if mmf_bitlinear_decode accepts M token rows with K input features (M <= MMF_STREAM_MAX_M and the codes of at
+ * least 8 rows fit in shared memory beside one slab of weights: K <= 16384 or so), else 0. */
+#define MMF_STREAM_MAX_M 64
+int mmf_bitlinear_decode_fits(int64_t M, int64_t K);
+
+/* The contraction of mmf_bitlinear for a decode step (M <= MMF_STREAM_MAX_M token rows): same arithmetic, same
+ * arguments and outputs, but the weights come from the slab-major copy (mmf_repack_slabs) and no workspace is needed.
+ * One persistent CTA per SM keeps the activation codes resident in shared memory, streams its slabs of weights by
+ * bulk TMA ahead of the grid dependency (programmatic dependent launch) and contracts them with mma.sync m16n8k32
+ * (s8 x s8 -> s32).  `status` (may be NULL): one device int that is set to 1 if a bounded device-side wait gave up.
+ * Replaces: F.linear(y_dequant, weight_quant(W)), mmfreelm/ops/fusedbitnet.py:456-458, for single-token forwards
+ * (the cached generation step, mmfreelm/models/hgrn_bit/modeling_hgrn_bit.py:335-338). */
+int mmf_bitlinear_decode(const int8_t* q, const float* dq, const int32_t* rowsum, const void* packed_slabs,
+                         const float* w_scale, int groups, void* out, int out_dtype, int64_t ld_out,
+                         int32_t* acc_out, int64_t M, int64_t N, int64_t K, int32_t* status, void* stream);
 
 /* BitLinear for a few token rows WITHOUT caller-provided scratch and without any allocation.
  * (No counterpart in the reference: it exists for hosts that must not allocate.)
@@ -183,21 +202,6 @@ int mmf_bitlinear_gemv_static(const int8_t* q, const float* dq, const int32_t* r
  * runs on the default stream and SYNCHRONISES; status_dev is one device int of scratch, tops_host a host
  * double. */
 int mmf_int8_mma_peak(int n_tokens, int iters, int* status_dev, double* tops_host);
-
-/* Tuning hook for experiments: overrides the automatic choice of the tensor-core kernel's
- * configuration for all later mmf_bitlinear calls of this process (value 0 = automatic again).
- * No counterpart in the reference. */
-#define MMF_TUNE_KSPLIT 0     /* K split / cluster size: 1, 2, 4 or 8                          */
-#define MMF_TUNE_TOKEN_TILE 1 /* token rows per tile: 16..128 (multiple of 16) or 256           */
-#define MMF_TUNE_DEEP_RING 2  /* 1 = prefer the deep-ring (no split) variant, 2 = never use it  */
-#define MMF_TUNE_WEIGHT_TILES 3 /* weight tiles per CTA for large M: 1 or 2                       */
-#define MMF_TUNE_B_STAGES 4   /* activation-tile ring depth (128 K per stage)                  */
-#define MMF_TUNE_A_STAGES 5   /* unpacked-weight stages held in tensor memory (even)           */
-#define MMF_TUNE_W_STAGES 6   /* packed-weight ring depth (even)                               */
-#define MMF_TUNE_PERSISTENT 7 /* persistent large-M kernel: 1 = whenever M > 128, 2 = never, 10+v = its compiled shape v (1..4) whenever M > 128 */
-#define MMF_TUNE_PROBE_COMMITS 8 /* mmf_int8_mma_peak: tcgen05.commit instructions issued per 4 MMAs */
-#define MMF_TUNE_ACCUMULATORS 9 /* accumulators consecutive MMAs rotate through at few token columns: 1, 2 or 4 */
-int mmf_tuning(int knob, int value);
 
 /* ------------------------------------------------------------------------------------
  * HGRN recurrence  h_t = f_t * h_{t-1} + x_t  (element-wise, fp32 state).
@@ -280,6 +284,15 @@ int mmf_gatenorm_quant(const void* g, int64_t ld_g, const void* o, int64_t ld_o,
 int mmf_decode_mix(const void* ifg, int64_t ld, int dtype, const void* lower_bound, float* state,
                    const float* gnorm_w, float eps_g, const float* nw, float eps_bl, int8_t* q, float* dq,
                    int32_t* rowsum, int64_t M, int64_t D, void* stream);
+
+/* mmf_decode_mix with a padding mask: mask is uint8 [M] (device), 1 = token, 0 = padding position; a masked row's
+ * input to the recurrence is zero (its forget gate still decays the state), mask == NULL means no padding.  The mask is
+ * read AFTER the kernel has synchronised with the preceding launches (it may be written by them).
+ * Replaces: `i = i.mul_(attention_mask.unsqueeze(-1))`, mmfreelm/layers/hgrn_bit.py:119-120, for a one-token forward
+ * (the attention_mask[:, -1:] of a cached generation step, mmfreelm/models/hgrn_bit/modeling_hgrn_bit.py:335-338). */
+int mmf_decode_mix_masked(const void* ifg, int64_t ld, int dtype, const void* lower_bound, const uint8_t* mask,
+                          float* state, const float* gnorm_w, float eps_g, const float* nw, float eps_bl, int8_t* q,
+                          float* dq, int32_t* rowsum, int64_t M, int64_t D, void* stream);
 
 /* z = silu(gate) * up rounded to `dtype`, then the BitLinear prologue with norm weight nw.
  * gate/up: the two halves of gate_proj's output, rows `ld` elements apart.

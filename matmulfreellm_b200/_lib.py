@@ -12,10 +12,12 @@ from pathlib import Path
 LIB_PATH = Path(__file__).resolve().parent / "libmmfree_b200.so"
 
 F32, BF16, F16 = 0, 1, 2
-KERNEL_AUTO, KERNEL_GEMV, KERNEL_MMA, KERNEL_STREAM = 0, 1, 2, 3
+KERNEL_AUTO, KERNEL_GEMV, KERNEL_MMA = 0, 1, 2
+KERNEL_STREAM = 3   # Python-level selector: the decode kernel (mmf_bitlinear_decode)
+STREAM_MAX_M = 64
 TILE_ROWS, TILE_K = 128, 64
 ABSMEAN_PARTIALS = 1024
-ABI_VERSION = 1
+ABI_VERSION = 2
 
 _ERR_NAMES = {
     -1: "MMF_ERR_BAD_ARG", -2: "MMF_ERR_BAD_SHAPE", -3: "MMF_ERR_ALIGN", -4: "MMF_ERR_CUDA",
@@ -36,10 +38,13 @@ PROTOTYPES = {
     "mmf_bitlinear_workspace_bytes": (c_int64, [c_int64, c_int64, c_int64]),
     "mmf_bitlinear": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int64,
                               c_void_p, c_int64, c_int64, c_int64, c_void_p, c_int64, c_int, c_void_p]),
+    "mmf_repack_slabs": (c_int, [c_void_p, c_int64, c_int64, c_void_p, c_void_p]),
+    "mmf_bitlinear_decode_fits": (c_int, [c_int64, c_int64]),
+    "mmf_bitlinear_decode": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int64,
+                                     c_void_p, c_int64, c_int64, c_int64, c_void_p, c_void_p]),
     "mmf_bitlinear_gemv_static": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int64,
                                           c_int64, c_int64, c_int64, c_void_p]),
     "mmf_int8_mma_peak": (c_int, [c_int, c_int, c_void_p, c_void_p]),
-    "mmf_tuning": (c_int, [c_int, c_int]),
     "mmf_hgrn_workspace_bytes": (c_int64, [c_int64, c_int64, c_int64]),
     "mmf_hgrn_scan": (c_int, [c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_int, c_void_p, c_int64,
                               c_int64, c_int64, c_int, c_void_p, c_int64, c_void_p]),
@@ -55,6 +60,8 @@ PROTOTYPES = {
                                    c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_void_p]),
     "mmf_decode_mix": (c_int, [c_void_p, c_int64, c_int, c_void_p, c_void_p, c_void_p, c_float, c_void_p, c_float, c_void_p,
                                c_void_p, c_void_p, c_int64, c_int64, c_void_p]),
+    "mmf_decode_mix_masked": (c_int, [c_void_p, c_int64, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_float, c_void_p, c_float,
+                                      c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_void_p]),
     "mmf_swiglu_quant": (c_int, [c_void_p, c_void_p, c_int64, c_int, c_void_p, c_float, c_void_p, c_void_p, c_void_p,
                                  c_int64, c_int64, c_void_p]),
     "mmf_rmsnorm": (c_int, [c_void_p, c_int, c_void_p, c_int, c_void_p, c_float, c_void_p, c_void_p, c_int64,
@@ -78,6 +85,19 @@ class MMFreeError(RuntimeError):
 
 
 _lib = None
+EXPERIMENTS_LIB_PATH = LIB_PATH.with_name("libmmfree_b200_experiments.so")
+_EXPERIMENT_PROTOTYPES = {"mmf_tuning": (c_int, [c_int, c_int])}
+
+
+def _open(path: Path, prototypes) -> ctypes.CDLL:
+    lib = ctypes.CDLL(str(path))
+    for name, (res, args) in prototypes.items():
+        fn = getattr(lib, name)  # AttributeError here = header and library out of sync
+        fn.restype = res
+        fn.argtypes = args
+    if lib.mmf_abi_version() != ABI_VERSION:
+        raise RuntimeError(f"{path.name} ABI {lib.mmf_abi_version()} != binding ABI {ABI_VERSION}")
+    return lib
 
 
 def load() -> ctypes.CDLL:
@@ -89,15 +109,35 @@ def load() -> ctypes.CDLL:
         raise RuntimeError(
             f"{LIB_PATH} is missing. Build it with `python -m matmulfreellm_b200._build` "
             "(needs nvcc); there is no fallback implementation.")
-    lib = ctypes.CDLL(str(LIB_PATH))
-    for name, (res, args) in PROTOTYPES.items():
-        fn = getattr(lib, name)  # AttributeError here = header and library out of sync
-        fn.restype = res
-        fn.argtypes = args
-    if lib.mmf_abi_version() != ABI_VERSION:
-        raise RuntimeError(f"libmmfree_b200 ABI {lib.mmf_abi_version()} != binding ABI {ABI_VERSION}")
-    _lib = lib
-    return lib
+    _lib = _open(LIB_PATH, PROTOTYPES)
+    return _lib
+
+
+class experiments_library:
+    """Context manager for kernel experiments and the configuration-sweep tests: inside it every call of this module
+    goes to libmmfree_b200_experiments.so (the same sources built with -DMMF_EXPERIMENTS), which also exports
+    mmf_tuning; on exit all overrides are reset and the product library is current again."""
+
+    KNOBS = 10
+    _handle = None
+
+    def __enter__(self):
+        global _lib
+        cls = experiments_library
+        if cls._handle is None:
+            if not EXPERIMENTS_LIB_PATH.exists():
+                raise RuntimeError(f"{EXPERIMENTS_LIB_PATH} is missing: python -m matmulfreellm_b200._build")
+            cls._handle = _open(EXPERIMENTS_LIB_PATH, {**PROTOTYPES, **_EXPERIMENT_PROTOTYPES})
+        self._saved = load()
+        _lib = cls._handle
+        return cls._handle
+
+    def __exit__(self, *exc):
+        global _lib
+        for k in range(self.KNOBS):
+            experiments_library._handle.mmf_tuning(k, 0)
+        _lib = self._saved
+        return False
 
 
 # kernels each entry point launches per successful call (for launch accounting in benchmarks)

@@ -30,8 +30,6 @@ int bitlinear_gemv_launch(const BitLinearArgs& a, cudaStream_t st, bool force_sp
 int bitlinear_mma_launch(const BitLinearArgs& a, cudaStream_t st);
 int bitlinear_mma_prefill_launch(const BitLinearArgs& a, cudaStream_t st, int variant);   // persistent kernel for many token rows
 int bitlinear_mma_prefill_tile(const BitLinearArgs& a, int variant);                       // its token tile
-bool bitlinear_stream_fits(const BitLinearArgs& a);                                        // decode kernel (1..64 token rows): can it take this problem?
-int bitlinear_stream_launch(const BitLinearArgs& a, cudaStream_t st);
 
 // out = acc * (dq * w_scale), the one place the dequantising epilogue is defined
 __device__ __forceinline__ float bitlinear_dequant(int32_t acc, float dq, float w_scale) {

@@ -300,8 +300,8 @@ extern "C" int mmf_bitlinear(const int8_t* q, const float* dq, const int32_t* ro
     MMF_REQUIRE(mmf_aligned(q, 16) && mmf_aligned(packed, 16), MMF_ERR_ALIGN,
                 "mmf_bitlinear: q and packed must be 16-byte aligned");
     MMF_REQUIRE(!workspace || mmf_aligned(workspace, 16), MMF_ERR_ALIGN, "mmf_bitlinear: workspace must be 16-byte aligned");
-    MMF_REQUIRE(kernel == MMF_KERNEL_AUTO || kernel == MMF_KERNEL_GEMV || kernel == MMF_KERNEL_MMA || kernel == MMF_KERNEL_STREAM,
-                MMF_ERR_BAD_ARG, "mmf_bitlinear: unknown kernel selector %d", kernel);
+    MMF_REQUIRE(kernel == MMF_KERNEL_AUTO || kernel == MMF_KERNEL_GEMV || kernel == MMF_KERNEL_MMA, MMF_ERR_BAD_ARG,
+                "mmf_bitlinear: unknown kernel selector %d", kernel);
     if (M == 0) return MMF_OK;
     BitLinearArgs a;
     a.q = q; a.dq = dq; a.rowsum = rowsum; a.packed = (const uint4*)packed; a.w_scale = w_scale;
@@ -309,8 +309,6 @@ extern "C" int mmf_bitlinear(const int8_t* q, const float* dq, const int32_t* ro
     a.M = (int)M; a.N = (int)N; a.K = (int)K; a.groups = groups;
     a.ws = (int32_t*)workspace; a.ws_bytes = workspace ? workspace_bytes : 0;
     cudaStream_t st = (cudaStream_t)stream;
-    if (kernel == MMF_KERNEL_STREAM || (kernel == MMF_KERNEL_AUTO && M <= MMF_STREAM_MAX_M && bitlinear_stream_fits(a)))
-        return bitlinear_stream_launch(a, st);
     const bool use_mma = kernel == MMF_KERNEL_MMA || (kernel == MMF_KERNEL_AUTO && M >= MMF_MMA_MIN_M);
     return use_mma ? bitlinear_mma_launch(a, st) : bitlinear_gemv_launch(a, st, false);
 }

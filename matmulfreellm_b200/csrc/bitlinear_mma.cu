@@ -160,9 +160,8 @@ bitlinear_mma_kernel(const __grid_constant__ CUtensorMap q_map, BitLinearArgs a,
     const int warp = tid >> 5, lane = tid & 31;
     const int ks = blockIdx.x, tile = blockIdx.y * p.wt, mt = blockIdx.z;
     const int ntile = min(p.wt, p.n_tiles - tile);   // weight tiles this CTA owns (2 = dual-tile mode for large M)
-    long long* trace = nullptr;
-    if (tid == 0 && a.ws && a.ws[1] == MMF_TRACE_MAGIC && (blockIdx.x | blockIdx.y | blockIdx.z) == 0)
-        trace = reinterpret_cast<long long*>(a.ws + 8);
+    long long* const trace = MMF_TRACE_PTR((tid == 0 && a.ws && a.ws[1] == MMF_TRACE_MAGIC && (blockIdx.x | blockIdx.y | blockIdx.z) == 0)
+                                               ? reinterpret_cast<long long*>(a.ws + 8) : nullptr);
     trace_mark(trace, 0);
     pdl_trigger();   // the next kernel may start its own prologue (and weight stream) right away
     const int g = tile / p.group_tiles;
@@ -239,8 +238,8 @@ bitlinear_mma_kernel(const __grid_constant__ CUtensorMap q_map, BitLinearArgs a,
             const uint32_t nacc = (uint32_t)p.nacc, NTc = (uint32_t)p.NT;
             bool live = true;
             int i = 0;
-            long long* mtrace = (a.ws && a.ws[1] == MMF_TRACE_MAGIC && (blockIdx.x | blockIdx.y | blockIdx.z) == 0)
-                                    ? reinterpret_cast<long long*>(a.ws + 8) : nullptr;
+            long long* const mtrace = MMF_TRACE_PTR((a.ws && a.ws[1] == MMF_TRACE_MAGIC && (blockIdx.x | blockIdx.y | blockIdx.z) == 0)
+                                                        ? reinterpret_cast<long long*>(a.ws + 8) : nullptr);
             if (p.wt == 1 && (nacc == 1 || nacc == 2 || nacc == 4)) {
                 // lean path (one weight tile, whole 128-K stages): the issuing thread is a serial instruction
                 // stream, so every instruction here costs tensor-pipe time.  MMA k of a stage goes to accumulator
@@ -487,9 +486,12 @@ bitlinear_mma_kernel(const __grid_constant__ CUtensorMap q_map, BitLinearArgs a,
 
 }  // namespace
 
-// tuning overrides (0 = automatic), see mmf_tuning()
+// Configuration overrides for kernel experiments.  They exist only in the experiments build (-DMMF_EXPERIMENTS, a
+// second shared library that the configuration-sweep tests load); the product library has no mutable global state:
+// every override is the constant 0 (automatic) there and the code paths it selects are compiled out.
+#ifdef MMF_EXPERIMENTS
+#include "../../include/mmfree_b200_experiments.h"
 static int g_force_ksplit = 0, g_force_nt = 0, g_force_deep = 0, g_force_wt = 0, g_force_sb = 0, g_force_sa = 0, g_force_sw = 0, g_force_persistent = 0, g_force_nacc = 0;
-
 extern int g_probe_commits;
 
 extern "C" int mmf_tuning(int knob, int value) {
@@ -507,6 +509,9 @@ extern "C" int mmf_tuning(int knob, int value) {
         default: return mmf_set_error(MMF_ERR_BAD_ARG, "mmf_tuning: unknown knob %d", knob);
     }
 }
+#else
+static constexpr int g_force_ksplit = 0, g_force_nt = 0, g_force_deep = 0, g_force_wt = 0, g_force_sb = 0, g_force_sa = 0, g_force_sw = 0, g_force_persistent = 0, g_force_nacc = 0;
+#endif
 
 namespace {
 

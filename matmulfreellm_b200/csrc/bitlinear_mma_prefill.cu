@@ -146,8 +146,8 @@ bitlinear_mma_prefill_kernel(const __grid_constant__ CUtensorMap q_map, const __
     const int S = (p.KC + 1) / 2;              // 128-K stages per work item
     const int first = blockIdx.x, step = gridDim.x;
     // optional phase trace of CTA 0 (armed by MMF_TRACE_MAGIC in workspace word 1): 28 clock64 slots in the header
-    long long* trace = (lane == 0 && blockIdx.x == 0 && a.ws && a.ws[1] == MMF_TRACE_MAGIC)
-                           ? reinterpret_cast<long long*>(a.ws + 8) : nullptr;
+    long long* const trace = MMF_TRACE_PTR((lane == 0 && blockIdx.x == 0 && a.ws && a.ws[1] == MMF_TRACE_MAGIC)
+                           ? reinterpret_cast<long long*>(a.ws + 8) : nullptr);
     if (tid == 0) trace_mark(trace, 0);
 
     if (warp == C::WARP_W) {

@@ -405,8 +405,8 @@ gatenorm_quant_kernel(const T* __restrict__ gx, int64_t ld_g, const T* __restric
 //   h = f*h + x  (fp32 state, updated in place);  o = round(h);  then gatenorm_quant(g_raw, o).
 template <typename T, int P, int LAT>
 __global__ void __launch_bounds__(FT, LAT)
-decode_mix_kernel(const T* __restrict__ ifg, int64_t ld, const T* __restrict__ lb, float* __restrict__ state,
-                  const float* __restrict__ gw, float eps_g, const float* __restrict__ nw, float eps_bl,
+decode_mix_kernel(const T* __restrict__ ifg, int64_t ld, const T* __restrict__ lb, const uint8_t* __restrict__ mask,
+                  float* __restrict__ state, const float* __restrict__ gw, float eps_g, const float* __restrict__ nw, float eps_bl,
                   int8_t* __restrict__ q, float* __restrict__ dq, int32_t* __restrict__ rowsum, int64_t M, int D) {
     extern __shared__ __align__(16) float sw[];   // [3][D]: g_norm weight, BitLinear norm weight, lower bound (as float)
     __shared__ RedScratch red;
@@ -425,6 +425,8 @@ decode_mix_kernel(const T* __restrict__ ifg, int64_t ld, const T* __restrict__ l
     const T* fr = ir + D;
     const T* gr = ir + 2 * D;
     float* st = state + m * (int64_t)D;
+    // a padding position (mask 0) contributes no input: i * 0, as `i.mul_(attention_mask)` does; the forget gate still applies
+    const bool keep = mask == nullptr || mask[m] != 0;
     float gv[P], ov[P];
     double ss = 0.0;
     ROW_FOREACH(V, D, it, c) {
@@ -444,7 +446,7 @@ decode_mix_kernel(const T* __restrict__ ifg, int64_t ld, const T* __restrict__ l
                     const float oml = round_to<T>(__fsub_rn(1.0f, lbv));
                     f = round_to<T>(__fadd_rn(lbv, round_to<T>(__fmul_rn(oml, f))));
                 }
-                const float x = round_to<T>(silu_mul(iv[i + j], round_to<T>(__fsub_rn(1.0f, f))));
+                const float x = keep ? round_to<T>(silu_mul(iv[i + j], round_to<T>(__fsub_rn(1.0f, f)))) : 0.0f;
                 hh[j] = fmaf(f, hh[j], x);
                 ov[it * V + i + j] = round_to<T>(hh[j]);
             }
@@ -626,6 +628,12 @@ extern "C" int mmf_gatenorm_quant(const void* g, int64_t ld_g, const void* o, in
 extern "C" int mmf_decode_mix(const void* ifg, int64_t ld, int dtype, const void* lower_bound, float* state,
                               const float* gnorm_w, float eps_g, const float* nw, float eps_bl, int8_t* q, float* dq,
                               int32_t* rowsum, int64_t M, int64_t D, void* stream) {
+    return mmf_decode_mix_masked(ifg, ld, dtype, lower_bound, nullptr, state, gnorm_w, eps_g, nw, eps_bl, q, dq, rowsum, M, D, stream);
+}
+
+extern "C" int mmf_decode_mix_masked(const void* ifg, int64_t ld, int dtype, const void* lower_bound, const uint8_t* mask,
+                                     float* state, const float* gnorm_w, float eps_g, const float* nw, float eps_bl,
+                                     int8_t* q, float* dq, int32_t* rowsum, int64_t M, int64_t D, void* stream) {
     MMF_REQUIRE(ifg && state && q && dq && rowsum, MMF_ERR_BAD_ARG, "mmf_decode_mix: null pointer");
     FUSED_ROW_CHECKS("mmf_decode_mix", D);
     const int es = mmf_dtype_size(dtype);
@@ -639,7 +647,7 @@ extern "C" int mmf_decode_mix(const void* ifg, int64_t ld, int dtype, const void
         FUSED_DISPATCH_P(D, P, { FUSED_DISPATCH_LAT(M, LAT, {
             FUSED_SMEM_ATTR((decode_mix_kernel<T, P, LAT>), smem);
             MMF_CUDA(mmf_launch_pdl(decode_mix_kernel<T, P, LAT>, dim3((unsigned)M), dim3(FT), smem, (cudaStream_t)stream, (const T*)ifg, ld,
-                                    (const T*)lower_bound, state, gnorm_w, eps_g, nw, eps_bl, q, dq, rowsum, M, (int)D));
+                                    (const T*)lower_bound, mask, state, gnorm_w, eps_g, nw, eps_bl, q, dq, rowsum, M, (int)D));
         }); });
     });
     MMF_LAUNCH_CHECK("decode_mix_kernel");

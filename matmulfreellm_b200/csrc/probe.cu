@@ -97,7 +97,11 @@ int8_mma_peak_kernel(int n_tokens, int iters, int* status, int commits) {
 
 }  // namespace
 
-int g_probe_commits = 0;   // mmf_tuning(MMF_TUNE_PROBE_COMMITS, n)
+#ifdef MMF_EXPERIMENTS
+int g_probe_commits = 0;   // mmf_tuning(MMF_TUNE_PROBE_COMMITS, n), experiments build only
+#else
+static constexpr int g_probe_commits = 0;
+#endif
 
 extern "C" int mmf_int8_mma_peak(int n_tokens, int iters, int* status_dev, double* tops_host) {
     MMF_REQUIRE(status_dev && tops_host, MMF_ERR_BAD_ARG, "mmf_int8_mma_peak: null pointer");

@@ -170,11 +170,19 @@ __device__ __forceinline__ void tmem_wait_ld() { asm volatile("tcgen05.wait::ld.
 
 __device__ __forceinline__ void cluster_arrive() { asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory"); }
 __device__ __forceinline__ void cluster_wait() { asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory"); }
-// optional phase trace of CTA (0,0,0): armed by writing MMF_TRACE_MAGIC into workspace word 1
+// Phase trace for kernel experiments, compiled only into the experiments build (-DMMF_EXPERIMENTS): CTA (0,0,0) writes
+// clock64 stamps into the workspace header when word 1 of the workspace holds MMF_TRACE_MAGIC.  In the product build
+// MMF_TRACE_PTR(...) is a null constant and every trace statement folds away (no extra load in any kernel prologue).
+#ifdef MMF_EXPERIMENTS
 constexpr int MMF_TRACE_MAGIC = 0x7ace;
+#define MMF_TRACE_PTR(...) (__VA_ARGS__)
 __device__ __forceinline__ void trace_mark(long long* trace, int slot) {
     if (trace) trace[slot] = clock64();
 }
+#else
+#define MMF_TRACE_PTR(...) (static_cast<long long*>(nullptr))
+__device__ __forceinline__ void trace_mark(long long*, int) {}
+#endif
 
 // K-major operand tile in shared memory, 128-byte swizzle: rows of 128 bytes, 8-row groups 1024 B apart.
 __device__ __forceinline__ uint64_t make_b_desc(uint32_t smem_addr) {

@@ -215,7 +215,8 @@ class FusedRunner:
                 want_hidden: bool = False, attention_mask=None):
         """states: list of fp32 [B, ..., h]-shaped tensors advanced in place.  attention_mask: optional [B, T], zero at
         (left-)padding positions — their input to the recurrence is dropped, as the reference's attention layer does
-        (layers/hgrn_bit.py:119-120); only used for T > 1.  Returns (logits | None, hidden | None)."""
+        (layers/hgrn_bit.py:119-120), for a prompt inside the scan and for a single decode token inside the step kernel.
+        Returns (logits | None, hidden | None)."""
         model = self.lm.model
         if inputs_embeds is None:
             x = kernels.embedding(model.embeddings.weight, input_ids)
@@ -226,7 +227,7 @@ class FusedRunner:
         x = x.reshape(M, h)
         lbs = self.lower_bounds
         mask = None
-        if attention_mask is not None and T > 1:
+        if attention_mask is not None:
             mask = (attention_mask.to(x.device) != 0).to(torch.uint8).contiguous()
         stream, z = x, None                      # residual stream, last block's MLP output
         for i, L in enumerate(self.layers):
@@ -239,7 +240,7 @@ class FusedRunner:
             lb = lbs[i] if (lbs is not None and i > 0) else None
             if T == 1:   # decode: gates, state update, gate-norm and o_proj's prologue in one kernel
                 q, dq, rs = kernels.decode_mix(ifg.view(M, 3 * h), lb, states[i].view(B, h), L["gnorm_w"], L["gnorm_eps"],
-                                               L["o_nw"], L["eps_bl"])
+                                               L["o_nw"], L["eps_bl"], mask=None if mask is None else mask.view(B))
             else:
                 o = kernels.hgrn_gated(ifg[:, :, :h], ifg[:, :, h:2 * h], lb, states[i].view(B, h), mask=mask)
                 q, dq, rs = kernels.gatenorm_quant(ifg.view(M, 3 * h)[:, 2 * h:], o.view(M, h), L["gnorm_w"], L["gnorm_eps"],

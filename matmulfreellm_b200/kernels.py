@@ -74,6 +74,7 @@ class PackedWeight:
     N: int                 # total output features (all groups)
     K: int
     groups: int = 1
+    slabs: Optional[torch.Tensor] = None   # uint8, the same codes in slab-major order (read by the decode kernel)
 
     @property
     def device(self) -> torch.device:
@@ -89,6 +90,17 @@ def absmean(w: torch.Tensor) -> torch.Tensor:
     out = torch.empty(1, dtype=torch.float32, device=w.device)
     _lib.call("mmf_absmean_f32", w.data_ptr(), w.numel(), partials.data_ptr(), out.data_ptr(), _stream())
     return out
+
+
+def ensure_slabs(pw: PackedWeight) -> PackedWeight:
+    """Attach the slab-major copy of the packed codes that the decode kernel streams (one contiguous piece per 16
+    output rows).  Doubles the weight's device memory (2 x 0.25 byte per weight); made once, when the weight is packed."""
+    if pw.slabs is None or pw.slabs.device != pw.packed.device:
+        _need_cuda(pw.packed)
+        slabs = torch.empty_like(pw.packed)
+        _lib.call("mmf_repack_slabs", pw.packed.data_ptr(), pw.N, pw.K, slabs.data_ptr(), _stream())
+        pw.slabs = slabs
+    return pw
 
 
 def pack_weight(w: torch.Tensor) -> PackedWeight:
@@ -107,7 +119,7 @@ def pack_weight(w: torch.Tensor) -> PackedWeight:
     nbytes = _lib.load().mmf_packed_bytes(N, K)
     packed = torch.empty(nbytes, dtype=torch.uint8, device=w.device)
     _lib.call("mmf_pack_ternary", w.data_ptr(), N, K, mean.data_ptr(), packed.data_ptr(), _stream())
-    return PackedWeight(packed, mean, N, K, 1)
+    return ensure_slabs(PackedWeight(packed, mean, N, K, 1))
 
 
 def stack_packed(parts: Sequence[PackedWeight]) -> PackedWeight:
@@ -119,8 +131,9 @@ def stack_packed(parts: Sequence[PackedWeight]) -> PackedWeight:
             raise ValueError("grouped BitLinears need identical [N,K]")
     if n % TILE_ROWS:
         raise ValueError(f"grouped BitLinears need out_features % {TILE_ROWS} == 0")
+    # both layouts are tile-major at the top level, so stacking along N is concatenation
     return PackedWeight(torch.cat([p.packed for p in parts]), torch.cat([p.scale for p in parts]), n * len(parts), K,
-                        len(parts))
+                        len(parts), torch.cat([ensure_slabs(p).slabs for p in parts]))
 
 
 def unpack_codes(pw: PackedWeight) -> torch.Tensor:
@@ -225,14 +238,34 @@ def bitlinear(q: torch.Tensor, dq: torch.Tensor, rowsum: torch.Tensor, pw: Packe
     if nbytes is None:
         nbytes = _ws_bytes[(M, pw.N, pw.K)] = _lib.load().mmf_bitlinear_workspace_bytes(M, pw.N, pw.K)
     ws = _workspace(q.device, nbytes)
+    # decode-sized calls take the decode kernel (persistent CTAs, resident codes, slab-major weight stream)
+    decode = kernel == KERNEL_STREAM or (kernel == KERNEL_AUTO and M <= _lib.STREAM_MAX_M and pw.slabs is not None
+                                         and _decode_fits(M, pw.K))
     try:
-        _lib.call("mmf_bitlinear", q.data_ptr(), dq.data_ptr(), rowsum.data_ptr(), pw.packed.data_ptr(),
-                  pw.scale.data_ptr(), G, out.data_ptr(), _code(out_dtype), out.stride(0), _ptr(acc), M, pw.N, pw.K,
-                  ws.data_ptr(), ws.numel(), kernel, _stream())
+        if decode:
+            if pw.slabs is None:
+                raise ValueError("this PackedWeight has no slab-major copy (kernels.ensure_slabs)")
+            _lib.call("mmf_bitlinear_decode", q.data_ptr(), dq.data_ptr(), rowsum.data_ptr(), pw.slabs.data_ptr(),
+                      pw.scale.data_ptr(), G, out.data_ptr(), _code(out_dtype), out.stride(0), _ptr(acc), M, pw.N, pw.K,
+                      ws.data_ptr(), _stream())
+        else:
+            _lib.call("mmf_bitlinear", q.data_ptr(), dq.data_ptr(), rowsum.data_ptr(), pw.packed.data_ptr(),
+                      pw.scale.data_ptr(), G, out.data_ptr(), _code(out_dtype), out.stride(0), _ptr(acc), M, pw.N, pw.K,
+                      ws.data_ptr(), ws.numel(), kernel, _stream())
     except _lib.MMFreeError:
         _rezero_workspaces()  # a failed launch may have left partial sums behind
         raise
     return (out, acc) if return_acc else out
+
+
+_decode_fit_cache: dict = {}
+
+
+def _decode_fits(M: int, K: int) -> bool:
+    r = _decode_fit_cache.get((M, K))
+    if r is None:
+        r = _decode_fit_cache[(M, K)] = bool(_lib.load().mmf_bitlinear_decode_fits(M, K))
+    return r
 
 
 # ------------------------------------------------------------------------------------------
@@ -335,10 +368,14 @@ def gatenorm_quant(g: torch.Tensor, o: torch.Tensor, gnorm_w: Optional[torch.Ten
 
 
 def decode_mix(ifg: torch.Tensor, lower_bound: Optional[torch.Tensor], state: torch.Tensor,
-               gnorm_w: Optional[torch.Tensor], eps_g: float, bl_norm_w: Optional[torch.Tensor], eps_bl: float):
+               gnorm_w: Optional[torch.Tensor], eps_g: float, bl_norm_w: Optional[torch.Tensor], eps_bl: float,
+               mask: Optional[torch.Tensor] = None):
     """One decode step of the token mixer: ifg [M, 3D] = i | f | g projections of the new token of M sequences;
-    `state` fp32 [M, D] is advanced in place; returns o_proj's input codes (q, dq, rowsum)."""
-    _need_cuda(ifg, state, lower_bound, gnorm_w, bl_norm_w)
+    `state` fp32 [M, D] is advanced in place; returns o_proj's input codes (q, dq, rowsum).  `mask`: optional uint8 [M],
+    0 where the new token is padding (its input to the recurrence is dropped)."""
+    _need_cuda(ifg, state, lower_bound, gnorm_w, bl_norm_w, mask)
+    if mask is not None and (mask.dtype != torch.uint8 or mask.numel() != ifg.shape[0] or not mask.is_contiguous()):
+        raise ValueError("mask must be a contiguous uint8 tensor with one entry per row")
     M, D3 = ifg.shape
     D = D3 // 3
     if ifg.stride(1) != 1 or state.dtype != torch.float32 or state.numel() != M * D or not state.is_contiguous():
@@ -347,9 +384,9 @@ def decode_mix(ifg: torch.Tensor, lower_bound: Optional[torch.Tensor], state: to
         raise ValueError("lower_bound must be contiguous [D] in the activation dtype")
     q, dq, rs = _codes_buffers(1, M, D, ifg.device)
     if M:
-        _lib.call("mmf_decode_mix", ifg.data_ptr(), ifg.stride(0), _code(ifg.dtype), _ptr(lower_bound), state.data_ptr(),
-                  _ptr(gnorm_w), float(eps_g), _ptr(bl_norm_w), float(eps_bl), q.data_ptr(), dq.data_ptr(), rs.data_ptr(),
-                  M, D, _stream())
+        _lib.call("mmf_decode_mix_masked", ifg.data_ptr(), ifg.stride(0), _code(ifg.dtype), _ptr(lower_bound), _ptr(mask),
+                  state.data_ptr(), _ptr(gnorm_w), float(eps_g), _ptr(bl_norm_w), float(eps_bl), q.data_ptr(), dq.data_ptr(),
+                  rs.data_ptr(), M, D, _stream())
     return q, dq, rs
 
 

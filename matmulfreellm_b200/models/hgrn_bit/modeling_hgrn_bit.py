@@ -86,7 +86,9 @@ class HGRNBitPreTrainedModel(PreTrainedModel):
                 module.weight.data[module.padding_idx].zero_()
         if rescale_prenorm_residual:  # 1/sqrt(2L) on the two residual-writing projections (:142-156)
             for name, p in module.named_parameters():
-                if name in ("o_proj.weight", "down_proj.weight"):
+                # a parameter that from_pretrained has just loaded is marked by transformers and must not be rescaled
+                # again (the wrapped nn.init functions above honour the mark by themselves; this in-place division does not)
+                if name in ("o_proj.weight", "down_proj.weight") and not getattr(p, "_is_hf_initialized", False):
                     with torch.no_grad():
                         p /= math.sqrt(num_residuals_per_layer * self.config.num_hidden_layers)
 
@@ -175,7 +177,8 @@ class HGRNBitModel(HGRNBitPreTrainedModel):
 
 
 class HGRNBitForCausalLM(HGRNBitPreTrainedModel):
-    _tied_weights_keys = ["lm_head.weight"]
+    # transformers >= 5 wants {tied parameter: its source}; only used when config.tie_word_embeddings is set
+    _tied_weights_keys = {"lm_head.weight": "model.embeddings.weight"}
 
     def __init__(self, config):
         super().__init__(config)
@@ -316,9 +319,6 @@ class HGRNBitForCausalLM(HGRNBitPreTrainedModel):
         if self.config.expand_ratio != 1 or self.config.hidden_size % 16 or self.config.intermediate_size is not None \
                 and self.config.intermediate_size % 16:
             return False
-        ref = input_ids if input_ids is not None else inputs_embeds
-        if attention_mask is not None and ref.shape[1] == 1 and not bool(attention_mask.all()):
-            return False   # a masked single token: module path (the fused decode step has no mask input)
         return True
 
     def _forward_fused(self, input_ids, inputs_embeds, past_key_values, use_cache, last_token_only, attention_mask=None):
@@ -358,8 +358,26 @@ class HGRNBitForCausalLM(HGRNBitPreTrainedModel):
         (a CUDA generator; the default one if None) and is deterministic given those.  `attention_mask` marks
         left padding of the prompt.  Greedy decoding replays each step from a CUDA graph (`use_graph=False` runs the
         same kernels step by step).  Returns [B, prompt + new] token ids like GenerationMixin.generate."""
-        if kwargs.get("num_beams", 1) != 1 or kwargs.get("top_k"):
-            raise NotImplementedError("only greedy decoding and temperature / top-p sampling are implemented")
+        # The reference hands every other option to transformers' GenerationMixin (:311-324).  Options that would change
+        # the result and are not implemented here are refused instead of being silently ignored; the neutral value of
+        # an option (what GenerationMixin does when it is absent) is accepted.
+        neutral = {"num_beams": (1,), "top_k": (None, 0), "repetition_penalty": (None, 1.0), "min_length": (None, 0),
+                   "min_new_tokens": (None, 0), "num_return_sequences": (None, 1), "length_penalty": (None, 1.0),
+                   "no_repeat_ngram_size": (None, 0), "use_cache": (None, True), "return_dict_in_generate": (None, False),
+                   "output_scores": (None, False), "output_hidden_states": (None, False), "output_attentions": (None, False),
+                   "stopping_criteria": (None,), "logits_processor": (None,), "num_beam_groups": (None, 1),
+                   "penalty_alpha": (None,), "typical_p": (None, 1.0), "bad_words_ids": (None,), "pad_token_id": None}
+        for name, value in kwargs.items():
+            if name not in neutral:
+                raise NotImplementedError(f"generate(): option `{name}` is not implemented (greedy decoding and temperature / "
+                                          f"top-p sampling with eos_token_id, max_new_tokens / max_length are)")
+            allowed = neutral[name]
+            if allowed is not None and not any(value is a or value == a for a in allowed):
+                raise NotImplementedError(f"generate(): `{name}={value!r}` is not implemented (only {allowed[-1]!r})")
+        pad_token_id = kwargs.get("pad_token_id")
+        if pad_token_id is not None and eos_token_id is not None and pad_token_id != eos_token_id:
+            raise NotImplementedError("generate(): finished sequences are padded with eos_token_id; a different pad_token_id "
+                                      "is not implemented")
 
         def pick(logits):
             if not do_sample:

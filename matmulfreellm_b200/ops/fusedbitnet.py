@@ -70,16 +70,19 @@ class BitLinear(nn.Linear):
             return self._pack(explicit=False)
         if w.numel() == 0 or self._packed_from is None:
             if self._packed.device != w.device:
-                self._packed = kernels.PackedWeight(self._packed.packed.to(w.device), self._packed.scale.to(w.device),
-                                                    self._packed.N, self._packed.K, self._packed.groups)
+                self._packed = self._moved(w.device)
             return self._packed
         src, version, dtype, explicit = self._packed_from
         if src is not w or w._version != version or (w.dtype != dtype and not explicit):
             return self._pack(explicit=False)
         if self._packed.device != w.device:     # the module moved: the codes move with it
-            self._packed = kernels.PackedWeight(self._packed.packed.to(w.device), self._packed.scale.to(w.device),
-                                                self._packed.N, self._packed.K, self._packed.groups)
+            self._packed = self._moved(w.device)
         return self._packed
+
+    def _moved(self, device) -> kernels.PackedWeight:
+        p = self._packed
+        return kernels.PackedWeight(p.packed.to(device), p.scale.to(device), p.N, p.K, p.groups,
+                                    None if p.slabs is None else p.slabs.to(device))
 
     def norm_weight_f32(self) -> torch.Tensor:
         w = self.norm.weight

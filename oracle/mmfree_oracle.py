@@ -407,3 +407,61 @@ def sample_top_p_ref(logits, temperature: float, top_p: float, uniforms):
         out[m] = idx
         margin[m] = min(np.abs(c[kept] - target).min() / total, nucleus[m])
     return out, margin
+
+
+def greedy_parity(oracle: "OracleHGRNBit", ids: torch.Tensor, steps: int, decoder, prompt_logits) -> dict:
+    """Greedy decoding of a device implementation against this oracle, with the allowance for divergence MEASURED in
+    the same run instead of assumed.
+
+    `decoder` is any object with `prefill(ids_on_device) -> first tokens`, `step() -> next tokens` (feeding its own
+    arg-max back through `decoder.ids` [B,1]), and after a step `decoder.last_logits` [B,V]; `prompt_logits(ids)`
+    returns the device implementation's logits [B,V] for the last prompt position.
+
+    1. The oracle decodes freely: tokens, logits and top-2 margin of every step.
+    2. Teacher-forced pass: the decoder is fed the ORACLE's tokens; err[b,t] = max over the vocabulary of the logit
+       difference at that step.  Rows with err 0 are bit-identical to the oracle's.
+    3. Free-running pass: the decoder feeds itself.  Until a sequence first differs from the oracle, its computation
+       is the teacher-forced one, so at the first differing step t* the two arg-maxes can only disagree if
+       margin[b,t*] <= 2*err[b,t*]; a sequence that differs anywhere else has a wrong token.  After t* the sequence
+       follows another path and is not compared further.
+    Returns a dict: `explained` (every first difference satisfies the inequality), `violations` (list of (b, t*, margin,
+    err)), `identical_fraction` (over all B*steps tokens), `identical_sequences`, `err_median`, `err_max` (over rows),
+    `exact_rows` (fraction of rows with err == 0), `min_margin`."""
+    B = ids.shape[0]
+    dev = decoder.ids.device
+    logits, states = oracle.forward(ids, last_only=True)
+    ref_tokens, ref_logits, margins = [], [], []
+    for _ in range(steps):
+        last = logits[:, -1].float()
+        top2 = last.topk(2, dim=-1).values
+        margins.append(top2[:, 0] - top2[:, 1])
+        ref_logits.append(last)
+        nxt = last.argmax(-1)
+        ref_tokens.append(nxt)
+        logits, states = oracle.forward(nxt[:, None], states, last_only=True)
+    ref_tokens, margins = torch.stack(ref_tokens, 1), torch.stack(margins, 1)
+
+    err = torch.zeros(B, steps)
+    decoder.prefill(ids.to(dev))
+    err[:, 0] = (prompt_logits(ids).float().cpu() - ref_logits[0]).abs().amax(-1)
+    for t in range(steps - 1):
+        decoder.ids.copy_(ref_tokens[:, t:t + 1].to(dev))
+        decoder.step()
+        err[:, t + 1] = (decoder.last_logits.float().cpu() - ref_logits[t + 1]).abs().amax(-1)
+
+    toks = [decoder.prefill(ids.to(dev)).clone().cpu()]
+    for _ in range(steps - 1):
+        toks.append(decoder.step().clone().cpu())
+    toks = torch.stack(toks, 1)
+    same = toks == ref_tokens
+    violations, full = [], 0
+    for b in range(B):
+        if bool(same[b].all()):
+            full += 1
+            continue
+        t = int(torch.nonzero(~same[b])[0])
+        if not float(margins[b, t]) <= 2.0 * float(err[b, t]):
+            violations.append((b, t, float(margins[b, t]), float(err[b, t])))
+    return {"explained": not violations, "violations": violations, "identical_fraction": same.float().mean().item(),
+            "identical_sequences": full, "err_median": err.median().item(), "err_max": err.max().item(),
+            "exact_rows": (err == 0).float().mean().item(), "min_margin": margins.min().item()}

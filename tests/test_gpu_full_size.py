@@ -113,68 +113,12 @@ def _build(sd, cfg, dtype):
     return model.to(dtype)
 
 
-def greedy_parity(model, oracle, ids, steps, decoder):
-    """Greedy decoding of `model` through `decoder` (a GreedyDecoder) against `oracle`.
-
-    1. The oracle decodes freely and records, per step, its tokens, its top-2 logit margin and its logits.
-    2. Teacher-forced pass: the decoder is fed the ORACLE's tokens and its logits are compared with the oracle's at
-       every step; `err` = the largest logit difference seen in that pass.  Two implementations whose logits differ
-       by at most err can only disagree on an arg-max where the top-2 margin is below 2*err.
-    3. Free-running pass: the decoder's own tokens must equal the oracle's at every step of every sequence up to the
-       first step where the oracle's margin is below 2*err (after such a step the sequence follows another, equally
-       valid path and is not compared further).
-    Returns (fraction of identical tokens, err, smallest margin, number of sequences compared over all steps)."""
-    B = ids.shape[0]
-    logits, states = oracle.forward(ids, last_only=True)
-    ref_tokens, ref_logits, margins = [], [], []
-    for _ in range(steps):
-        last = logits[:, -1].float()
-        top2 = last.topk(2, dim=-1).values
-        margins.append(top2[:, 0] - top2[:, 1])
-        ref_logits.append(last)
-        nxt = last.argmax(-1)
-        ref_tokens.append(nxt)
-        logits, states = oracle.forward(nxt[:, None], states, last_only=True)
-    ref_tokens, margins = torch.stack(ref_tokens, 1), torch.stack(margins, 1)
-
-    # teacher-forced: after the prompt pass the decoder holds the logits of step 0; feeding token t gives step t+1
-    decoder.prefill(ids.cuda())
-    err = 0.0
-    got_logits = _last_logits_after_prefill(model, ids)
-    err = max(err, (got_logits - ref_logits[0]).abs().max().item())
-    for t in range(steps - 1):
-        decoder.ids.copy_(ref_tokens[:, t:t + 1].cuda())
-        decoder.step()
-        err = max(err, (decoder.last_logits.float().cpu() - ref_logits[t + 1]).abs().max().item())
-
-    # free-running
-    first = decoder.prefill(ids.cuda()).clone()
-    toks = [first.cpu()]
-    for _ in range(steps - 1):
-        toks.append(decoder.step().clone().cpu())
-    toks = torch.stack(toks, 1)
-    same = toks == ref_tokens
-    full = 0
-    for b in range(B):
-        ambiguous = torch.nonzero(margins[b] < 2 * err)
-        limit = int(ambiguous[0]) if len(ambiguous) else steps     # tokens up to and excluding this step must agree
-        assert bool(same[b, :limit].all()), (
-            f"sequence {b} left the oracle's path at step {int(torch.nonzero(~same[b])[0])} where the oracle's top-2 margin "
-            f"{margins[b, int(torch.nonzero(~same[b])[0])]:.3e} exceeds twice the measured logit error {err:.3e}")
-        full += int(limit == steps)
-    return same.float().mean().item(), err, margins.min().item(), full
-
-
-def _last_logits_after_prefill(model, ids):
-    return model(ids.cuda(), use_cache=False, last_token_only=True).logits[:, -1].float().cpu()
-
-
 def test_model_with_1p3b_layer_shapes_vs_oracle(K):
     """Hidden 2048, intermediate 5632, vocabulary 32000, two blocks, bf16 activations, weights N(0, 0.02).
     (a) prompt pass, batch 4 x 48 tokens: last-position logits and per-block states against the integer oracle;
-    (b) 64 greedy steps at batch 32 through the CUDA-graph decoder: tokens identical to the oracle's wherever the
-        oracle's own top-2 margin exceeds twice the logit error measured in the teacher-forced pass of the same run,
-        that error itself bounded, and most sequences identical over all 64 steps."""
+    (b) 64 greedy steps at batch 32 through the CUDA-graph decoder (oracle.greedy_parity): a sequence may leave the
+        oracle's path only at a step whose top-2 margin is within twice the logit error measured for that row in the
+        teacher-forced pass of the same run; that error is bounded and the identical-token fraction is asserted."""
     from matmulfreellm_b200.engine import GreedyDecoder
     cfg = O.OracleConfig(vocab_size=32000, hidden_size=2048, num_hidden_layers=2, intermediate_size=5632)
     sd = O.random_weights(cfg, seed=13)
@@ -194,10 +138,18 @@ def test_model_with_1p3b_layer_shapes_vs_oracle(K):
 
     ids32 = torch.randint(0, 32000, (32, 16), generator=torch.Generator().manual_seed(15))
     dec = GreedyDecoder(model, 32)
-    frac, err, min_margin, full = greedy_parity(model, oracle, ids32, 64, dec)
+    r = O.greedy_parity(oracle, ids32, 64, dec,
+                        lambda ids: model(ids.cuda(), use_cache=False, last_token_only=True).logits[:, -1])
     assert dec.graph is not None, "the decode steps did not run from the CUDA graph"
     K.check_status()
-    print(f"[1.3B shapes, batch 32, 64 steps] identical tokens {frac:.4f}; teacher-forced logit error {err:.3e} "
-          f"(logit scale {scale:.3f}); smallest oracle top-2 margin {min_margin:.3e}; {full}/32 sequences compared over all steps")
-    assert err <= 1e-1 * scale, "teacher-forced logits drifted beyond the bf16 code-flip bound"
-    assert full >= 16 and frac >= 0.5
+    print(f"[1.3B shapes, batch 32, 64 steps] identical tokens {r['identical_fraction']:.4f}, {r['identical_sequences']}/32 sequences "
+          f"identical over all steps; teacher-forced logit error per row: median {r['err_median']:.3e}, max {r['err_max']:.3e} "
+          f"(logit scale {scale:.3f}), {r['exact_rows']:.3f} of the rows bit-identical; smallest oracle top-2 margin "
+          f"{r['min_margin']:.3e}")
+    # a sequence may leave the oracle's path only at a step where the oracle's top-2 margin is within twice the logit
+    # error measured for that very row in the teacher-forced pass of this run
+    assert r["explained"], r["violations"]
+    # bf16 logits: a row differs from the oracle's by at most a few bf16 steps (2^-8 relative) ...
+    assert r["err_median"] <= 2 ** -6 * scale and r["err_max"] <= 1e-1 * scale
+    # ... and (measured: 0.92) most tokens are the oracle's even though near-flat random-init logits tie often
+    assert r["identical_fraction"] >= 0.8

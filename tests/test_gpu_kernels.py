@@ -37,6 +37,10 @@ def test_pack_ternary_bit_exact(K, N, Kdim):
     got = pw.packed.cpu().numpy().view(np.uint32)
     assert np.array_equal(got, O.pack_ternary(codes))
     assert np.array_equal(K.unpack_codes(pw).cpu().numpy(), codes)
+    # the decode kernel's copy: the same 16-byte pieces, slab-major ([tile][slab of 16 rows][chunk][row][16 B])
+    tiles, KC = -(-N // 128), Kdim // 64
+    want = got.reshape(tiles, KC, 8, 16, 4).transpose(0, 2, 1, 3, 4).reshape(-1)
+    assert np.array_equal(pw.slabs.cpu().numpy().view(np.uint32), want)
 
 
 def test_pack_ternary_edge_values(K):
@@ -222,8 +226,7 @@ def test_bitlinear_persistent_kernel(K):
     trailing 64-wide K stage: bit-exact accumulators and outputs in all three dtypes against the CUDA-core kernel;
     then a grouped (3 x norm weight) call."""
     from matmulfreellm_b200 import _lib
-    lib = _lib.load()
-    try:
+    with _lib.experiments_library() as lib:      # the build that exports the configuration overrides
         for (M, Kd, N) in [(300, 704, 384), (700, 2048, 512), (1024, 2560, 200), (129, 256, 128), (520, 4096, 256)]:
             x, w, _ = O.bitlinear_case(M, Kd, N, seed=M)
             pw = K.pack_weight(dev(w))
@@ -256,12 +259,10 @@ def test_bitlinear_persistent_kernel(K):
                     codes, mean = O.ternary_codes(ws[gi])
                     ref = O.bitlinear_int(x, nws[gi], codes, mean, 1e-6)[0]
                     assert torch.equal(out[:, gi * N:(gi + 1) * N].cpu(), ref.to(dt)), (knob, dt, gi)
-    finally:
-        lib.mmf_tuning(7, 0)
 
 
 def test_bitlinear_large_m_properties(K):
-    """BASELINE-size M: rows are independent, so a slice of a 4096-row call equals the same rows run alone,
+    """4096 token rows (a prompt-sized call): rows are independent, so a slice of a 4096-row call equals the same rows run alone,
     and the first rows match the oracle."""
     M, Kdim, N = 4096, 2048, 2048
     x, w, _ = O.bitlinear_case(M, Kdim, N, seed=9)
@@ -319,7 +320,8 @@ def test_hgrn_scan_vs_oracle(K, B, T, D, log):
 
 
 def test_hgrn_full_size_against_torch_loop(K):
-    """B=8, D=2048, T=2048 (BASELINE size) against a plain fp32 PyTorch loop on the same device."""
+    """B=8, D=2048, T=2048 (the size of the recurrence benchmark) against a plain fp32 PyTorch loop on the same device
+    (the CPU oracle checks the same size in tests/test_gpu_full_size.py)."""
     x, g_log = O.hgrn_case(8, 2048, 2048, seed=0, dtype=torch.bfloat16)
     xd, gd = dev(x).squeeze(1), dev(g_log).squeeze(1)
     o, ht = K.hgrn_scan(xd, gd, None, True, gate_is_log=True, state_dtype=torch.float32)
@@ -601,8 +603,7 @@ def test_bitlinear_mma_configurations_agree(K):
     """Every configuration the tensor-core kernel can be tuned into (K split over clusters of 2/4/8, the deep ring,
     128- or 256-token tiles, two weight tiles per CTA) gives the same int32 accumulators as the CUDA-core kernel."""
     from matmulfreellm_b200 import _lib
-    lib = _lib.load()
-    try:
+    with _lib.experiments_library() as lib:      # the build that exports the configuration overrides
         for (M, Kd, N) in [(32, 2048, 2048), (40, 704, 384), (300, 2048, 512)]:
             x, w, _ = O.bitlinear_case(M, Kd, N, seed=M)
             pw = K.pack_weight(dev(w))
@@ -623,9 +624,6 @@ def test_bitlinear_mma_configurations_agree(K):
                             lib.mmf_tuning(kk, 0)
                     K.check_status()
                     assert torch.equal(acc, acc_ref) and torch.equal(out, ref), (M, Kd, N, knob, v)
-    finally:
-        for kk in range(8):
-            lib.mmf_tuning(kk, 0)
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
