@@ -122,7 +122,7 @@ int mmf_act_quant(const void* x, int dtype, int64_t ld_x, const float* norm_w, i
 #define MMF_KERNEL_AUTO 0
 #define MMF_KERNEL_GEMV 1 /* CUDA-core dp4a, weight-streaming, any M (slow for large M) */
 #define MMF_KERNEL_MMA 2  /* tcgen05 kind::i8 tensor-core tiles, weights unpacked into TMEM */
-#define MMF_MMA_MIN_M 5
+#define MMF_MMA_MIN_M 3
 
 /* Bytes of int32 workspace mmf_bitlinear may need for split-K partial sums (a multiple of
  * 256; includes a 256-byte header whose first word is a status flag — 0, or 1 if a bounded
@@ -145,29 +145,6 @@ int mmf_bitlinear(const int8_t* q, const float* dq, const int32_t* rowsum, const
                   const float* w_scale, int groups, void* out, int out_dtype, int64_t ld_out,
                   int32_t* acc_out, int64_t M, int64_t N, int64_t K, void* workspace,
                   int64_t workspace_bytes, int kernel, void* stream);
-
-/* Slab-major copy of a packed weight for mmf_bitlinear_decode (no counterpart in the reference: a layout choice of
- * this library).  The tile-major layout of mmf_pack_ternary keeps a 16-row slab as K/64 pieces of 256 bytes that lie
- * 2 KB apart; the decode kernel fetches whole slabs with one bulk copy each, so it reads a second copy in which slab
- * s (16 rows) of tile t occupies the (K/64)*256 contiguous bytes at ((t*8 + s) * (K/64)) * 256: chunk c at + c*256,
- * row r of the slab at + r*16, the 16 bytes themselves unchanged.  `slabs`: mmf_packed_bytes(N, K) bytes. */
-int mmf_repack_slabs(const void* packed, int64_t N, int64_t K, void* slabs, void* stream);
-
-/* 1 if mmf_bitlinear_decode accepts M token rows with K input features (M <= MMF_STREAM_MAX_M and the codes of at
- * least 8 rows fit in shared memory beside one slab of weights: K <= 16384 or so), else 0. */
-#define MMF_STREAM_MAX_M 64
-int mmf_bitlinear_decode_fits(int64_t M, int64_t K);
-
-/* The contraction of mmf_bitlinear for a decode step (M <= MMF_STREAM_MAX_M token rows): same arithmetic, same
- * arguments and outputs, but the weights come from the slab-major copy (mmf_repack_slabs) and no workspace is needed.
- * One persistent CTA per SM keeps the activation codes resident in shared memory, streams its slabs of weights by
- * bulk TMA ahead of the grid dependency (programmatic dependent launch) and contracts them with mma.sync m16n8k32
- * (s8 x s8 -> s32).  `status` (may be NULL): one device int that is set to 1 if a bounded device-side wait gave up.
- * Replaces: F.linear(y_dequant, weight_quant(W)), mmfreelm/ops/fusedbitnet.py:456-458, for single-token forwards
- * (the cached generation step, mmfreelm/models/hgrn_bit/modeling_hgrn_bit.py:335-338). */
-int mmf_bitlinear_decode(const int8_t* q, const float* dq, const int32_t* rowsum, const void* packed_slabs,
-                         const float* w_scale, int groups, void* out, int out_dtype, int64_t ld_out,
-                         int32_t* acc_out, int64_t M, int64_t N, int64_t K, int32_t* status, void* stream);
 
 /* BitLinear for a few token rows WITHOUT caller-provided scratch and without any allocation.
  * (No counterpart in the reference: it exists for hosts that must not allocate.)
@@ -202,6 +179,13 @@ int mmf_bitlinear_gemv_static(const int8_t* q, const float* dq, const int32_t* r
  * runs on the default stream and SYNCHRONISES; status_dev is one device int of scratch, tops_host a host
  * double. */
 int mmf_int8_mma_peak(int n_tokens, int iters, int* status_dev, double* tops_host);
+
+/* Measurement aid (no counterpart in the reference): the two synchronisation costs that bound a chain of dependent
+ * decode kernels on the current GPU, in microseconds.  barrier_us: one grid-wide barrier among one resident CTA per SM
+ * (each CTA adds to a global counter with release semantics and polls it with acquire loads; cooperative launch, every
+ * wait bounded).  signal_us: one hand-over of a flag between two CTAs (release store -> the other CTA's acquire poll
+ * sees it).  scratch_dev: 256 device uints.  Runs on the default stream and SYNCHRONISES. */
+int mmf_sync_probe(int iters, unsigned* scratch_dev, double* barrier_us_host, double* signal_us_host);
 
 /* ------------------------------------------------------------------------------------
  * HGRN recurrence  h_t = f_t * h_{t-1} + x_t  (element-wise, fp32 state).

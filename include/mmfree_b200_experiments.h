@@ -9,6 +9,8 @@
 #ifndef MMFREE_B200_EXPERIMENTS_H
 #define MMFREE_B200_EXPERIMENTS_H
 
+#include <stdint.h>
+
 #ifdef __cplusplus
 extern "C" {
 #endif
@@ -26,6 +28,33 @@ extern "C" {
 #define MMF_TUNE_PROBE_COMMITS 8 /* mmf_int8_mma_peak: tcgen05.commit instructions issued per 4 MMAs */
 #define MMF_TUNE_ACCUMULATORS 9 /* accumulators consecutive MMAs rotate through at few token columns: 1, 2 or 4 */
 int mmf_tuning(int knob, int value);
+
+/* Timeline trace of mmf_prenorm_quant launches: buffer_dev is a device buffer of at least 8 + 8 * 1000 int64 ([0] = launch
+ * counter, then one record of 8 global-timer stamps per launch, taken by thread 0 of CTA 0: start, weights staged, grid
+ * dependency resolved, row loaded, first row sum done, second norm done, codes written, end); NULL switches it off. */
+int mmf_row_trace(long long* buffer_dev);
+
+/* Slab-major copy of a packed weight for mmf_bitlinear_decode (experiment; no counterpart in the reference).  The tile-major layout of mmf_pack_ternary keeps a 16-row slab as K/64 pieces of 256 bytes that lie
+ * 2 KB apart; the decode kernel fetches whole slabs with one bulk copy each, so it reads a second copy in which slab
+ * s (16 rows) of tile t occupies the (K/64)*256 contiguous bytes at ((t*8 + s) * (K/64)) * 256: chunk c at + c*256,
+ * row r of the slab at + r*16, the 16 bytes themselves unchanged.  `slabs`: mmf_packed_bytes(N, K) bytes. */
+int mmf_repack_slabs(const void* packed, int64_t N, int64_t K, void* slabs, void* stream);
+
+/* 1 if mmf_bitlinear_decode accepts M token rows with K input features (M <= MMF_STREAM_MAX_M and the codes of at
+ * least 8 rows fit in shared memory beside one slab of weights: K <= 16384 or so), else 0. */
+#define MMF_STREAM_MAX_M 64
+int mmf_bitlinear_decode_fits(int64_t M, int64_t K);
+
+/* The contraction of mmf_bitlinear for a decode step (M <= MMF_STREAM_MAX_M token rows): same arithmetic, same
+ * arguments and outputs, but the weights come from the slab-major copy (mmf_repack_slabs) and no workspace is needed.
+ * One persistent CTA per SM keeps the activation codes resident in shared memory, streams its slabs of weights by
+ * bulk TMA ahead of the grid dependency (programmatic dependent launch) and contracts them with mma.sync m16n8k32
+ * (s8 x s8 -> s32).  `status` (may be NULL): one device int that is set to 1 if a bounded device-side wait gave up.
+ * Replaces: F.linear(y_dequant, weight_quant(W)), mmfreelm/ops/fusedbitnet.py:456-458, for single-token forwards
+ * (the cached generation step, mmfreelm/models/hgrn_bit/modeling_hgrn_bit.py:335-338). */
+int mmf_bitlinear_decode(const int8_t* q, const float* dq, const int32_t* rowsum, const void* packed_slabs,
+                         const float* w_scale, int groups, void* out, int out_dtype, int64_t ld_out,
+                         int32_t* acc_out, int64_t M, int64_t N, int64_t K, int32_t* status, void* stream);
 
 #ifdef __cplusplus
 }

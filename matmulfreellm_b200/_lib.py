@@ -13,7 +13,7 @@ LIB_PATH = Path(__file__).resolve().parent / "libmmfree_b200.so"
 
 F32, BF16, F16 = 0, 1, 2
 KERNEL_AUTO, KERNEL_GEMV, KERNEL_MMA = 0, 1, 2
-KERNEL_STREAM = 3   # Python-level selector: the decode kernel (mmf_bitlinear_decode)
+KERNEL_STREAM = 3   # Python-level selector: the mma.sync decode experiment (mmf_bitlinear_decode, experiments build only)
 STREAM_MAX_M = 64
 TILE_ROWS, TILE_K = 128, 64
 ABSMEAN_PARTIALS = 1024
@@ -38,13 +38,10 @@ PROTOTYPES = {
     "mmf_bitlinear_workspace_bytes": (c_int64, [c_int64, c_int64, c_int64]),
     "mmf_bitlinear": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int64,
                               c_void_p, c_int64, c_int64, c_int64, c_void_p, c_int64, c_int, c_void_p]),
-    "mmf_repack_slabs": (c_int, [c_void_p, c_int64, c_int64, c_void_p, c_void_p]),
-    "mmf_bitlinear_decode_fits": (c_int, [c_int64, c_int64]),
-    "mmf_bitlinear_decode": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int64,
-                                     c_void_p, c_int64, c_int64, c_int64, c_void_p, c_void_p]),
     "mmf_bitlinear_gemv_static": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int64,
                                           c_int64, c_int64, c_int64, c_void_p]),
     "mmf_int8_mma_peak": (c_int, [c_int, c_int, c_void_p, c_void_p]),
+    "mmf_sync_probe": (c_int, [c_int, c_void_p, c_void_p, c_void_p]),
     "mmf_hgrn_workspace_bytes": (c_int64, [c_int64, c_int64, c_int64]),
     "mmf_hgrn_scan": (c_int, [c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_int, c_void_p, c_int64,
                               c_int64, c_int64, c_int, c_void_p, c_int64, c_void_p]),
@@ -86,7 +83,13 @@ class MMFreeError(RuntimeError):
 
 _lib = None
 EXPERIMENTS_LIB_PATH = LIB_PATH.with_name("libmmfree_b200_experiments.so")
-_EXPERIMENT_PROTOTYPES = {"mmf_tuning": (c_int, [c_int, c_int])}
+_EXPERIMENT_PROTOTYPES = {
+    "mmf_tuning": (c_int, [c_int, c_int]), "mmf_row_trace": (c_int, [c_void_p]),
+    "mmf_repack_slabs": (c_int, [c_void_p, c_int64, c_int64, c_void_p, c_void_p]),
+    "mmf_bitlinear_decode_fits": (c_int, [c_int64, c_int64]),
+    "mmf_bitlinear_decode": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int64,
+                                     c_void_p, c_int64, c_int64, c_int64, c_void_p, c_void_p]),
+}
 
 
 def _open(path: Path, prototypes) -> ctypes.CDLL:

@@ -113,8 +113,8 @@ def load_packed(path: str, device="cuda"):
             if (m.out_features, m.in_features) != (N, K):
                 raise ValueError(f"{name}: checkpoint has [{N}, {K}], the config builds [{m.out_features}, {m.in_features}]")
             m.weight = nn.Parameter(torch.empty(0, device=device, dtype=dtype), requires_grad=False)
-            m._packed = kernels.ensure_slabs(kernels.PackedWeight(torch.from_numpy(z[f"{name}.packed"].copy()).to(device),
-                                                                  torch.from_numpy(z[f"{name}.scale"].copy()).to(device), N, K, 1))
+            m._packed = kernels.PackedWeight(torch.from_numpy(z[f"{name}.packed"].copy()).to(device),
+                                             torch.from_numpy(z[f"{name}.scale"].copy()).to(device), N, K, 1)
             m._packed_from = None
             m.norm.weight = nn.Parameter(torch.from_numpy(z[f"{name}.norm"].copy()).to(device=device, dtype=dtype),
                                          requires_grad=False)

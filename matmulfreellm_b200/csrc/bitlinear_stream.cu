@@ -1,30 +1,35 @@
-// BitLinear for a decode step (1 .. 64 token rows): a persistent, latency-lean weight-streaming kernel.
+// BitLinear for a decode step (1 .. 64 token rows) as a persistent weight-streaming kernel on mma.sync — an EXPERIMENT,
+// compiled only into the experiments build (-DMMF_EXPERIMENTS); the product library does not contain it.
 //
-// A decode step is a chain of ~100 dependent contractions, each of which moves only a few megabytes of 2-bit weights:
-// what counts is the time from "the activation codes exist" to "the outputs are in memory", not throughput.  This
-// kernel therefore has no tensor-memory allocation, no cluster and no cross-CTA reduction:
+// Question it answers: a decode step is a chain of ~100 dependent contractions of a few megabytes each; would a kernel
+// with no tensor-memory allocation, no cluster and no cross-CTA reduction beat the tcgen05 kernel (bitlinear_mma.cu) and
+// the dp4a GEMV (bitlinear_gemv.cu) on latency?  Design:
 //
 //   * one CTA per SM; the CTA keeps ALL activation codes of its group resident in shared memory ([K/64] chunks of
 //     [tokens][64 bytes], copied once with cp.async after the grid-dependency wait) and walks over "slabs" of 16
 //     output rows (slab j of CTA b is slab b + j * CTAs of the group), so the codes cross L2 -> SM once per SM;
 //   * the 2-bit weights are read from a SLAB-MAJOR copy of the packed weight (mmf_repack_slabs): a slab's K/4 * 16
-//     bytes are contiguous, so one bulk-TMA copy fetches a whole slab into a ring of slabs.  Weights do not depend on
-//     the preceding kernel: the ring is filled BEFORE the grid-dependency wait (programmatic dependent launch), so
-//     after the wait only the codes have to travel.  (256-byte pieces of the tile-major layout, one bulk copy each,
-//     were measured first: the copy engine then bounds the launch at ~8 us whatever the token count.)
+//     bytes are contiguous, so one bulk-TMA copy fetches a whole slab into a ring of slabs, filled BEFORE the
+//     grid-dependency wait (programmatic dependent launch).  (256-byte pieces of the tile-major layout, one bulk copy
+//     each, were measured first: the copy engine then bounds the launch at ~8 us whatever the token count.)
 //   * four warps share a slab, each contracting every fourth 64-column chunk against ALL token tiles with mma.sync
 //     m16n8k32 (s8 x s8 -> s32): the A fragment (16 weight rows x 32 columns) is two 32-bit words of packed weights
-//     per thread, expanded with shift + mask in registers ((word >> 2i) & 0x03030303 is four consecutive columns as
-//     bytes) once per chunk and reused for every token tile; the B fragment is one 16-byte shared-memory load of
-//     codes per token tile and chunk.  The K order inside an MMA is permuted identically for both operands, so no
-//     data is rearranged.  The four partial sums meet in shared memory (one named barrier of 128 threads) and each
-//     warp finishes the token tiles it owns; two slabs are in flight per CTA;
-//   * measured on B200: mma.sync.m16n8k32.s8 sustains 4096 op/clk/SM (1.14 POP/s per GPU), so a 32-token step of
-//     a 1.3 B-parameter model needs about 75 us of tensor-pipe time — the same order as the 50 us its weight stream
-//     needs from HBM; tcgen05 would not make a 32-column tile faster, and costs a TMEM round trip per tile.
+//     per thread, expanded with shift + mask in registers, the B fragment one 16-byte shared-memory load of codes per
+//     token tile and chunk; the K order inside an MMA is permuted identically for both operands.  The four partial
+//     sums meet in shared memory (one named barrier of 128 threads); two slabs are in flight per CTA.
+//
+// Answer (measured on B200, HGRNBit-1.3B decode steps replayed from a CUDA graph): no.  A bare mma.sync.m16n8k32.s8 loop
+// sustains 4096 op/clk/SM, but with the 2-bit expansion and the shared-memory operand loads a warp issues one MMA per
+// ~23 cycles (188 - 215 cycles per 64-column chunk of 8 MMAs: shared-memory bandwidth for the codes and the issue slots
+// of the expansion bound it together), i.e. ~700 MAC/clk/SM at 32 tokens where the tcgen05 kernel reaches ~1950.  Whole
+// steps: batch 1: 0.69 ms (GEMV 0.62), batch 4: 0.79 (GEMV 0.84, tcgen05 ~0.75), batch 8: 0.82 (tcgen05 0.75), batch 32:
+// 1.06 (tcgen05 0.84).  Per launch inside the chain (timeline of CTA 0): 1.1 - 3.5 us from the predecessor's end to the
+// release of the grid dependency, 0.3 - 1.1 us for the codes, 0.4 - 2.4 us per slab.
 //
 // Weights are stored biased (+1): the epilogue subtracts the row's code sum, then dequantises (acc * (dq * mean|w|)).
-// Every wait is bounded; a wait that gives up sets the status word of the workspace (if one was passed).
+// Every wait is bounded; a wait that gives up sets the status word (if one was passed).
+#ifdef MMF_EXPERIMENTS
+#include "../../include/mmfree_b200_experiments.h"
 #include "bitlinear.cuh"
 #include "tcgen05.cuh"
 
@@ -49,7 +54,8 @@ struct StreamParams {
 };
 
 __device__ __forceinline__ void mma_s8(int (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
-    asm volatile("mma.sync.aligned.m16n8k32.row.col.s32.s8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+    // not volatile: a pure function of its operands, so the compiler may interleave it with the loads of later chunks
+    asm("mma.sync.aligned.m16n8k32.row.col.s32.s8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
                  : "+r"(c[0]), "+r"(c[1]), "+r"(c[2]), "+r"(c[3])
                  : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
@@ -122,6 +128,7 @@ bitlinear_stream_kernel(BitLinearArgs a, const uint8_t* __restrict__ slabs, Stre
         s_trace = nullptr;
         if (blockIdx.x == 0 && a.ws && a.ws[1] == MMF_TRACE_MAGIC) {
             const int idx = atomicAdd(a.ws + 2, 1);
+            a.ws[3] = idx;
             if (idx < 4000) s_trace = reinterpret_cast<long long*>(a.ws + 16) + 8 * idx;
         }
         if (s_trace) s_trace[0] = sk_now();
@@ -195,7 +202,7 @@ bitlinear_stream_kernel(BitLinearArgs a, const uint8_t* __restrict__ slabs, Stre
 
         if (sl < p.SL) {
             const uint8_t* bsrc = codes + gq * 64 + 16 * t;
-            int* myred = red + (size_t)sl * (SK_KP * MT * 128);
+            const int n_group = a.N / a.groups, n_base = g * n_group;
             bool ok = true;
             int jj = 0;
             for (int j = sl; j < nj && ok; j += p.SL, ++jj) {
@@ -204,11 +211,18 @@ bitlinear_stream_kernel(BitLinearArgs a, const uint8_t* __restrict__ slabs, Stre
                 if (!ok) break;
                 if (jj == 0) SK_TRACE(4);
                 const uint32_t* wsm = reinterpret_cast<const uint32_t*>(wring + (size_t)slot * slab_bytes) + gq * 4 + t;
-                int acc[MT][4];
+                // A dependent mma.sync waits for its predecessor (measured: a chain of 8 per accumulator made a slab take
+                // ~1 us where the tensor pipe needs 0.27), so every warp keeps 16 independent accumulators: the two K steps
+                // of a chunk, the MT token tiles, and CS = 8 / MT consecutive chunks of the warp go to different ones.
+                constexpr int CS = MT >= 8 ? 1 : 8 / MT;
+                int acc[CS][2][MT][4];
 #pragma unroll
-                for (int nt = 0; nt < MT; ++nt) acc[nt][0] = acc[nt][1] = acc[nt][2] = acc[nt][3] = 0;
-#pragma unroll 2
-                for (int c = kp; c < p.KC; c += SK_KP) {
+                for (int s2 = 0; s2 < CS; ++s2)
+#pragma unroll
+                    for (int h = 0; h < 2; ++h)
+#pragma unroll
+                        for (int nt = 0; nt < MT; ++nt) acc[s2][h][nt][0] = acc[s2][h][nt][1] = acc[s2][h][nt][2] = acc[s2][h][nt][3] = 0;
+                auto chunk = [&](int c, int (&accs)[2][MT][4]) {
                     const uint32_t lo = wsm[c * (SK_PIECE / 4)], hi = wsm[c * (SK_PIECE / 4) + 32];   // rows gq, gq + 8
                     const uint32_t a0 = lo & 0x03030303u, a1 = hi & 0x03030303u, a2 = (lo >> 2) & 0x03030303u,
                                    a3 = (hi >> 2) & 0x03030303u, a4 = (lo >> 4) & 0x03030303u, a5 = (hi >> 4) & 0x03030303u,
@@ -217,18 +231,29 @@ bitlinear_stream_kernel(BitLinearArgs a, const uint8_t* __restrict__ slabs, Stre
 #pragma unroll
                     for (int nt = 0; nt < MT; ++nt) {
                         const uint4 b = *reinterpret_cast<const uint4*>(bc + nt * 512);
-                        mma_s8(acc[nt], a0, a1, a2, a3, b.x, b.y);
-                        mma_s8(acc[nt], a4, a5, a6, a7, b.z, b.w);
+                        mma_s8(accs[0][nt], a0, a1, a2, a3, b.x, b.y);
+                        mma_s8(accs[1][nt], a4, a5, a6, a7, b.z, b.w);
                     }
+                };
+                for (int c = kp; c < p.KC; c += CS * SK_KP) {
+#pragma unroll
+                    for (int s2 = 0; s2 < CS; ++s2)
+                        if (c + s2 * SK_KP < p.KC) chunk(c + s2 * SK_KP, acc[s2]);
                 }
                 __syncwarp();
                 if (jj == 0) SK_TRACE(5);
                 if (lane == 0) mbar_arrive(&bar_wempty[slot]);   // this warp has read the slab's weights
                 // the four K parts meet in shared memory: [kp][tile][register][lane]
+                int* const myred = red + (size_t)sl * (SK_KP * MT * 128);
 #pragma unroll
                 for (int nt = 0; nt < MT; ++nt)
 #pragma unroll
-                    for (int r = 0; r < 4; ++r) myred[((kp * MT + nt) * 4 + r) * 32 + lane] = acc[nt][r];
+                    for (int r = 0; r < 4; ++r) {
+                        int v = 0;
+#pragma unroll
+                        for (int s2 = 0; s2 < CS; ++s2) v += acc[s2][0][nt][r] + acc[s2][1][nt][r];
+                        myred[((kp * MT + nt) * 4 + r) * 32 + lane] = v;
+                    }
                 named_barrier(2 + sl, SK_KP * 32);
                 const int slab = cb + j * p.ctas_per_group;
 #pragma unroll
@@ -250,9 +275,8 @@ bitlinear_stream_kernel(BitLinearArgs a, const uint8_t* __restrict__ slabs, Stre
                         const int sy = __shfl_xor_sync(0xffffffffu, odd ? v[2] : v[3], 4);
                         if (live[o]) {
                             const int m = p.m0 + nt * 8 + 2 * t + (gq & 1);
-                            const int n_group = a.N / a.groups;
-                            const int n = g * n_group + slab * SK_SLAB_ROWS + (gq & ~1);
-                            const int n_end = g * n_group + min(n_group, (slab + 1) * SK_SLAB_ROWS);   // rows of this group only
+                            const int n = n_base + slab * SK_SLAB_ROWS + (gq & ~1);
+                            const int n_end = n_base + min(n_group, (slab + 1) * SK_SLAB_ROWS);   // rows of this group only
                             const int lo0 = (odd ? sx : v[0]) - rsum[o], lo1 = (odd ? v[1] : sx) - rsum[o];
                             const int hi0 = (odd ? sy : v[2]) - rsum[o], hi1 = (odd ? v[3] : sy) - rsum[o];
                             if (n < n_end) store_pair(a, m, n, lo0, lo1, scale[o], pair_ok && n + 1 < n_end);
@@ -269,6 +293,13 @@ bitlinear_stream_kernel(BitLinearArgs a, const uint8_t* __restrict__ slabs, Stre
     if (tid == 0) SK_TRACE(6);
     __syncthreads();
     if (tid == 0) SK_TRACE(7);
+#ifdef MMF_EXPERIMENTS
+    // end time of EVERY CTA of the first 64 traced launches: [launch][256] at byte offset 512 KB of the status buffer
+    if (tid == 0 && a.ws && a.ws[1] == MMF_TRACE_MAGIC && blockIdx.x < 256) {
+        const int idx = a.ws[3];     // launch index published by CTA 0 (may lag by one launch for CTAs that end before CTA 0 starts)
+        if (idx >= 0 && idx < 64) reinterpret_cast<long long*>(a.ws + 131072)[idx * 256 + blockIdx.x] = sk_now();
+    }
+#endif
     if (*abort_flag) {
         __nanosleep(20000);
         if (tid == 0 && a.ws) atomicExch(reinterpret_cast<int*>(a.ws), 1);   // status word: a wait gave up
@@ -424,3 +455,4 @@ extern "C" int mmf_bitlinear_decode(const int8_t* q, const float* dq, const int3
     a.ws = status; a.ws_bytes = status ? 4 : 0;
     return bitlinear_stream_launch(a, packed_slabs, (cudaStream_t)stream);
 }
+#endif  // MMF_EXPERIMENTS

@@ -226,7 +226,21 @@ struct PrenormArgs {
     int8_t* q; float* dq; int32_t* rowsum; // [G][M][D], [G][M], [G][M]
     int64_t M; int D; int G;
     int round_sum_first;                   // 1: the reference added x+residual as a tensor op (rounded to T) before norm
+#ifdef MMF_EXPERIMENTS
+    long long* trace;                      // experiments build: 8 global-timer stamps of CTA 0 per launch (see mmf_row_trace)
+#endif
 };
+
+#ifdef MMF_EXPERIMENTS
+__device__ __forceinline__ long long row_now() {
+    long long t;
+    asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+    return t;
+}
+#define ROW_TRACE(slot) do { if (trace) trace[slot] = row_now(); } while (0)
+#else
+#define ROW_TRACE(slot) do { } while (0)
+#endif
 
 template <typename T, int P, int LAT>
 __global__ void __launch_bounds__(FT, LAT)
@@ -235,10 +249,20 @@ prenorm_quant_kernel(PrenormArgs a) {
     __shared__ RedScratch red;
     constexpr int V = 16 / sizeof(T);
     const int D = a.D;
+#ifdef MMF_EXPERIMENTS
+    long long* trace = nullptr;
+    if (threadIdx.x == 0 && blockIdx.x == 0 && a.trace) {
+        const int idx = atomicAdd(reinterpret_cast<int*>(a.trace), 1);
+        if (idx < 1000) trace = a.trace + 8 + 8 * idx;
+    }
+#endif
+    ROW_TRACE(0);
     pdl_trigger();
     stage_weights(sw, a.norm_w, D);
     for (int g = 0; g < a.G; ++g) stage_weights(sw + (1 + g) * D, a.nws[g], D);
+    ROW_TRACE(1);
     pdl_wait();
+    ROW_TRACE(2);
     __syncthreads();
 
     // Row loop (LAT = 0): the CTA's next row travels global -> shared memory by cp.async while the current one is
@@ -293,7 +317,9 @@ prenorm_quant_kernel(PrenormArgs a) {
             }
         }
         if (LAT == 0 && m + gridDim.x < a.M) fetch(m + gridDim.x);   // this thread's slots have just been read
+        ROW_TRACE(3);
         block_sum_d<1>(ss, red.d0);
+        ROW_TRACE(4);
         const float rstd1 = rstd_from_sumsq(ss[0], D, a.eps_norm);
         T* yo = a.y_out ? reinterpret_cast<T*>(a.y_out) + m * (int64_t)D : nullptr;
         double ss2 = 0.0;
@@ -316,9 +342,12 @@ prenorm_quant_kernel(PrenormArgs a) {
             }
             if (yo) store_rounded<T, V>(yo + c, o, bits);
         }
+        ROW_TRACE(5);
         if (a.G == 3) bitlinear_prologue<V, 3, P>(v, D, ss2, a.eps_bl, sw + D, a.q, a.dq, a.rowsum, a.M, m, red);
         else if (a.G == 1) bitlinear_prologue<V, 1, P>(v, D, ss2, a.eps_bl, sw + D, a.q, a.dq, a.rowsum, a.M, m, red);
+        ROW_TRACE(6);
     }
+    ROW_TRACE(7);
 }
 
 // y = round_T( ((g*rstd)*w) * o * sigmoid(o) ), then BitLinear prologue.  `ov` holds the gate row o in registers.
@@ -573,6 +602,12 @@ constexpr int64_t LAT_MAX_ROWS = MMF_LAT_MAX_ROWS;
 #define FUSED_SMEM_ATTR(kernel, smem) \
     if ((smem) + 2048 > 48 * 1024) MMF_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)(smem)))
 
+#ifdef MMF_EXPERIMENTS
+static long long* g_row_trace = nullptr;
+// experiments build only: device buffer ([0] = launch counter, records of 8 stamps from word 8 on) or NULL to switch off
+extern "C" int mmf_row_trace(long long* buffer_dev) { g_row_trace = buffer_dev; return MMF_OK; }
+#endif
+
 extern "C" int mmf_prenorm_quant(const void* x, int64_t ld_x, const void* residual, int64_t ld_res, int dtype,
                                  int round_sum_first, const float* norm_w, float eps_norm, void* residual_out,
                                  void* y_out, int groups, const float* nw0, const float* nw1, const float* nw2,
@@ -592,6 +627,9 @@ extern "C" int mmf_prenorm_quant(const void* x, int64_t ld_x, const void* residu
     a.x = x; a.ld_x = ld_x; a.res = residual; a.ld_res = ld_res; a.res_out = residual_out; a.y_out = y_out;
     a.norm_w = norm_w; a.eps_norm = eps_norm; a.nws[0] = nw0; a.nws[1] = nw1; a.nws[2] = nw2; a.eps_bl = eps_bl;
     a.q = q; a.dq = dq; a.rowsum = rowsum; a.M = M; a.D = (int)D; a.G = groups; a.round_sum_first = round_sum_first;
+#ifdef MMF_EXPERIMENTS
+    a.trace = g_row_trace;
+#endif
     MMF_DISPATCH(dtype, T, {
         FUSED_DISPATCH_P(D, P, { FUSED_DISPATCH_LAT(M, LAT, {
             const size_t smem = (size_t)(1 + groups) * D * sizeof(float) + (LAT ? 0 : (size_t)2 * D * sizeof(T));   // + row staging

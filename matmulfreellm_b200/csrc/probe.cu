@@ -134,3 +134,97 @@ extern "C" int mmf_int8_mma_peak(int n_tokens, int iters, int* status_dev, doubl
     *tops_host = 2.0 * 128.0 * n_tokens * 32.0 * (double)iters * sms / ((double)ms * 1e-3) / 1e12;
     return MMF_OK;
 }
+
+
+// =========================================================================================================
+// Synchronisation costs that shape the decode step (measurement aid, no counterpart in the reference)
+// =========================================================================================================
+namespace {
+
+constexpr long long SYNC_SPIN_LIMIT = 400000000ll;   // cycles: a wait that exceeds this gives up and sets the status word
+
+__device__ __forceinline__ unsigned probe_ld_acquire(const unsigned* p) {
+    unsigned v;
+    asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    return v;
+}
+__device__ __forceinline__ void probe_red_release(unsigned* p) {
+    asm volatile("red.release.gpu.global.add.u32 [%0], 1;" ::"l"(p) : "memory");
+}
+
+// `iters` grid-wide barriers: every CTA adds 1 to a counter (release) and polls it (acquire) until all have arrived
+__global__ void grid_barrier_probe_kernel(unsigned* counter, int iters, int* status) {
+    const unsigned n = gridDim.x;
+    bool ok = true;
+    for (int k = 0; k < iters && ok; ++k) {
+        __syncthreads();
+        if (threadIdx.x == 0) {
+            probe_red_release(counter);
+            const long long t0 = clock64();
+            while (probe_ld_acquire(counter) < (unsigned)(k + 1) * n) {
+                if (clock64() - t0 > SYNC_SPIN_LIMIT) { *status = 1; ok = false; break; }
+            }
+        }
+        ok = __syncthreads_and(ok);
+    }
+}
+
+// two CTAs hand a flag back and forth `iters` times: release store -> acquire poll, one direction at a time
+__global__ void signal_probe_kernel(unsigned* f0, unsigned* f1, int iters, int* status) {
+    if (threadIdx.x != 0) return;
+    for (int k = 1; k <= iters; ++k) {
+        unsigned* mine = blockIdx.x == 0 ? f0 : f1;
+        const unsigned* theirs = blockIdx.x == 0 ? f1 : f0;
+        if (blockIdx.x == 0) asm volatile("st.release.gpu.global.u32 [%0], %1;" ::"l"(mine), "r"((unsigned)k) : "memory");
+        const long long t0 = clock64();
+        while (probe_ld_acquire(theirs) < (unsigned)k)
+            if (clock64() - t0 > SYNC_SPIN_LIMIT) { *status = 2; return; }
+        if (blockIdx.x == 1) asm volatile("st.release.gpu.global.u32 [%0], %1;" ::"l"(mine), "r"((unsigned)k) : "memory");
+    }
+}
+
+}  // namespace
+
+extern "C" int mmf_sync_probe(int iters, unsigned* scratch_dev, double* barrier_us_host, double* signal_us_host) {
+    MMF_REQUIRE(scratch_dev && barrier_us_host && signal_us_host, MMF_ERR_BAD_ARG, "mmf_sync_probe: null pointer");
+    MMF_REQUIRE(iters > 0 && iters <= 100000, MMF_ERR_BAD_SHAPE, "mmf_sync_probe: iters must be in (0, 100000]");
+    int dev = 0, sms = 0, coop = 0;
+    MMF_CUDA(cudaGetDevice(&dev));
+    MMF_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
+    MMF_CUDA(cudaDeviceGetAttribute(&coop, cudaDevAttrCooperativeLaunch, dev));
+    MMF_REQUIRE(coop, MMF_ERR_ARCH, "mmf_sync_probe: the device does not support cooperative launches");
+    cudaEvent_t e0, e1;
+    MMF_CUDA(cudaEventCreate(&e0));
+    MMF_CUDA(cudaEventCreate(&e1));
+    // scratch: [0] barrier counter, [64] and [128] the two flags (separate cache lines), [192] status
+    MMF_CUDA(cudaMemset(scratch_dev, 0, 256 * sizeof(unsigned)));
+    unsigned* counter = scratch_dev;
+    unsigned *f0 = scratch_dev + 64, *f1 = scratch_dev + 128;
+    int* status = reinterpret_cast<int*>(scratch_dev + 192);
+    float ms = 0.0f;
+    {
+        // co-resident by construction: a cooperative launch of one CTA per SM fails rather than run partially
+        void* args[] = {&counter, &iters, &status};
+        MMF_CUDA(cudaEventRecord(e0));
+        MMF_CUDA(cudaLaunchCooperativeKernel((void*)grid_barrier_probe_kernel, dim3(sms), dim3(256), args, 0, 0));
+        MMF_CUDA(cudaEventRecord(e1));
+        MMF_CUDA(cudaEventSynchronize(e1));
+        MMF_CUDA(cudaEventElapsedTime(&ms, e0, e1));
+        *barrier_us_host = ms * 1e3 / iters;
+    }
+    {
+        void* args[] = {&f0, &f1, &iters, &status};
+        MMF_CUDA(cudaEventRecord(e0));
+        MMF_CUDA(cudaLaunchCooperativeKernel((void*)signal_probe_kernel, dim3(2), dim3(32), args, 0, 0));
+        MMF_CUDA(cudaEventRecord(e1));
+        MMF_CUDA(cudaEventSynchronize(e1));
+        MMF_CUDA(cudaEventElapsedTime(&ms, e0, e1));
+        *signal_us_host = ms * 1e3 / iters / 2;
+    }
+    cudaEventDestroy(e0);
+    cudaEventDestroy(e1);
+    int st = 0;
+    MMF_CUDA(cudaMemcpy(&st, status, sizeof(int), cudaMemcpyDeviceToHost));
+    MMF_REQUIRE(st == 0, MMF_ERR_TIMEOUT, "mmf_sync_probe: a bounded wait gave up (status %d)", st);
+    return MMF_OK;
+}

@@ -93,8 +93,8 @@ def absmean(w: torch.Tensor) -> torch.Tensor:
 
 
 def ensure_slabs(pw: PackedWeight) -> PackedWeight:
-    """Attach the slab-major copy of the packed codes that the decode kernel streams (one contiguous piece per 16
-    output rows).  Doubles the weight's device memory (2 x 0.25 byte per weight); made once, when the weight is packed."""
+    """Attach the slab-major copy of the packed codes that the mma.sync decode experiment streams (one contiguous piece per
+    16 output rows).  Only available inside `_lib.experiments_library()`; made on first use."""
     if pw.slabs is None or pw.slabs.device != pw.packed.device:
         _need_cuda(pw.packed)
         slabs = torch.empty_like(pw.packed)
@@ -119,7 +119,7 @@ def pack_weight(w: torch.Tensor) -> PackedWeight:
     nbytes = _lib.load().mmf_packed_bytes(N, K)
     packed = torch.empty(nbytes, dtype=torch.uint8, device=w.device)
     _lib.call("mmf_pack_ternary", w.data_ptr(), N, K, mean.data_ptr(), packed.data_ptr(), _stream())
-    return ensure_slabs(PackedWeight(packed, mean, N, K, 1))
+    return PackedWeight(packed, mean, N, K, 1)
 
 
 def stack_packed(parts: Sequence[PackedWeight]) -> PackedWeight:
@@ -131,9 +131,9 @@ def stack_packed(parts: Sequence[PackedWeight]) -> PackedWeight:
             raise ValueError("grouped BitLinears need identical [N,K]")
     if n % TILE_ROWS:
         raise ValueError(f"grouped BitLinears need out_features % {TILE_ROWS} == 0")
-    # both layouts are tile-major at the top level, so stacking along N is concatenation
+    # the layout is tile-major at the top level, so stacking along N is concatenation
     return PackedWeight(torch.cat([p.packed for p in parts]), torch.cat([p.scale for p in parts]), n * len(parts), K,
-                        len(parts), torch.cat([ensure_slabs(p).slabs for p in parts]))
+                        len(parts))
 
 
 def unpack_codes(pw: PackedWeight) -> torch.Tensor:
@@ -238,13 +238,9 @@ def bitlinear(q: torch.Tensor, dq: torch.Tensor, rowsum: torch.Tensor, pw: Packe
     if nbytes is None:
         nbytes = _ws_bytes[(M, pw.N, pw.K)] = _lib.load().mmf_bitlinear_workspace_bytes(M, pw.N, pw.K)
     ws = _workspace(q.device, nbytes)
-    # decode-sized calls take the decode kernel (persistent CTAs, resident codes, slab-major weight stream)
-    decode = kernel == KERNEL_STREAM or (kernel == KERNEL_AUTO and M <= _lib.STREAM_MAX_M and pw.slabs is not None
-                                         and _decode_fits(M, pw.K))
     try:
-        if decode:
-            if pw.slabs is None:
-                raise ValueError("this PackedWeight has no slab-major copy (kernels.ensure_slabs)")
+        if kernel == KERNEL_STREAM:       # the mma.sync decode experiment: exists in the experiments build only
+            ensure_slabs(pw)
             _lib.call("mmf_bitlinear_decode", q.data_ptr(), dq.data_ptr(), rowsum.data_ptr(), pw.slabs.data_ptr(),
                       pw.scale.data_ptr(), G, out.data_ptr(), _code(out_dtype), out.stride(0), _ptr(acc), M, pw.N, pw.K,
                       ws.data_ptr(), _stream())
@@ -256,16 +252,6 @@ def bitlinear(q: torch.Tensor, dq: torch.Tensor, rowsum: torch.Tensor, pw: Packe
         _rezero_workspaces()  # a failed launch may have left partial sums behind
         raise
     return (out, acc) if return_acc else out
-
-
-_decode_fit_cache: dict = {}
-
-
-def _decode_fits(M: int, K: int) -> bool:
-    r = _decode_fit_cache.get((M, K))
-    if r is None:
-        r = _decode_fit_cache[(M, K)] = bool(_lib.load().mmf_bitlinear_decode_fits(M, K))
-    return r
 
 
 # ------------------------------------------------------------------------------------------
@@ -535,3 +521,14 @@ def int8_mma_peak_tops(n_tokens: int = 256, iters: int = 200000) -> float:
     torch.cuda.synchronize()
     _lib.call("mmf_int8_mma_peak", n_tokens, iters, status.data_ptr(), ctypes.addressof(tops))
     return tops.value
+
+
+def sync_probe(iters: int = 2000):
+    """(grid-barrier microseconds, one-way signal microseconds) of the current GPU: what one grid-wide barrier among one
+    resident CTA per SM costs, and what handing a flag from one CTA to another costs.  Synchronises."""
+    scratch = torch.zeros(256, dtype=torch.int32, device="cuda")
+    _lib.require_device(torch.cuda.current_device())
+    barrier, signal = ctypes.c_double(0.0), ctypes.c_double(0.0)
+    torch.cuda.synchronize()
+    _lib.call("mmf_sync_probe", iters, scratch.data_ptr(), ctypes.addressof(barrier), ctypes.addressof(signal))
+    return barrier.value, signal.value

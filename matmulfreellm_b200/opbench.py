@@ -4,6 +4,7 @@
     python -m matmulfreellm_b200.opbench hgrn --B 8 --T 2048 --D 2048 [--gate log|linear]
     python -m matmulfreellm_b200.opbench rowwise --M 4096 --D 2048
     python -m matmulfreellm_b200.opbench int8peak
+    python -m matmulfreellm_b200.opbench sync           (grid-wide barrier and CTA-to-CTA signal cost)
     python -m matmulfreellm_b200.opbench prefill --batch 16 --seq 2048 --layers 2
     python -m matmulfreellm_b200.opbench sweep          (the BitLinear op sweep: 5 token counts x 4 layer shapes)
 
@@ -105,6 +106,13 @@ def rowwise(a):
                       "gb_per_s": nbytes / t / 1e9}))
 
 
+def sync(a):
+    barrier, signal = K.sync_probe(2000)
+    print(json.dumps({"op": "sync", "grid_barrier_us": barrier, "cta_to_cta_signal_us": signal,
+                      "what": "one barrier among one resident CTA per SM (release add + acquire poll on one counter); one "
+                              "release store -> acquire poll hand-over between two CTAs"}))
+
+
 def int8peak(a):
     """Bare tcgen05.mma kind::i8 issue loop with pseudo-random operands: a burst of about 7 ms (the GPU holds its
     maximum clock) and a loop of about 3 s (the clock settles under the power cap)."""
@@ -173,12 +181,13 @@ def main():
     r = sub.add_parser("rowwise")
     r.add_argument("--M", type=int, default=4096); r.add_argument("--D", type=int, default=2048); r.add_argument("--iters", type=int, default=10)
     sub.add_parser("int8peak")
+    sub.add_parser("sync")
     sub.add_parser("sweep")
     pf = sub.add_parser("prefill")
     pf.add_argument("--batch", type=int, default=16); pf.add_argument("--seq", type=int, default=2048)
     pf.add_argument("--layers", type=int, default=2); pf.add_argument("--iters", type=int, default=2)
     a = ap.parse_args()
-    {"bitlinear": bitlinear, "hgrn": hgrn, "rowwise": rowwise, "int8peak": int8peak, "prefill": prefill, "sweep": sweep}[a.op](a)
+    {"bitlinear": bitlinear, "hgrn": hgrn, "rowwise": rowwise, "int8peak": int8peak, "sync": sync, "prefill": prefill, "sweep": sweep}[a.op](a)
 
 
 if __name__ == "__main__":

@@ -37,10 +37,6 @@ def test_pack_ternary_bit_exact(K, N, Kdim):
     got = pw.packed.cpu().numpy().view(np.uint32)
     assert np.array_equal(got, O.pack_ternary(codes))
     assert np.array_equal(K.unpack_codes(pw).cpu().numpy(), codes)
-    # the decode kernel's copy: the same 16-byte pieces, slab-major ([tile][slab of 16 rows][chunk][row][16 B])
-    tiles, KC = -(-N // 128), Kdim // 64
-    want = got.reshape(tiles, KC, 8, 16, 4).transpose(0, 2, 1, 3, 4).reshape(-1)
-    assert np.array_equal(pw.slabs.cpu().numpy().view(np.uint32), want)
 
 
 def test_pack_ternary_edge_values(K):
@@ -163,25 +159,31 @@ STREAM_CASES = [(1, 256, 128), (1, 2048, 2048), (2, 704, 256), (4, 5632, 2048), 
 
 @pytest.mark.parametrize("M,Kdim,N", STREAM_CASES)
 def test_bitlinear_stream_bit_exact(K, M, Kdim, N):
-    """The decode kernel (persistent CTAs, resident codes, mma.sync per 16 rows x 8 tokens): every token-tile count
-    1..8, a ragged last slab (N = 200), K with a trailing chunk group (704 = 11 chunks), and problems whose codes do
-    not fit in shared memory at once (32 x 6912, 64 x 5632: run as two launches over token blocks)."""
-    _bitlinear_check(K, M, Kdim, N, K.KERNEL_STREAM)
+    """The mma.sync decode experiment (persistent CTAs, resident codes, 16 rows x 8 tokens per MMA; experiments build
+    only): every token-tile count 1..8, a ragged last slab (N = 200), K with a trailing chunk group (704 = 11 chunks),
+    and problems whose codes do not fit in shared memory at once (32 x 6912, 64 x 5632: two launches over token blocks)."""
+    from matmulfreellm_b200 import _lib
+    with _lib.experiments_library():
+        _bitlinear_check(K, M, Kdim, N, K.KERNEL_STREAM)
 
 
-def test_bitlinear_stream_is_the_default_for_decode_batches(K):
-    """AUTO takes the decode kernel up to 64 token rows: identical accumulators and outputs to the forced selection, and
-    strided output rows (ld_out > N) are honoured."""
+def test_bitlinear_stream_layout_and_strided_output(K):
+    """Slab-major copy of the packed codes, and strided output rows (ld_out > N), in the experiments build."""
+    from matmulfreellm_b200 import _lib
     x, w, _ = O.bitlinear_case(32, 2048, 384, seed=5)
     pw = K.pack_weight(dev(w))
     q, dq, rs = K.act_quant(dev(x), None, 1e-6)
     a, acc_a = K.bitlinear(q, dq, rs, pw, torch.bfloat16, return_acc=True)
-    b, acc_b = K.bitlinear(q, dq, rs, pw, torch.bfloat16, kernel=K.KERNEL_STREAM, return_acc=True)
-    c, acc_c = K.bitlinear(q, dq, rs, pw, torch.bfloat16, kernel=K.KERNEL_MMA, return_acc=True)
-    assert torch.equal(a, b) and torch.equal(acc_a, acc_b) and torch.equal(a, c) and torch.equal(acc_a, acc_c)
-    wide = torch.zeros(32, 512, dtype=torch.bfloat16, device="cuda")
-    K.bitlinear(q, dq, rs, pw, torch.bfloat16, kernel=K.KERNEL_STREAM, out=wide[:, 64:448])
+    with _lib.experiments_library():
+        b, acc_b = K.bitlinear(q, dq, rs, pw, torch.bfloat16, kernel=K.KERNEL_STREAM, return_acc=True)
+        wide = torch.zeros(32, 512, dtype=torch.bfloat16, device="cuda")
+        K.bitlinear(q, dq, rs, pw, torch.bfloat16, kernel=K.KERNEL_STREAM, out=wide[:, 64:448])
+    assert torch.equal(a, b) and torch.equal(acc_a, acc_b)
     assert torch.equal(wide[:, 64:448], a) and int(wide[:, :64].abs().sum()) == 0 and int(wide[:, 448:].abs().sum()) == 0
+    # the same 16-byte pieces, slab-major ([tile][slab of 16 rows][chunk][row][16 B])
+    got = pw.packed.cpu().numpy().view(np.uint32)
+    want = got.reshape(3, 32, 8, 16, 4).transpose(0, 2, 1, 3, 4).reshape(-1)
+    assert np.array_equal(pw.slabs.cpu().numpy().view(np.uint32), want)
     K.check_status()
 
 
@@ -196,8 +198,11 @@ def test_bitlinear_grouped(K, M):
     pw = K.stack_packed([K.pack_weight(dev(w)) for w in ws])
     qs = [K.act_quant(dev(x), dev(nw), 1e-6) for nw in nws]
     q = torch.cat([t[0] for t in qs]); dq = torch.cat([t[1] for t in qs]); rs = torch.cat([t[2] for t in qs])
-    for kernel in (K.KERNEL_AUTO, K.KERNEL_STREAM, K.KERNEL_GEMV, K.KERNEL_MMA):
-        out = K.bitlinear(q, dq, rs, pw, torch.float32, kernel=kernel)
+    from matmulfreellm_b200 import _lib
+    outs = {kernel: K.bitlinear(q, dq, rs, pw, torch.float32, kernel=kernel) for kernel in (K.KERNEL_AUTO, K.KERNEL_GEMV, K.KERNEL_MMA)}
+    with _lib.experiments_library():
+        outs[K.KERNEL_STREAM] = K.bitlinear(q, dq, rs, pw, torch.float32, kernel=K.KERNEL_STREAM)
+    for kernel, out in outs.items():
         for gi in range(3):
             codes, mean = O.ternary_codes(ws[gi])
             ref = O.bitlinear_int(x, nws[gi], codes, mean, 1e-6)[0]
