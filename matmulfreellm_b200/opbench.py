@@ -5,6 +5,8 @@
     python -m matmulfreellm_b200.opbench rowwise --M 4096 --D 2048
     python -m matmulfreellm_b200.opbench int8peak
     python -m matmulfreellm_b200.opbench sync           (grid-wide barrier and CTA-to-CTA signal cost)
+    python -m matmulfreellm_b200.opbench chain --M 32   (the BitLinear launches of one decode step as a dependent chain)
+    python -m matmulfreellm_b200.opbench timeline --batch 32   (experiments build: where a decode step's kernels spend time)
     python -m matmulfreellm_b200.opbench prefill --batch 16 --seq 2048 --layers 2
     python -m matmulfreellm_b200.opbench sweep          (the BitLinear op sweep: 5 token counts x 4 layer shapes)
 
@@ -113,6 +115,87 @@ def sync(a):
                               "release store -> acquire poll hand-over between two CTAs"}))
 
 
+def _model(layers):
+    from .models import HGRNBitConfig, HGRNBitForCausalLM
+    from .ops.fusedbitnet import BitLinear
+    dev = torch.device("cuda")
+    cfg = HGRNBitConfig(vocab_size=32000, hidden_size=2048, num_hidden_layers=layers, intermediate_size=5632)
+    with torch.device(dev):
+        model = HGRNBitForCausalLM(cfg).eval()
+    g = torch.Generator(device=dev).manual_seed(1234)
+    with torch.no_grad():
+        for m in model.modules():
+            if isinstance(m, BitLinear):
+                m.weight.normal_(0.0, 0.02, generator=g)
+        model.model.embeddings.weight.normal_(0.0, 0.02, generator=g)
+    model.pack_weights()
+    return model.to(torch.bfloat16)
+
+
+def chain(a):
+    """The 97 BitLinear contractions of one HGRNBit-1.3B decode step (pre-quantised inputs, nothing else) replayed from
+    a CUDA graph as a dependent chain, per kernel: the tcgen05 kernel, the dp4a GEMV, and (experiments build) the
+    mma.sync decode experiment."""
+    from . import _lib, engine
+    model = _model(24)
+    orig = K.bitlinear
+    out = {"op": "chain", "M": a.M, "launches": 97}
+
+    def run(kernel):
+        def forced(q, dq, rs, pw, dt, kernel_=None, return_acc=False, out=None, **kw):
+            return orig(q, dq, rs, pw, dt, kernel=kernel, return_acc=return_acc, out=out)
+        K.bitlinear = forced
+        try:
+            probe = engine.WeightStreamProbe(model, a.M, torch.bfloat16)
+            t = _time(probe.run, a.iters)
+            return {"us_per_launch": t * 1e6 / probe.launches, "weight_gb_per_s": probe.packed_bytes / t / 1e9}
+        finally:
+            K.bitlinear = orig
+
+    out["tcgen05"] = run(K.KERNEL_MMA)
+    out["gemv_dp4a"] = run(K.KERNEL_GEMV)
+    with _lib.experiments_library():
+        out["mma_sync_experiment"] = run(K.KERNEL_STREAM)
+    print(json.dumps(out))
+
+
+def timeline(a):
+    """Experiments build: global-timer stamps of CTA 0 of every prenorm_quant launch of one decode step (replayed from
+    a CUDA graph): how long after the grid dependency resolves the row is loaded, reduced, normalised and quantised, and
+    how far apart consecutive launches of the chain are."""
+    from . import _lib
+    from .engine import GreedyDecoder
+    with _lib.experiments_library() as lib:
+        model = _model(a.layers)
+        buf = torch.zeros(8 + 8 * 1000, dtype=torch.int64, device="cuda")
+        lib.mmf_row_trace(buf.data_ptr())          # before the capture: the pointer is baked into the graph
+        try:
+            dec = GreedyDecoder(model, a.batch)
+            dec.prefill(torch.randint(0, 32000, (a.batch, 8), device="cuda"))
+            for _ in range(3):
+                dec.step()
+            torch.cuda.synchronize()
+            buf.zero_()
+            torch.cuda.synchronize()
+            dec.step()
+            torch.cuda.synchronize()
+        finally:
+            lib.mmf_row_trace(None)
+        n = int(buf.view(torch.int32)[0].item())
+        rec = buf[8:8 + 8 * n].view(n, 8).cpu()
+        rows = []
+        for i in range(n):
+            r = [int(x - rec[i, 2]) for x in rec[i].tolist()]
+            rows.append({"start_before_release_ns": -r[0], "row_loaded_ns": r[3], "first_sum_ns": r[4], "second_norm_ns": r[5],
+                         "codes_written_ns": r[6], "end_ns": r[7],
+                         "since_previous_release_ns": int(rec[i, 2] - rec[i - 1, 2]) if i else None})
+        med = lambda key: sorted(x[key] for x in rows[1:])[len(rows[1:]) // 2]
+        print(json.dumps({"op": "timeline", "batch": a.batch, "layers": a.layers, "prenorm_quant_launches": n,
+                          "median_ns_after_release": {k: med(k) for k in ("row_loaded_ns", "first_sum_ns", "second_norm_ns",
+                                                                            "codes_written_ns", "end_ns")},
+                          "median_ns_between_prenorm_releases": med("since_previous_release_ns"), "first_launches": rows[:5]}))
+
+
 def int8peak(a):
     """Bare tcgen05.mma kind::i8 issue loop with pseudo-random operands: a burst of about 7 ms (the GPU holds its
     maximum clock) and a loop of about 3 s (the clock settles under the power cap)."""
@@ -125,20 +208,9 @@ def int8peak(a):
 def prefill(a):
     """Prompt pass of a random-init HGRNBit with the 1.3B layer shapes (hidden 2048, intermediate 5632, vocab 32000) and
     `--layers` blocks through the fused chain; last-position logits only."""
-    from .models import HGRNBitConfig, HGRNBitForCausalLM
-    from .ops.fusedbitnet import BitLinear
     dev = torch.device("cuda")
-    cfg = HGRNBitConfig(vocab_size=32000, hidden_size=2048, num_hidden_layers=a.layers, intermediate_size=5632)
-    with torch.device(dev):
-        model = HGRNBitForCausalLM(cfg).eval()
-    g = torch.Generator(device=dev).manual_seed(1234)
-    with torch.no_grad():
-        for m in model.modules():
-            if isinstance(m, BitLinear):
-                m.weight.normal_(0.0, 0.02, generator=g)
-        model.model.embeddings.weight.normal_(0.0, 0.02, generator=g)
-    model.pack_weights()
-    model = model.to(torch.bfloat16)
+    model = _model(a.layers)
+    g = torch.Generator(device=dev).manual_seed(99)
     ids = torch.randint(0, 32000, (a.batch, a.seq), device=dev, generator=g)
     with torch.no_grad():
         t = _time(lambda: model(input_ids=ids, use_cache=True, last_token_only=True), a.iters)
@@ -182,12 +254,16 @@ def main():
     r.add_argument("--M", type=int, default=4096); r.add_argument("--D", type=int, default=2048); r.add_argument("--iters", type=int, default=10)
     sub.add_parser("int8peak")
     sub.add_parser("sync")
+    ch = sub.add_parser("chain")
+    ch.add_argument("--M", type=int, default=32); ch.add_argument("--iters", type=int, default=20)
+    tl = sub.add_parser("timeline")
+    tl.add_argument("--batch", type=int, default=32); tl.add_argument("--layers", type=int, default=4)
     sub.add_parser("sweep")
     pf = sub.add_parser("prefill")
     pf.add_argument("--batch", type=int, default=16); pf.add_argument("--seq", type=int, default=2048)
     pf.add_argument("--layers", type=int, default=2); pf.add_argument("--iters", type=int, default=2)
     a = ap.parse_args()
-    {"bitlinear": bitlinear, "hgrn": hgrn, "rowwise": rowwise, "int8peak": int8peak, "sync": sync, "prefill": prefill, "sweep": sweep}[a.op](a)
+    {"bitlinear": bitlinear, "hgrn": hgrn, "rowwise": rowwise, "int8peak": int8peak, "sync": sync, "chain": chain, "timeline": timeline, "prefill": prefill, "sweep": sweep}[a.op](a)
 
 
 if __name__ == "__main__":
