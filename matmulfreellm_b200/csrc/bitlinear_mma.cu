@@ -160,10 +160,16 @@ bitlinear_mma_kernel(const __grid_constant__ CUtensorMap q_map, BitLinearArgs a,
     const int warp = tid >> 5, lane = tid & 31;
     const int ks = blockIdx.x, tile = blockIdx.y * p.wt, mt = blockIdx.z;
     const int ntile = min(p.wt, p.n_tiles - tile);   // weight tiles this CTA owns (2 = dual-tile mode for large M)
-    long long* const trace = MMF_TRACE_PTR((tid == 0 && a.ws && a.ws[1] == MMF_TRACE_MAGIC && (blockIdx.x | blockIdx.y | blockIdx.z) == 0)
-                                               ? reinterpret_cast<long long*>(a.ws + 8) : nullptr);
+#ifdef MMF_EXPERIMENTS
+    __shared__ long long* s_trace;
+    if (tid == 0) s_trace = (a.ws && a.ws[1] == MMF_TRACE_MAGIC && (blockIdx.x | blockIdx.y | blockIdx.z) == 0) ? trace_record(a.ws) : nullptr;
+    long long* const trace = tid == 0 ? s_trace : nullptr;
+#else
+    long long* const trace = nullptr;
+#endif
     trace_mark(trace, 0);
     pdl_trigger();   // the next kernel may start its own prologue (and weight stream) right away
+    if (tid == WARP_B * 32) tma_prefetch_map(&q_map);   // descriptor ready before the dependency wait ends
     const int g = tile / p.group_tiles;
     const int m0 = mt * p.NT;
     const int stage0 = ks * p.stages_per_cta;
@@ -238,8 +244,11 @@ bitlinear_mma_kernel(const __grid_constant__ CUtensorMap q_map, BitLinearArgs a,
             const uint32_t nacc = (uint32_t)p.nacc, NTc = (uint32_t)p.NT;
             bool live = true;
             int i = 0;
-            long long* const mtrace = MMF_TRACE_PTR((a.ws && a.ws[1] == MMF_TRACE_MAGIC && (blockIdx.x | blockIdx.y | blockIdx.z) == 0)
-                                                        ? reinterpret_cast<long long*>(a.ws + 8) : nullptr);
+#ifdef MMF_EXPERIMENTS
+            long long* const mtrace = s_trace;     // written before the __syncthreads above
+#else
+            long long* const mtrace = nullptr;
+#endif
             if (p.wt == 1 && (nacc == 1 || nacc == 2 || nacc == 4)) {
                 // lean path (one weight tile, whole 128-K stages): the issuing thread is a serial instruction
                 // stream, so every instruction here costs tensor-pipe time.  MMA k of a stage goes to accumulator
@@ -253,7 +262,7 @@ bitlinear_mma_kernel(const __grid_constant__ CUtensorMap q_map, BitLinearArgs a,
                     if (!p.merged && !mbar_wait(&bars[BAR_B_FULL + bq.slot], bq.ph, abort_flag)) { live = false; break; }
                     if (!mbar_wait(&bars[BAR_A_FULL + aq.slot], aq.ph, abort_flag)) { live = false; break; }
                     tc_fence_after();
-                    if (mtrace && i < 10) mtrace[8 + i] = clock64();
+                    if (mtrace && i < 8) mtrace[8 + i] = trace_now();
                     uint32_t a_addr = tmem_a + aq.slot * 32;
                     uint32_t b_lo = b_lo0 + (uint32_t)bq.slot * b_desc_step;
                     asm volatile(
@@ -338,7 +347,7 @@ bitlinear_mma_kernel(const __grid_constant__ CUtensorMap q_map, BitLinearArgs a,
             wv[0] = *reinterpret_cast<const uint4*>(wsrc);
             wv[1] = nch > 1 ? *reinterpret_cast<const uint4*>(wsrc + MMF_TILE_ROWS * 16) : wv[0];
             mbar_arrive(&bars[BAR_W_EMPTY + ws]);             // the packed bytes are in registers now
-            if (trace && i < 10) trace[18 + i] = clock64();
+            if (trace && i < 6) trace[16 + i] = trace_now();
             ok = __all_sync(0xffffffffu, mbar_wait(&bars[BAR_A_EMPTY + as], aq.ph ^ 1, abort_flag));
             if (!ok) break;   // uniform per warp: the .sync.aligned tcgen05 ops below need the whole warp
 #pragma unroll
@@ -356,7 +365,7 @@ bitlinear_mma_kernel(const __grid_constant__ CUtensorMap q_map, BitLinearArgs a,
             tmem_wait_st();
             tc_fence_before();
             mbar_arrive(&bars[BAR_A_FULL + as]);
-            if (trace && i < 10) trace[19 + i] = clock64();
+            if (trace && i < 6) trace[22 + i] = trace_now();
             if (dual) { w.next(); aq.next(); } else { w.next2(); aq.next2(); }
         }
         trace_mark(trace, 3);

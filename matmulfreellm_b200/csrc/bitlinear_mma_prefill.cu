@@ -132,6 +132,7 @@ bitlinear_mma_prefill_kernel(const __grid_constant__ CUtensorMap q_map, const __
     const int tid = threadIdx.x;
     const int warp = tid >> 5, lane = tid & 31;
     pdl_trigger();
+    if (threadIdx.x == 0) { tma_prefetch_map(&q_map); tma_prefetch_map(&out_map); }
 
     if (tid < C::BAR_COUNT) mbar_init(&bars[tid], C::bar_count(tid));
     if (tid == C::BAR_COUNT) s_abort = 0;

@@ -214,7 +214,11 @@ __device__ __forceinline__ int block_sum(int v, int* red) {
 // a single IEEE round-to-nearest fp32 operation, never contracted into an fma.
 // ---------------------------------------------------------------------------------------
 __device__ __forceinline__ float rstd_from_sumsq(double sumsq, int64_t K, float eps) {
-    const float mean = (float)(sumsq / (double)K);
+    // K a power of two (2048, 4096 ...): scaling by 2^-n is the exact quotient, without the ~100-instruction fp64 division
+    // that otherwise sits on the critical path of every row kernel of a decode step
+    const double q = (K & (K - 1)) == 0 ? sumsq * __longlong_as_double((1023ll - (long long)(__ffsll((long long)K) - 1)) << 52)
+                                        : sumsq / (double)K;
+    const float mean = (float)q;
     return __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(mean, eps)));
 }
 // e^-x and the reciprocal through the special-function unit (ex2.approx, rcp.approx: relative error about 2^-22 each).

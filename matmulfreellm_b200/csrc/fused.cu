@@ -226,6 +226,8 @@ struct PrenormArgs {
     int8_t* q; float* dq; int32_t* rowsum; // [G][M][D], [G][M], [G][M]
     int64_t M; int D; int G;
     int round_sum_first;                   // 1: the reference added x+residual as a tensor op (rounded to T) before norm
+    int gsplit;                            // 1: grid.y = G CTAs per row, CTA y does projection y alone (decode-sized calls: the G
+                                           //    prologues of a row run side by side instead of one after the other)
 #ifdef MMF_EXPERIMENTS
     long long* trace;                      // experiments build: 8 global-timer stamps of CTA 0 per launch (see mmf_row_trace)
 #endif
@@ -251,15 +253,17 @@ prenorm_quant_kernel(PrenormArgs a) {
     const int D = a.D;
 #ifdef MMF_EXPERIMENTS
     long long* trace = nullptr;
-    if (threadIdx.x == 0 && blockIdx.x == 0 && a.trace) {
+    if (threadIdx.x == 0 && blockIdx.x == 0 && blockIdx.y == 0 && a.trace) {
         const int idx = atomicAdd(reinterpret_cast<int*>(a.trace), 1);
         if (idx < 1000) trace = a.trace + 8 + 8 * idx;
     }
 #endif
     ROW_TRACE(0);
     pdl_trigger();
+    const int gy = a.gsplit ? blockIdx.y : 0;          // projection of this CTA when the projections are split over CTAs
+    const int Gs = a.gsplit ? 1 : a.G;                 // projections this CTA quantises
     stage_weights(sw, a.norm_w, D);
-    for (int g = 0; g < a.G; ++g) stage_weights(sw + (1 + g) * D, a.nws[g], D);
+    for (int g = 0; g < Gs; ++g) stage_weights(sw + (1 + g) * D, a.nws[gy + g], D);
     ROW_TRACE(1);
     pdl_wait();
     ROW_TRACE(2);
@@ -267,7 +271,7 @@ prenorm_quant_kernel(PrenormArgs a) {
 
     // Row loop (LAT = 0): the CTA's next row travels global -> shared memory by cp.async while the current one is
     // processed (thread-private 16-byte slots: no barrier, only the thread's own wait)
-    T* sx = reinterpret_cast<T*>(sw + (1 + a.G) * D);   // [D] x row, [D] residual row (LAT = 0 only)
+    T* sx = reinterpret_cast<T*>(sw + (1 + Gs) * D);   // [D] x row, [D] residual row (LAT = 0 only)
     T* sr = sx + D;
     auto fetch = [&](int64_t row) {
         ROW_FOREACH(V, D, it, c) {
@@ -282,7 +286,7 @@ prenorm_quant_kernel(PrenormArgs a) {
         const T* xr = LAT == 0 ? sx : reinterpret_cast<const T*>(a.x) + m * a.ld_x;
         const T* rr = a.res ? (LAT == 0 ? sr : reinterpret_cast<const T*>(a.res) + m * a.ld_res) : nullptr;
         if (LAT == 0) cp_async_wait_all();
-        T* ro = a.res_out ? reinterpret_cast<T*>(a.res_out) + m * (int64_t)D : nullptr;
+        T* ro = (a.res_out && gy == 0) ? reinterpret_cast<T*>(a.res_out) + m * (int64_t)D : nullptr;
         float v[P];
         double ss[1] = {0.0};
         ROW_FOREACH(V, D, it, c) {
@@ -321,7 +325,7 @@ prenorm_quant_kernel(PrenormArgs a) {
         block_sum_d<1>(ss, red.d0);
         ROW_TRACE(4);
         const float rstd1 = rstd_from_sumsq(ss[0], D, a.eps_norm);
-        T* yo = a.y_out ? reinterpret_cast<T*>(a.y_out) + m * (int64_t)D : nullptr;
+        T* yo = (a.y_out && gy == 0) ? reinterpret_cast<T*>(a.y_out) + m * (int64_t)D : nullptr;
         double ss2 = 0.0;
         ROW_FOREACH(V, D, it, c) {
             float o[V], w[V];
@@ -343,7 +347,10 @@ prenorm_quant_kernel(PrenormArgs a) {
             if (yo) store_rounded<T, V>(yo + c, o, bits);
         }
         ROW_TRACE(5);
-        if (a.G == 3) bitlinear_prologue<V, 3, P>(v, D, ss2, a.eps_bl, sw + D, a.q, a.dq, a.rowsum, a.M, m, red);
+        if (a.gsplit)
+            bitlinear_prologue<V, 1, P>(v, D, ss2, a.eps_bl, sw + D, a.q + (int64_t)gy * a.M * D, a.dq + (int64_t)gy * a.M,
+                                        a.rowsum + (int64_t)gy * a.M, a.M, m, red);
+        else if (a.G == 3) bitlinear_prologue<V, 3, P>(v, D, ss2, a.eps_bl, sw + D, a.q, a.dq, a.rowsum, a.M, m, red);
         else if (a.G == 1) bitlinear_prologue<V, 1, P>(v, D, ss2, a.eps_bl, sw + D, a.q, a.dq, a.rowsum, a.M, m, red);
         ROW_TRACE(6);
     }
@@ -627,14 +634,19 @@ extern "C" int mmf_prenorm_quant(const void* x, int64_t ld_x, const void* residu
     a.x = x; a.ld_x = ld_x; a.res = residual; a.ld_res = ld_res; a.res_out = residual_out; a.y_out = y_out;
     a.norm_w = norm_w; a.eps_norm = eps_norm; a.nws[0] = nw0; a.nws[1] = nw1; a.nws[2] = nw2; a.eps_bl = eps_bl;
     a.q = q; a.dq = dq; a.rowsum = rowsum; a.M = M; a.D = (int)D; a.G = groups; a.round_sum_first = round_sum_first;
+    // decode-sized call with three projections: one CTA per (row, projection).  The shared statistics are recomputed
+    // by each of the three CTAs (same loads, same operations, same results), the three quantisation passes run side by
+    // side: measured 1.5 us -> 0.8 us of prologue after the grid dependency resolves
+    a.gsplit = groups == 3 && M <= 128 ? 1 : 0;
 #ifdef MMF_EXPERIMENTS
     a.trace = g_row_trace;
 #endif
     MMF_DISPATCH(dtype, T, {
         FUSED_DISPATCH_P(D, P, { FUSED_DISPATCH_LAT(M, LAT, {
-            const size_t smem = (size_t)(1 + groups) * D * sizeof(float) + (LAT ? 0 : (size_t)2 * D * sizeof(T));   // + row staging
+            const size_t smem = (size_t)(1 + (a.gsplit ? 1 : groups)) * D * sizeof(float) + (LAT ? 0 : (size_t)2 * D * sizeof(T));   // + row staging
             FUSED_SMEM_ATTR((prenorm_quant_kernel<T, P, LAT>), smem);
-            MMF_CUDA(mmf_launch_pdl(prenorm_quant_kernel<T, P, LAT>, dim3(row_grid(prenorm_quant_kernel<T, P, LAT>, smem, M)), dim3(FT), smem, (cudaStream_t)stream, a));
+            const dim3 grid(a.gsplit ? (unsigned)M : row_grid(prenorm_quant_kernel<T, P, LAT>, smem, M), a.gsplit ? 3u : 1u);
+            MMF_CUDA(mmf_launch_pdl(prenorm_quant_kernel<T, P, LAT>, grid, dim3(FT), smem, (cudaStream_t)stream, a));
         }); });
     });
     MMF_LAUNCH_CHECK("prenorm_quant_kernel");

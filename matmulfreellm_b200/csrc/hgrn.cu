@@ -168,6 +168,11 @@ hgrn_scan_kernel(const __grid_constant__ CUtensorMap x_map, const __grid_constan
                  const void* __restrict__ h0, void* __restrict__ ht, int state_dt, int T, int D, int NT, int chunk_len,
                  HgrnWs ws) {
     pdl_trigger();
+    if (threadIdx.x == 0) {   // descriptors into the descriptor cache before the dependency wait ends
+        asm volatile("prefetch.tensormap [%0];" ::"l"(&x_map) : "memory");
+        asm volatile("prefetch.tensormap [%0];" ::"l"(&g_map) : "memory");
+        asm volatile("prefetch.tensormap [%0];" ::"l"(&o_map) : "memory");
+    }
     extern __shared__ uint8_t smem_dyn[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_dyn) + 127) & ~uintptr_t(127));
     constexpr int XB = HG_TS * HG_BD * sizeof(TX);  // bytes of one x stage (= one output tile)

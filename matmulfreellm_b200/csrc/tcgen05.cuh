@@ -102,6 +102,11 @@ __device__ __forceinline__ bool elect_one() {
     return pred != 0;
 }
 
+// Fetch a tensor map into the descriptor cache ahead of its first use: the first TMA copy of a kernel otherwise pays
+// for the 128-byte descriptor read from the kernel's parameter space on its critical path (after the grid-dependency wait)
+__device__ __forceinline__ void tma_prefetch_map(const CUtensorMap* map) {
+    asm volatile("prefetch.tensormap [%0];" ::"l"(map) : "memory");
+}
 __device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, uint64_t* bar, int x, int y) {
     asm volatile(
         "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
@@ -176,12 +181,23 @@ __device__ __forceinline__ void cluster_wait() { asm volatile("barrier.cluster.w
 #ifdef MMF_EXPERIMENTS
 constexpr int MMF_TRACE_MAGIC = 0x7ace;
 #define MMF_TRACE_PTR(...) (__VA_ARGS__)
+__device__ __forceinline__ long long trace_now() {
+    long long t;
+    asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));   // nanoseconds, comparable across SMs and launches
+    return t;
+}
 __device__ __forceinline__ void trace_mark(long long* trace, int slot) {
-    if (trace) trace[slot] = clock64();
+    if (trace) trace[slot] = trace_now();
+}
+// one record of 32 stamps per traced launch: word 2 of the workspace counts launches, records start at word 16
+__device__ __forceinline__ long long* trace_record(int32_t* ws) {
+    const int idx = atomicAdd(ws + 2, 1);
+    return idx < 2000 ? reinterpret_cast<long long*>(ws + 16) + 32 * idx : nullptr;
 }
 #else
 #define MMF_TRACE_PTR(...) (static_cast<long long*>(nullptr))
 __device__ __forceinline__ void trace_mark(long long*, int) {}
+__device__ __forceinline__ long long trace_now() { return 0; }   // only reached behind a null trace pointer
 #endif
 
 // K-major operand tile in shared memory, 128-byte swizzle: rows of 128 bytes, 8-row groups 1024 B apart.
