@@ -180,12 +180,15 @@ int mmf_bitlinear_gemv_static(const int8_t* q, const float* dq, const int32_t* r
  * double. */
 int mmf_int8_mma_peak(int n_tokens, int iters, int* status_dev, double* tops_host);
 
-/* Measurement aid (no counterpart in the reference): the two synchronisation costs that bound a chain of dependent
- * decode kernels on the current GPU, in microseconds.  barrier_us: one grid-wide barrier among one resident CTA per SM
- * (each CTA adds to a global counter with release semantics and polls it with acquire loads; cooperative launch, every
- * wait bounded).  signal_us: one hand-over of a flag between two CTAs (release store -> the other CTA's acquire poll
- * sees it).  scratch_dev: 256 device uints.  Runs on the default stream and SYNCHRONISES. */
-int mmf_sync_probe(int iters, unsigned* scratch_dev, double* barrier_us_host, double* signal_us_host);
+/* Measurement aid (no counterpart in the reference): the synchronisation costs that bound a chain of dependent decode
+ * kernels on the current GPU, in microseconds.  barrier_us: one grid-wide barrier among one resident CTA per SM (each
+ * CTA adds to a global counter with release semantics and polls it with acquire loads; cooperative launch, every wait
+ * bounded).  signal_us: one hand-over of a flag between two CTAs (release store -> the other CTA's acquire poll sees
+ * it).  chain_pdl_us / chain_plain_us: time per kernel of a chain of 200 dependent one-CTA-per-SM kernels replayed from
+ * a CUDA graph, launched with / without the programmatic-dependent-launch attribute.  scratch_dev: 256 device uints.
+ * Runs on streams of its own and SYNCHRONISES. */
+int mmf_sync_probe(int iters, unsigned* scratch_dev, double* barrier_us_host, double* signal_us_host,
+                   double* chain_pdl_us_host, double* chain_plain_us_host);
 
 /* ------------------------------------------------------------------------------------
  * HGRN recurrence  h_t = f_t * h_{t-1} + x_t  (element-wise, fp32 state).

@@ -41,7 +41,7 @@ PROTOTYPES = {
     "mmf_bitlinear_gemv_static": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int64,
                                           c_int64, c_int64, c_int64, c_void_p]),
     "mmf_int8_mma_peak": (c_int, [c_int, c_int, c_void_p, c_void_p]),
-    "mmf_sync_probe": (c_int, [c_int, c_void_p, c_void_p, c_void_p]),
+    "mmf_sync_probe": (c_int, [c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p]),
     "mmf_hgrn_workspace_bytes": (c_int64, [c_int64, c_int64, c_int64]),
     "mmf_hgrn_scan": (c_int, [c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_int, c_void_p, c_int64,
                               c_int64, c_int64, c_int, c_void_p, c_int64, c_void_p]),

@@ -183,10 +183,67 @@ __global__ void signal_probe_kernel(unsigned* f0, unsigned* f1, int iters, int* 
     }
 }
 
+// one link of a chain of dependent kernels: reads what its predecessor wrote, writes what its successor reads
+__global__ void chain_link_kernel(const unsigned* in, unsigned* out) {
+    pdl_trigger();
+    pdl_wait();
+    if (threadIdx.x == 0) out[blockIdx.x & 31] = in[blockIdx.x & 31] + 1u;
+}
+
+// microseconds per kernel of a chain of `n` dependent launches of `blocks` x `threads` replayed from a CUDA graph, with or
+// without the programmatic-dependent-launch attribute
+int chain_us(int n, int blocks, int threads, bool pdl, unsigned* a, unsigned* b, double* us) {
+    cudaStream_t st;
+    MMF_CUDA(cudaStreamCreateWithFlags(&st, cudaStreamNonBlocking));
+    cudaGraph_t graph = nullptr;
+    cudaGraphExec_t exec = nullptr;
+    MMF_CUDA(cudaStreamBeginCapture(st, cudaStreamCaptureModeThreadLocal));
+    for (int i = 0; i < n; ++i) {
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = dim3(blocks);
+        cfg.blockDim = dim3(threads);
+        cfg.stream = st;
+        cudaLaunchAttribute attr[1];
+        attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[0].val.programmaticStreamSerializationAllowed = 1;
+        cfg.attrs = attr;
+        cfg.numAttrs = pdl ? 1 : 0;
+        const cudaError_t e = cudaLaunchKernelEx(&cfg, chain_link_kernel, (const unsigned*)((i & 1) ? b : a), (i & 1) ? a : b);
+        if (e != cudaSuccess) {
+            cudaStreamEndCapture(st, &graph);
+            if (graph) cudaGraphDestroy(graph);
+            cudaStreamDestroy(st);
+            return mmf_set_error(MMF_ERR_CUDA, "mmf_sync_probe: launch inside capture failed: %s", cudaGetErrorString(e));
+        }
+    }
+    MMF_CUDA(cudaStreamEndCapture(st, &graph));
+    MMF_CUDA(cudaGraphInstantiate(&exec, graph, 0));
+    for (int i = 0; i < 3; ++i) MMF_CUDA(cudaGraphLaunch(exec, st));
+    MMF_CUDA(cudaStreamSynchronize(st));
+    cudaEvent_t e0, e1;
+    MMF_CUDA(cudaEventCreate(&e0));
+    MMF_CUDA(cudaEventCreate(&e1));
+    MMF_CUDA(cudaEventRecord(e0, st));
+    for (int i = 0; i < 10; ++i) MMF_CUDA(cudaGraphLaunch(exec, st));
+    MMF_CUDA(cudaEventRecord(e1, st));
+    MMF_CUDA(cudaStreamSynchronize(st));
+    float ms = 0.0f;
+    MMF_CUDA(cudaEventElapsedTime(&ms, e0, e1));
+    *us = ms * 1e3 / (10.0 * n);
+    cudaEventDestroy(e0);
+    cudaEventDestroy(e1);
+    cudaGraphExecDestroy(exec);
+    cudaGraphDestroy(graph);
+    cudaStreamDestroy(st);
+    return MMF_OK;
+}
+
 }  // namespace
 
-extern "C" int mmf_sync_probe(int iters, unsigned* scratch_dev, double* barrier_us_host, double* signal_us_host) {
-    MMF_REQUIRE(scratch_dev && barrier_us_host && signal_us_host, MMF_ERR_BAD_ARG, "mmf_sync_probe: null pointer");
+extern "C" int mmf_sync_probe(int iters, unsigned* scratch_dev, double* barrier_us_host, double* signal_us_host,
+                              double* chain_pdl_us_host, double* chain_plain_us_host) {
+    MMF_REQUIRE(scratch_dev && barrier_us_host && signal_us_host && chain_pdl_us_host && chain_plain_us_host, MMF_ERR_BAD_ARG,
+                "mmf_sync_probe: null pointer");
     MMF_REQUIRE(iters > 0 && iters <= 100000, MMF_ERR_BAD_SHAPE, "mmf_sync_probe: iters must be in (0, 100000]");
     int dev = 0, sms = 0, coop = 0;
     MMF_CUDA(cudaGetDevice(&dev));
@@ -226,5 +283,10 @@ extern "C" int mmf_sync_probe(int iters, unsigned* scratch_dev, double* barrier_
     int st = 0;
     MMF_CUDA(cudaMemcpy(&st, status, sizeof(int), cudaMemcpyDeviceToHost));
     MMF_REQUIRE(st == 0, MMF_ERR_TIMEOUT, "mmf_sync_probe: a bounded wait gave up (status %d)", st);
-    return MMF_OK;
+    // a chain of 200 dependent one-CTA-per-SM kernels: what a launch boundary costs with and without the
+    // programmatic-dependent-launch attribute
+    int rc = chain_us(200, sms, 256, true, scratch_dev + 64, scratch_dev + 128, chain_pdl_us_host);
+    if (rc != MMF_OK) return rc;
+    rc = chain_us(200, sms, 256, false, scratch_dev + 64, scratch_dev + 128, chain_plain_us_host);
+    return rc;
 }

@@ -524,11 +524,12 @@ def int8_mma_peak_tops(n_tokens: int = 256, iters: int = 200000) -> float:
 
 
 def sync_probe(iters: int = 2000):
-    """(grid-barrier microseconds, one-way signal microseconds) of the current GPU: what one grid-wide barrier among one
-    resident CTA per SM costs, and what handing a flag from one CTA to another costs.  Synchronises."""
+    """Synchronisation costs of the current GPU in microseconds: (grid barrier among one resident CTA per SM, one-way
+    flag hand-over between two CTAs, per-kernel time of a dependent chain with programmatic dependent launch, the same
+    without).  Synchronises."""
     scratch = torch.zeros(256, dtype=torch.int32, device="cuda")
     _lib.require_device(torch.cuda.current_device())
-    barrier, signal = ctypes.c_double(0.0), ctypes.c_double(0.0)
+    vals = [ctypes.c_double(0.0) for _ in range(4)]
     torch.cuda.synchronize()
-    _lib.call("mmf_sync_probe", iters, scratch.data_ptr(), ctypes.addressof(barrier), ctypes.addressof(signal))
-    return barrier.value, signal.value
+    _lib.call("mmf_sync_probe", iters, scratch.data_ptr(), *[ctypes.addressof(v) for v in vals])
+    return tuple(v.value for v in vals)

@@ -1,6 +1,6 @@
 """Op-level micro-benchmarks of the C-ABI kernels (also the command lines used for profiler captures).
 
-    python -m matmulfreellm_b200.opbench bitlinear --M 32 --K 2048 --N 11264 [--kernel auto|gemv|mma] [--iters 20]
+    python -m matmulfreellm_b200.opbench bitlinear --M 32 --K 2048 --N 11264 [--kernel auto|gemv|mma|decode] [--iters 20]
     python -m matmulfreellm_b200.opbench hgrn --B 8 --T 2048 --D 2048 [--gate log|linear]
     python -m matmulfreellm_b200.opbench rowwise --M 4096 --D 2048
     python -m matmulfreellm_b200.opbench int8peak
@@ -38,6 +38,14 @@ def _time(fn, iters):
 
 
 def bitlinear(a):
+    if a.kernel == "decode":      # the mma.sync decode experiment exists in the experiments build only
+        from . import _lib
+        with _lib.experiments_library():
+            return _bitlinear(a)
+    return _bitlinear(a)
+
+
+def _bitlinear(a):
     dev = torch.device("cuda")
     g = torch.Generator(device=dev).manual_seed(0)
     nbuf = max(1, a.buffers)
@@ -50,7 +58,7 @@ def bitlinear(a):
     x[:, torch.randperm(a.K, device=dev, generator=g)[: a.K // 100]] *= 20
     q, dq, rs = K.act_quant(x.bfloat16(), None, 1e-6)
     out = torch.empty(a.M, a.N, device=dev, dtype=torch.bfloat16)
-    kern = {"auto": K.KERNEL_AUTO, "gemv": K.KERNEL_GEMV, "mma": K.KERNEL_MMA}[a.kernel]
+    kern = {"auto": K.KERNEL_AUTO, "gemv": K.KERNEL_GEMV, "mma": K.KERNEL_MMA, "decode": K.KERNEL_STREAM}[a.kernel]
     state = {"i": 0}
 
     def fn():
@@ -109,10 +117,12 @@ def rowwise(a):
 
 
 def sync(a):
-    barrier, signal = K.sync_probe(2000)
+    barrier, signal, chain_pdl, chain_plain = K.sync_probe(2000)
     print(json.dumps({"op": "sync", "grid_barrier_us": barrier, "cta_to_cta_signal_us": signal,
+                      "dependent_kernel_chain_us_per_kernel": {"programmatic_dependent_launch": chain_pdl, "plain": chain_plain},
                       "what": "one barrier among one resident CTA per SM (release add + acquire poll on one counter); one "
-                              "release store -> acquire poll hand-over between two CTAs"}))
+                              "release store -> acquire poll hand-over between two CTAs; 200 dependent trivial kernels "
+                              "(one CTA per SM) replayed from a CUDA graph"}))
 
 
 def _model(layers):
@@ -181,6 +191,33 @@ def timeline(a):
             torch.cuda.synchronize()
         finally:
             lib.mmf_row_trace(None)
+        # the same step with the tcgen05 kernel's trace armed (word 1 of the split-K workspace of the capture stream)
+        for ws in list(K._ws_cache.values()):
+            w32 = ws.view(torch.int32)
+            w32[2] = 0
+            w32[1] = 0x7ACE
+        torch.cuda.synchronize()
+        dec.step()
+        torch.cuda.synchronize()
+        mma_rows = []
+        for ws in list(K._ws_cache.values()):
+            w32 = ws.view(torch.int32)
+            m = int(w32[2].item())
+            w32[1] = 0
+            w32[2] = 0
+            if m == 0:
+                continue
+            r = ws[64:64 + m * 256].view(torch.int64).view(m, 32).cpu()
+            for i in range(m):
+                v = r[i].tolist()
+                mm = [x for x in v[8:16] if x > 0]
+                if not mm:
+                    continue
+                m0 = mm[0]
+                mma_rows.append({"start_before_first_mma_ns": int(m0 - v[0]), "last_mma_issue_ns": int(mm[-1] - m0),
+                                 "accumulators_complete_ns": int(v[4] - m0), "partials_pushed_ns": int(v[5] - m0),
+                                 "cluster_barrier_done_ns": int(v[6] - m0) if v[6] > 0 else None, "end_ns": int(v[7] - m0),
+                                 "previous_end_to_first_mma_ns": int(m0 - r[i - 1, 7]) if i else None})
         n = int(buf.view(torch.int32)[0].item())
         rec = buf[8:8 + 8 * n].view(n, 8).cpu()
         rows = []
@@ -193,7 +230,8 @@ def timeline(a):
         print(json.dumps({"op": "timeline", "batch": a.batch, "layers": a.layers, "prenorm_quant_launches": n,
                           "median_ns_after_release": {k: med(k) for k in ("row_loaded_ns", "first_sum_ns", "second_norm_ns",
                                                                             "codes_written_ns", "end_ns")},
-                          "median_ns_between_prenorm_releases": med("since_previous_release_ns"), "first_launches": rows[:5]}))
+                          "median_ns_between_prenorm_releases": med("since_previous_release_ns"), "first_launches": rows[:5],
+                          "tcgen05_kernel_launches_ns_after_first_mma": mma_rows[:9]}))
 
 
 def int8peak(a):
