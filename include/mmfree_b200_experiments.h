@@ -27,6 +27,7 @@ extern "C" {
 #define MMF_TUNE_PERSISTENT 7 /* persistent large-M kernel: 1 = whenever M > 128, 2 = never, 10+v = its compiled shape v (1..4) whenever M > 128 */
 #define MMF_TUNE_PROBE_COMMITS 8 /* mmf_int8_mma_peak: tcgen05.commit instructions issued per 4 MMAs */
 #define MMF_TUNE_ACCUMULATORS 9 /* accumulators consecutive MMAs rotate through at few token columns: 1, 2 or 4 */
+#define MMF_TUNE_ASYNC_REDUCE 10 /* split-K partial sums by st.async + the owner's mbarrier: 1 = on, 2 = off, 0 = library default */
 int mmf_tuning(int knob, int value);
 
 /* Timeline trace of mmf_prenorm_quant launches: buffer_dev is a device buffer of at least 8 + 8 * 1000 int64 ([0] = launch

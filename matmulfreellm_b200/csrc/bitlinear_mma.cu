@@ -41,6 +41,10 @@ constexpr int MAX_SB = 32;        // activation stages (128 K each)
 constexpr int MAX_SW = 32;        // packed-weight stages (128 K = 4 KB each)
 constexpr int W_STAGE_BYTES = 2 * MMF_TILE_ROWS * 16;  // two 64-K chunks
 
+#ifndef MMF_ASYNC_REDUCE_DEFAULT
+#define MMF_ASYNC_REDUCE_DEFAULT 1
+#endif
+
 struct MmaParams {
     int KC;              // K / 64
     int n_tiles, group_tiles;
@@ -52,13 +56,15 @@ struct MmaParams {
     int nacc;            // independent accumulators (NT columns each) that consecutive MMAs rotate through
     int SA, SB, SW;      // ring depths: unpacked-A stages in TMEM, activation stages, packed-weight stages
     int merged;          // SA == SB and both rings share one full / one empty barrier per stage (one wait, one commit)
+    int async_red;       // split-K: partial sums travel as st.async with the byte count credited to the owner's mbarrier,
+                         // each owner waits for its own bytes only (no second cluster barrier)
     uint32_t idesc;
 };
 
 // ---------------------------------------------------
 constexpr int BAR_B_FULL = 0, BAR_B_EMPTY = BAR_B_FULL + MAX_SB, BAR_W_FULL = BAR_B_EMPTY + MAX_SB,
               BAR_W_EMPTY = BAR_W_FULL + MAX_SW, BAR_A_FULL = BAR_W_EMPTY + MAX_SW, BAR_A_EMPTY = BAR_A_FULL + MAX_SA,
-              BAR_ACC = BAR_A_EMPTY + MAX_SA, NUM_BARS = BAR_ACC + 1;
+              BAR_ACC = BAR_A_EMPTY + MAX_SA, BAR_RED = BAR_ACC + 1, NUM_BARS = BAR_RED + 1;
 
 __device__ __forceinline__ uint32_t bar_count(int i, int merged) {
     // merged rings: a stage's "full" barrier also takes the activation producer's expect_tx arrival
@@ -77,6 +83,12 @@ __device__ __forceinline__ uint32_t peer_addr(const void* my_smem_addr, uint32_t
 }
 __device__ __forceinline__ void st_cluster_b32(uint32_t cluster_addr, uint32_t v) {
     asm volatile("st.shared::cluster.b32 [%0], %1;" ::"r"(cluster_addr), "r"(v) : "memory");
+}
+// 4 bytes into a peer's shared memory; on arrival the peer's mbarrier is credited with the 4 bytes
+__device__ __forceinline__ void st_async_b32(uint32_t cluster_addr, uint32_t v, uint32_t cluster_mbar) {
+    asm volatile("st.async.weak.shared::cluster.mbarrier::complete_tx::bytes.b32 [%0], %1, [%2];" ::"r"(cluster_addr), "r"(v),
+                 "r"(cluster_mbar)
+                 : "memory");
 }
 __device__ __forceinline__ void st_peer_v4(void* my_smem_addr, uint32_t peer_rank, const int4& v) {
     uint32_t remote;
@@ -184,6 +196,10 @@ bitlinear_mma_kernel(const __grid_constant__ CUtensorMap q_map, BitLinearArgs a,
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
+    // split-K with asynchronous pushes: this CTA will receive NT/ksplit token columns x 128 rows x 4 bytes from each of the
+    // ksplit CTAs of its cluster (its own share included); credits that arrive before this line only make the count
+    // negative for a moment
+    if (p.ksplit > 1 && p.async_red && tid == 0) mbar_expect_tx(&bars[BAR_RED], (uint32_t)(p.NT * MMF_TILE_ROWS * 4));
     // cluster barrier #1 (arrive now, wait before the first remote store): a peer's shared memory may only be
     // written once that peer is known to be running
     if (p.ksplit > 1) cluster_arrive();
@@ -417,12 +433,17 @@ bitlinear_mma_kernel(const __grid_constant__ CUtensorMap q_map, BitLinearArgs a,
                         // [my rank] (the own columns included): part[rank][column in the owner's slice][row]
                         int o = (gi * 16) / per, cl = gi * 16 - o * per;
                         uint32_t dst = peer_addr(part + ((int64_t)ks * per) * MMF_TILE_ROWS + row, (uint32_t)o);
+                        uint32_t rbar = p.async_red ? peer_addr(&bars[BAR_RED], (uint32_t)o) : 0u;
 #pragma unroll
                         for (int j = 0; j < 16; ++j) {
-                            st_cluster_b32(dst + (uint32_t)(cl * MMF_TILE_ROWS * 4), v0[j]);
+                            if (p.async_red) st_async_b32(dst + (uint32_t)(cl * MMF_TILE_ROWS * 4), v0[j], rbar);
+                            else st_cluster_b32(dst + (uint32_t)(cl * MMF_TILE_ROWS * 4), v0[j]);
                             if (++cl == per) {
                                 cl = 0;
-                                if (++o < p.ksplit) dst = peer_addr(part + ((int64_t)ks * per) * MMF_TILE_ROWS + row, (uint32_t)o);
+                                if (++o < p.ksplit) {
+                                    dst = peer_addr(part + ((int64_t)ks * per) * MMF_TILE_ROWS + row, (uint32_t)o);
+                                    if (p.async_red) rbar = peer_addr(&bars[BAR_RED], (uint32_t)o);
+                                }
                             }
                         }
                     }
@@ -452,8 +473,15 @@ bitlinear_mma_kernel(const __grid_constant__ CUtensorMap q_map, BitLinearArgs a,
             }
         } else {
             const int per = p.NT / p.ksplit;                  // token columns each CTA of the cluster finishes
-            cluster_arrive();                                 // barrier #2 orders all pushes before the owners' reads
-            cluster_wait();
+            if (p.async_red) {
+                // every partial sum destined for this CTA credits BAR_RED on arrival: wait for this CTA's own bytes only.  A
+                // CTA that leaves after this wait has nothing in flight towards it, and its own pushes go to CTAs that stay
+                // until they have received them.
+                ok = __all_sync(0xffffffffu, mbar_wait(&bars[BAR_RED], 0, abort_flag)) && ok;
+            } else {
+                cluster_arrive();                             // barrier #2 orders all pushes before the owners' reads
+                cluster_wait();
+            }
             trace_mark(trace, 6);
             if (ok && !*abort_flag) {
                 for (int cl = cth; cl < per; cl += UNPACK_THREADS / 16) {
@@ -477,10 +505,12 @@ bitlinear_mma_kernel(const __grid_constant__ CUtensorMap q_map, BitLinearArgs a,
         trace_mark(trace, 7);
     }
 
-    if (p.ksplit > 1 && warp >= NUM_UNPACK_WARPS) {   // the three service warps take part in both cluster barriers
+    if (p.ksplit > 1 && warp >= NUM_UNPACK_WARPS) {   // the three service warps take part in the cluster barriers
         cluster_wait();
-        cluster_arrive();
-        cluster_wait();
+        if (!p.async_red) {
+            cluster_arrive();
+            cluster_wait();
+        }
     }
 
     // teardown: everyone meets, TMEM goes back; on the error path give copies in flight time to land first
@@ -500,7 +530,7 @@ bitlinear_mma_kernel(const __grid_constant__ CUtensorMap q_map, BitLinearArgs a,
 // every override is the constant 0 (automatic) there and the code paths it selects are compiled out.
 #ifdef MMF_EXPERIMENTS
 #include "../../include/mmfree_b200_experiments.h"
-static int g_force_ksplit = 0, g_force_nt = 0, g_force_deep = 0, g_force_wt = 0, g_force_sb = 0, g_force_sa = 0, g_force_sw = 0, g_force_persistent = 0, g_force_nacc = 0;
+static int g_force_ksplit = 0, g_force_nt = 0, g_force_deep = 0, g_force_wt = 0, g_force_sb = 0, g_force_sa = 0, g_force_sw = 0, g_force_persistent = 0, g_force_nacc = 0, g_force_async_red = 0;
 extern int g_probe_commits;
 
 extern "C" int mmf_tuning(int knob, int value) {
@@ -515,11 +545,12 @@ extern "C" int mmf_tuning(int knob, int value) {
         case MMF_TUNE_PERSISTENT: g_force_persistent = value; return MMF_OK;
         case MMF_TUNE_PROBE_COMMITS: g_probe_commits = value; return MMF_OK;
         case MMF_TUNE_ACCUMULATORS: g_force_nacc = value; return MMF_OK;
+        case MMF_TUNE_ASYNC_REDUCE: g_force_async_red = value; return MMF_OK;
         default: return mmf_set_error(MMF_ERR_BAD_ARG, "mmf_tuning: unknown knob %d", knob);
     }
 }
 #else
-static constexpr int g_force_ksplit = 0, g_force_nt = 0, g_force_deep = 0, g_force_wt = 0, g_force_sb = 0, g_force_sa = 0, g_force_sw = 0, g_force_persistent = 0, g_force_nacc = 0;
+static constexpr int g_force_ksplit = 0, g_force_nt = 0, g_force_deep = 0, g_force_wt = 0, g_force_sb = 0, g_force_sa = 0, g_force_sw = 0, g_force_persistent = 0, g_force_nacc = 0, g_force_async_red = 0;
 #endif
 
 namespace {
@@ -641,6 +672,7 @@ int bitlinear_mma_launch(const BitLinearArgs& a, cudaStream_t st) {
     MMF_REQUIRE(choose_config(a, p, smem), MMF_ERR_BAD_SHAPE, "mmf_bitlinear(mma): no kernel configuration fits M=%d N=%d K=%d", a.M,
                 a.N, a.K);
     const int m_tiles = (a.M + p.NT - 1) / p.NT;
+    p.async_red = g_force_async_red == 1 ? 1 : g_force_async_red == 2 ? 0 : MMF_ASYNC_REDUCE_DEFAULT;
     // instruction descriptor: D=S32, A=S8 (TMEM), B=S8 (smem, K-major), M=128, N=NT
     p.idesc = (2u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(p.NT >> 3) << 17) | ((uint32_t)(128 >> 4) << 24);
 

@@ -614,9 +614,14 @@ def test_bitlinear_mma_configurations_agree(K):
             pw = K.pack_weight(dev(w))
             q, dq, rs = K.act_quant(dev(x), None, 1e-6)
             ref, acc_ref = K.bitlinear(q, dq, rs, pw, torch.float32, kernel=K.KERNEL_GEMV, return_acc=True)
-            for knob, values in ((0, (1, 2, 4, 8)), (2, (1,)), (1, (128, 256)), (3, (2,))):
+            # knob 10 = split-K partial sums by st.async + the owner's mbarrier (1 = on, 2 = off), tried with every K split
+            for knob, values in ((0, (1, 2, 4, 8)), (2, (1,)), (1, (128, 256)), (3, (2,)), (10, (2, 4, 8, 0))):
                 for v in values:
-                    lib.mmf_tuning(knob, v)
+                    if knob == 10:
+                        lib.mmf_tuning(10, 1)
+                        lib.mmf_tuning(0, v)
+                    else:
+                        lib.mmf_tuning(knob, v)
                     if knob == 3:
                         lib.mmf_tuning(1, 128)
                     try:
@@ -625,7 +630,7 @@ def test_bitlinear_mma_configurations_agree(K):
                         assert e.code == -2
                         continue
                     finally:
-                        for kk in range(8):
+                        for kk in range(11):
                             lib.mmf_tuning(kk, 0)
                     K.check_status()
                     assert torch.equal(acc, acc_ref) and torch.equal(out, ref), (M, Kd, N, knob, v)
