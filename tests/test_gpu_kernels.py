@@ -609,7 +609,7 @@ def test_bitlinear_mma_configurations_agree(K):
     128- or 256-token tiles, two weight tiles per CTA) gives the same int32 accumulators as the CUDA-core kernel."""
     from matmulfreellm_b200 import _lib
     with _lib.experiments_library() as lib:      # the build that exports the configuration overrides
-        for (M, Kd, N) in [(32, 2048, 2048), (40, 704, 384), (300, 2048, 512)]:
+        for (M, Kd, N) in [(32, 2048, 2048), (40, 704, 384), (300, 2048, 512), (9, 2048, 200), (70, 2048, 256), (128, 5632, 128)]:
             x, w, _ = O.bitlinear_case(M, Kd, N, seed=M)
             pw = K.pack_weight(dev(w))
             q, dq, rs = K.act_quant(dev(x), None, 1e-6)
