@@ -251,3 +251,80 @@ __device__ __forceinline__ float2 sigmoid2(float2 x) {
     return make_float2(rcp_fast(d.x), rcp_fast(d.y));
 }
 __device__ __forceinline__ float2 silu_mul2(float2 x, float2 y) { return __fmul2_rn(__fmul2_rn(x, y), sigmoid2(x)); }
+
+// ---------------------------------------------------------------------------------------
+// HGRNBitAttention's gate math on a pair of channels (shared by the scan and the fused decode step, so that both
+// produce the same bits):
+//   f = round(sigmoid(f_raw)); with a lower bound lb: f = round(lb + round(round(1-lb)*f));
+//   x = round(silu(i_raw) * round(1-f));            every round() is to the activation dtype TX
+// ---------------------------------------------------------------------------------------
+// a pair of 16-bit activations as one 32-bit register
+template <typename T> struct Pair16 { using type = float2; };
+template <> struct Pair16<__nv_bfloat16> { using type = __nv_bfloat162; };
+template <> struct Pair16<__half> { using type = __half2; };
+__device__ __forceinline__ float2 unpack2(__nv_bfloat162 v) {
+    const uint32_t u = *reinterpret_cast<const uint32_t*>(&v);
+    return make_float2(__uint_as_float(u << 16), __uint_as_float(u & 0xffff0000u));
+}
+__device__ __forceinline__ float2 unpack2(__half2 v) { return __half22float2(v); }
+__device__ __forceinline__ void pack2(__nv_bfloat162& d, float2 v) { d = __floats2bfloat162_rn(v.x, v.y); }
+__device__ __forceinline__ void pack2(__half2& d, float2 v) { d = __floats2half2_rn(v.x, v.y); }
+
+// sigmoid of four values with two reciprocals instead of four: 1/a = b * (1/(a*b)), 1/b = a * (1/(a*b)).  The caller
+// keeps the arguments >= RAW_GATE_MIN so that the product a*b stays finite.
+constexpr float RAW_GATE_MIN = -40.0f;
+__device__ __forceinline__ void sigmoid_pairs(float2 g, float2 x, float2& sg, float2& sx) {
+    const float2 nl2e = make_float2(-1.4426950408889634f, -1.4426950408889634f);
+    const float2 tg = __fmul2_rn(g, nl2e), tx = __fmul2_rn(x, nl2e);
+    float2 eg, ex;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(eg.x) : "f"(tg.x));
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(eg.y) : "f"(tg.y));
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(ex.x) : "f"(tx.x));
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(ex.y) : "f"(tx.y));
+    const float2 one = make_float2(1.0f, 1.0f);
+    const float2 a = __fadd2_rn(one, eg), b = __fadd2_rn(one, ex);
+    const float2 p = __fmul2_rn(a, b);
+    const float2 r = make_float2(rcp_fast(p.x), rcp_fast(p.y));
+    sg = __fmul2_rn(b, r);
+    sx = __fmul2_rn(a, r);
+}
+// both raw projections of a channel pair limited to >= RAW_GATE_MIN (below it sigmoid and silu are zero to 17 digits),
+// on the packed pair for a 16-bit dtype
+__device__ __forceinline__ float2 raw_gate_floor(float2 v) { return make_float2(fmaxf(v.x, RAW_GATE_MIN), fmaxf(v.y, RAW_GATE_MIN)); }
+__device__ __forceinline__ __nv_bfloat162 raw_gate_floor(__nv_bfloat162 v) { return __hmax2(v, __float2bfloat162_rn(RAW_GATE_MIN)); }
+__device__ __forceinline__ __half2 raw_gate_floor(__half2 v) { return __hmax2(v, __float2half2_rn(RAW_GATE_MIN)); }
+
+// In: xv = i_raw, f = f_raw of two adjacent channels, already passed through raw_gate_floor; out: xv = x_t, f = f_t.  With a 16-bit activation dtype the steps
+// between two roundings run on the packed pair: the product, sum and difference of two 16-bit floats rounded once to
+// 16 bits (mul / add / sub on the packed type) equal the fp32 operation followed by the rounding, because the fp32 result
+// is exact or nowhere near a 16-bit rounding boundary.  lbv = lower bound, oml = round(1 - lb) (pass {0, 1} without one).
+template <typename TX>
+__device__ __forceinline__ void raw_gate_pair(float2& xv, float2& f, bool has_lb, float2 lbv, float2 oml) {
+    float2 sg, sx;
+    sigmoid_pairs(f, xv, sg, sx);
+    float2 omf;
+    if constexpr (sizeof(TX) == 2) {
+        typename Pair16<TX>::type f16, lb16, oml16, one16, omf16, x16;
+        pack2(f16, sg);
+        if (has_lb) {
+            pack2(lb16, lbv);                  // exact: both are values of TX already
+            pack2(oml16, oml);
+            f16 = __hadd2(lb16, __hmul2(oml16, f16));
+        }
+        pack2(one16, make_float2(1.0f, 1.0f));
+        omf16 = __hsub2(one16, f16);
+        f = unpack2(f16);
+        omf = unpack2(omf16);
+        pack2(x16, __fmul2_rn(__fmul2_rn(xv, omf), sx));
+        xv = unpack2(x16);
+    } else {
+        f = sg;
+        if (has_lb) {
+            // scalar on purpose: a packed multiply feeding a packed add can be merged into a fused multiply-add
+            f.x = __fadd_rn(lbv.x, __fmul_rn(oml.x, f.x));
+            f.y = __fadd_rn(lbv.y, __fmul_rn(oml.y, f.y));
+        }
+        omf = make_float2(__fsub_rn(1.0f, f.x), __fsub_rn(1.0f, f.y));
+        xv = __fmul2_rn(__fmul2_rn(xv, omf), sx);
+    }
+}

@@ -475,16 +475,19 @@ decode_mix_kernel(const T* __restrict__ ifg, int64_t ld, const T* __restrict__ l
             float4 h4 = *reinterpret_cast<const float4*>(st + c + i);
             float hh[4] = {h4.x, h4.y, h4.z, h4.w};
 #pragma unroll
-            for (int j = 0; j < 4; ++j) {
-                float f = round_to<T>(sigmoidf_(fv[i + j]));
+            for (int j = 0; j < 4; j += 2) {
+                float2 xv = raw_gate_floor(make_float2(iv[i + j], iv[i + j + 1])), f = raw_gate_floor(make_float2(fv[i + j], fv[i + j + 1]));
+                float2 lbv = make_float2(0.0f, 0.0f), oml = make_float2(1.0f, 1.0f);
                 if (lb) {
-                    const float lbv = sw[2 * D + c + i + j];
-                    const float oml = round_to<T>(__fsub_rn(1.0f, lbv));
-                    f = round_to<T>(__fadd_rn(lbv, round_to<T>(__fmul_rn(oml, f))));
+                    lbv = *reinterpret_cast<const float2*>(&sw[2 * D + c + i + j]);
+                    oml = make_float2(round_to<T>(__fsub_rn(1.0f, lbv.x)), round_to<T>(__fsub_rn(1.0f, lbv.y)));
                 }
-                const float x = keep ? round_to<T>(silu_mul(iv[i + j], round_to<T>(__fsub_rn(1.0f, f)))) : 0.0f;
-                hh[j] = fmaf(f, hh[j], x);
+                raw_gate_pair<T>(xv, f, lb != nullptr, lbv, oml);
+                if (!keep) xv = make_float2(0.0f, 0.0f);
+                hh[j] = fmaf(f.x, hh[j], xv.x);
+                hh[j + 1] = fmaf(f.y, hh[j + 1], xv.y);
                 ov[it * V + i + j] = round_to<T>(hh[j]);
+                ov[it * V + i + j + 1] = round_to<T>(hh[j + 1]);
             }
             *reinterpret_cast<float4*>(st + c + i) = make_float4(hh[0], hh[1], hh[2], hh[3]);
         }

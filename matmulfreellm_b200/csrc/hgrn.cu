@@ -2,14 +2,16 @@
 //
 // Work decomposition: one CTA owns 64 channels of one sequence and one chunk of the time axis.
 // [64 timesteps x 64 channels] tiles of x and g arrive in shared memory by tiled TMA (one elected
-// thread issues them, a 3-deep ring of mbarrier-tracked stages) and the output tile leaves by a TMA
-// store from a double-buffered shared-memory tile, so no thread spends instructions on addressing
+// thread issues them, a 2- or 3-deep ring of mbarrier-tracked stages) and the output tile leaves by a
+// TMA store from a double-buffered shared-memory tile, so no thread spends instructions on addressing
 // or copying global memory and x, g, o are each touched exactly once (8 B per element for bf16 x/o
-// and an fp32 gate).  Inside a stage warp `sub` scans timesteps [8*sub, 8*sub+8) of all 64 channels
-// from a zero state — lane = channel pair, packed 2-element shared-memory accesses — and the eight
-// sub-chunk aggregates (gate product, local end state) meet in shared memory: every thread folds the
-// ones before it and the carry of the previous stage into its carry-in and fixes its eight states
-// up, h_t = h_local_t + prod_t * carry (fp32 throughout).
+// and an fp32 gate, 6 B with the 16-bit raw gate).  Inside a stage warp `sub` scans timesteps
+// [8*sub, 8*sub+8) of all 64 channels from a zero state — lane = channel pair, packed 2-element
+// shared-memory accesses — and the eight sub-chunk aggregates (gate product, local end state) meet in
+// shared memory: every thread folds the ones before it and the carry of the previous stage into its
+// carry-in and fixes its eight states up, h_t = h_local_t + prod_t * carry (fp32 throughout).
+// With a 16-bit gate a CTA holds 48 KB and four of them share an SM (two with an fp32 gate).  Halving the CTA
+// (32 timesteps, 4 warps, eight per SM) to spread a 512-CTA grid more evenly was measured and is 40 % slower.
 //
 // When B*D/64 CTAs would leave most SMs idle the time axis is split into NT chunks
 // ("chunked parallel scan"): pass 1 reduces every chunk but the last to its aggregate
@@ -25,7 +27,8 @@ constexpr int HG_TS = 64;       // timesteps per stage
 constexpr int HG_SUB = 8;       // sub-chunks (warps) per stage
 constexpr int HG_SUBT = HG_TS / HG_SUB;   // timesteps per thread and stage
 constexpr int HG_THREADS = (HG_BD / 2) * HG_SUB;
-constexpr int HG_STAGES = 3;    // TMA ring depth
+// TMA ring depth: two stages when x and g are both 16-bit (the raw projections inside the model), three when the gate is fp32
+template <typename TX, typename TG> struct HgStages { static constexpr int value = sizeof(TX) + sizeof(TG) <= 4 ? 2 : 3; };
 constexpr long long HG_WAIT_LIMIT = 2000000000ll;   // clock cycles (about a second) before a wait gives up
 
 __device__ int g_hgrn_wait_failed = 0;   // set when a bounded wait on a TMA stage gave up
@@ -134,35 +137,33 @@ constexpr int HG_RAW = 2;     // x, g are the raw i/f projection outputs (HGRNBi
                               //   f = round(sigmoid(g)); with a lower bound lb: f = round(lb + round(round(1-lb)*f))
                               //   x = round(silu(x_raw) * round(1-f));  every round() is to the activation dtype TX
 
-// raw (x, g) of a channel pair -> (x_t, f_t) of the recurrence; in raw mode every rounding converts both channels
-// with one packed instruction
+// load of a raw projection pair: in raw mode limited from below (on the packed pair for a 16-bit dtype)
+template <int MODE> __device__ __forceinline__ float2 ld2g(const float* p) {
+    const float2 v = *reinterpret_cast<const float2*>(p);
+    return MODE == 2 ? raw_gate_floor(v) : v;
+}
+template <int MODE> __device__ __forceinline__ float2 ld2g(const __nv_bfloat16* p) {
+    const __nv_bfloat162 v = *reinterpret_cast<const __nv_bfloat162*>(p);
+    return unpack2(MODE == 2 ? raw_gate_floor(v) : v);
+}
+template <int MODE> __device__ __forceinline__ float2 ld2g(const __half* p) {
+    const __half2 v = *reinterpret_cast<const __half2*>(p);
+    return unpack2(MODE == 2 ? raw_gate_floor(v) : v);
+}
+
+// raw (x, g) of a channel pair -> (x_t, f_t) of the recurrence
 template <typename TX, int MODE>
 __device__ __forceinline__ void gate_transform2(float2& xv, float2& f, bool has_lb, float2 lbv, float2 oml) {
     if (MODE == HG_LOG) { f.x = exp_gate(f.x); f.y = exp_gate(f.y); }
-    if (MODE == HG_RAW) {
-        f = sigmoid2(f);
-        round_pair<TX>(f.x, f.y);
-        if (has_lb) {
-            // scalar on purpose: a packed multiply feeding a packed add can be merged into a fused multiply-add, and
-            // for a float activation dtype no rounding step separates the two
-            f.x = __fmul_rn(oml.x, f.x); f.y = __fmul_rn(oml.y, f.y);
-            round_pair<TX>(f.x, f.y);
-            f.x = __fadd_rn(lbv.x, f.x); f.y = __fadd_rn(lbv.y, f.y);
-            round_pair<TX>(f.x, f.y);
-        }
-        float2 omf = __fadd2_rn(make_float2(1.0f, 1.0f), make_float2(-f.x, -f.y));   // 1 - f (the negation is exact)
-        round_pair<TX>(omf.x, omf.y);
-        xv = silu_mul2(xv, omf);
-        round_pair<TX>(xv.x, xv.y);
-    }
+    if (MODE == HG_RAW) raw_gate_pair<TX>(xv, f, has_lb, lbv, oml);
 }
 
 // AGG = true : pass 1, chunks 0..NT-2 -> aggregates (no o written)
 // AGG = false: pass 2 (or the only pass when NT == 1) -> o, ht
-// Tensor maps: x, g, o as [B][T][D] with box [1][64][64]; rows past T read as zero and are not stored, channels
-// past D likewise.  chunk_len is a multiple of 64, so only the last stage of the last chunk can be partial.
+// Tensor maps: x, g, o as [B][T][D] with box [1][HG_TS][64]; rows past T read as zero and are not stored, channels
+// past D likewise.  chunk_len is a multiple of HG_TS, so only the last stage of the last chunk can be partial.
 template <typename TX, typename TG, int MODE, bool AGG>
-__global__ void __launch_bounds__(HG_THREADS)
+__global__ void __launch_bounds__(HG_THREADS, 4)
 hgrn_scan_kernel(const __grid_constant__ CUtensorMap x_map, const __grid_constant__ CUtensorMap g_map,
                  const __grid_constant__ CUtensorMap o_map, const TX* __restrict__ lb, const uint8_t* __restrict__ mask,
                  const void* __restrict__ h0, void* __restrict__ ht, int state_dt, int T, int D, int NT, int chunk_len,
@@ -175,6 +176,7 @@ hgrn_scan_kernel(const __grid_constant__ CUtensorMap x_map, const __grid_constan
     }
     extern __shared__ uint8_t smem_dyn[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_dyn) + 127) & ~uintptr_t(127));
+    constexpr int HG_STAGES = HgStages<TX, TG>::value;
     constexpr int XB = HG_TS * HG_BD * sizeof(TX);  // bytes of one x stage (= one output tile)
     constexpr int GB = HG_TS * HG_BD * sizeof(TG);
     TX* sx = reinterpret_cast<TX*>(smem);
@@ -217,9 +219,9 @@ hgrn_scan_kernel(const __grid_constant__ CUtensorMap x_map, const __grid_constan
     if (tid == 0)
         for (int s = 0; s < HG_STAGES; ++s) issue(s);
 
-    const bool has_lb = MODE == HG_RAW && lb != nullptr && ch_ok;
+    const bool has_lb = MODE == HG_RAW && lb != nullptr;      // uniform over the kernel
     float2 lbv = make_float2(0.0f, 0.0f), oml = make_float2(1.0f, 1.0f);
-    if (has_lb) {
+    if (has_lb && ch_ok) {
         lbv = ld2(lb + ch);
         oml.x = round_to<TX>(__fsub_rn(1.0f, lbv.x));
         oml.y = round_to<TX>(__fsub_rn(1.0f, lbv.y));
@@ -267,7 +269,7 @@ hgrn_scan_kernel(const __grid_constant__ CUtensorMap x_map, const __grid_constan
             if (rows == HG_TS) {
 #pragma unroll
                 for (int j = 0; j < HG_SUBT; ++j) {
-                    float2 xv = ld2(px + j * HG_BD), f = ld2(pg + j * HG_BD);
+                    float2 xv = ld2g<MODE>(px + j * HG_BD), f = ld2g<MODE>(pg + j * HG_BD);
                     gate_transform2<TX, MODE>(xv, f, has_lb, lbv, oml);
                     if (pm && !pm[j]) xv = make_float2(0.0f, 0.0f);
                     h = __ffma2_rn(f, h, xv);      // both channels in one packed f32x2 instruction
@@ -277,7 +279,7 @@ hgrn_scan_kernel(const __grid_constant__ CUtensorMap x_map, const __grid_constan
             } else {
 #pragma unroll
                 for (int j = 0; j < HG_SUBT; ++j) {
-                    float2 xv = ld2(px + j * HG_BD), f = ld2(pg + j * HG_BD);
+                    float2 xv = ld2g<MODE>(px + j * HG_BD), f = ld2g<MODE>(pg + j * HG_BD);
                     gate_transform2<TX, MODE>(xv, f, has_lb, lbv, oml);
                     if (sub * HG_SUBT + j >= rows) {   // steps past the end of the sequence are the identity
                         xv = make_float2(0.0f, 0.0f);
@@ -369,7 +371,7 @@ hgrn_step_kernel(const TX* __restrict__ x, int64_t ld_x, const TG* __restrict__ 
     if (idx >= B * D) return;
     const int64_t b = idx / D;
     const int ch = (int)(idx - b * D);
-    float2 xv = ld2(x + b * ld_x + ch), f = ld2(g + b * ld_g + ch);
+    float2 xv = ld2g<MODE>(x + b * ld_x + ch), f = ld2g<MODE>(g + b * ld_g + ch);
     const bool has_lb = MODE == HG_RAW && lb != nullptr;
     float2 lbv = make_float2(0.0f, 0.0f), oml = make_float2(1.0f, 1.0f);
     if (has_lb) {
@@ -403,7 +405,7 @@ int hgrn_num_chunks(int64_t B, int64_t T, int64_t D) {
 
 template <typename TX, typename TG>
 size_t hgrn_smem_bytes() {
-    return (size_t)HG_STAGES * HG_TS * HG_BD * (sizeof(TX) + sizeof(TG)) + (size_t)2 * HG_TS * HG_BD * sizeof(TX) + 128;
+    return (size_t)HgStages<TX, TG>::value * HG_TS * HG_BD * (sizeof(TX) + sizeof(TG)) + (size_t)2 * HG_TS * HG_BD * sizeof(TX) + 128;
 }
 
 // [B][T][D] view with row pitch `ld` elements (batch pitch T*ld), box = one [64 timesteps x 64 channels] tile

@@ -90,6 +90,13 @@ def hgrn(a):
     gate = glog if a.gate == "log" else glog.exp()
     h0 = torch.zeros(a.B, a.D, device=dev)
     fn = lambda: K.hgrn_scan(x, gate, h0, True, gate_is_log=a.gate == "log", state_dtype=torch.float32)
+    per_element = 8.0
+    if a.gate == "raw":     # the in-model op: raw i / f projection outputs (slabs of one [B,T,3D] tensor), gate math fused in
+        ifg = torch.randn(a.B, a.T, 3 * a.D, device=dev, generator=g).bfloat16()
+        lb = torch.rand(a.D, device=dev, generator=g).bfloat16()
+        o = torch.empty(a.B, a.T, a.D, device=dev, dtype=torch.bfloat16)
+        fn = lambda: K.hgrn_gated(ifg[..., :a.D], ifg[..., a.D:2 * a.D], lb, h0, out=o)
+        per_element = 6.0
     if getattr(a, "graph", 0):     # small problems: device time without host launch cost
         fn()
         torch.cuda.synchronize()
@@ -100,8 +107,8 @@ def hgrn(a):
         t = _time(graph.replay, a.iters) / a.graph
     else:
         t = _time(fn, a.iters)
-    nbytes = 8.0 * x.numel() + (8.0 * a.B * a.D if a.T == 1 else 0.0)     # a single step also reads and writes the state
-    print(json.dumps({"op": "hgrn_scan", "B": a.B, "T": a.T, "D": a.D, "us": t * 1e6, "algorithmic_bytes": nbytes,
+    nbytes = per_element * x.numel() + (8.0 * a.B * a.D if a.T == 1 else 0.0)     # a single step also reads and writes the state
+    print(json.dumps({"op": "hgrn_scan", "gate": a.gate, "B": a.B, "T": a.T, "D": a.D, "us": t * 1e6, "algorithmic_bytes": nbytes,
                       "gb_per_s": nbytes / t / 1e9}))
 
 
