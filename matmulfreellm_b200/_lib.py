@@ -121,7 +121,7 @@ class experiments_library:
     goes to libmmfree_b200_experiments.so (the same sources built with -DMMF_EXPERIMENTS), which also exports
     mmf_tuning; on exit all overrides are reset and the product library is current again."""
 
-    KNOBS = 11
+    KNOBS = 13
     _handle = None
 
     def __enter__(self):

@@ -362,7 +362,6 @@ bitlinear_mma_kernel(const __grid_constant__ CUtensorMap q_map, BitLinearArgs a,
             uint4 wv[2];
             wv[0] = *reinterpret_cast<const uint4*>(wsrc);
             wv[1] = nch > 1 ? *reinterpret_cast<const uint4*>(wsrc + MMF_TILE_ROWS * 16) : wv[0];
-            mbar_arrive(&bars[BAR_W_EMPTY + ws]);             // the packed bytes are in registers now
             if (trace && i < 6) trace[16 + i] = trace_now();
             ok = __all_sync(0xffffffffu, mbar_wait(&bars[BAR_A_EMPTY + as], aq.ph ^ 1, abort_flag));
             if (!ok) break;   // uniform per warp: the .sync.aligned tcgen05 ops below need the whole warp
@@ -379,6 +378,9 @@ bitlinear_mma_kernel(const __grid_constant__ CUtensorMap q_map, BitLinearArgs a,
                 }
             }
             tmem_wait_st();
+            // the packed-weight slot goes back only after the stores that consumed the loaded registers have completed: an
+            // arrive issued right after the shared-memory loads can be performed while they are still in flight
+            mbar_arrive(&bars[BAR_W_EMPTY + ws]);
             tc_fence_before();
             mbar_arrive(&bars[BAR_A_FULL + as]);
             if (trace && i < 6) trace[22 + i] = trace_now();
@@ -532,6 +534,8 @@ bitlinear_mma_kernel(const __grid_constant__ CUtensorMap q_map, BitLinearArgs a,
 #include "../../include/mmfree_b200_experiments.h"
 static int g_force_ksplit = 0, g_force_nt = 0, g_force_deep = 0, g_force_wt = 0, g_force_sb = 0, g_force_sa = 0, g_force_sw = 0, g_force_persistent = 0, g_force_nacc = 0, g_force_async_red = 0;
 extern int g_probe_commits;
+extern int g_probe_issuers;
+extern int g_pf_skip;
 
 extern "C" int mmf_tuning(int knob, int value) {
     switch (knob) {
@@ -544,6 +548,8 @@ extern "C" int mmf_tuning(int knob, int value) {
         case MMF_TUNE_W_STAGES: g_force_sw = value; return MMF_OK;
         case MMF_TUNE_PERSISTENT: g_force_persistent = value; return MMF_OK;
         case MMF_TUNE_PROBE_COMMITS: g_probe_commits = value; return MMF_OK;
+        case MMF_TUNE_PROBE_ISSUERS: g_probe_issuers = value; return MMF_OK;
+        case MMF_TUNE_PREFILL_SKIP: g_pf_skip = value; return MMF_OK;
         case MMF_TUNE_ACCUMULATORS: g_force_nacc = value; return MMF_OK;
         case MMF_TUNE_ASYNC_REDUCE: g_force_async_red = value; return MMF_OK;
         default: return mmf_set_error(MMF_ERR_BAD_ARG, "mmf_tuning: unknown knob %d", knob);

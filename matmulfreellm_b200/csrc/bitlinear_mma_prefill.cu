@@ -34,7 +34,7 @@
 namespace {
 
 // Compile-time shape of one variant of the kernel.
-template <int NT_, int GROUPS_, int SA_, int SB_, int SW_, bool DOUBLE_, bool MERGED_, bool STAGE_OUT_>
+template <int NT_, int GROUPS_, int SA_, int SB_, int SW_, bool DOUBLE_, bool MERGED_, bool STAGE_OUT_, int ISSUERS_ = 1>
 struct PfCfg {
     static constexpr int NT = NT_;                   // token columns per tile
     static constexpr int GROUPS = GROUPS_;           // unpack groups of four warps that take 128-K stages in turn
@@ -42,13 +42,25 @@ struct PfCfg {
     static constexpr int SB = SB_;                   // activation stages (NT * 128 bytes each)
     static constexpr int SW = SW_;                   // packed-weight stages (4 KB each)
     static constexpr int NACC = DOUBLE_ ? 2 : 1;     // accumulators: with two, MMAs of the next item overlap the epilogue
-    // MERGED: the A ring and the activation ring advance together (same depth, same slot), so one "full" barrier
-    // (128 unpack arrivals + the TMA producer's expect_tx) and one "empty" barrier serve a stage: the issuing
-    // thread then executes one wait and one tcgen05.commit per stage instead of two of each
+    // MERGED: the A ring and the activation ring share their barriers: one "full" barrier per stage (128 unpack arrivals +
+    // the TMA producer's expect_tx) and one "empty" barrier, so the issuing thread executes one wait and one
+    // tcgen05.commit per stage instead of two of each.  The barriers are indexed by the activation ring (depth SB, a
+    // multiple of SA): stage s uses activation slot s % SB and A slot s % SA, and the unpack group that refills an A slot
+    // waits for the commit of stage s - SA (barrier (s - SA) % SB).  The activation ring can thus run further ahead than
+    // the four A stages tensor memory has room for — an activation tile comes from L2 with about a microsecond of latency.
     static constexpr bool MERGED = MERGED_;
+    static constexpr int AR = MERGED_ ? SB_ : SA_;   // number of A_FULL / A_EMPTY barriers
+    // ISSUERS: threads (one per warp) that issue the MMAs of a stage, each for its own NT / ISSUERS token columns of the
+    // tile and of the accumulator.  In a bare issue loop the ~67 cycles an MMA costs its issuing thread overlap between
+    // two threads (69 cycles per MMA with one thread, 35 with two).  In this kernel two issuers changed nothing
+    // (each still executes four MMAs, a commit and a wait per stage, and it is that per-stage sequence, slowed by the
+    // epilogue warps sharing its scheduler, that paces the loop), so the compiled default is one; shapes 5 and 6 keep the
+    // two-issuer form for comparison.
+    static constexpr int ISSUERS = ISSUERS_;
+    static constexpr int NH = NT / ISSUERS;          // token columns per issuer
     static constexpr int UNPACK_WARPS = 4 * GROUPS, EPI_WARPS = 8;
     static constexpr int WARP_W = UNPACK_WARPS + EPI_WARPS, WARP_B = WARP_W + 1, WARP_MMA = WARP_W + 2;
-    static constexpr int THREADS = (WARP_MMA + 1) * 32;
+    static constexpr int THREADS = (WARP_MMA + ISSUERS) * 32;
     static constexpr int B_STAGE = NT * 128;
     static constexpr int W_STAGE = 2 * MMF_TILE_ROWS * 16;
     // STAGE_OUT: 2-byte outputs leave through a [NT][128] shared-memory tile and one TMA store per work item
@@ -56,21 +68,30 @@ struct PfCfg {
     static constexpr int OUT_STAGE = STAGE_OUT ? NT * MMF_TILE_ROWS * 2 : 0;
     static constexpr int SMEM = 1024 + SB * B_STAGE + SW * W_STAGE + OUT_STAGE;
     static constexpr int B_FULL = 0, B_EMPTY = B_FULL + SB, W_FULL = B_EMPTY + SB, W_EMPTY = W_FULL + SW,
-                         A_FULL = W_EMPTY + SW, A_EMPTY = A_FULL + SA, ACC_FULL = A_EMPTY + SA, ACC_EMPTY = ACC_FULL + 2,
+                         A_FULL = W_EMPTY + SW, A_EMPTY = A_FULL + AR, ACC_FULL = A_EMPTY + AR, ACC_EMPTY = ACC_FULL + 2,
                          BAR_COUNT = ACC_EMPTY + 2;
     static_assert(NACC * NT + SA * 32 <= 512, "accumulators and the A ring must fit tensor memory");
-    static_assert(!MERGED || SA == SB, "merged rings have one depth");
+    static_assert(!MERGED || SB % SA == 0, "merged rings: the activation ring is a whole number of A rings deep");
     __host__ __device__ static constexpr int b_full(int slot) { return (MERGED ? A_FULL : B_FULL) + slot; }
     __host__ __device__ static constexpr int b_empty(int slot) { return (MERGED ? A_EMPTY : B_EMPTY) + slot; }
     static_assert(NT % 32 == 0 && NT <= 256, "token tile");
+    static_assert((ISSUERS == 1 || ISSUERS == 2) && NH % 16 == 0, "each issuer's columns: a multiple of 16 (MMA N) and of 8 (swizzle atom)");
     static_assert(SMEM + 5 * 1024 <= 227 * 1024, "shared memory (dynamic + static) per CTA");
     __device__ static uint32_t bar_count(int i) {
-        if (MERGED && i >= A_FULL && i < A_EMPTY) return 129u;   // one unpack group + the activation producer
-        if (i >= W_EMPTY && i < A_EMPTY) return 128u;   // the 128 threads of one unpack group
         if (i >= ACC_EMPTY) return (uint32_t)EPI_WARPS;
+        if (i >= A_EMPTY) return (uint32_t)ISSUERS;              // A_EMPTY, ACC_FULL: one tcgen05.commit per issuer
+        if (MERGED && i >= A_FULL) return 129u;                  // one unpack group + the activation producer
+        if (i >= W_EMPTY) return 128u;                           // W_EMPTY, A_FULL: the 128 threads of one unpack group
+        if (i >= B_EMPTY && i < W_FULL) return (uint32_t)ISSUERS;
         return 1u;
     }
 };
+
+#ifdef MMF_EXPERIMENTS
+#define PF_SKIP(x) (x)
+#else
+#define PF_SKIP(x) false
+#endif
 
 struct PfParams {
     int KC;            // K / 64
@@ -79,6 +100,8 @@ struct PfParams {
     int m_tiles;       // token tiles
     int n_work;        // n_tiles * m_tiles
     int tma_out;       // outputs go through the shared-memory tile and out_map (2-byte dtype, 16-byte aligned rows)
+    int skip;          // experiments build only (wrong results, timing only): 1 = no activation loads, 2 = no weight
+                       // expansion, 4 = no output stores; 0 in the product build
     uint32_t idesc;
 };
 
@@ -147,9 +170,9 @@ bitlinear_mma_prefill_kernel(const __grid_constant__ CUtensorMap q_map, const __
     const int S = (p.KC + 1) / 2;              // 128-K stages per work item
     const int first = blockIdx.x, step = gridDim.x;
     // optional phase trace of CTA 0 (armed by MMF_TRACE_MAGIC in workspace word 1): 28 clock64 slots in the header
-    long long* const trace = MMF_TRACE_PTR((lane == 0 && blockIdx.x == 0 && a.ws && a.ws[1] == MMF_TRACE_MAGIC)
+    long long* trace = MMF_TRACE_PTR((lane == 0 && blockIdx.x == 0 && a.ws && a.ws[1] == MMF_TRACE_MAGIC)
                            ? reinterpret_cast<long long*>(a.ws + 8) : nullptr);
-    if (tid == 0) trace_mark(trace, 0);
+    if (tid == 0) { trace_mark(trace, 0); if (trace) trace[26] = clock64(); }   // 26 / 27: SM clock count at both ends
 
     if (warp == C::WARP_W) {
         // ------------------------------------------------------------ packed weights (bulk TMA); independent of the
@@ -179,16 +202,20 @@ bitlinear_mma_prefill_kernel(const __grid_constant__ CUtensorMap q_map, const __
                 const int y = (tile / p.group_tiles) * a.M + mt * C::NT;
                 for (int i = 0; i < S; ++i, bq.next()) {
                     if (!mbar_wait(&bars[C::b_empty(bq.slot)], bq.ph ^ 1, abort_flag)) { live = false; break; }
+                    if (PF_SKIP(p.skip & 1)) { mbar_arrive(&bars[C::b_full(bq.slot)]); continue; }
                     mbar_expect_tx(&bars[C::b_full(bq.slot)], (uint32_t)C::B_STAGE);
                     tma_load_2d(b_ring + bq.slot * C::B_STAGE, &q_map, &bars[C::b_full(bq.slot)], i * 128, y);
                 }
             }
         }
-    } else if (warp == C::WARP_MMA) {
-        // ------------------------------------------------------------ MMA issue: a serial instruction stream, kept short
+    } else if (warp >= C::WARP_MMA) {
+        // ------------------------------------------------------------ MMA issue: a serial instruction stream per issuer,
+        // kept short; issuer `half` owns token columns [half * NH, half * NH + NH) of the tile and of the accumulator
         if (elect_one()) {
+            const int half = warp - C::WARP_MMA;
+            if (half != 0) trace = nullptr;
             PfRing bq{0, 0, C::SB}, aq{0, 0, C::SA};
-            const uint64_t b_desc0 = make_b_desc(smem_u32(b_ring));
+            const uint64_t b_desc0 = make_b_desc(smem_u32(b_ring + half * (C::NH * 128)));
             const uint32_t b_lo0 = (uint32_t)b_desc0, b_hi = (uint32_t)(b_desc0 >> 32);
             const uint32_t b_desc_step = (uint32_t)C::B_STAGE >> 4;
             const int nfull = p.KC / 2;          // whole 128-K stages; a trailing 64-K stage issues two MMAs
@@ -199,13 +226,13 @@ bitlinear_mma_prefill_kernel(const __grid_constant__ CUtensorMap q_map, const __
                 const int ab = C::NACC == 2 ? (it & 1) : 0;              // accumulator of this work item
                 if (!mbar_wait(&bars[C::ACC_EMPTY + ab], (uint32_t)(((it / C::NACC) & 1) ^ 1), abort_flag)) break;
                 tc_fence_after();
-                const uint32_t d_addr = tmem_base + (uint32_t)ab * C::NT;
+                const uint32_t d_addr = tmem_base + (uint32_t)ab * C::NT + (uint32_t)half * C::NH;
                 if (it >= 1 && it < 5) trace_mark(trace, 1 + (it - 1) * 3);
                 
                 uint32_t accum = 0;
                 for (int i = 0; i < S; ++i, bq.next(), aq.next()) {
-                    if (!C::MERGED && !mbar_wait(&bars[C::B_FULL + bq.slot], bq.ph, abort_flag)) { live = false; break; }
-                    if (!mbar_wait(&bars[C::A_FULL + aq.slot], aq.ph, abort_flag)) { live = false; break; }
+                    if (!mbar_wait(&bars[C::b_full(bq.slot)], bq.ph, abort_flag)) { live = false; break; }
+                    if (!C::MERGED && !mbar_wait(&bars[C::A_FULL + aq.slot], aq.ph, abort_flag)) { live = false; break; }
                     tc_fence_after();
                     if (i == 0 && it >= 1 && it < 5) trace_mark(trace, 2 + (it - 1) * 3);
                     uint32_t a_addr = tmem_a + aq.slot * 32;
@@ -237,13 +264,14 @@ bitlinear_mma_prefill_kernel(const __grid_constant__ CUtensorMap q_map, const __
                         mma_i8_ts(d_addr, a_addr + 8, bd + 2, p.idesc, 1u);
                     }
                     accum = 1;
-                    tc_commit(&bars[C::A_EMPTY + aq.slot]);   // frees the A stage (and the activation stage) when these MMAs retire
-                    if (!C::MERGED) tc_commit(&bars[C::B_EMPTY + bq.slot]);
+                    tc_commit(&bars[C::b_empty(bq.slot)]);   // frees the activation stage (merged: and the A stage) when these MMAs retire
+                    if (!C::MERGED) tc_commit(&bars[C::A_EMPTY + aq.slot]);
                 }
                 if (live) tc_commit(&bars[C::ACC_FULL + ab]);
                 if (it >= 1 && it < 5) trace_mark(trace, 3 + (it - 1) * 3);
-                
             }
+            trace_mark(trace, 25);
+            if (trace) trace[27] = clock64();
         }
     } else if (warp < C::UNPACK_WARPS) {
         // ------------------------------------------------------------ unpack: lane <-> TMEM lane <-> weight row
@@ -265,13 +293,18 @@ bitlinear_mma_prefill_kernel(const __grid_constant__ CUtensorMap q_map, const __
                 uint4 wv[2];
                 wv[0] = *reinterpret_cast<const uint4*>(wsrc);
                 wv[1] = nch > 1 ? *reinterpret_cast<const uint4*>(wsrc + MMF_TILE_ROWS * 16) : wv[0];
-                mbar_arrive(&bars[C::W_EMPTY + w.slot]);          // the packed bytes are in registers now
-                ok = __all_sync(0xffffffffu, mbar_wait(&bars[C::A_EMPTY + aq.slot], aq.ph ^ 1, abort_flag));
+                // the MMAs that read this A slot last (stage sg - SA) must have retired
+                if (C::MERGED) {
+                    const int t = sg - C::SA;
+                    if (t >= 0) ok = __all_sync(0xffffffffu, mbar_wait(&bars[C::A_EMPTY + t % C::SB], (uint32_t)((t / C::SB) & 1), abort_flag));
+                } else {
+                    ok = __all_sync(0xffffffffu, mbar_wait(&bars[C::A_EMPTY + aq.slot], aq.ph ^ 1, abort_flag));
+                }
                 if (!ok) break;   // uniform per warp: the .sync.aligned tcgen05 ops below need the whole warp
                 tc_fence_after();
 #pragma unroll
                 for (int h = 0; h < 2; ++h) {
-                    if (h < nch) {
+                    if (h < nch && !PF_SKIP(p.skip & 2)) {
                         const uint32_t words[4] = {wv[h].x, wv[h].y, wv[h].z, wv[h].w};
                         uint32_t r[16];
 #pragma unroll
@@ -282,8 +315,14 @@ bitlinear_mma_prefill_kernel(const __grid_constant__ CUtensorMap q_map, const __
                     }
                 }
                 tmem_wait_st();
+                // The packed-weight slot goes back only now, after the stores that consumed the loaded registers have
+                // completed.  An arrive placed right after the two shared-memory loads can be performed while those loads
+                // are still in flight (nothing orders an mbarrier arrive behind an earlier load whose result it does not
+                // use): with a shallow weight ring the refill then overwrote the slot under the second load, and single
+                // 8-lane wavefronts of it returned the next work item's weights.
+                mbar_arrive(&bars[C::W_EMPTY + w.slot]);
                 tc_fence_before();
-                mbar_arrive(&bars[C::A_FULL + aq.slot]);
+                mbar_arrive(&bars[C::A_FULL + (C::MERGED ? sg % C::SB : aq.slot)]);
 #pragma unroll
                 for (int k = 0; k < C::GROUPS; ++k) { w.next(); aq.next(); }
             }
@@ -340,7 +379,7 @@ bitlinear_mma_prefill_kernel(const __grid_constant__ CUtensorMap q_map, const __
                     if (lane == 0) mbar_arrive(&bars[C::ACC_EMPTY + ab]);
                     if (ew == 0 && it < 4) trace_mark(trace, 14 + it * 3);
                 }
-                const int ncols = mvalid - c * 16;
+                const int ncols = PF_SKIP(p.skip & 4) ? 0 : mvalid - c * 16;
                 if (staged) {
                     // columns past M carry zero constants and rows past N garbage: the TMA store clips both
                     const int cc = col0 + c * 16;
@@ -395,6 +434,14 @@ bitlinear_mma_prefill_kernel(const __grid_constant__ CUtensorMap q_map, const __
     if (warp == C::WARP_MMA) tmem_dealloc(tmem_base, 512u);
 }
 
+}  // namespace
+#ifdef MMF_EXPERIMENTS
+int g_pf_skip = 0;     // mmf_tuning(MMF_TUNE_PREFILL_SKIP, bits)
+#else
+static constexpr int g_pf_skip = 0;
+#endif
+namespace {
+
 template <typename C>
 int pf_launch(const BitLinearArgs& a, cudaStream_t st) {
     PfParams p;
@@ -405,8 +452,9 @@ int pf_launch(const BitLinearArgs& a, cudaStream_t st) {
     const int64_t n_work = (int64_t)p.n_tiles * p.m_tiles;
     MMF_REQUIRE(n_work < (1ll << 31), MMF_ERR_BAD_SHAPE, "mmf_bitlinear(mma): problem too large");
     p.n_work = (int)n_work;
-    // instruction descriptor: D=S32, A=S8 (TMEM), B=S8 (smem, K-major), M=128, N=NT
-    p.idesc = (2u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(C::NT >> 3) << 17) | ((uint32_t)(128 >> 4) << 24);
+    p.skip = g_pf_skip;
+    // instruction descriptor: D=S32, A=S8 (TMEM), B=S8 (smem, K-major), M=128, N=NH (one issuer's columns)
+    p.idesc = (2u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(C::NH >> 3) << 17) | ((uint32_t)(128 >> 4) << 24);
 
     MmfEncodeTiledFn encode = mmf_encode_tiled();
     MMF_REQUIRE(encode != nullptr, MMF_ERR_CUDA, "mmf_bitlinear(mma): cuTensorMapEncodeTiled is not available from the driver");
@@ -459,9 +507,14 @@ int pf_launch(const BitLinearArgs& a, cudaStream_t st) {
 // (the epilogue of one work item overlaps the main loop of the next).  3: as 2 with the TMA-store epilogue.  4: as 1
 // with separate A / activation rings (two waits and two commits per stage), kept for comparison.
 using PfLongK = PfCfg<256, 2, 6, 6, 6, false, true, false>;
-using PfOverlap = PfCfg<192, 3, 4, 4, 8, true, true, false>;
+using PfOverlap = PfCfg<192, 3, 4, 8, 6, true, true, false>;
 using PfOverlapTma = PfCfg<192, 3, 4, 4, 8, true, true, true>;
 using PfSeparate = PfCfg<256, 2, 8, 5, 8, false, false, false>;
+// 5, 6: shapes 1 and 2 with two issuing threads (128 / 96 columns per MMA each), kept for comparison
+using PfLongK2 = PfCfg<256, 2, 6, 6, 6, false, true, false, 2>;
+using PfOverlap2 = PfCfg<192, 3, 4, 4, 8, true, true, false, 2>;
+// 7: shape 2 with the activation ring as deep as the A ring (four stages), as it was before; kept for comparison
+using PfOverlapShallow = PfCfg<192, 3, 4, 4, 8, true, true, false>;
 
 int pf_pick(const BitLinearArgs& a, int variant) { return variant ? variant : (a.K >= 4096 ? 1 : 2); }
 
@@ -469,7 +522,7 @@ int pf_pick(const BitLinearArgs& a, int variant) { return variant ? variant : (a
 
 int bitlinear_mma_prefill_tile(const BitLinearArgs& a, int variant) {
     const int v = pf_pick(a, variant);
-    return v == 2 || v == 3 ? 192 : 256;
+    return v == 2 || v == 3 || v == 6 || v == 7 ? 192 : 256;
 }
 
 // Launch the persistent kernel (large M).  Same argument contract as bitlinear_mma_launch; `variant` selects one
@@ -479,6 +532,9 @@ int bitlinear_mma_prefill_launch(const BitLinearArgs& a, cudaStream_t st, int va
         case 1: return pf_launch<PfLongK>(a, st);
         case 3: return pf_launch<PfOverlapTma>(a, st);
         case 4: return pf_launch<PfSeparate>(a, st);
+        case 5: return pf_launch<PfLongK2>(a, st);
+        case 6: return pf_launch<PfOverlap2>(a, st);
+        case 7: return pf_launch<PfOverlapShallow>(a, st);
         default: return pf_launch<PfOverlap>(a, st);
     }
 }

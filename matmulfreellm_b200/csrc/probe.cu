@@ -8,9 +8,9 @@ namespace {
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
 
 __global__ void __launch_bounds__(128)
-int8_mma_peak_kernel(int n_tokens, int iters, int* status, int commits) {
+int8_mma_peak_kernel(int n_tokens, int iters, int* status, int commits, int issuers) {
     extern __shared__ uint8_t smem_raw[];
-    __shared__ __align__(8) uint64_t bar;
+    __shared__ __align__(8) uint64_t bar[2];
     __shared__ __align__(8) uint64_t scratch_bar[2];   // target of the extra commits of the issue-cost experiment
     __shared__ uint32_t s_tmem;
     uint8_t* base = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -22,7 +22,8 @@ int8_mma_peak_kernel(int n_tokens, int iters, int* status, int commits) {
         reinterpret_cast<uint32_t*>(base)[i] = h;
     }
     if (threadIdx.x == 0) {
-        asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(smem_u32(&bar)) : "memory");
+        asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(smem_u32(&bar[0])) : "memory");
+        asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(smem_u32(&bar[1])) : "memory");
         asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(smem_u32(&scratch_bar[0])) : "memory");
         asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(smem_u32(&scratch_bar[1])) : "memory");
     }
@@ -56,7 +57,10 @@ int8_mma_peak_kernel(int n_tokens, int iters, int* status, int commits) {
         __syncthreads();
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     }
-    if (threadIdx.x == 0) {
+    // issue-cost experiment: with two issuers (n_tokens <= 128) the first thread of warps 0 and 1 each issue half of the
+    // MMAs into an accumulator of their own — does the per-instruction issue cost of one thread overlap with the other's?
+    const int who = threadIdx.x >> 5;
+    if ((threadIdx.x & 31) == 0 && who < issuers) {
         // shared-memory descriptor of a K-major, 128-byte-swizzled tile; instruction descriptor S32 += S8 x S8
         uint64_t bd = 0;
         bd |= (uint64_t)((smem_u32(base) & 0x3FFFFu) >> 4);
@@ -65,28 +69,30 @@ int8_mma_peak_kernel(int n_tokens, int iters, int* status, int commits) {
         bd |= (uint64_t)1 << 46;
         bd |= (uint64_t)2 << 61;
         const uint32_t idesc = (2u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(n_tokens >> 3) << 17) | ((uint32_t)(128 >> 4) << 24);
+        const uint32_t acc = tmem + (uint32_t)who * 128u;
+        const int mine = iters / issuers;
 #pragma unroll 4
-        for (int i = 0; i < iters; ++i) {
+        for (int i = 0; i < mine; ++i) {
             const uint32_t a_addr = tmem + 256 + (uint32_t)(i & 7) * 8;
             const uint64_t b = bd + (uint64_t)((i & 3) * 2);
             asm volatile(
                 "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
                 "tcgen05.mma.cta_group::1.kind::i8 [%0], [%1], %2, %3, {%5, %5, %5, %5}, p;\n\t}"
-                ::"r"(tmem), "r"(a_addr), "l"(b), "r"(idesc), "r"(i > 0 ? 1u : 0u), "r"(0u)
+                ::"r"(acc), "r"(a_addr), "l"(b), "r"(idesc), "r"(i > 0 ? 1u : 0u), "r"(0u)
                 : "memory");
-            // issue-cost experiment: `commits` tcgen05.commit instructions after every fourth MMA, as a pipelined
-            // kernel issues them to release its operand stages
+            // `commits` tcgen05.commit instructions after every fourth MMA, as a pipelined kernel issues them to release
+            // its operand stages
             if ((i & 3) == 3)
                 for (int c = 0; c < commits; ++c)
                     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];"
                                  ::"r"(smem_u32(&scratch_bar[c & 1])) : "memory");
         }
-        asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(&bar)) : "memory");
+        asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(&bar[who])) : "memory");
         const long long t0 = clock64();
         uint32_t done = 0;
         while (!done) {   // bounded wait for the MMAs to retire
             asm volatile("{\n\t.reg .pred P1;\n\tmbarrier.try_wait.parity.shared::cta.b64 P1, [%1], %2;\n\tselp.b32 %0, 1, 0, P1;\n\t}"
-                         : "=r"(done) : "r"(smem_u32(&bar)), "r"(0u) : "memory");
+                         : "=r"(done) : "r"(smem_u32(&bar[who])), "r"(0u) : "memory");
             if (clock64() - t0 > 4000000000ll) { atomicExch(status, 1); break; }
         }
     }
@@ -99,8 +105,10 @@ int8_mma_peak_kernel(int n_tokens, int iters, int* status, int commits) {
 
 #ifdef MMF_EXPERIMENTS
 int g_probe_commits = 0;   // mmf_tuning(MMF_TUNE_PROBE_COMMITS, n), experiments build only
+int g_probe_issuers = 0;   // mmf_tuning(MMF_TUNE_PROBE_ISSUERS, 2): two issuing threads, experiments build only
 #else
 static constexpr int g_probe_commits = 0;
+static constexpr int g_probe_issuers = 0;
 #endif
 
 extern "C" int mmf_int8_mma_peak(int n_tokens, int iters, int* status_dev, double* tops_host) {
@@ -111,15 +119,16 @@ extern "C" int mmf_int8_mma_peak(int n_tokens, int iters, int* status_dev, doubl
     MMF_CUDA(cudaGetDevice(&dev));
     MMF_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
     const size_t smem = 1024 + (size_t)n_tokens * 128;
+    const int issuers = g_probe_issuers == 2 && n_tokens <= 128 ? 2 : 1;
     MMF_CUDA(cudaFuncSetAttribute(int8_mma_peak_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)(150 * 1024)));
     cudaEvent_t e0, e1;
     MMF_CUDA(cudaEventCreate(&e0));
     MMF_CUDA(cudaEventCreate(&e1));
     MMF_CUDA(cudaMemset(status_dev, 0, sizeof(int)));
     // 150 KB of shared memory per CTA keeps it at one CTA per SM (each allocates all of tensor memory)
-    int8_mma_peak_kernel<<<sms, 128, 150 * 1024>>>(n_tokens, 64, status_dev, g_probe_commits);     // warm-up
+    int8_mma_peak_kernel<<<sms, 128, 150 * 1024>>>(n_tokens, 64, status_dev, g_probe_commits, issuers);     // warm-up
     MMF_CUDA(cudaEventRecord(e0));
-    int8_mma_peak_kernel<<<sms, 128, 150 * 1024>>>(n_tokens, iters, status_dev, g_probe_commits);
+    int8_mma_peak_kernel<<<sms, 128, 150 * 1024>>>(n_tokens, iters, status_dev, g_probe_commits, issuers);
     MMF_CUDA(cudaEventRecord(e1));
     MMF_CUDA(cudaEventSynchronize(e1));
     MMF_LAUNCH_CHECK("int8_mma_peak_kernel");
