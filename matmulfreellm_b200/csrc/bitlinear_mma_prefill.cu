@@ -7,16 +7,20 @@
 //  * the single thread that issues the MMAs is a serial instruction stream in which one tcgen05.mma costs
 //    about 67 cycles and one tcgen05.commit about 90 (measured), so a stage of four MMAs must not carry
 //    more than one commit and one barrier wait: the unpacked-A ring (TMEM) and the activation ring (shared
-//    memory) have the same depth and advance together, one "full" barrier per stage collects the 128
-//    arrivals of an unpack group plus the TMA transaction bytes, one "empty" barrier (a single commit)
-//    hands both buffers back;
+//    memory) share their barriers — one "full" barrier per stage collects the arrivals of an unpack group
+//    plus the TMA transaction bytes, one "empty" barrier (a single commit) hands both buffers back.  The
+//    activation ring is eight stages deep on those barriers although tensor memory has room for only four
+//    A stages (an activation tile comes from L2 with about a microsecond of latency);
 //  * two tile shapes: 192 token columns with TWO accumulators (2 x 192 + 4 x 32 A-stage columns = all 512
 //    TMEM columns) — the MMAs of the next work item run while the epilogue drains the previous
 //    accumulator; and, for long K, 256 token columns with one accumulator and rings six deep — each MMA
 //    then fills the tensor pipe for 133 cycles, which hides the issue cost completely, and the exposed
 //    epilogue is amortised over many stages;
-//  * every CTA walks a list of (weight tile, token tile) work items, weight tile fastest, so that the
-//    CTAs running at the same time share a few activation tiles in L2; barriers, TMEM and the three
+//  * pairs of CTAs (a cluster of two, tcgen05 cta_group::2) whenever the weight tiles pair up: each CTA keeps
+//    its own weight tile, A ring, accumulators and epilogue, but loads only half of every activation tile;
+//    one thread of the even CTA issues 256-row MMAs for both, whose commits reach both CTAs' barriers;
+//  * every CTA (pair) walks a list of (weight tile (pair), token tile) work items, weight tile fastest, so that
+//    the CTAs running at the same time share a few activation tiles in L2; barriers, TMEM and the three
 //    rings (packed weights, unpacked A stages, activation tiles) are set up once and keep streaming
 //    across work items — while the epilogue drains one accumulator, the producers and the unpack warps
 //    already fill the rings for the next item;
@@ -24,9 +28,15 @@
 //    per-token code sum (weights are stored +1 biased), dequantise and store; the accumulator is handed
 //    back to the MMA warp as soon as its last chunk sits in registers.
 //
-// Warp roles: 4 x GROUPS unpack warps (groups of four take 128-K stages in turn), then 8 epilogue warps (TMEM
-// lane quarter = warp % 4, column half by warp), then the packed-weight producer, the activation producer and
-// the TMEM owner + MMA issuer.  Every wait is bounded and reports through the status word.
+// Warp roles: warp 0 owns tensor memory and issues the MMAs, warps 2 and 3 produce the packed-weight and the
+// activation ring, then 4 x GROUPS unpack warps (groups of four take 128-K stages in turn), then 8 epilogue warps
+// (TMEM lane quarter = warp % 4, column half by warp).  Every wait is bounded and reports through the status word.
+//
+// What paces it (measured with parts switched off, timing only): with no activation loads, no weight expansion and
+// no output stores the loop reaches 95 % of the tensor pipe with one issuing thread, so the issuing thread is not
+// the limit by itself; output stores cost 16 points, activation loads 11, the weight expansion 3.  A stage then
+// takes the issuing thread about 480 cycles against 400 of pipe time, with or without a second issuing thread,
+// with the issuer in the first or the last warp, and with or without probing the next stage's barrier early.
 #include "bitlinear.cuh"
 #include "tcgen05.cuh"
 #include "tensor_map.cuh"
@@ -34,7 +44,7 @@
 namespace {
 
 // Compile-time shape of one variant of the kernel.
-template <int NT_, int GROUPS_, int SA_, int SB_, int SW_, bool DOUBLE_, bool MERGED_, bool STAGE_OUT_, int ISSUERS_ = 1>
+template <int NT_, int GROUPS_, int SA_, int SB_, int SW_, bool DOUBLE_, bool MERGED_, bool STAGE_OUT_, int ISSUERS_ = 1, bool PAIR_ = false>
 struct PfCfg {
     static constexpr int NT = NT_;                   // token columns per tile
     static constexpr int GROUPS = GROUPS_;           // unpack groups of four warps that take 128-K stages in turn
@@ -59,9 +69,20 @@ struct PfCfg {
     static constexpr int ISSUERS = ISSUERS_;
     static constexpr int NH = NT / ISSUERS;          // token columns per issuer
     static constexpr int UNPACK_WARPS = 4 * GROUPS, EPI_WARPS = 8;
-    static constexpr int WARP_W = UNPACK_WARPS + EPI_WARPS, WARP_B = WARP_W + 1, WARP_MMA = WARP_W + 2;
-    static constexpr int THREADS = (WARP_MMA + ISSUERS) * 32;
-    static constexpr int B_STAGE = NT * 128;
+    // warps 0..3: MMA issuer(s), packed-weight producer, activation producer; then the unpack warps, then the epilogue warps
+    // (both start at a multiple of four: warp % 4 is the tensor-memory lane quarter a warp may touch)
+    static constexpr int WARP_MMA = 0, WARP_W = 2, WARP_B = 3, UNPACK0 = 4, EPI0 = UNPACK0 + UNPACK_WARPS;
+    static constexpr int THREADS = (EPI0 + EPI_WARPS) * 32;
+    // PAIR: two CTAs (a cluster of two, on two SMs) work as one MMA unit (cta_group::2).  Each owns one weight tile of a
+    // pair — its own packed-weight stream, unpack warps, A ring, accumulators and epilogue, exactly as alone — but the
+    // activation tile is split: each CTA loads NT / 2 of its token rows, and the MMAs, issued by one thread of the even
+    // CTA for both, read both halves.  An activation byte is then written to shared memory once per 256 weight rows
+    // instead of once per 128: with the B operand read at 61 bytes per clock by the tensor pipe and written at the same
+    // rate by TMA, a single CTA sits at the bandwidth of its shared memory.
+    static constexpr bool PAIR = PAIR_;
+    static constexpr int CG = PAIR_ ? 2 : 1;
+    static constexpr int B_ROWS = PAIR_ ? NT / 2 : NT;   // token rows of the tile this CTA loads
+    static constexpr int B_STAGE = B_ROWS * 128;
     static constexpr int W_STAGE = 2 * MMF_TILE_ROWS * 16;
     // STAGE_OUT: 2-byte outputs leave through a [NT][128] shared-memory tile and one TMA store per work item
     static constexpr bool STAGE_OUT = STAGE_OUT_;
@@ -76,11 +97,15 @@ struct PfCfg {
     __host__ __device__ static constexpr int b_empty(int slot) { return (MERGED ? A_EMPTY : B_EMPTY) + slot; }
     static_assert(NT % 32 == 0 && NT <= 256, "token tile");
     static_assert((ISSUERS == 1 || ISSUERS == 2) && NH % 16 == 0, "each issuer's columns: a multiple of 16 (MMA N) and of 8 (swizzle atom)");
+    static_assert(!PAIR || (MERGED && ISSUERS == 1 && !STAGE_OUT && NT % 32 == 0), "pair mode: merged rings, one issuer, direct stores");
     static_assert(SMEM + 5 * 1024 <= 227 * 1024, "shared memory (dynamic + static) per CTA");
     __device__ static uint32_t bar_count(int i) {
-        if (i >= ACC_EMPTY) return (uint32_t)EPI_WARPS;
+        if (i >= ACC_EMPTY) return (uint32_t)(EPI_WARPS * CG);   // pair: the other CTA's epilogue warps arrive here too
         if (i >= A_EMPTY) return (uint32_t)ISSUERS;              // A_EMPTY, ACC_FULL: one tcgen05.commit per issuer
-        if (MERGED && i >= A_FULL) return 129u;                  // one unpack group + the activation producer
+        // per CTA: one unpack group + the activation producer; in pair mode lane 0 of each unpack warp arrives for its warp
+        // (an arrive that crosses to the other CTA costs far more than a local one: 128 of them per stage ran the kernel
+        // at 40 % of its speed)
+        if (MERGED && i >= A_FULL) return PAIR ? 9u : 129u;   // pair: 2 x 4 unpack warps + the issuing CTA's activation producer
         if (i >= W_EMPTY) return 128u;                           // W_EMPTY, A_FULL: the 128 threads of one unpack group
         if (i >= B_EMPTY && i < W_FULL) return (uint32_t)ISSUERS;
         return 1u;
@@ -98,7 +123,8 @@ struct PfParams {
     int n_tiles;       // weight tiles
     int group_tiles;   // weight tiles per group
     int m_tiles;       // token tiles
-    int n_work;        // n_tiles * m_tiles
+    int n_work;        // work items: (weight tile, token tile), in pair mode (pair of weight tiles, token tile)
+    int tile_slots;    // weight-tile slots per token tile: n_tiles, in pair mode n_tiles / 2
     int tma_out;       // outputs go through the shared-memory tile and out_map (2-byte dtype, 16-byte aligned rows)
     int skip;          // experiments build only (wrong results, timing only): 1 = no activation loads, 2 = no weight
                        // expansion, 4 = no output stores; 0 in the product build
@@ -159,16 +185,20 @@ bitlinear_mma_prefill_kernel(const __grid_constant__ CUtensorMap q_map, const __
 
     if (tid < C::BAR_COUNT) mbar_init(&bars[tid], C::bar_count(tid));
     if (tid == C::BAR_COUNT) s_abort = 0;
-    if (warp == C::WARP_MMA) tmem_alloc(&s_tmem_base, 512u);
+    if (warp == C::WARP_MMA) tmem_alloc_cg<C::CG>(&s_tmem_base, 512u);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     tc_fence_before();
     __syncthreads();
+    if (C::PAIR) { cluster_arrive(); cluster_wait(); }   // the other CTA's barriers exist before anything arrives on them
     tc_fence_after();
+    const uint32_t rank = C::PAIR ? cluster_ctarank() : 0u;   // 0: the CTA that issues the pair's MMAs
     const uint32_t tmem_base = s_tmem_base;
     const uint32_t tmem_a = tmem_base + C::NACC * C::NT;
     volatile int* abort_flag = &s_abort;
     const int S = (p.KC + 1) / 2;              // 128-K stages per work item
-    const int first = blockIdx.x, step = gridDim.x;
+    const int first = C::PAIR ? (int)(blockIdx.x >> 1) : (int)blockIdx.x, step = C::PAIR ? (int)(gridDim.x >> 1) : (int)gridDim.x;
+    // work item -> this CTA's weight tile (pair mode: tiles 2s and 2s + 1 of slot s) and the token tile
+    auto item_tile = [&](int wk) { return C::PAIR ? 2 * (wk % p.tile_slots) + (int)rank : wk % p.tile_slots; };
     // optional phase trace of CTA 0 (armed by MMF_TRACE_MAGIC in workspace word 1): 28 clock64 slots in the header
     long long* trace = MMF_TRACE_PTR((lane == 0 && blockIdx.x == 0 && a.ws && a.ws[1] == MMF_TRACE_MAGIC)
                            ? reinterpret_cast<long long*>(a.ws + 8) : nullptr);
@@ -181,7 +211,7 @@ bitlinear_mma_prefill_kernel(const __grid_constant__ CUtensorMap q_map, const __
             PfRing w{0, 0, C::SW};
             bool live = true;
             for (int wk = first; wk < p.n_work && live; wk += step) {
-                const int tile = wk % p.n_tiles;
+                const int tile = item_tile(wk);
                 const uint8_t* src = reinterpret_cast<const uint8_t*>(a.packed) + (int64_t)tile * p.KC * (MMF_TILE_ROWS * 16);
                 for (int i = 0; i < S; ++i, w.next()) {
                     const uint32_t bytes = (uint32_t)min(2, p.KC - i * 2) * (MMF_TILE_ROWS * 16);
@@ -198,20 +228,26 @@ bitlinear_mma_prefill_kernel(const __grid_constant__ CUtensorMap q_map, const __
             PfRing bq{0, 0, C::SB};
             bool live = true;
             for (int wk = first; wk < p.n_work && live; wk += step) {
-                const int tile = wk % p.n_tiles, mt = wk / p.n_tiles;
-                const int y = (tile / p.group_tiles) * a.M + mt * C::NT;
+                const int tile = item_tile(wk), mt = wk / p.tile_slots;
+                const int y = (tile / p.group_tiles) * a.M + mt * C::NT + (int)rank * C::B_ROWS;
                 for (int i = 0; i < S; ++i, bq.next()) {
                     if (!mbar_wait(&bars[C::b_empty(bq.slot)], bq.ph ^ 1, abort_flag)) { live = false; break; }
+                    if (C::PAIR && rank != 0) {
+                        // this CTA's half of the tile lands here; its bytes are counted by the issuing CTA's "full" barrier,
+                        // whose own producer announces the bytes of both halves (a transaction count may run negative)
+                        tma_load_2d_pair(b_ring + bq.slot * C::B_STAGE, &q_map, cluster_addr(&bars[C::b_full(bq.slot)], 0u), i * 128, y);
+                        continue;
+                    }
                     if (PF_SKIP(p.skip & 1)) { mbar_arrive(&bars[C::b_full(bq.slot)]); continue; }
-                    mbar_expect_tx(&bars[C::b_full(bq.slot)], (uint32_t)C::B_STAGE);
+                    mbar_expect_tx(&bars[C::b_full(bq.slot)], (uint32_t)(C::CG * C::B_STAGE));
                     tma_load_2d(b_ring + bq.slot * C::B_STAGE, &q_map, &bars[C::b_full(bq.slot)], i * 128, y);
                 }
             }
         }
-    } else if (warp >= C::WARP_MMA) {
+    } else if (warp < C::ISSUERS) {
         // ------------------------------------------------------------ MMA issue: a serial instruction stream per issuer,
         // kept short; issuer `half` owns token columns [half * NH, half * NH + NH) of the tile and of the accumulator
-        if (elect_one()) {
+        if (elect_one() && rank == 0) {
             const int half = warp - C::WARP_MMA;
             if (half != 0) trace = nullptr;
             PfRing bq{0, 0, C::SB}, aq{0, 0, C::SA};
@@ -238,44 +274,49 @@ bitlinear_mma_prefill_kernel(const __grid_constant__ CUtensorMap q_map, const __
                     uint32_t a_addr = tmem_a + aq.slot * 32;
                     uint32_t b_lo = b_lo0 + (uint32_t)bq.slot * b_desc_step;
                     if (i < nfull) {
-                        asm volatile(
-                            "{\n\t.reg .pred p;\n\t.reg .b64 d0, d1, d2, d3;\n\t"
-                            "setp.ne.b32 p, %4, 0;\n\t"
-                            "mov.b64 d0, {%1, %3};\n\t"
-                            "add.u32 %1, %1, 2;\n\t"
-                            "mov.b64 d1, {%1, %3};\n\t"
-                            "add.u32 %1, %1, 2;\n\t"
-                            "mov.b64 d2, {%1, %3};\n\t"
-                            "add.u32 %1, %1, 2;\n\t"
-                            "mov.b64 d3, {%1, %3};\n\t"
-                            "tcgen05.mma.cta_group::1.kind::i8 [%2], [%0], d0, %5, p;\n\t"
-                            "add.u32 %0, %0, 8;\n\t"
-                            "tcgen05.mma.cta_group::1.kind::i8 [%2], [%0], d1, %5, 1;\n\t"
-                            "add.u32 %0, %0, 8;\n\t"
-                            "tcgen05.mma.cta_group::1.kind::i8 [%2], [%0], d2, %5, 1;\n\t"
-                            "add.u32 %0, %0, 8;\n\t"
-                            "tcgen05.mma.cta_group::1.kind::i8 [%2], [%0], d3, %5, 1;\n\t}"
-                            : "+r"(a_addr), "+r"(b_lo)
-                            : "r"(d_addr), "r"(b_hi), "r"(accum), "r"(p.idesc)
-                            : "memory");
+#define PF_FOUR_MMAS(CGS)                                                                                        \
+                        asm volatile(                                                                            \
+                            "{\n\t.reg .pred p;\n\t.reg .b64 d0, d1, d2, d3;\n\t"                                 \
+                            "setp.ne.b32 p, %4, 0;\n\t"                                                          \
+                            "mov.b64 d0, {%1, %3};\n\t"                                                          \
+                            "add.u32 %1, %1, 2;\n\t"                                                             \
+                            "mov.b64 d1, {%1, %3};\n\t"                                                          \
+                            "add.u32 %1, %1, 2;\n\t"                                                             \
+                            "mov.b64 d2, {%1, %3};\n\t"                                                          \
+                            "add.u32 %1, %1, 2;\n\t"                                                             \
+                            "mov.b64 d3, {%1, %3};\n\t"                                                          \
+                            "tcgen05.mma.cta_group::" CGS ".kind::i8 [%2], [%0], d0, %5, p;\n\t"                  \
+                            "add.u32 %0, %0, 8;\n\t"                                                             \
+                            "tcgen05.mma.cta_group::" CGS ".kind::i8 [%2], [%0], d1, %5, 1;\n\t"                  \
+                            "add.u32 %0, %0, 8;\n\t"                                                             \
+                            "tcgen05.mma.cta_group::" CGS ".kind::i8 [%2], [%0], d2, %5, 1;\n\t"                  \
+                            "add.u32 %0, %0, 8;\n\t"                                                             \
+                            "tcgen05.mma.cta_group::" CGS ".kind::i8 [%2], [%0], d3, %5, 1;\n\t}"                 \
+                            : "+r"(a_addr), "+r"(b_lo)                                                           \
+                            : "r"(d_addr), "r"(b_hi), "r"(accum), "r"(p.idesc)                                   \
+                            : "memory")
+                        if constexpr (C::PAIR) PF_FOUR_MMAS("2"); else PF_FOUR_MMAS("1");
+#undef PF_FOUR_MMAS
                     } else {
                         const uint64_t bd = ((uint64_t)b_hi << 32) | b_lo;
-                        mma_i8_ts(d_addr, a_addr, bd, p.idesc, accum);
-                        mma_i8_ts(d_addr, a_addr + 8, bd + 2, p.idesc, 1u);
+                        mma_i8_ts_cg<C::CG>(d_addr, a_addr, bd, p.idesc, accum);
+                        mma_i8_ts_cg<C::CG>(d_addr, a_addr + 8, bd + 2, p.idesc, 1u);
                     }
                     accum = 1;
-                    tc_commit(&bars[C::b_empty(bq.slot)]);   // frees the activation stage (merged: and the A stage) when these MMAs retire
+                    tc_commit_cg<C::CG>(&bars[C::b_empty(bq.slot)]);   // frees the activation stage (merged: and the A stage; pair: in both CTAs) when these MMAs retire
                     if (!C::MERGED) tc_commit(&bars[C::A_EMPTY + aq.slot]);
                 }
-                if (live) tc_commit(&bars[C::ACC_FULL + ab]);
+                if (live) tc_commit_cg<C::CG>(&bars[C::ACC_FULL + ab]);
                 if (it >= 1 && it < 5) trace_mark(trace, 3 + (it - 1) * 3);
             }
             trace_mark(trace, 25);
             if (trace) trace[27] = clock64();
         }
-    } else if (warp < C::UNPACK_WARPS) {
+    } else if (warp < C::UNPACK0) {
+        // spare warp of the first four
+    } else if (warp < C::EPI0) {
         // ------------------------------------------------------------ unpack: lane <-> TMEM lane <-> weight row
-        const int qd = warp & 3, gp = warp >> 2;
+        const int qd = warp & 3, gp = (warp - C::UNPACK0) >> 2;
         const int row = qd * 32 + lane;
         const uint32_t lane_addr = (uint32_t)(qd * 32) << 16;
         PfRing w{0, 0, C::SW}, aq{0, 0, C::SA};
@@ -322,7 +363,15 @@ bitlinear_mma_prefill_kernel(const __grid_constant__ CUtensorMap q_map, const __
                 // 8-lane wavefronts of it returned the next work item's weights.
                 mbar_arrive(&bars[C::W_EMPTY + w.slot]);
                 tc_fence_before();
-                mbar_arrive(&bars[C::A_FULL + (C::MERGED ? sg % C::SB : aq.slot)]);
+                if (C::PAIR) {
+                    __syncwarp();          // tcgen05.wait::st is warp-wide: every lane's stores have completed
+                    if (lane == 0) {
+                        if (rank != 0) mbar_arrive_remote(cluster_addr(&bars[C::A_FULL + sg % C::SB], 0u));
+                        else mbar_arrive(&bars[C::A_FULL + sg % C::SB]);
+                    }
+                } else {
+                    mbar_arrive(&bars[C::A_FULL + (C::MERGED ? sg % C::SB : aq.slot)]);
+                }
 #pragma unroll
                 for (int k = 0; k < C::GROUPS; ++k) { w.next(); aq.next(); }
             }
@@ -330,7 +379,7 @@ bitlinear_mma_prefill_kernel(const __grid_constant__ CUtensorMap q_map, const __
         }
     } else {
         // ------------------------------------------------------------ epilogue: TMEM -> registers -> global memory
-        const int ew = warp - C::UNPACK_WARPS;
+        const int ew = warp - C::EPI0;
         const int lq = ew & 3, hf = ew >> 2;
         const uint32_t lane_addr = (uint32_t)(lq * 32) << 16;
         const int col0 = hf * (C::NT / 2);
@@ -342,7 +391,7 @@ bitlinear_mma_prefill_kernel(const __grid_constant__ CUtensorMap q_map, const __
         bool ok = true;
         int it = 0;
         for (int wk = first; wk < p.n_work && ok; wk += step, ++it) {
-            const int tile = wk % p.n_tiles, mt = wk / p.n_tiles;
+            const int tile = item_tile(wk), mt = wk / p.tile_slots;
             const int g = tile / p.group_tiles;
             const int m0 = mt * C::NT;
             float* sc = s_scale[it & 1];
@@ -376,7 +425,10 @@ bitlinear_mma_prefill_kernel(const __grid_constant__ CUtensorMap q_map, const __
                     // the whole accumulator half is in registers: hand it back to the MMA warp
                     tc_fence_before();
                     __syncwarp();
-                    if (lane == 0) mbar_arrive(&bars[C::ACC_EMPTY + ab]);
+                    if (lane == 0) {
+                        if (C::PAIR && rank != 0) mbar_arrive_remote(cluster_addr(&bars[C::ACC_EMPTY + ab], 0u));
+                        else mbar_arrive(&bars[C::ACC_EMPTY + ab]);
+                    }
                     if (ew == 0 && it < 4) trace_mark(trace, 14 + it * 3);
                 }
                 const int ncols = PF_SKIP(p.skip & 4) ? 0 : mvalid - c * 16;
@@ -431,7 +483,10 @@ bitlinear_mma_prefill_kernel(const __grid_constant__ CUtensorMap q_map, const __
     }
     tc_fence_before();
     __syncthreads();
-    if (warp == C::WARP_MMA) tmem_dealloc(tmem_base, 512u);
+    // pair: neither CTA leaves (or frees tensor memory) while the other may still arrive on its barriers, read its half of
+    // an activation tile or run MMAs on its tensor memory
+    if (C::PAIR) { cluster_arrive(); cluster_wait(); }
+    if (warp == C::WARP_MMA) tmem_dealloc_cg<C::CG>(tmem_base, 512u);
 }
 
 }  // namespace
@@ -449,19 +504,22 @@ int pf_launch(const BitLinearArgs& a, cudaStream_t st) {
     p.n_tiles = (a.N + MMF_TILE_ROWS - 1) / MMF_TILE_ROWS;
     p.group_tiles = p.n_tiles / a.groups;
     p.m_tiles = (a.M + C::NT - 1) / C::NT;
-    const int64_t n_work = (int64_t)p.n_tiles * p.m_tiles;
+    p.tile_slots = C::PAIR ? p.n_tiles / 2 : p.n_tiles;
+    MMF_REQUIRE(!C::PAIR || (p.n_tiles % 2 == 0 && p.group_tiles % 2 == 0 && a.N % MMF_TILE_ROWS == 0), MMF_ERR_BAD_SHAPE,
+                "mmf_bitlinear(mma): the paired kernel needs an even number of whole weight tiles per projection");
+    const int64_t n_work = (int64_t)p.tile_slots * p.m_tiles;
     MMF_REQUIRE(n_work < (1ll << 31), MMF_ERR_BAD_SHAPE, "mmf_bitlinear(mma): problem too large");
     p.n_work = (int)n_work;
     p.skip = g_pf_skip;
-    // instruction descriptor: D=S32, A=S8 (TMEM), B=S8 (smem, K-major), M=128, N=NH (one issuer's columns)
-    p.idesc = (2u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(C::NH >> 3) << 17) | ((uint32_t)(128 >> 4) << 24);
+    // instruction descriptor: D=S32, A=S8 (TMEM), B=S8 (smem, K-major), M=128 (256 across a pair), N=NH (one issuer's columns)
+    p.idesc = (2u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(C::NH >> 3) << 17) | ((uint32_t)((C::PAIR ? 256 : 128) >> 4) << 24);
 
     MmfEncodeTiledFn encode = mmf_encode_tiled();
     MMF_REQUIRE(encode != nullptr, MMF_ERR_CUDA, "mmf_bitlinear(mma): cuTensorMapEncodeTiled is not available from the driver");
     CUtensorMap q_map;
     const cuuint64_t gdim[2] = {(cuuint64_t)a.K, (cuuint64_t)a.groups * (cuuint64_t)a.M};
     const cuuint64_t gstride[1] = {(cuuint64_t)a.K};
-    const cuuint32_t box[2] = {128u, (cuuint32_t)C::NT};
+    const cuuint32_t box[2] = {128u, (cuuint32_t)C::B_ROWS};
     const cuuint32_t estr[2] = {1u, 1u};
     const CUresult cr = encode(&q_map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<int8_t*>(a.q), gdim, gstride, box, estr,
                                CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
@@ -488,15 +546,24 @@ int pf_launch(const BitLinearArgs& a, cudaStream_t st) {
     auto kernel = bitlinear_mma_prefill_kernel<C>;
     MMF_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM));
     cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = dim3((unsigned)(p.n_work < sms ? p.n_work : sms));
+    // one CTA per SM; in pair mode one cluster of two per work item in flight, an even number of CTAs
+    const int ctas = C::PAIR ? 2 * (p.n_work < sms / 2 ? p.n_work : sms / 2) : (p.n_work < sms ? p.n_work : sms);
+    cfg.gridDim = dim3((unsigned)ctas);
     cfg.blockDim = dim3(C::THREADS);
     cfg.dynamicSmemBytes = C::SMEM;
     cfg.stream = st;
-    cudaLaunchAttribute attr[1];
+    cudaLaunchAttribute attr[2];
     attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
+    if (C::PAIR) {
+        attr[1].id = cudaLaunchAttributeClusterDimension;
+        attr[1].val.clusterDim.x = 2;
+        attr[1].val.clusterDim.y = 1;
+        attr[1].val.clusterDim.z = 1;
+        cfg.numAttrs = 2;
+    }
     MMF_CUDA(cudaLaunchKernelEx(&cfg, kernel, q_map, out_map, a, p));
     MMF_LAUNCH_CHECK("bitlinear_mma_prefill_kernel");
     return MMF_OK;
@@ -515,14 +582,24 @@ using PfLongK2 = PfCfg<256, 2, 6, 6, 6, false, true, false, 2>;
 using PfOverlap2 = PfCfg<192, 3, 4, 4, 8, true, true, false, 2>;
 // 7: shape 2 with the activation ring as deep as the A ring (four stages), as it was before; kept for comparison
 using PfOverlapShallow = PfCfg<192, 3, 4, 4, 8, true, true, false>;
+// 8, 9: shapes 2 and 1 run by pairs of CTAs (cta_group::2): each CTA loads half of every activation tile
+using PfOverlapPair = PfCfg<192, 3, 4, 8, 6, true, true, false, 1, true>;
+using PfLongKPair = PfCfg<256, 2, 6, 6, 6, false, true, false, 1, true>;
 
-int pf_pick(const BitLinearArgs& a, int variant) { return variant ? variant : (a.K >= 4096 ? 1 : 2); }
+// Default: the paired shapes when every projection is a whole, even number of weight tiles (each pair of CTAs then takes
+// two tiles of one projection), else the single-CTA shapes.
+int pf_pick(const BitLinearArgs& a, int variant) {
+    if (variant) return variant;
+    const int n_tiles = (a.N + MMF_TILE_ROWS - 1) / MMF_TILE_ROWS;
+    const bool pairs = a.N % MMF_TILE_ROWS == 0 && n_tiles % a.groups == 0 && (n_tiles / a.groups) % 2 == 0;
+    return a.K >= 4096 ? (pairs ? 9 : 1) : (pairs ? 8 : 2);
+}
 
 }  // namespace
 
 int bitlinear_mma_prefill_tile(const BitLinearArgs& a, int variant) {
     const int v = pf_pick(a, variant);
-    return v == 2 || v == 3 || v == 6 || v == 7 ? 192 : 256;
+    return v == 2 || v == 3 || v == 6 || v == 7 || v == 8 ? 192 : 256;
 }
 
 // Launch the persistent kernel (large M).  Same argument contract as bitlinear_mma_launch; `variant` selects one
@@ -535,6 +612,8 @@ int bitlinear_mma_prefill_launch(const BitLinearArgs& a, cudaStream_t st, int va
         case 5: return pf_launch<PfLongK2>(a, st);
         case 6: return pf_launch<PfOverlap2>(a, st);
         case 7: return pf_launch<PfOverlapShallow>(a, st);
+        case 8: return pf_launch<PfOverlapPair>(a, st);
+        case 9: return pf_launch<PfLongKPair>(a, st);
         default: return pf_launch<PfOverlap>(a, st);
     }
 }

@@ -101,6 +101,107 @@ int8_mma_peak_kernel(int n_tokens, int iters, int* status, int commits, int issu
     if (threadIdx.x < 32) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, 512;" ::"r"(tmem) : "memory");
 }
 
+
+#ifdef MMF_EXPERIMENTS
+// The same bare issue loop for a pair of CTAs (cluster of two, cta_group::2): the even CTA's thread 0 issues MMAs of
+// 256 rows x n_tokens columns; each CTA holds 128 rows of A in tensor memory and n_tokens / 2 rows of B in shared memory.
+// `commits`: a multicast tcgen05.commit after every fourth MMA.
+__global__ void __launch_bounds__(128)
+int8_mma_peak_pair_kernel(int n_tokens, int iters, int* status, int commits) {
+    extern __shared__ uint8_t smem_raw[];
+    __shared__ __align__(8) uint64_t bar;
+    __shared__ __align__(8) uint64_t scratch_bar[2];
+    __shared__ uint32_t s_tmem;
+    uint8_t* base = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    for (int i = threadIdx.x; i < (n_tokens * 128) / 4; i += blockDim.x) {
+        uint32_t h = (uint32_t)i * 2654435761u + blockIdx.x * 40503u;
+        h ^= h >> 15; h *= 2246822519u; h ^= h >> 13;
+        reinterpret_cast<uint32_t*>(base)[i] = h;
+    }
+    if (threadIdx.x == 0) {
+        asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(smem_u32(&bar)) : "memory");
+        asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(smem_u32(&scratch_bar[0])) : "memory");
+        asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(smem_u32(&scratch_bar[1])) : "memory");
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (threadIdx.x < 32) {
+        asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], 512;" ::"r"(smem_u32(&s_tmem)) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+    }
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+    asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const uint32_t tmem = s_tmem;
+    uint32_t rank;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(rank));
+    {
+        const uint32_t lane_addr = (uint32_t)((threadIdx.x >> 5) * 32) << 16;
+        for (int c = 0; c < 4; ++c) {
+            uint32_t r[16];
+#pragma unroll
+            for (int j = 0; j < 16; ++j) {
+                uint32_t h = (threadIdx.x * 64u + c * 16u + j) * 2654435761u + blockIdx.x * 7919u;
+                h ^= h >> 15; h *= 2246822519u; h ^= h >> 13;
+                r[j] = h;
+            }
+            asm volatile(
+                "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16};"
+                ::"r"(tmem + lane_addr + 256 + c * 16), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]),
+                "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15])
+                : "memory");
+        }
+        asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+        asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+        __syncthreads();
+        asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+        asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    }
+    if (threadIdx.x == 0 && rank == 0) {
+        uint64_t bd = 0;
+        bd |= (uint64_t)((smem_u32(base) & 0x3FFFFu) >> 4);
+        bd |= (uint64_t)1 << 16;
+        bd |= (uint64_t)(1024 >> 4) << 32;
+        bd |= (uint64_t)1 << 46;
+        bd |= (uint64_t)2 << 61;
+        const uint32_t idesc = (2u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(n_tokens >> 3) << 17) | ((uint32_t)(256 >> 4) << 24);
+#pragma unroll 4
+        for (int i = 0; i < iters; ++i) {
+            const uint32_t a_addr = tmem + 256 + (uint32_t)(i & 7) * 8;
+            const uint64_t b = bd + (uint64_t)((i & 3) * 2);
+            asm volatile(
+                "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+                "tcgen05.mma.cta_group::2.kind::i8 [%0], [%1], %2, %3, p;\n\t}"
+                ::"r"(tmem), "r"(a_addr), "l"(b), "r"(idesc), "r"(i > 0 ? 1u : 0u)
+                : "memory");
+            if ((i & 3) == 3)
+                for (int c = 0; c < commits; ++c)
+                    asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
+                                 ::"r"(smem_u32(&scratch_bar[c & 1])), "h"((uint16_t)3) : "memory");
+        }
+        asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
+                     ::"r"(smem_u32(&bar)), "h"((uint16_t)3) : "memory");
+    }
+    if (threadIdx.x == 0) {     // both CTAs: bounded wait for the MMAs to retire
+        const long long t0 = clock64();
+        uint32_t done = 0;
+        while (!done) {
+            asm volatile("{\n\t.reg .pred P1;\n\tmbarrier.try_wait.parity.shared::cta.b64 P1, [%1], %2;\n\tselp.b32 %0, 1, 0, P1;\n\t}"
+                         : "=r"(done) : "r"(smem_u32(&bar)), "r"(0u) : "memory");
+            if (clock64() - t0 > 4000000000ll) { atomicExch(status, 1); break; }
+        }
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+    asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+    if (threadIdx.x < 32) asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, 512;" ::"r"(tmem) : "memory");
+}
+#endif
+
 }  // namespace
 
 #ifdef MMF_EXPERIMENTS
@@ -126,6 +227,35 @@ extern "C" int mmf_int8_mma_peak(int n_tokens, int iters, int* status_dev, doubl
     MMF_CUDA(cudaEventCreate(&e1));
     MMF_CUDA(cudaMemset(status_dev, 0, sizeof(int)));
     // 150 KB of shared memory per CTA keeps it at one CTA per SM (each allocates all of tensor memory)
+#ifdef MMF_EXPERIMENTS
+    if (g_probe_issuers == 3) {      // pair mode (cta_group::2): clusters of two CTAs, 256-row MMAs
+        MMF_REQUIRE(n_tokens % 32 == 0, MMF_ERR_BAD_SHAPE, "mmf_int8_mma_peak(pair): n_tokens must be a multiple of 32");
+        MMF_CUDA(cudaFuncSetAttribute(int8_mma_peak_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)(150 * 1024)));
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = dim3((unsigned)(sms & ~1));
+        cfg.blockDim = dim3(128);
+        cfg.dynamicSmemBytes = 150 * 1024;
+        cudaLaunchAttribute attr[1];
+        attr[0].id = cudaLaunchAttributeClusterDimension;
+        attr[0].val.clusterDim.x = 2; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
+        cfg.attrs = attr; cfg.numAttrs = 1;
+        MMF_CUDA(cudaLaunchKernelEx(&cfg, int8_mma_peak_pair_kernel, n_tokens, 64, status_dev, g_probe_commits));
+        MMF_CUDA(cudaEventRecord(e0));
+        MMF_CUDA(cudaLaunchKernelEx(&cfg, int8_mma_peak_pair_kernel, n_tokens, iters, status_dev, g_probe_commits));
+        MMF_CUDA(cudaEventRecord(e1));
+        MMF_CUDA(cudaEventSynchronize(e1));
+        MMF_LAUNCH_CHECK("int8_mma_peak_pair_kernel");
+        float msp = 0.0f;
+        MMF_CUDA(cudaEventElapsedTime(&msp, e0, e1));
+        cudaEventDestroy(e0);
+        cudaEventDestroy(e1);
+        int stp = 0;
+        MMF_CUDA(cudaMemcpy(&stp, status_dev, sizeof(int), cudaMemcpyDeviceToHost));
+        MMF_REQUIRE(stp == 0, MMF_ERR_TIMEOUT, "mmf_int8_mma_peak(pair): the MMAs did not retire in time");
+        *tops_host = 2.0 * 256.0 * n_tokens * 32.0 * (double)iters * (sms / 2) / ((double)msp * 1e-3) / 1e12;
+        return MMF_OK;
+    }
+#endif
     int8_mma_peak_kernel<<<sms, 128, 150 * 1024>>>(n_tokens, 64, status_dev, g_probe_commits, issuers);     // warm-up
     MMF_CUDA(cudaEventRecord(e0));
     int8_mma_peak_kernel<<<sms, 128, 150 * 1024>>>(n_tokens, iters, status_dev, g_probe_commits, issuers);

@@ -173,6 +173,62 @@ __device__ __forceinline__ void tmem_ld16(uint32_t addr, uint32_t (&r)[16]) {
 __device__ __forceinline__ void tmem_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
 __device__ __forceinline__ void tmem_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 
+// ---- forms for a pair of CTAs working as one MMA unit (cta_group::2): one thread of the even CTA of the pair issues
+// MMAs of 256 rows (128 of A and of D in each CTA's tensor memory) whose B operand is split between the two CTAs'
+// shared memories.  Every tcgen05 instruction of such a kernel that takes a cta_group carries ::2.
+template <int CG> __device__ __forceinline__ void tmem_alloc_cg(uint32_t* slot, uint32_t cols) {
+    if constexpr (CG == 2) {
+        asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(slot)), "r"(cols) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+    } else {
+        tmem_alloc(slot, cols);
+    }
+}
+template <int CG> __device__ __forceinline__ void tmem_dealloc_cg(uint32_t addr, uint32_t cols) {
+    if constexpr (CG == 2) asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(addr), "r"(cols) : "memory");
+    else tmem_dealloc(addr, cols);
+}
+// commit of the pair's MMAs: arrives on the barrier at this offset in both CTAs of the pair (CG == 2) or in this CTA
+template <int CG> __device__ __forceinline__ void tc_commit_cg(uint64_t* bar) {
+    if constexpr (CG == 2)
+        asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
+                     ::"r"(smem_u32(bar)), "h"((uint16_t)3) : "memory");
+    else tc_commit(bar);
+}
+template <int CG> __device__ __forceinline__ void mma_i8_ts_cg(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
+    if constexpr (CG == 2)
+        asm volatile(
+            "{\n\t.reg .pred p;\n\t"
+            "setp.ne.b32 p, %4, 0;\n\t"
+            "tcgen05.mma.cta_group::2.kind::i8 [%0], [%1], %2, %3, p;\n\t}"
+            ::"r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate)
+            : "memory");
+    else mma_i8_ts(d_tmem, a_tmem, b_desc, idesc, accumulate);
+}
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+    uint32_t r;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+    return r;
+}
+// shared::cluster address of the object at `my_smem_addr` in the CTA with rank `rank` of this cluster
+__device__ __forceinline__ uint32_t cluster_addr(const void* my_smem_addr, uint32_t rank) {
+    uint32_t r;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(smem_u32(my_smem_addr)), "r"(rank));
+    return r;
+}
+// Arrive on a barrier of another CTA of the cluster.  Relaxed: what the arrival announces (tensor-memory stores that
+// tcgen05.wait::st has seen complete, accumulator columns already read into registers) is finished before the
+// instruction issues, and a release at cluster scope stalls the arriving thread for most of a microsecond.
+__device__ __forceinline__ void mbar_arrive_remote(uint32_t cluster_bar_addr) {
+    asm volatile("mbarrier.arrive.relaxed.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_bar_addr) : "memory");
+}
+// tiled load into this CTA's shared memory whose completion bytes are credited to a barrier of the pair's other CTA
+__device__ __forceinline__ void tma_load_2d_pair(void* dst, const CUtensorMap* map, uint32_t cluster_bar_addr, int x, int y) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+        ::"r"(smem_u32(dst)), "l"(map), "r"(cluster_bar_addr), "r"(x), "r"(y)
+        : "memory");
+}
 __device__ __forceinline__ void cluster_arrive() { asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory"); }
 __device__ __forceinline__ void cluster_wait() { asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory"); }
 // Phase trace for kernel experiments, compiled only into the experiments build (-DMMF_EXPERIMENTS): CTA (0,0,0) writes
