@@ -539,9 +539,10 @@ def run_ours(args):
             del w
             q, dq, rs = K.act_quant(torch.randn(Mtok, Kd, device=device).bfloat16(), None, 1e-6)
             out = torch.empty(Mtok, N, device=device, dtype=torch.bfloat16)
-            K.bitlinear(q, dq, rs, pw, torch.bfloat16, out=out)
+            for _ in range(3):      # warm-up: steady state (the timed launches then queue behind one another)
+                K.bitlinear(q, dq, rs, pw, torch.bfloat16, out=out)
             torch.cuda.synchronize()
-            t = device_time_ms(lambda: K.bitlinear(q, dq, rs, pw, torch.bfloat16, out=out), 5, stream)
+            t = device_time_ms(lambda: K.bitlinear(q, dq, rs, pw, torch.bfloat16, out=out), 20, stream)
             tops = 2.0 * Mtok * Kd * N / (t * 1e-3) / 1e12
             ops[f"M16384_K{Kd}_N{N}"] = {"us": t * 1e3, "tops": tops, "frac_of_int8_peak": tops / peak_tops}
             del pw, q, dq, rs, out
@@ -552,12 +553,27 @@ def run_ours(args):
         for T in (2048, 8192):
             x = torch.randn(8, T, 2048, device=device).bfloat16()
             g = torch.nn.functional.logsigmoid(torch.randn(8, T, 2048, device=device))
-            K.hgrn_scan(x, g, None, True, gate_is_log=True, state_dtype=torch.float32)
+            for _ in range(3):
+                K.hgrn_scan(x, g, None, True, gate_is_log=True, state_dtype=torch.float32)
             torch.cuda.synchronize()
-            t = device_time_ms(lambda: K.hgrn_scan(x, g, None, True, gate_is_log=True, state_dtype=torch.float32), 5, stream)
+            t = device_time_ms(lambda: K.hgrn_scan(x, g, None, True, gate_is_log=True, state_dtype=torch.float32), 20, stream)
             gbs = 8.0 * x.numel() / (t * 1e-3) / 1e9
             hg[f"B8_T{T}_D2048"] = {"us": t * 1e3, "gb_per_s": gbs, "frac_of_hbm_peak": gbs / peak_gbs}
             del x, g
+        # the scan as the model runs it on a prompt: raw i / f projections of 16 x 2048 tokens (column slabs of one
+        # [B, T, 3D] bf16 tensor), gate math fused in, 6 algorithmic bytes per element
+        ifg = torch.randn(16, 2048, 3 * 2048, device=device).bfloat16()
+        lb = torch.rand(2048, device=device).bfloat16()
+        st0 = torch.zeros(16, 2048, device=device)
+        o_raw = torch.empty(16, 2048, 2048, device=device, dtype=torch.bfloat16)
+        raw = lambda: K.hgrn_gated(ifg[..., :2048], ifg[..., 2048:4096], lb, st0, out=o_raw)
+        for _ in range(3):
+            raw()
+        torch.cuda.synchronize()
+        t = device_time_ms(raw, 20, stream)
+        gbs = 6.0 * o_raw.numel() / (t * 1e-3) / 1e9
+        hg["raw_gate_B16_T2048_D2048"] = {"us": t * 1e3, "gb_per_s": gbs, "frac_of_hbm_peak": gbs / peak_gbs}
+        del ifg, lb, st0, o_raw
         extras["hgrn_scan"] = hg
         # the 2.7B shapes (32 blocks, hidden 2560, intermediate 6912) at the per-GPU batch of the 8-GPU throughput
         # configuration (512 sequences / 8)
