@@ -74,7 +74,7 @@ def config_dict(args, world):
 
 # dram__bytes_read+write of one bitlinear_mma_kernel launch (M=32, K=2048, N=11264) from the profiler, per byte of
 # packed weights that launch streams; DRAM traffic of this kernel is the weight stream plus the activation codes
-NCU_DRAM_BYTES_PER_WEIGHT_BYTE = 6.124 / 5.767
+NCU_DRAM_BYTES_PER_WEIGHT_BYTE = 5.883 / 5.767
 
 
 def peaks():
@@ -494,7 +494,7 @@ def run_ours(args):
         "bound": "hbm", "kernel": "bitlinear (2-bit weight stream; %d launches per step)" % probe.launches,
         "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
         "traffic": bytes_per_launch * NCU_DRAM_BYTES_PER_WEIGHT_BYTE if B == 32 else None,
-        "traffic_source": "ncu dram bytes of the gate_proj launch at batch 32 (6.124 MB for 5.767 MB of packed weights), "
+        "traffic_source": "ncu dram bytes of the gate_proj launch at batch 32 (5.883 MB for 5.767 MB of packed weights), "
                           "scaled to the average launch by weight bytes; see profiles/bitlinear_mma_M32_K2048_N11264.md",
         "peak_source": peak_src, "bytes_per_launch": bytes_per_launch, "us_per_launch": probe_ms * 1e3 / probe.launches,
         "weight_bytes_per_step": probe.packed_bytes,
