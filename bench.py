@@ -458,9 +458,8 @@ def run_ours(args):
         ids_host.copy_(dec.next.cpu()[:, None])
 
         def e2e_step():
-            dec.ids.copy_(ids_host, non_blocking=True)       # H2D: this step's input tokens
-            dec.step()
-            out_host.copy_(dec.next, non_blocking=True)      # D2H: the step's result
+            # H2D of this step's input tokens, the step, D2H of its result: one graph launch (GreedyDecoder.step_host)
+            dec.step_host(ids_host, out_host)
             torch.cuda.current_stream().synchronize()
             ids_host.copy_(out_host[:, None])                # the host closes the loop
 

@@ -37,6 +37,7 @@ class GreedyDecoder:
         # through Python (about 19 us of host time each), which is more than the GPU needs for a short prompt
         self._prompt_seen: dict = {}       # prompt length -> times seen
         self._prompt_graphs: dict = {}     # prompt length -> (graph, static ids buffer), at most PROMPT_GRAPHS entries
+        self._host_graphs: dict = {}       # (ids_host ptr, out_host ptr) -> (graph with the two copies, the buffers)
 
     def _step_eager(self):
         out = self.model(input_ids=self.ids, past_key_values=self.cache, use_cache=True)
@@ -45,7 +46,9 @@ class GreedyDecoder:
         self.last_logits = out.logits[:, -1]
         kernels.argmax_rows(self.last_logits, out=self.next)
 
-    def _capture(self):
+    def _capture(self, ids_host: Optional[torch.Tensor] = None, out_host: Optional[torch.Tensor] = None):
+        """Capture one decode step.  With pinned host buffers the copy of the input ids to the device and of the new
+        tokens back are nodes of the same graph (returned, not stored in self.graph)."""
         saved = [tuple(s.clone() for s in layer) for layer in self.cache.states]
         saved_ids = self.ids.clone()
         side = torch.cuda.Stream(device=self.device)
@@ -59,13 +62,19 @@ class GreedyDecoder:
         # capture on the warm-up stream: its split-K workspace already exists (and is zero), so no fill of a
         # fresh workspace is recorded into the graph
         with torch.cuda.graph(graph, stream=side):
+            if ids_host is not None:
+                self.ids.copy_(ids_host, non_blocking=True)
             self._step_eager()
+            if out_host is not None:
+                out_host.copy_(self.next, non_blocking=True)
         self.kernels_per_step = _lib.launch_count - before
-        self.graph = graph
+        if ids_host is None and out_host is None:
+            self.graph = graph
         for layer, keep in zip(self.cache.states, saved):   # undo the warm-up steps' effect on the state
             for dst, src in zip(layer, keep):
                 dst.copy_(src)
         self.ids.copy_(saved_ids)
+        return graph
 
     PROMPT_GRAPH_MAX_TOKENS = 8192   # larger prompts are bound by the GPU, and their graphs would pin gigabytes
     PROMPT_GRAPHS = 4
@@ -136,6 +145,28 @@ class GreedyDecoder:
                 self._capture()
             self.graph.replay()
         return self.next
+
+    @torch.no_grad()
+    def step_host(self, ids_host: torch.Tensor, out_host: torch.Tensor) -> None:
+        """One decode step driven from the host: the token ids [B, 1] are read from `ids_host`, the new tokens [B] are
+        written to `out_host` (both int64 in pinned memory).  The two copies and the step's kernels are one CUDA graph
+        launch; the call returns once it is enqueued — synchronise the stream before reading `out_host`."""
+        if not (ids_host.is_pinned() and out_host.is_pinned()):
+            raise ValueError("step_host needs pinned host buffers")
+        if ids_host.shape != self.ids.shape or out_host.shape != self.next.shape or ids_host.dtype != torch.int64 \
+                or out_host.dtype != torch.int64:
+            raise ValueError(f"step_host needs int64 buffers of shape {tuple(self.ids.shape)} and {tuple(self.next.shape)}")
+        if not self._use_graph:
+            self.ids.copy_(ids_host, non_blocking=True)
+            self.step()
+            out_host.copy_(self.next, non_blocking=True)
+            return
+        key = (ids_host.data_ptr(), out_host.data_ptr())
+        entry = self._host_graphs.get(key)
+        if entry is None:
+            entry = (self._capture(ids_host, out_host), ids_host, out_host)   # the graph keeps pointing at these buffers
+            self._host_graphs = {key: entry}
+        entry[0].replay()
 
     @torch.no_grad()
     def generate(self, prompt_ids: torch.Tensor, max_new_tokens: int) -> torch.Tensor:

@@ -475,6 +475,36 @@ def test_decoder_replays_repeated_prompt_lengths_from_a_graph(mm):
     mm.kernels.check_status()
 
 
+def test_decoder_step_driven_from_pinned_host_buffers(mm):
+    """`GreedyDecoder.step_host`: ids in from pinned host memory, new tokens out to pinned host memory, the two copies
+    captured in the same CUDA graph as the step — the token stream equals the device-resident loop, and unpinned or
+    misshaped buffers are refused."""
+    from matmulfreellm_b200.engine import GreedyDecoder
+    cfg = tiny_cfg()
+    sd = O.random_weights(cfg, seed=8)
+    model = build_gpu_model(sd, cfg, torch.bfloat16)
+    ids = torch.randint(0, 32000, (3, 7), generator=torch.Generator().manual_seed(3)).cuda()
+    ref = GreedyDecoder(model, 3)
+    want = [ref.prefill(ids).clone()]
+    for _ in range(12):
+        want.append(ref.step().clone())
+    dec = GreedyDecoder(model, 3)
+    ids_host = torch.empty(3, 1, dtype=torch.int64).pin_memory()
+    out_host = torch.empty(3, dtype=torch.int64).pin_memory()
+    first = dec.prefill(ids).cpu()
+    assert torch.equal(first, want[0].cpu())
+    ids_host.copy_(first[:, None])
+    for t in range(12):
+        dec.step_host(ids_host, out_host)
+        torch.cuda.current_stream().synchronize()
+        assert torch.equal(out_host, want[t + 1].cpu()), t
+        ids_host.copy_(out_host[:, None])
+    with pytest.raises(ValueError):
+        dec.step_host(torch.empty(3, 1, dtype=torch.int64), out_host)
+    with pytest.raises(ValueError):
+        dec.step_host(ids_host, torch.empty(4, dtype=torch.int64).pin_memory())
+
+
 def test_generate_graph_path_equals_step_loop(mm):
     """`generate` replays greedy decode steps from a CUDA graph; tokens, the handling of eos (finished sequences
     keep emitting it, the result ends where the last sequence finishes) and left-padded prompts must equal the
