@@ -66,6 +66,29 @@ def test_bitlinear_sweep_large_m_vs_oracle(K, M, Kdim, N):
     K.check_status()
 
 
+@pytest.mark.parametrize("Kdim,N", [(2048, 2048), (2560, 2560), (5632, 2048)])
+def test_bitlinear_large_m_repeatable(K, Kdim, N):
+    """The same 16384-row call 60 times: every run returns the bits of the first one, whose sampled rows equal the
+    oracle's.  (A synchronisation slip between the weight stream and the unpack warps once showed up as 4 - 32 wrong rows
+    in one run out of seven, only with the fast bf16 epilogue; a single comparison would have missed it.)"""
+    M = 16384
+    x, w, _ = O.bitlinear_case(M, Kdim, N, seed=7 + Kdim)
+    codes, mean = O.ternary_codes(w)
+    q_ref, dq_ref, _ = O.act_codes(x, None, 1e-6)
+    pw = K.pack_weight(w.cuda())
+    q, dq, rs = K.act_quant(x.cuda(), None, 1e-6)
+    first = K.bitlinear(q, dq, rs, pw, torch.bfloat16).clone()
+    rows = _sample_rows(M, 128, seed=N)[::8]
+    acc_ref = O.bitlinear_acc(q_ref[rows], codes)
+    want = torch.from_numpy(acc_ref.astype(np.float32) * (dq_ref[rows] * np.float32(mean))[:, None]).to(torch.bfloat16)
+    assert torch.equal(first[torch.from_numpy(rows).cuda()].cpu(), want)
+    out = torch.empty_like(first)
+    for rep in range(60):
+        K.bitlinear(q, dq, rs, pw, torch.bfloat16, out=out)
+        assert torch.equal(out, first), rep
+    K.check_status()
+
+
 @pytest.mark.parametrize("T", [2048, 8192])
 @pytest.mark.parametrize("log", [True, False])
 def test_hgrn_full_size_vs_oracle(K, T, log):
