@@ -84,7 +84,11 @@ struct PfCfg {
     static constexpr int B_ROWS = PAIR_ ? NT / 2 : NT;   // token rows of the tile this CTA loads
     static constexpr int B_STAGE = B_ROWS * 128;
     static constexpr int W_STAGE = 2 * MMF_TILE_ROWS * 16;
-    // STAGE_OUT: 2-byte outputs leave through a [NT][128] shared-memory tile and one TMA store per work item
+    // STAGE_OUT: 2-byte outputs leave through a shared-memory tile and two TMA stores per work item.  The epilogue warps
+    // read the accumulator in the 16x256b fragment layout (a thread holds two adjacent token columns of rows r and r + 8,
+    // like an MMA accumulator fragment), convert pairs with one packed instruction and transpose with stmatrix: 2 loads +
+    // 2 stmatrix per 16 columns x 32 rows instead of 1 load + 16 two-byte stores.  The tile is two [NT][64 rows] halves in
+    // the 128-byte-swizzle layout (stmatrix writes conflict-free; the TMA store undoes the swizzle).
     static constexpr bool STAGE_OUT = STAGE_OUT_;
     static constexpr int OUT_STAGE = STAGE_OUT ? NT * MMF_TILE_ROWS * 2 : 0;
     static constexpr int SMEM = 1024 + SB * B_STAGE + SW * W_STAGE + OUT_STAGE;
@@ -97,7 +101,7 @@ struct PfCfg {
     __host__ __device__ static constexpr int b_empty(int slot) { return (MERGED ? A_EMPTY : B_EMPTY) + slot; }
     static_assert(NT % 32 == 0 && NT <= 256, "token tile");
     static_assert((ISSUERS == 1 || ISSUERS == 2) && NH % 16 == 0, "each issuer's columns: a multiple of 16 (MMA N) and of 8 (swizzle atom)");
-    static_assert(!PAIR || (MERGED && ISSUERS == 1 && !STAGE_OUT && NT % 32 == 0), "pair mode: merged rings, one issuer, direct stores");
+    static_assert(!PAIR || (MERGED && ISSUERS == 1 && NT % 32 == 0), "pair mode: merged rings, one issuer");
     static_assert(SMEM + 5 * 1024 <= 227 * 1024, "shared memory (dynamic + static) per CTA");
     __device__ static uint32_t bar_count(int i) {
         if (i >= ACC_EMPTY) return (uint32_t)(EPI_WARPS * CG);   // pair: the other CTA's epilogue warps arrive here too
@@ -161,6 +165,29 @@ __device__ __forceinline__ void pf_store_chunk(const BitLinearArgs& a, const uin
             p += a.ld_out;
         }
     }
+}
+
+// accumulator fragment: 16 TMEM lanes x 16 columns starting at `taddr`; thread t receives, for the two 8-column blocks
+// k = 0, 1: r[4k] = (lane t/4, column 8k + 2(t%4)), r[4k+1] = (same lane, next column), r[4k+2], r[4k+3] = lane t/4 + 8
+__device__ __forceinline__ void tmem_ld_frag16(uint32_t taddr, uint32_t (&r)[8]) {
+    asm volatile("tcgen05.ld.sync.aligned.16x256b.x2.b32 {%0, %1, %2, %3, %4, %5, %6, %7}, [%8];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7])
+                 : "r"(taddr)
+                 : "memory");
+}
+// four 8x8 matrices of 16-bit elements, each stored transposed: thread 8i + j supplies the address of the 16 bytes that
+// receive column j of matrix i
+__device__ __forceinline__ void stmatrix_x4_trans(uint32_t smem_addr, uint32_t a, uint32_t b, uint32_t c, uint32_t d) {
+    asm volatile("stmatrix.sync.aligned.m8n8.x4.trans.shared.b16 [%0], {%1, %2, %3, %4};" ::"r"(smem_addr), "r"(a), "r"(b), "r"(c), "r"(d)
+                 : "memory");
+}
+__device__ __forceinline__ uint32_t pack_out2(float lo, float hi, int out_dtype) {
+    if (out_dtype == MMF_BF16) {
+        const __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+        return *reinterpret_cast<const uint32_t*>(&v);
+    }
+    const __half2 v = __floats2half2_rn(lo, hi);
+    return *reinterpret_cast<const uint32_t*>(&v);
 }
 
 template <typename C>
@@ -386,7 +413,16 @@ bitlinear_mma_prefill_kernel(const __grid_constant__ CUtensorMap q_map, const __
         const int eidx = ew * 32 + lane;              // the token column (< NT) whose constants this thread stages
         uint16_t* ostage = reinterpret_cast<uint16_t*>(w_ring + C::SW * C::W_STAGE);   // [NT][128] output tile (STAGE_OUT)
         const bool staged = C::STAGE_OUT && p.tma_out;
-        const int nl = lq * 32 + lane;                // weight row inside the tile
+        // stmatrix address of this lane for accumulator fragments of lanes [lq*32 + 16*h2, +16): lane 8i + j writes token
+        // column 8(i/2) + j of the chunk, rows 8(i%2).. of the fragment; half tile by row / 64, 16-byte chunk XOR (token % 8)
+        uint32_t st_off[2];
+#pragma unroll
+        for (int h2 = 0; h2 < 2; ++h2) {
+            const int i = lane >> 3, j = lane & 7;
+            const int n0 = lq * 32 + 16 * h2 + 8 * (i & 1);
+            st_off[h2] = (uint32_t)((n0 >> 6) * (C::NT * 128) + (8 * (i >> 1) + j) * 128 + ((((n0 & 63) >> 3) ^ j) << 4));
+        }
+        const uint32_t ostage_u32 = smem_u32(ostage);
         pdl_wait();                                   // dq / rowsum come from the preceding kernel
         bool ok = true;
         int it = 0;
@@ -413,6 +449,46 @@ bitlinear_mma_prefill_kernel(const __grid_constant__ CUtensorMap q_map, const __
             const int n = tile * MMF_TILE_ROWS + lq * 32 + lane;
             const bool n_ok = n < a.N;
             const int mvalid = min(C::NT / 2, a.M - m0 - col0);    // valid token columns in this warp's half (may be <= 0)
+            if (staged) {
+                // columns past M carry zero constants and rows past N garbage: the TMA store clips both
+                uint32_t fr[2][2][8];
+                const uint32_t acc_col = tmem_base + (uint32_t)ab * C::NT + (uint32_t)col0;
+                const uint32_t lane_lo = (uint32_t)(lq * 32) << 16, lane_hi = (uint32_t)(lq * 32 + 16) << 16;
+                tmem_ld_frag16(acc_col + lane_lo, fr[0][0]);
+                tmem_ld_frag16(acc_col + lane_hi, fr[0][1]);
+#pragma unroll
+                for (int c = 0; c < C::NT / 32; ++c) {
+                    tmem_wait_ld();
+                    if (c + 1 < C::NT / 32) {
+                        tmem_ld_frag16(acc_col + lane_lo + (c + 1) * 16, fr[(c + 1) & 1][0]);
+                        tmem_ld_frag16(acc_col + lane_hi + (c + 1) * 16, fr[(c + 1) & 1][1]);
+                    } else {
+                        tc_fence_before();
+                        __syncwarp();
+                        if (lane == 0) {
+                            if (C::PAIR && rank != 0) mbar_arrive_remote(cluster_addr(&bars[C::ACC_EMPTY + ab], 0u));
+                            else mbar_arrive(&bars[C::ACC_EMPTY + ab]);
+                        }
+                        if (ew == 0 && it < 4) trace_mark(trace, 14 + it * 3);
+                    }
+                    if (PF_SKIP(p.skip & 4)) continue;
+                    const int cc = col0 + c * 16;
+                    // this thread's token columns: cc + 8k + 2(lane % 4) and the next one, k = 0, 1
+                    const int2 r0 = *reinterpret_cast<const int2*>(rs + cc + 2 * (lane & 3));
+                    const int2 r1 = *reinterpret_cast<const int2*>(rs + cc + 8 + 2 * (lane & 3));
+                    const float2 s0 = *reinterpret_cast<const float2*>(sc + cc + 2 * (lane & 3));
+                    const float2 s1 = *reinterpret_cast<const float2*>(sc + cc + 8 + 2 * (lane & 3));
+#pragma unroll
+                    for (int h2 = 0; h2 < 2; ++h2) {
+                        const uint32_t (&f)[8] = fr[c & 1][h2];
+                        const uint32_t p0 = pack_out2(__fmul_rn((float)((int32_t)f[0] - r0.x), s0.x), __fmul_rn((float)((int32_t)f[1] - r0.y), s0.y), a.out_dtype);
+                        const uint32_t p1 = pack_out2(__fmul_rn((float)((int32_t)f[2] - r0.x), s0.x), __fmul_rn((float)((int32_t)f[3] - r0.y), s0.y), a.out_dtype);
+                        const uint32_t p2 = pack_out2(__fmul_rn((float)((int32_t)f[4] - r1.x), s1.x), __fmul_rn((float)((int32_t)f[5] - r1.y), s1.y), a.out_dtype);
+                        const uint32_t p3 = pack_out2(__fmul_rn((float)((int32_t)f[6] - r1.x), s1.x), __fmul_rn((float)((int32_t)f[7] - r1.y), s1.y), a.out_dtype);
+                        stmatrix_x4_trans(ostage_u32 + st_off[h2] + (uint32_t)(cc * 128), p0, p1, p2, p3);
+                    }
+                }
+            } else {
             uint32_t v[2][16];
             const uint32_t acc_addr = tmem_base + (uint32_t)ab * C::NT + lane_addr + col0;
             tmem_ld16(acc_addr, v[0]);
@@ -432,27 +508,7 @@ bitlinear_mma_prefill_kernel(const __grid_constant__ CUtensorMap q_map, const __
                     if (ew == 0 && it < 4) trace_mark(trace, 14 + it * 3);
                 }
                 const int ncols = PF_SKIP(p.skip & 4) ? 0 : mvalid - c * 16;
-                if (staged) {
-                    // columns past M carry zero constants and rows past N garbage: the TMA store clips both
-                    const int cc = col0 + c * 16;
-                    uint16_t* po = ostage + cc * MMF_TILE_ROWS + nl;
-#pragma unroll
-                    for (int j4 = 0; j4 < 4; ++j4) {
-                        const int4 r4 = *reinterpret_cast<const int4*>(rs + cc + j4 * 4);
-                        const float4 s4 = *reinterpret_cast<const float4*>(sc + cc + j4 * 4);
-                        const int rr[4] = {r4.x, r4.y, r4.z, r4.w};
-                        const float ss[4] = {s4.x, s4.y, s4.z, s4.w};
-#pragma unroll
-                        for (int j = 0; j < 4; ++j) {
-                            const float f = __fmul_rn((float)((int32_t)v[c & 1][j4 * 4 + j] - rr[j]), ss[j]);
-                            po[(j4 * 4 + j) * MMF_TILE_ROWS] =
-                                a.out_dtype == MMF_BF16 ? __bfloat16_as_ushort(__float2bfloat16_rn(f)) : __half_as_ushort(__float2half_rn(f));
-                        }
-                    }
-                    if (a.acc_out && n_ok)
-                        for (int j = 0; j < 16 && j < ncols; ++j)
-                            a.acc_out[(int64_t)(m0 + cc + j) * a.N + n] = (int32_t)v[c & 1][j] - rs[cc + j];
-                } else if (n_ok && ncols > 0) {
+                if (n_ok && ncols > 0) {
                     const int cc = col0 + c * 16;
                     if (a.acc_out) {
                         for (int j = 0; j < 16 && j < ncols; ++j)
@@ -463,12 +519,14 @@ bitlinear_mma_prefill_kernel(const __grid_constant__ CUtensorMap q_map, const __
                     else pf_store_chunk<float>(a, v[c & 1], rs + cc, sc + cc, m0 + cc, n, ncols);
                 }
             }
+            }
             if (ew == 0 && it < 4) trace_mark(trace, 15 + it * 3);
             if (staged) {
                 fence_async_smem();
                 asm volatile("bar.sync 1, %0;" ::"n"(C::EPI_WARPS * 32) : "memory");
-                if (ew == 0 && lane == 0) {
+                if (ew == 0 && lane == 0 && !PF_SKIP(p.skip & 4)) {
                     tma_store_2d(&out_map, ostage, tile * MMF_TILE_ROWS, m0);
+                    tma_store_2d(&out_map, reinterpret_cast<const uint8_t*>(ostage) + C::NT * 128, tile * MMF_TILE_ROWS + 64, m0);
                     bulk_commit();
                 }
             }
@@ -529,12 +587,13 @@ int pf_launch(const BitLinearArgs& a, cudaStream_t st) {
     // output map for the staged epilogue: [M][N] rows of ld_out elements, box = one [NT tokens x 128 rows] tile
     CUtensorMap out_map = q_map;
     p.tma_out = 0;
-    if (C::STAGE_OUT && a.out_dtype != MMF_F32 && mmf_aligned(a.out, 16) && (a.ld_out * 2) % 16 == 0) {
+    // (calls that also want the int32 accumulators take the direct-store epilogue)
+    if (C::STAGE_OUT && a.out_dtype != MMF_F32 && !a.acc_out && mmf_aligned(a.out, 16) && (a.ld_out * 2) % 16 == 0) {
         const cuuint64_t odim[2] = {(cuuint64_t)a.N, (cuuint64_t)a.M};
         const cuuint64_t ostride[1] = {(cuuint64_t)a.ld_out * 2};
-        const cuuint32_t obox[2] = {(cuuint32_t)MMF_TILE_ROWS, (cuuint32_t)C::NT};
+        const cuuint32_t obox[2] = {64u, (cuuint32_t)C::NT};     // one half tile: [NT tokens][64 rows], 128-byte swizzle
         const CUresult cr2 = encode(&out_map, CU_TENSOR_MAP_DATA_TYPE_UINT16, 2, a.out, odim, ostride, obox, estr,
-                                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
                                     CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
         MMF_REQUIRE(cr2 == CUDA_SUCCESS, MMF_ERR_CUDA, "mmf_bitlinear(mma): cuTensorMapEncodeTiled (output) failed (%d)", (int)cr2);
         p.tma_out = 1;
@@ -585,6 +644,9 @@ using PfOverlapShallow = PfCfg<192, 3, 4, 4, 8, true, true, false>;
 // 8, 9: shapes 2 and 1 run by pairs of CTAs (cta_group::2): each CTA loads half of every activation tile
 using PfOverlapPair = PfCfg<192, 3, 4, 8, 6, true, true, false, 1, true>;
 using PfLongKPair = PfCfg<256, 2, 6, 6, 6, false, true, false, 1, true>;
+// 10, 11: shapes 8 and 9 with the stmatrix + TMA-store epilogue
+using PfOverlapPairSt = PfCfg<192, 3, 4, 8, 6, true, true, true, 1, true>;
+using PfLongKPairSt = PfCfg<256, 2, 6, 6, 6, false, true, true, 1, true>;
 
 // Default: the paired shapes when every projection is a whole, even number of weight tiles (each pair of CTAs then takes
 // two tiles of one projection), else the single-CTA shapes.
@@ -592,14 +654,14 @@ int pf_pick(const BitLinearArgs& a, int variant) {
     if (variant) return variant;
     const int n_tiles = (a.N + MMF_TILE_ROWS - 1) / MMF_TILE_ROWS;
     const bool pairs = a.N % MMF_TILE_ROWS == 0 && n_tiles % a.groups == 0 && (n_tiles / a.groups) % 2 == 0;
-    return a.K >= 4096 ? (pairs ? 9 : 1) : (pairs ? 8 : 2);
+    return a.K >= 4096 ? (pairs ? 11 : 1) : (pairs ? 10 : 2);    // paired shapes with the stmatrix + TMA-store epilogue
 }
 
 }  // namespace
 
 int bitlinear_mma_prefill_tile(const BitLinearArgs& a, int variant) {
     const int v = pf_pick(a, variant);
-    return v == 2 || v == 3 || v == 6 || v == 7 || v == 8 ? 192 : 256;
+    return v == 2 || v == 3 || v == 6 || v == 7 || v == 8 || v == 10 ? 192 : 256;
 }
 
 // Launch the persistent kernel (large M).  Same argument contract as bitlinear_mma_launch; `variant` selects one
@@ -614,6 +676,8 @@ int bitlinear_mma_prefill_launch(const BitLinearArgs& a, cudaStream_t st, int va
         case 7: return pf_launch<PfOverlapShallow>(a, st);
         case 8: return pf_launch<PfOverlapPair>(a, st);
         case 9: return pf_launch<PfLongKPair>(a, st);
+        case 10: return pf_launch<PfOverlapPairSt>(a, st);
+        case 11: return pf_launch<PfLongKPairSt>(a, st);
         default: return pf_launch<PfOverlap>(a, st);
     }
 }
