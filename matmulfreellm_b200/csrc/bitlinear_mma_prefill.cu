@@ -260,6 +260,7 @@ bitlinear_mma_prefill_kernel(const __grid_constant__ CUtensorMap q_map, const __
                 for (int i = 0; i < S; ++i, bq.next()) {
                     if (!mbar_wait(&bars[C::b_empty(bq.slot)], bq.ph ^ 1, abort_flag)) { live = false; break; }
                     if (C::PAIR && rank != 0) {
+                        if (PF_SKIP(p.skip & 1)) continue;
                         // this CTA's half of the tile lands here; its bytes are counted by the issuing CTA's "full" barrier,
                         // whose own producer announces the bytes of both halves (a transaction count may run negative)
                         tma_load_2d_pair(b_ring + bq.slot * C::B_STAGE, &q_map, cluster_addr(&bars[C::b_full(bq.slot)], 0u), i * 128, y);
