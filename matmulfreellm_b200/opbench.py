@@ -263,6 +263,74 @@ def prefill(a):
                       "tokens_per_s_per_layer_block": a.batch * a.seq / t * a.layers}))
 
 
+def pfknobs(a):
+    """The persistent prefill BitLinear kernel under its experiment switches (experiments build): every compiled shape
+    (`MMF_TUNE_PERSISTENT` = 10 + v) and, for the default shape, the timing-only switches that leave out the activation
+    loads (1), the 2-bit expansion (2), the output stores (4) or all three (7) — results are wrong with a switch on, only
+    the time means something; then the timeline of CTA 0 (global timer) for the first work items; then a bare issue
+    loop with one thread, two threads and a pair of CTAs.  3 warm-up + 20 timed launches per figure; over a run this long
+    the GPU settles under its power cap, so later figures read lower than the first (the traced launch reports its SM clock)."""
+    from matmulfreellm_b200 import _lib
+    dev = torch.device("cuda")
+    g = torch.Generator(device=dev).manual_seed(1)
+    x = torch.randn(a.M, a.K, device=dev, generator=g).bfloat16()
+    w = torch.randn(a.N, a.K, device=dev, generator=g) * 0.02
+    pw = K.pack_weight(w)
+    q, dq, rs = K.act_quant(x, None, 1e-6)
+    out = torch.empty(a.M, a.N, device=dev, dtype=torch.bfloat16)
+    fn = lambda: K.bitlinear(q, dq, rs, pw, torch.bfloat16, out=out)
+    ops = 2.0 * a.M * a.K * a.N
+    res = {"op": "prefill_kernel_experiments", "M": a.M, "K": a.K, "N": a.N}
+    with _lib.experiments_library() as lib:
+        peak = K.int8_mma_peak_tops(256, 200000)
+        res["int8_peak_tops"] = peak
+        shapes = {}
+        for v in (0, 1, 2, 5, 6, 7, 8, 9, 10, 11):
+            lib.mmf_tuning(7, 10 + v if v else 0)
+            try:
+                t = _time(fn, 20)
+                shapes[f"shape_{v}"] = {"us": t * 1e6, "frac_of_int8_peak": ops / t / 1e12 / peak}
+            except _lib.MMFreeError as e:
+                shapes[f"shape_{v}"] = {"refused": str(e)[:80]}
+        lib.mmf_tuning(7, 0)
+        res["compiled_shapes"] = shapes
+        skips = {}
+        for bits in (0, 1, 2, 4, 7):
+            lib.mmf_tuning(12, bits)
+            t = _time(fn, 20)
+            skips[f"skip_{bits}"] = {"us": t * 1e6, "frac_of_int8_peak": ops / t / 1e12 / peak}
+        lib.mmf_tuning(12, 0)
+        res["parts_switched_off"] = skips
+        for _ in range(3):
+            fn()
+        torch.cuda.synchronize()
+        ws = list(K._ws_cache.values())[0]
+        w32 = ws.view(torch.int32)
+        w32[1] = 0x7ACE
+        torch.cuda.synchronize()
+        fn()
+        torch.cuda.synchronize()
+        w32[1] = 0
+        rec = ws[32:32 + 28 * 8].view(torch.int64).cpu().tolist()
+        ws[32:32 + 28 * 8].zero_()
+        rel = [(v - rec[0]) if v else 0 for v in rec]
+        res["timeline_cta0_ns"] = {
+            "sm_clock_ghz": (rec[27] - rec[26]) / max(1, rec[25] - rec[0]),
+            "mma_thread_items_1_to_4_start_firststage_allissued": [rel[1 + i * 3:4 + i * 3] for i in range(4)],
+            "epilogue_items_0_to_3_accfull_handedback_stored": [rel[13 + i * 3:16 + i * 3] for i in range(4)]}
+        loop = {}
+        for commits in (0, 1):
+            lib.mmf_tuning(8, commits)
+            for n in (64, 128, 192):
+                for mode, name in ((1, "one_thread"), (2, "two_threads"), (3, "cta_pair")):
+                    if mode == 2 and n > 128:
+                        continue
+                    lib.mmf_tuning(11, mode)
+                    loop[f"commits_per_4_mma_{commits}_columns_{n}_{name}"] = K.int8_mma_peak_tops(n, 100000)
+        res["bare_issue_loop_tops"] = loop
+    print(json.dumps(res))
+
+
 def sweep(a):
     """FusedBitLinear op sweep: M in {1,16,256,4096,16384} x (K,N) in {(2048,2048),(2048,11264),(5632,2048),(2560,2560)}.
     Small M: 24 launches over 24 distinct weight buffers (more than L2 in total for the larger shapes) replayed from one
@@ -298,6 +366,9 @@ def main():
     r = sub.add_parser("rowwise")
     r.add_argument("--M", type=int, default=4096); r.add_argument("--D", type=int, default=2048); r.add_argument("--iters", type=int, default=10)
     sub.add_parser("int8peak")
+    pk = sub.add_parser("pfknobs")
+    pk.add_argument("--M", type=int, default=16384); pk.add_argument("--K", type=int, default=2048)
+    pk.add_argument("--N", type=int, default=11264)
     sub.add_parser("sync")
     ch = sub.add_parser("chain")
     ch.add_argument("--M", type=int, default=32); ch.add_argument("--iters", type=int, default=20)
@@ -308,7 +379,7 @@ def main():
     pf.add_argument("--batch", type=int, default=16); pf.add_argument("--seq", type=int, default=2048)
     pf.add_argument("--layers", type=int, default=2); pf.add_argument("--iters", type=int, default=2)
     a = ap.parse_args()
-    {"bitlinear": bitlinear, "hgrn": hgrn, "rowwise": rowwise, "int8peak": int8peak, "sync": sync, "chain": chain, "timeline": timeline, "prefill": prefill, "sweep": sweep}[a.op](a)
+    {"bitlinear": bitlinear, "hgrn": hgrn, "rowwise": rowwise, "int8peak": int8peak, "sync": sync, "chain": chain, "timeline": timeline, "prefill": prefill, "sweep": sweep, "pfknobs": pfknobs}[a.op](a)
 
 
 if __name__ == "__main__":
