@@ -29,24 +29,33 @@ constexpr int MAX_D = FT * MAX_PER;
 // Kernels are compiled for P = 8, 16, 24 and 32 row values per thread (D <= 2048, 4096, 6144, 8192): the row lives in
 // registers, so the smaller instantiations leave room for more resident CTAs.
 
-// One-sync block reductions: warp shuffle, lane 0 parks the partial in a slot that is used once per row,
-// one barrier, then every thread folds the FW partials in a fixed order.
-template <int K>
+// A row is worked on by RT threads (RT / 32 warps): the whole CTA (RT = FT: one row at a time, decode steps, long
+// rows) or a quarter of it (RT = 64: four rows side by side — a thread then holds four times as many values of its
+// row, and the per-row cost of the reductions below, a good part of all instructions at 8 values per thread, is spread
+// over four times as many).  The threads of a row meet at a barrier of their own.
+template <int RT> __device__ __forceinline__ void row_sync() {
+    if constexpr (RT == FT) __syncthreads();
+    else asm volatile("bar.sync %0, %1;" ::"r"(1 + (int)(threadIdx.x / RT)), "n"(RT) : "memory");
+}
+// One-sync row reductions: warp shuffle, lane 0 parks the partial in a slot that is used once per row,
+// one barrier, then every thread folds the RT / 32 partials in a fixed order.
+template <int K, int RT>
 __device__ __forceinline__ void block_sum_d(double (&v)[K], double* slot /* K*FW, 16-byte aligned */) {
-    const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
+    constexpr int RW = RT / 32;
+    const int lane = threadIdx.x & 31, wid = (threadIdx.x % RT) >> 5;
 #pragma unroll
     for (int k = 0; k < K; ++k) v[k] = warp_sum(v[k]);
     if (lane == 0) {
 #pragma unroll
-        for (int k = 0; k < K; ++k) slot[k * FW + wid] = v[k];
+        for (int k = 0; k < K; ++k) slot[k * RW + wid] = v[k];
     }
-    __syncthreads();
+    row_sync<RT>();
 #pragma unroll
     for (int k = 0; k < K; ++k) {
         double t = 0.0;
 #pragma unroll
-        for (int w = 0; w < FW; w += 2) {
-            const double2 p = *reinterpret_cast<const double2*>(slot + k * FW + w);
+        for (int w = 0; w < RW; w += 2) {
+            const double2 p = *reinterpret_cast<const double2*>(slot + k * RW + w);
             t += p.x;
             t += p.y;
         }
@@ -55,46 +64,58 @@ __device__ __forceinline__ void block_sum_d(double (&v)[K], double* slot /* K*FW
 }
 // maximum of non-negative, non-NaN floats: their bit patterns order like unsigned integers, so one warp-wide
 // integer reduction instruction replaces five shuffle + max rounds
-template <int K>
+template <int K, int RT>
 __device__ __forceinline__ void block_max_f(float (&v)[K], float* slot) {
-    const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
+    constexpr int RW = RT / 32;
+    const int lane = threadIdx.x & 31, wid = (threadIdx.x % RT) >> 5;
 #pragma unroll
     for (int k = 0; k < K; ++k) v[k] = __uint_as_float(__reduce_max_sync(0xffffffffu, __float_as_uint(v[k])));
     if (lane == 0) {
 #pragma unroll
-        for (int k = 0; k < K; ++k) slot[k * FW + wid] = v[k];
+        for (int k = 0; k < K; ++k) slot[k * RW + wid] = v[k];
     }
-    __syncthreads();
+    row_sync<RT>();
 #pragma unroll
     for (int k = 0; k < K; ++k) {
         float t = 0.0f;
+        if constexpr (RW >= 4) {
 #pragma unroll
-        for (int w = 0; w < FW; w += 4) {
-            const float4 p = *reinterpret_cast<const float4*>(slot + k * FW + w);
-            t = fmaxf(fmaxf(t, p.x), fmaxf(p.y, fmaxf(p.z, p.w)));
+            for (int w = 0; w < RW; w += 4) {
+                const float4 p = *reinterpret_cast<const float4*>(slot + k * RW + w);
+                t = fmaxf(fmaxf(t, p.x), fmaxf(p.y, fmaxf(p.z, p.w)));
+            }
+        } else {
+            const float2 p = *reinterpret_cast<const float2*>(slot + k * RW);
+            t = fmaxf(p.x, p.y);
         }
         v[k] = t;
     }
 }
-// block-wide integer sums; only thread 0 receives them (it is the one that writes them out)
-template <int K>
+// row-wide integer sums; only the row's first thread receives them (it is the one that writes them out)
+template <int K, int RT>
 __device__ __forceinline__ void block_sum_i_t0(int (&v)[K], int* slot) {
-    const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
+    constexpr int RW = RT / 32;
+    const int lane = threadIdx.x & 31, wid = (threadIdx.x % RT) >> 5;
 #pragma unroll
     for (int k = 0; k < K; ++k) v[k] = __reduce_add_sync(0xffffffffu, v[k]);
     if (lane == 0) {
 #pragma unroll
-        for (int k = 0; k < K; ++k) slot[k * FW + wid] = v[k];
+        for (int k = 0; k < K; ++k) slot[k * RW + wid] = v[k];
     }
-    __syncthreads();
-    if (threadIdx.x == 0) {
+    row_sync<RT>();
+    if (threadIdx.x % RT == 0) {
 #pragma unroll
         for (int k = 0; k < K; ++k) {
             int t = 0;
+            if constexpr (RW >= 4) {
 #pragma unroll
-            for (int w = 0; w < FW; w += 4) {
-                const int4 p = *reinterpret_cast<const int4*>(slot + k * FW + w);
-                t += (p.x + p.y) + (p.z + p.w);
+                for (int w = 0; w < RW; w += 4) {
+                    const int4 p = *reinterpret_cast<const int4*>(slot + k * RW + w);
+                    t += (p.x + p.y) + (p.z + p.w);
+                }
+            } else {
+                const int2 p = *reinterpret_cast<const int2*>(slot + k * RW);
+                t = p.x + p.y;
             }
             v[k] = t;
         }
@@ -134,16 +155,17 @@ __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commi
 __device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wait_group 0;" ::: "memory"); }
 
 // iterate over the 16-byte vectors of a row held as v[P] (P: the enclosing template parameter): vector `it` of this thread starts at column c
+// (RT, the threads per row, is a template parameter or constant of the enclosing function)
 #define ROW_FOREACH(V, D, it, c) \
-    _Pragma("unroll") for (int it = 0, c = threadIdx.x * (V); it < P / (V); ++it, c += FT * (V)) if (c < (D))
+    _Pragma("unroll") for (int it = 0, c = (int)(threadIdx.x % RT) * (V); it < P / (V); ++it, c += RT * (V)) if (c < (D))
 
 // BitLinear prologue on a register-resident row `v` (values already in T precision): shared sum of squares
 // `ss`, then per projection g: y = (v*rstd)*nw_g, absmax -> scale -> int8 codes, dq, rowsum.
-template <int V, int G, int P>
+template <int V, int G, int P, int RT = FT>
 __device__ __forceinline__ void bitlinear_prologue(float (&v)[P], int D, double ss, float eps, const float* snw /* smem [G][D] */,
                                                    int8_t* q, float* dq, int32_t* rowsum, int64_t M, int64_t m, RedScratch& red) {
     double s1[1] = {ss};
-    block_sum_d<1>(s1, red.d1);
+    block_sum_d<1, RT>(s1, red.d1);
     const float rstd = rstd_from_sumsq(s1[0], D, eps);
     float amax[G];
 #pragma unroll
@@ -173,7 +195,7 @@ __device__ __forceinline__ void bitlinear_prologue(float (&v)[P], int D, double 
             }
         }
     }
-    block_max_f<G>(amax, red.f0);
+    block_max_f<G, RT>(amax, red.f0);
     int lsum[G];
 #pragma unroll
     for (int g = 0; g < G; ++g) {
@@ -207,10 +229,10 @@ __device__ __forceinline__ void bitlinear_prologue(float (&v)[P], int D, double 
             if constexpr (V == 8) *reinterpret_cast<uint2*>(qr + c) = make_uint2(words[0], words[1]);
             else *reinterpret_cast<uint32_t*>(qr + c) = words[0];
         }
-        if (threadIdx.x == 0) dq[(int64_t)g * M + m] = __fdiv_rn(a, 127.0f);
+        if (threadIdx.x % RT == 0) dq[(int64_t)g * M + m] = __fdiv_rn(a, 127.0f);
     }
-    block_sum_i_t0<G>(lsum, red.i0);
-    if (threadIdx.x == 0) {
+    block_sum_i_t0<G, RT>(lsum, red.i0);
+    if (threadIdx.x % RT == 0) {
 #pragma unroll
         for (int g = 0; g < G; ++g) rowsum[(int64_t)g * M + m] = lsum[g];
     }
@@ -244,11 +266,14 @@ __device__ __forceinline__ long long row_now() {
 #define ROW_TRACE(slot) do { } while (0)
 #endif
 
-template <typename T, int P, int LAT>
+template <typename T, int P, int LAT, int RT = FT>
 __global__ void __launch_bounds__(FT, LAT)
 prenorm_quant_kernel(PrenormArgs a) {
     extern __shared__ __align__(16) float sw[];   // [1 + G][D]: block norm weight, then the BitLinear norm weights
-    __shared__ RedScratch red;
+    constexpr int RPC = FT / RT;                  // rows this CTA works on side by side
+    __shared__ RedScratch reds[RPC];
+    RedScratch& red = reds[threadIdx.x / RT];
+    const int rg = threadIdx.x / RT;
     constexpr int V = 16 / sizeof(T);
     const int D = a.D;
 #ifdef MMF_EXPERIMENTS
@@ -271,7 +296,7 @@ prenorm_quant_kernel(PrenormArgs a) {
 
     // Row loop (LAT = 0): the CTA's next row travels global -> shared memory by cp.async while the current one is
     // processed (thread-private 16-byte slots: no barrier, only the thread's own wait)
-    T* sx = reinterpret_cast<T*>(sw + (1 + Gs) * D);   // [D] x row, [D] residual row (LAT = 0 only)
+    T* sx = reinterpret_cast<T*>(sw + (1 + Gs) * D) + (size_t)rg * 2 * D;   // per row in flight: [D] x row, [D] residual row (LAT = 0 only)
     T* sr = sx + D;
     auto fetch = [&](int64_t row) {
         ROW_FOREACH(V, D, it, c) {
@@ -280,9 +305,10 @@ prenorm_quant_kernel(PrenormArgs a) {
         }
         cp_async_commit();
     };
-    if (LAT == 0 && blockIdx.x < a.M) fetch(blockIdx.x);
-    // a CTA takes rows blockIdx.x, blockIdx.x + gridDim.x, ...: with many rows the staged norm weights are reused
-    for (int64_t m = blockIdx.x; m < a.M; m += gridDim.x) {
+    const int64_t row0 = (int64_t)blockIdx.x * RPC + rg, row_step = (int64_t)gridDim.x * RPC;
+    if (LAT == 0 && row0 < a.M) fetch(row0);
+    // a CTA takes rows blockIdx.x (* RPC + its row slot), + gridDim.x (* RPC), ...: with many rows the staged norm weights are reused
+    for (int64_t m = row0; m < a.M; m += row_step) {
         const T* xr = LAT == 0 ? sx : reinterpret_cast<const T*>(a.x) + m * a.ld_x;
         const T* rr = a.res ? (LAT == 0 ? sr : reinterpret_cast<const T*>(a.res) + m * a.ld_res) : nullptr;
         if (LAT == 0) cp_async_wait_all();
@@ -320,9 +346,9 @@ prenorm_quant_kernel(PrenormArgs a) {
                 ss[0] += (double)x[i] * (double)x[i];
             }
         }
-        if (LAT == 0 && m + gridDim.x < a.M) fetch(m + gridDim.x);   // this thread's slots have just been read
+        if (LAT == 0 && m + row_step < a.M) fetch(m + row_step);   // this thread's slots have just been read
         ROW_TRACE(3);
-        block_sum_d<1>(ss, red.d0);
+        block_sum_d<1, RT>(ss, red.d0);
         ROW_TRACE(4);
         const float rstd1 = rstd_from_sumsq(ss[0], D, a.eps_norm);
         T* yo = (a.y_out && gy == 0) ? reinterpret_cast<T*>(a.y_out) + m * (int64_t)D : nullptr;
@@ -348,22 +374,22 @@ prenorm_quant_kernel(PrenormArgs a) {
         }
         ROW_TRACE(5);
         if (a.gsplit)
-            bitlinear_prologue<V, 1, P>(v, D, ss2, a.eps_bl, sw + D, a.q + (int64_t)gy * a.M * D, a.dq + (int64_t)gy * a.M,
-                                        a.rowsum + (int64_t)gy * a.M, a.M, m, red);
-        else if (a.G == 3) bitlinear_prologue<V, 3, P>(v, D, ss2, a.eps_bl, sw + D, a.q, a.dq, a.rowsum, a.M, m, red);
-        else if (a.G == 1) bitlinear_prologue<V, 1, P>(v, D, ss2, a.eps_bl, sw + D, a.q, a.dq, a.rowsum, a.M, m, red);
+            bitlinear_prologue<V, 1, P, RT>(v, D, ss2, a.eps_bl, sw + D, a.q + (int64_t)gy * a.M * D, a.dq + (int64_t)gy * a.M,
+                                            a.rowsum + (int64_t)gy * a.M, a.M, m, red);
+        else if (a.G == 3) bitlinear_prologue<V, 3, P, RT>(v, D, ss2, a.eps_bl, sw + D, a.q, a.dq, a.rowsum, a.M, m, red);
+        else if (a.G == 1) bitlinear_prologue<V, 1, P, RT>(v, D, ss2, a.eps_bl, sw + D, a.q, a.dq, a.rowsum, a.M, m, red);
         ROW_TRACE(6);
     }
     ROW_TRACE(7);
 }
 
 // y = round_T( ((g*rstd)*w) * o * sigmoid(o) ), then BitLinear prologue.  `ov` holds the gate row o in registers.
-template <typename T, int V, int P>
+template <typename T, int V, int P, int RT = FT>
 __device__ __forceinline__ void gatenorm_tail(float (&gv)[P], const float (&ov)[P], double ssg, int D, float eps_g, float eps_bl,
                                               const float* sw /* [2][D]: g_norm weight, BitLinear norm weight */, int8_t* q, float* dq,
                                               int32_t* rowsum, int64_t M, int64_t m, RedScratch& red) {
     double s0[1] = {ssg};
-    block_sum_d<1>(s0, red.d0);
+    block_sum_d<1, RT>(s0, red.d0);
     const float rstd = rstd_from_sumsq(s0[0], D, eps_g);
     double ss2 = 0.0;
     ROW_FOREACH(V, D, it, c) {
@@ -386,16 +412,19 @@ __device__ __forceinline__ void gatenorm_tail(float (&gv)[P], const float (&ov)[
             ss2 += (double)t[i] * (double)t[i];
         }
     }
-    bitlinear_prologue<V, 1, P>(gv, D, ss2, eps_bl, sw + D, q, dq, rowsum, M, m, red);
+    bitlinear_prologue<V, 1, P, RT>(gv, D, ss2, eps_bl, sw + D, q, dq, rowsum, M, m, red);
 }
 
-template <typename T, int P, int LAT>
+template <typename T, int P, int LAT, int RT = FT>
 __global__ void __launch_bounds__(FT, LAT)
 gatenorm_quant_kernel(const T* __restrict__ gx, int64_t ld_g, const T* __restrict__ o, int64_t ld_o,
                       const float* __restrict__ gw, float eps_g, const float* __restrict__ nw, float eps_bl,
                       int8_t* __restrict__ q, float* __restrict__ dq, int32_t* __restrict__ rowsum, int64_t M, int D) {
     extern __shared__ __align__(16) float sw[];
-    __shared__ RedScratch red;
+    constexpr int RPC = FT / RT;                  // rows this CTA works on side by side
+    __shared__ RedScratch reds[RPC];
+    RedScratch& red = reds[threadIdx.x / RT];
+    const int rg = threadIdx.x / RT;
     constexpr int V = 16 / sizeof(T);
     pdl_trigger();
     stage_weights(sw, gw, D);
@@ -403,7 +432,7 @@ gatenorm_quant_kernel(const T* __restrict__ gx, int64_t ld_g, const T* __restric
     pdl_wait();
     __syncthreads();
     // Row loop (LAT = 0): next row by cp.async into thread-private slots, as in prenorm_quant_kernel
-    T* sg = reinterpret_cast<T*>(sw + 2 * D);   // [D] g row, [D] o row (LAT = 0 only)
+    T* sg = reinterpret_cast<T*>(sw + 2 * D) + (size_t)rg * 2 * D;   // per row in flight: [D] g row, [D] o row (LAT = 0 only)
     T* so = sg + D;
     auto fetch = [&](int64_t row) {
         ROW_FOREACH(V, D, it, c) {
@@ -412,9 +441,10 @@ gatenorm_quant_kernel(const T* __restrict__ gx, int64_t ld_g, const T* __restric
         }
         cp_async_commit();
     };
-    if (LAT == 0 && blockIdx.x < M) fetch(blockIdx.x);
-    // a CTA takes rows blockIdx.x, blockIdx.x + gridDim.x, ...: with many rows the staged norm weights are reused
-    for (int64_t m = blockIdx.x; m < M; m += gridDim.x) {
+    const int64_t row0 = (int64_t)blockIdx.x * RPC + rg, row_step = (int64_t)gridDim.x * RPC;
+    if (LAT == 0 && row0 < M) fetch(row0);
+    // a CTA takes rows blockIdx.x (* RPC + its row slot), + gridDim.x (* RPC), ...: with many rows the staged norm weights are reused
+    for (int64_t m = row0; m < M; m += row_step) {
         const T* gr = LAT == 0 ? sg : gx + m * ld_g;
         const T* orow = LAT == 0 ? so : o + m * ld_o;
         if (LAT == 0) cp_async_wait_all();
@@ -431,8 +461,8 @@ gatenorm_quant_kernel(const T* __restrict__ gx, int64_t ld_g, const T* __restric
                 ss += (double)a[i] * (double)a[i];
             }
         }
-        if (LAT == 0 && m + gridDim.x < M) fetch(m + gridDim.x);   // this thread's slots have just been read
-        gatenorm_tail<T, V, P>(gv, ov, ss, D, eps_g, eps_bl, sw, q, dq, rowsum, M, m, red);
+        if (LAT == 0 && m + row_step < M) fetch(m + row_step);   // this thread's slots have just been read
+        gatenorm_tail<T, V, P, RT>(gv, ov, ss, D, eps_g, eps_bl, sw, q, dq, rowsum, M, m, red);
     }
 }
 
@@ -447,6 +477,7 @@ decode_mix_kernel(const T* __restrict__ ifg, int64_t ld, const T* __restrict__ l
     extern __shared__ __align__(16) float sw[];   // [3][D]: g_norm weight, BitLinear norm weight, lower bound (as float)
     __shared__ RedScratch red;
     constexpr int V = 16 / sizeof(T);
+    constexpr int RT = FT;                        // the whole CTA works on one row
     pdl_trigger();
     stage_weights(sw, gw, D);
     stage_weights(sw + D, nw, D);
@@ -508,6 +539,7 @@ swiglu_quant_kernel(const T* __restrict__ gate, const T* __restrict__ up, int64_
     extern __shared__ __align__(16) float sw[];
     __shared__ RedScratch red;
     constexpr int V = 16 / sizeof(T);
+    constexpr int RT = FT;                        // the whole CTA works on one row
     pdl_trigger();
     stage_weights(sw, nw, D);
     pdl_wait();
@@ -584,10 +616,24 @@ static int resident_ctas(const void* kernel, size_t smem) {
 // one CTA per row while all of them are resident at once; beyond that exactly one resident set of CTAs, which loop
 // over the rows (a partial second wave would leave SMs idle at the end)
 template <typename Kern>
-static inline unsigned row_grid(Kern kernel, size_t smem, int64_t M) {
+static inline unsigned row_grid(Kern kernel, size_t smem, int64_t M, int rows_per_cta = 1) {
     const int64_t cap = (int64_t)148 * resident_ctas(reinterpret_cast<const void*>(kernel), smem);
-    return (unsigned)(M < cap ? M : cap);
+    const int64_t want = (M + rows_per_cta - 1) / rows_per_cta;
+    return (unsigned)(want < cap ? want : cap);
 }
+// Prompt-sized calls (MMF_FOUR_ROWS_MIN_M rows and more): four rows per CTA with 64 threads each for rows of at most 2048
+// values, two rows with 128 threads each up to 4096 values.  A thread then holds up to 32 values of its row instead of
+// 8 - 16, so the reductions of a row (two fp64 sums, the absmax, the code sum: a fifth of all instructions at 8 values
+// per thread) cost a quarter (half) per value, and a row's threads meet at a barrier of 64 (128) instead of 256.
+// Measured at 32768 rows of 2048 values: 220 -> 160 us (three projections), 150 -> 89 us (one), 150 -> 104 us (gate norm).
+constexpr int ROW_QUARTER = 64, ROW_HALF = 128;
+// run `...` with RT bound to the threads per row of a prompt-sized call on rows of D values (D <= ROW_HALF * MAX_PER)
+#define FUSED_DISPATCH_RT(D, RT, ...)                                              \
+    if ((D) <= ROW_QUARTER * MAX_PER) { constexpr int RT = ROW_QUARTER; __VA_ARGS__; } \
+    else { constexpr int RT = ROW_HALF; __VA_ARGS__; }
+#ifndef MMF_FOUR_ROWS_MIN_M
+#define MMF_FOUR_ROWS_MIN_M 3072
+#endif
 
 // Run `...` with `P` (row values per thread) bound to the smallest compiled size that holds a row of D values.
 #define FUSED_DISPATCH_P(D, P, ...)                                   \
@@ -644,6 +690,17 @@ extern "C" int mmf_prenorm_quant(const void* x, int64_t ld_x, const void* residu
 #ifdef MMF_EXPERIMENTS
     a.trace = g_row_trace;
 #endif
+    if (M >= MMF_FOUR_ROWS_MIN_M && D <= ROW_HALF * MAX_PER && !a.gsplit) {
+        MMF_DISPATCH(dtype, T, { FUSED_DISPATCH_RT(D, RT, {
+            constexpr int P = MAX_PER, RPC = FT / RT;
+            const size_t smem = (size_t)(1 + groups) * D * sizeof(float) + (size_t)RPC * 2 * D * sizeof(T);   // + row staging
+            FUSED_SMEM_ATTR((prenorm_quant_kernel<T, P, 0, RT>), smem);
+            const dim3 grid(row_grid(prenorm_quant_kernel<T, P, 0, RT>, smem, M, RPC));
+            MMF_CUDA(mmf_launch_pdl(prenorm_quant_kernel<T, P, 0, RT>, grid, dim3(FT), smem, (cudaStream_t)stream, a));
+        }); });
+        MMF_LAUNCH_CHECK("prenorm_quant_kernel");
+        return MMF_OK;
+    }
     MMF_DISPATCH(dtype, T, {
         FUSED_DISPATCH_P(D, P, { FUSED_DISPATCH_LAT(M, LAT, {
             const size_t smem = (size_t)(1 + (a.gsplit ? 1 : groups)) * D * sizeof(float) + (LAT ? 0 : (size_t)2 * D * sizeof(T));   // + row staging
@@ -666,6 +723,18 @@ extern "C" int mmf_gatenorm_quant(const void* g, int64_t ld_g, const void* o, in
                     mmf_aligned(gnorm_w, 16) && mmf_aligned(nw, 16),
                 MMF_ERR_ALIGN, "mmf_gatenorm_quant: rows and norm weights must be 16-byte aligned");
     if (M == 0) return MMF_OK;
+    if (M >= MMF_FOUR_ROWS_MIN_M && D <= ROW_HALF * MAX_PER) {
+        MMF_DISPATCH(dtype, T, { FUSED_DISPATCH_RT(D, RT, {
+            constexpr int P = MAX_PER, RPC = FT / RT;
+            const size_t smem = (size_t)2 * D * sizeof(float) + (size_t)RPC * 2 * D * sizeof(T);   // + row staging
+            FUSED_SMEM_ATTR((gatenorm_quant_kernel<T, P, 0, RT>), smem);
+            MMF_CUDA(mmf_launch_pdl(gatenorm_quant_kernel<T, P, 0, RT>, dim3(row_grid(gatenorm_quant_kernel<T, P, 0, RT>, smem, M, RPC)),
+                                    dim3(FT), smem, (cudaStream_t)stream, (const T*)g, ld_g, (const T*)o, ld_o, gnorm_w, eps_g, nw, eps_bl, q, dq,
+                                    rowsum, M, (int)D));
+        }); });
+        MMF_LAUNCH_CHECK("gatenorm_quant_kernel");
+        return MMF_OK;
+    }
     MMF_DISPATCH(dtype, T, {
         FUSED_DISPATCH_P(D, P, { FUSED_DISPATCH_LAT(M, LAT, {
             const size_t smem = (size_t)2 * D * sizeof(float) + (LAT ? 0 : (size_t)2 * D * sizeof(T));   // + row staging

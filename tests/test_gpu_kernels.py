@@ -569,6 +569,47 @@ def test_fused_row_kernels_many_rows(K, dtype, D):
     check(lambda sl: K.swiglu_quant(gu[sl], bl[2], 1e-6), 1)
 
 
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16, torch.float32])
+@pytest.mark.parametrize("D", [512, 704, 2048, 2560])
+def test_fused_row_kernels_four_rows_per_cta(K, dtype, D):
+    """From 3072 rows on, rows of at most 2048 values are worked on four at a time per CTA (64 threads and up to 32 values
+    per thread each), rows of at most 4096 values two at a time.  A 4099-row call (ragged against the four row slots) must reproduce, bit for bit, the same rows run in
+    250-row calls (one CTA per row, checked against the oracle above); the codes of the three-projection call are also
+    compared with the oracle directly."""
+    g = torch.Generator().manual_seed(D + 1)
+    M = 4099
+    x = dev((torch.randn(M, D, generator=g) * 2).to(dtype))
+    res = dev(torch.randn(M, D, generator=g).to(dtype))
+    nw = dev(1.0 + 0.1 * torch.randn(D, generator=g))
+    bl = [dev(1.0 + 0.1 * torch.randn(D, generator=g)) for _ in range(3)]
+    parts = [slice(i, min(M, i + 250)) for i in range(0, M, 250)]
+
+    def check(fn, n_groups):
+        big = fn(slice(0, M))
+        small = [fn(sl) for sl in parts]
+        for k, t in enumerate(big):
+            if t is None:
+                continue
+            if n_groups > 1 and t.shape[0] == n_groups * M:       # group-major codes / scales
+                t = t.view(n_groups, M, *t.shape[1:])
+                ref = torch.cat([sm[k].view(n_groups, -1, *t.shape[2:]) for sm in small], dim=1)
+            else:
+                ref = torch.cat([sm[k] for sm in small], dim=0)
+            assert torch.equal(t, ref), (k, D, dtype)
+        return big
+
+    q, dq, rs, _, y = check(lambda sl: K.prenorm_quant(x[sl], res[sl], nw, 1e-6, bl, 1e-6, False, want_residual_out=True, want_y=True), 3)
+    for gi in range(3):
+        q_ref, dq_ref, rs_ref = O.act_codes(y.cpu(), bl[gi].cpu(), 1e-6)
+        assert np.array_equal(q[gi * M:(gi + 1) * M].cpu().numpy(), q_ref)
+        assert np.array_equal(dq[gi * M:(gi + 1) * M].cpu().numpy(), dq_ref)
+        assert np.array_equal(rs[gi * M:(gi + 1) * M].cpu().numpy(), rs_ref)
+    check(lambda sl: K.prenorm_quant(x[sl], None, nw, 1e-6, [bl[0]], 1e-6, True), 1)
+    check(lambda sl: K.prenorm_quant(x[sl], res[sl], nw, 1e-6, [], 1e-6, True, want_residual_out=True, want_y=True), 0)
+    check(lambda sl: K.gatenorm_quant(x[sl], res[sl], nw, 1e-6, bl[1], 1e-6), 1)
+    K.check_status()
+
+
 @pytest.mark.parametrize("dtype,tol", [(torch.bfloat16, 1e-2), (torch.float32, 1e-4)])
 @pytest.mark.parametrize("B,T,D", [(3, 1, 256), (2, 70, 128), (1, 1024, 64)])
 def test_hgrn_gated_vs_oracle(K, dtype, tol, B, T, D):
