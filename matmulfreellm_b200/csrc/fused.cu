@@ -532,14 +532,16 @@ decode_mix_kernel(const T* __restrict__ ifg, int64_t ld, const T* __restrict__ l
 }
 
 // z = round_T(silu(gate)*up), then BitLinear prologue.  gate/up are the two halves of a [M, 2D] tensor.
-template <typename T, int P, int LAT>
+template <typename T, int P, int LAT, int RT = FT>
 __global__ void __launch_bounds__(FT, LAT)
 swiglu_quant_kernel(const T* __restrict__ gate, const T* __restrict__ up, int64_t ld, const float* __restrict__ nw,
                     float eps_bl, int8_t* __restrict__ q, float* __restrict__ dq, int32_t* __restrict__ rowsum, int64_t M, int D) {
     extern __shared__ __align__(16) float sw[];
-    __shared__ RedScratch red;
+    constexpr int RPC = FT / RT;                  // rows this CTA works on side by side
+    __shared__ RedScratch reds[RPC];
+    RedScratch& red = reds[threadIdx.x / RT];
+    const int rg = threadIdx.x / RT;
     constexpr int V = 16 / sizeof(T);
-    constexpr int RT = FT;                        // the whole CTA works on one row
     pdl_trigger();
     stage_weights(sw, nw, D);
     pdl_wait();
@@ -547,7 +549,7 @@ swiglu_quant_kernel(const T* __restrict__ gate, const T* __restrict__ up, int64_
     // Row loop (LAT = 0): the next row of this CTA travels global -> shared memory by cp.async while the current one is
     // reduced and quantised, so its load latency is hidden without holding it in registers.  Every thread copies and
     // later reads the same 16-byte slots, so the copies need no barrier, only the thread's own wait.
-    T* sg = reinterpret_cast<T*>(sw + D);   // [D] gate row, [D] up row (LAT = 0 only)
+    T* sg = reinterpret_cast<T*>(sw + D) + (size_t)rg * 2 * D;   // per row in flight: [D] gate row, [D] up row (LAT = 0 only)
     T* su = sg + D;
     auto fetch = [&](int64_t row) {
         ROW_FOREACH(V, D, it, c) {
@@ -556,9 +558,10 @@ swiglu_quant_kernel(const T* __restrict__ gate, const T* __restrict__ up, int64_
         }
         cp_async_commit();
     };
-    if (LAT == 0 && blockIdx.x < M) fetch(blockIdx.x);
-    // a CTA takes rows blockIdx.x, blockIdx.x + gridDim.x, ...: with many rows the staged norm weights are reused
-    for (int64_t m = blockIdx.x; m < M; m += gridDim.x) {
+    const int64_t row0 = (int64_t)blockIdx.x * RPC + rg, row_step = (int64_t)gridDim.x * RPC;
+    if (LAT == 0 && row0 < M) fetch(row0);
+    // a CTA takes rows blockIdx.x (* RPC + its row slot), + gridDim.x (* RPC), ...: with many rows the staged norm weights are reused
+    for (int64_t m = row0; m < M; m += row_step) {
         const T* gr = LAT == 0 ? sg : gate + m * ld;
         const T* ur = LAT == 0 ? su : up + m * ld;
         if (LAT == 0) cp_async_wait_all();
@@ -582,8 +585,8 @@ swiglu_quant_kernel(const T* __restrict__ gate, const T* __restrict__ up, int64_
                 ss += (double)gv[i] * (double)gv[i];
             }
         }
-        if (LAT == 0 && m + gridDim.x < M) fetch(m + gridDim.x);   // this thread's slots have just been read
-        bitlinear_prologue<V, 1, P>(v, D, ss, eps_bl, sw, q, dq, rowsum, M, m, red);
+        if (LAT == 0 && m + row_step < M) fetch(m + row_step);   // this thread's slots have just been read
+        bitlinear_prologue<V, 1, P, RT>(v, D, ss, eps_bl, sw, q, dq, rowsum, M, m, red);
     }
 }
 
@@ -601,7 +604,7 @@ swiglu_quant_kernel(const T* __restrict__ gate, const T* __restrict__ up, int64_
 // (kernel, smem) and remembered per host thread
 static int resident_ctas(const void* kernel, size_t smem) {
     struct Entry { const void* k; size_t s; int occ; };
-    thread_local Entry cache[24];
+    thread_local Entry cache[64];
     thread_local int n = 0;
     for (int i = 0; i < n; ++i)
         if (cache[i].k == kernel && cache[i].s == smem) return cache[i].occ;
@@ -610,7 +613,7 @@ static int resident_ctas(const void* kernel, size_t smem) {
         (void)cudaGetLastError();
         occ = 4;
     }
-    if (n < 24) cache[n++] = Entry{kernel, smem, occ};
+    if (n < 64) cache[n++] = Entry{kernel, smem, occ};
     return occ;
 }
 // one CTA per row while all of them are resident at once; beyond that exactly one resident set of CTAs, which loop
@@ -784,6 +787,25 @@ extern "C" int mmf_swiglu_quant(const void* gate, const void* up, int64_t ld, in
     MMF_REQUIRE(mmf_aligned(gate, 16) && mmf_aligned(up, 16) && mmf_aligned(q, 16) && (ld * es) % 16 == 0 && mmf_aligned(nw, 16),
                 MMF_ERR_ALIGN, "mmf_swiglu_quant: rows and norm weight must be 16-byte aligned");
     if (M == 0) return MMF_OK;
+    // prompt-sized calls: rows side by side in one CTA as in mmf_prenorm_quant; a row of the MLP width (5632, 6912) takes
+    // two rows per CTA with 128 threads and up to 56 values per thread each
+#define SWIGLU_ROWS(RT, P)                                                                                                        \
+    MMF_DISPATCH(dtype, T, {                                                                                                      \
+        constexpr int RPC = FT / (RT);                                                                                            \
+        const size_t smem = (size_t)D * sizeof(float) + (size_t)RPC * 2 * D * sizeof(T);                                          \
+        FUSED_SMEM_ATTR((swiglu_quant_kernel<T, P, 0, RT>), smem);                                                                \
+        MMF_CUDA(mmf_launch_pdl(swiglu_quant_kernel<T, P, 0, RT>, dim3(row_grid(swiglu_quant_kernel<T, P, 0, RT>, smem, M, RPC)),  \
+                                dim3(FT), smem, (cudaStream_t)stream, (const T*)gate, (const T*)up, ld, nw, eps_bl, q, dq, rowsum, M, \
+                                (int)D));                                                                                         \
+    });                                                                                                                           \
+    MMF_LAUNCH_CHECK("swiglu_quant_kernel");                                                                                      \
+    return MMF_OK
+    if (M >= MMF_FOUR_ROWS_MIN_M && D <= ROW_HALF * 56) {
+        if (D <= ROW_QUARTER * MAX_PER) { SWIGLU_ROWS(ROW_QUARTER, MAX_PER); }
+        if (D <= ROW_HALF * MAX_PER) { SWIGLU_ROWS(ROW_HALF, MAX_PER); }
+        SWIGLU_ROWS(ROW_HALF, 56);
+    }
+#undef SWIGLU_ROWS
     MMF_DISPATCH(dtype, T, {
         FUSED_DISPATCH_P(D, P, { FUSED_DISPATCH_LAT(M, LAT, {
             const size_t smem = (size_t)D * sizeof(float) + (LAT ? 0 : (size_t)2 * D * sizeof(T));   // + row staging in the row loop

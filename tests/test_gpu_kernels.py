@@ -607,6 +607,27 @@ def test_fused_row_kernels_four_rows_per_cta(K, dtype, D):
     check(lambda sl: K.prenorm_quant(x[sl], None, nw, 1e-6, [bl[0]], 1e-6, True), 1)
     check(lambda sl: K.prenorm_quant(x[sl], res[sl], nw, 1e-6, [], 1e-6, True, want_residual_out=True, want_y=True), 0)
     check(lambda sl: K.gatenorm_quant(x[sl], res[sl], nw, 1e-6, bl[1], 1e-6), 1)
+    gu = dev(torch.randn(M, 2 * D, generator=g).to(dtype))
+    check(lambda sl: K.swiglu_quant(gu[sl], bl[2], 1e-6), 1)
+    K.check_status()
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
+@pytest.mark.parametrize("D", [5632, 6912])
+def test_swiglu_quant_two_rows_per_cta(K, dtype, D):
+    """Rows of the MLP width on a prompt: two rows per CTA, 128 threads and up to 56 values per thread each; a 3100-row
+    call equals the same rows run in 250-row calls bit for bit, and the first rows match the oracle's codes."""
+    g = torch.Generator().manual_seed(D)
+    M = 3100
+    gu = dev(torch.randn(M, 2 * D, generator=g).to(dtype))
+    nw = dev(1.0 + 0.1 * torch.randn(D, generator=g))
+    q, dq, rs = K.swiglu_quant(gu, nw, 1e-6)
+    for i in range(0, M, 250):
+        qs, dqs, rss = K.swiglu_quant(gu[i:i + 250], nw, 1e-6)
+        assert torch.equal(q[i:i + 250], qs) and torch.equal(dq[i:i + 250], dqs) and torch.equal(rs[i:i + 250], rss), i
+    z_ref = O.swiglu_ref(gu[:64, :D].cpu(), gu[:64, D:].cpu())
+    q_ref, dq_ref, _ = O.act_codes(z_ref, nw.cpu(), 1e-6)
+    _codes_close(q[:64], dq[:64], q_ref, dq_ref, exact=False)
     K.check_status()
 
 
