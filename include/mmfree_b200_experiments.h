@@ -24,7 +24,7 @@ extern "C" {
 #define MMF_TUNE_B_STAGES 4   /* activation-tile ring depth (128 K per stage)                  */
 #define MMF_TUNE_A_STAGES 5   /* unpacked-weight stages held in tensor memory (even)           */
 #define MMF_TUNE_W_STAGES 6   /* packed-weight ring depth (even)                               */
-#define MMF_TUNE_PERSISTENT 7 /* persistent large-M kernel: 1 = whenever M > 128, 2 = never, 10+v = its compiled shape v (1..11) whenever M > 128 */
+#define MMF_TUNE_PERSISTENT 7 /* persistent large-M kernel: 1 = whenever M > 128, 2 = never, 10+v = its compiled shape v (1..12) whenever M > 128 */
 #define MMF_TUNE_PROBE_COMMITS 8 /* mmf_int8_mma_peak: tcgen05.commit instructions issued per 4 MMAs */
 #define MMF_TUNE_ACCUMULATORS 9 /* accumulators consecutive MMAs rotate through at few token columns: 1, 2 or 4 */
 #define MMF_TUNE_PROBE_ISSUERS 11 /* mmf_int8_mma_peak: 2 = two threads issue the MMAs, each into its own accumulator (<= 128 token columns); 3 = pairs of CTAs (cta_group::2), 256-row MMAs */

@@ -648,6 +648,8 @@ using PfLongKPair = PfCfg<256, 2, 6, 6, 6, false, true, false, 1, true>;
 // 10, 11: shapes 8 and 9 with the stmatrix + TMA-store epilogue
 using PfOverlapPairSt = PfCfg<192, 3, 4, 8, 6, true, true, true, 1, true>;
 using PfLongKPairSt = PfCfg<256, 2, 6, 6, 6, false, true, true, 1, true>;
+// 12: shape 11 with rings eight deep (all of tensor memory: 256 accumulator columns + 8 x 32 A-stage columns)
+using PfLongKPairSt8 = PfCfg<256, 2, 8, 8, 6, false, true, true, 1, true>;
 
 // Default: the paired shapes when every projection is a whole, even number of weight tiles (each pair of CTAs then takes
 // two tiles of one projection), else the single-CTA shapes.
@@ -655,7 +657,17 @@ int pf_pick(const BitLinearArgs& a, int variant) {
     if (variant) return variant;
     const int n_tiles = (a.N + MMF_TILE_ROWS - 1) / MMF_TILE_ROWS;
     const bool pairs = a.N % MMF_TILE_ROWS == 0 && n_tiles % a.groups == 0 && (n_tiles / a.groups) % 2 == 0;
-    return a.K >= 4096 ? (pairs ? 11 : 1) : (pairs ? 10 : 2);    // paired shapes with the stmatrix + TMA-store epilogue
+    if (!pairs) return a.K >= 4096 ? 1 : 2;
+    // paired shapes with the stmatrix + TMA-store epilogue: the 256-token tile for long K, and for shorter K when its work
+    // items fill the 74 CTA pairs' last round clearly better than those of the 192-token tile (e.g. N = 2048, M = 16384:
+    // 512 items = 6.9 rounds against 688 items = 9.3 rounds)
+    if (a.K >= 4096) return 12;
+    auto fill = [&](int nt) {
+        const double items = (double)(n_tiles / 2) * (double)((a.M + nt - 1) / nt), units = 74.0;
+        const double rounds = (double)(long long)((items + units - 1) / units);
+        return items / (rounds * units);
+    };
+    return fill(256) > fill(192) + 0.03 ? 12 : 10;
 }
 
 }  // namespace
@@ -679,6 +691,7 @@ int bitlinear_mma_prefill_launch(const BitLinearArgs& a, cudaStream_t st, int va
         case 9: return pf_launch<PfLongKPair>(a, st);
         case 10: return pf_launch<PfOverlapPairSt>(a, st);
         case 11: return pf_launch<PfLongKPairSt>(a, st);
+        case 12: return pf_launch<PfLongKPairSt8>(a, st);
         default: return pf_launch<PfOverlap>(a, st);
     }
 }

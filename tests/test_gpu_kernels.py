@@ -225,10 +225,10 @@ def test_bitlinear_matches_reference_output(K, golden):
 
 
 def test_bitlinear_persistent_kernel(K):
-    """The persistent large-M tensor-core kernel, forced on (knob 7 = 1: shape chosen by the library; 11..19: each
+    """The persistent large-M tensor-core kernel, forced on (knob 7 = 1: shape chosen by the library; 11..22: each
     compiled shape — 256-token tile with one accumulator, 192-token tile with two accumulators, the same with the
-    TMA-store epilogue, separate rings, two issuing threads, the shallow activation ring, and the two shapes run by pairs
-    of CTAs) for problems with a ragged last token tile, a ragged last weight tile and a trailing 64-wide K stage:
+    TMA-store epilogue, separate rings, two issuing threads, the shallow activation ring, the two shapes run by pairs
+    of CTAs, and those with the fragment / stmatrix / TMA-store epilogue and with rings eight deep) for problems with a ragged last token tile, a ragged last weight tile and a trailing 64-wide K stage:
     bit-exact accumulators and outputs in all three dtypes against the CUDA-core kernel; the paired shapes refuse a
     projection that is not an even number of whole weight tiles; then a grouped (3 x norm weight) call."""
     from matmulfreellm_b200 import _lib
@@ -240,7 +240,7 @@ def test_bitlinear_persistent_kernel(K):
             lib.mmf_tuning(7, 2)
             ref, acc_ref = K.bitlinear(q, dq, rs, pw, torch.float32, kernel=K.KERNEL_GEMV, return_acc=True)
             pairable = N % 256 == 0
-            for knob in (1, 11, 12, 13, 14, 15, 16, 17, 18, 19):
+            for knob in (1, 11, 12, 13, 14, 15, 16, 17, 18, 19, 20, 21, 22):
                 lib.mmf_tuning(7, knob)
                 if knob >= 18 and not pairable:
                     with pytest.raises(_lib.MMFreeError) as e:
@@ -262,7 +262,7 @@ def test_bitlinear_persistent_kernel(K):
         pw = K.stack_packed([K.pack_weight(dev(w)) for w in ws])
         qs = [K.act_quant(dev(x), dev(nw), 1e-6) for nw in nws]
         q = torch.cat([t[0] for t in qs]); dq = torch.cat([t[1] for t in qs]); rs = torch.cat([t[2] for t in qs])
-        for knob in (11, 12, 13, 18, 19):
+        for knob in (11, 12, 13, 18, 19, 20, 21, 22):
             lib.mmf_tuning(7, knob)
             for dt in (torch.float32, torch.bfloat16):
                 out = K.bitlinear(q, dq, rs, pw, dt, kernel=K.KERNEL_MMA)
