@@ -66,6 +66,29 @@ def test_bitlinear_sweep_large_m_vs_oracle(K, M, Kdim, N):
     K.check_status()
 
 
+def test_bitlinear_grouped_large_m(K):
+    """The three-projection call of a prompt pass (i / f / g: one activation row, three code groups, three stacked weight
+    matrices) at 4096 token rows equals three single-projection calls, which the sweep above compares with the oracle."""
+    M, Kdim, N = 4096, 2048, 2048
+    x, _, _ = O.bitlinear_case(M, Kdim, N, seed=31)
+    g = torch.Generator().manual_seed(32)
+    ws = [torch.randn(N, Kdim, generator=g) * 0.02 for _ in range(3)]
+    nws = [1.0 + 0.1 * torch.randn(Kdim, generator=g) for _ in range(3)]
+    pws = [K.pack_weight(w.cuda()) for w in ws]
+    pw = K.stack_packed(pws)
+    qs = [K.act_quant(x.cuda(), nw.cuda(), 1e-6) for nw in nws]
+    q = torch.cat([t[0] for t in qs]); dq = torch.cat([t[1] for t in qs]); rs = torch.cat([t[2] for t in qs])
+    for dt in (torch.bfloat16, torch.float32):
+        out = K.bitlinear(q, dq, rs, pw, dt)
+        K.check_status()
+        for gi in range(3):
+            single = K.bitlinear(qs[gi][0], qs[gi][1], qs[gi][2], pws[gi], dt)
+            assert torch.equal(out[:, gi * N:(gi + 1) * N], single), (dt, gi)
+    codes, mean = O.ternary_codes(ws[1])
+    ref = O.bitlinear_int(x[:64], nws[1], codes, mean, 1e-6)[0]
+    assert torch.equal(K.bitlinear(q, dq, rs, pw, torch.float32)[:64, N:2 * N].cpu(), ref)
+
+
 @pytest.mark.parametrize("Kdim,N", [(2048, 2048), (2560, 2560), (5632, 2048)])
 def test_bitlinear_large_m_repeatable(K, Kdim, N):
     """The same 16384-row call 60 times: every run returns the bits of the first one, whose sampled rows equal the
