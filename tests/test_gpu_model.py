@@ -252,6 +252,13 @@ def test_long_prompt_uses_persistent_kernel_with_identical_results(mm):
     assert torch.equal(a.logits, b.logits)
     for x, y in zip(a.past_key_values, b.past_key_values):
         assert torch.equal(x[0], y[0])
+    # 3072 rows also put the row-wise kernels on their four-rows-per-CTA build.  Sequences are independent, so one of them
+    # run alone (512 rows: one row per CTA, another contraction tiling) must give the same bits.
+    for i in (0, 5):
+        c = model(ids[i:i + 1], use_cache=True)
+        assert torch.equal(c.logits[0], a.logits[i])
+        for x, y in zip(c.past_key_values, a.past_key_values):
+            assert torch.equal(x[0][0], y[0][i])
     from matmulfreellm_b200 import kernels
     kernels.check_status()
 
