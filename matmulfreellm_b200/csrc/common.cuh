@@ -7,6 +7,7 @@
 #include <stdint.h>
 
 #include "../../include/mmfree_b200.h"
+#include <cuda/std/type_traits>
 
 // ---------------------------------------------------------------------------------------
 // host-side error plumbing
@@ -117,6 +118,29 @@ template <typename T, int V>
 __device__ __forceinline__ void store_rounded(T* p, const float (&x)[V], const uint32_t (&bits)[V / 2]) {
     if constexpr (sizeof(T) == 2) *reinterpret_cast<uint4*>(p) = make_uint4(bits[0], bits[1], bits[2], bits[3]);
     else *reinterpret_cast<float4*>(p) = make_float4(x[0], x[1], x[2], x[3]);
+}
+
+// ss += sum of x[i]^2 in fp64 for V values that round_vec has just rounded to T (`bits`: the packed T values).  For
+// bf16 the fp64 operand is assembled from the 16 bits with two integer instructions per value — sign dropped (it is
+// squared), exponent rebiased: ((b & 0x7fff) << 13) + (896 << 20) is the high word of the double, the low word is zero —
+// instead of an fp32 -> fp64 conversion, which runs on the special-function pipe (16 results per clock and SM: the pipe
+// that bounds the gate-norm and swiglu kernels on prompts).  A zero or subnormal bf16 value reads as about 2^-127, whose
+// square, 1e-77, cannot reach the fp32 statistic.  The square and the sum are the same fp64 fused multiply-add as before.
+template <typename T, int V>
+__device__ __forceinline__ void sumsq_rounded(const float (&x)[V], const uint32_t (&bits)[V / 2], double& ss) {
+    if constexpr (sizeof(T) == 2 && !cuda::std::is_same<T, __half>::value) {
+#pragma unroll
+        for (int i = 0; i < V / 2; ++i) {
+            const uint32_t u = bits[i];
+            const double d0 = __hiloint2double((int)(((u & 0x7fffu) << 13) + 0x38000000u), 0);
+            const double d1 = __hiloint2double((int)(((u >> 3) & 0x0fffe000u) + 0x38000000u), 0);
+            ss = fma(d0, d0, ss);
+            ss = fma(d1, d1, ss);
+        }
+    } else {
+#pragma unroll
+        for (int i = 0; i < V; ++i) ss += (double)x[i] * (double)x[i];
+    }
 }
 
 // int8 activation code clamp(rint(p), -128, 127) for |p| < 2^22 without conversion instructions: adding 1.5 * 2^23

@@ -366,10 +366,8 @@ prenorm_quant_kernel(PrenormArgs a) {
             }
             round_vec<T, V>(o, bits);
 #pragma unroll
-            for (int i = 0; i < V; ++i) {
-                v[it * V + i] = o[i];
-                ss2 += (double)o[i] * (double)o[i];
-            }
+            for (int i = 0; i < V; ++i) v[it * V + i] = o[i];
+            sumsq_rounded<T, V>(o, bits, ss2);
             if (yo) store_rounded<T, V>(yo + c, o, bits);
         }
         ROW_TRACE(5);
@@ -407,10 +405,8 @@ __device__ __forceinline__ void gatenorm_tail(float (&gv)[P], const float (&ov)[
         }
         round_vec<T, V>(t, bits);
 #pragma unroll
-        for (int i = 0; i < V; ++i) {
-            gv[it * V + i] = t[i];
-            ss2 += (double)t[i] * (double)t[i];
-        }
+        for (int i = 0; i < V; ++i) gv[it * V + i] = t[i];
+        sumsq_rounded<T, V>(t, bits, ss2);
     }
     bitlinear_prologue<V, 1, P, RT>(gv, D, ss2, eps_bl, sw + D, q, dq, rowsum, M, m, red);
 }
@@ -580,10 +576,8 @@ swiglu_quant_kernel(const T* __restrict__ gate, const T* __restrict__ up, int64_
             uint32_t bits[V / 2];
             round_vec<T, V>(gv, bits);
     #pragma unroll
-            for (int i = 0; i < V; ++i) {
-                v[it * V + i] = gv[i];
-                ss += (double)gv[i] * (double)gv[i];
-            }
+            for (int i = 0; i < V; ++i) v[it * V + i] = gv[i];
+            sumsq_rounded<T, V>(gv, bits, ss);
         }
         if (LAT == 0 && m + row_step < M) fetch(m + row_step);   // this thread's slots have just been read
         bitlinear_prologue<V, 1, P, RT>(v, D, ss, eps_bl, sw, q, dq, rowsum, M, m, red);
