@@ -482,6 +482,26 @@ def test_decoder_replays_repeated_prompt_lengths_from_a_graph(mm):
     mm.kernels.check_status()
 
 
+def test_prompt_graph_with_the_persistent_contraction(mm):
+    """A prompt of 8 x 256 tokens on 2048-wide layers is large enough for the persistent contraction kernel (clusters of
+    two CTAs, programmatic dependent launch); captured in the decoder's prompt graph and replayed it gives the tokens of the
+    eager pass."""
+    from matmulfreellm_b200.engine import GreedyDecoder
+    cfg = O.OracleConfig(vocab_size=32000, hidden_size=2048, num_hidden_layers=1, intermediate_size=5632)
+    sd = O.random_weights(cfg, seed=17)
+    model = build_gpu_model(sd, cfg, torch.bfloat16)
+    g = torch.Generator().manual_seed(18)
+    prompts = [torch.randint(0, 32000, (8, 256), generator=g).cuda() for _ in range(3)]
+    ref = GreedyDecoder(model, 8, use_graph=False)
+    want = [ref.generate(p, 4) for p in prompts]
+    dec = GreedyDecoder(model, 8)
+    got = [dec.generate(p, 4) for p in prompts]          # eager, capture + replay, replay
+    assert 256 in dec._prompt_graphs
+    for a, b in zip(got, want):
+        assert torch.equal(a, b)
+    mm.kernels.check_status()
+
+
 def test_decoder_step_driven_from_pinned_host_buffers(mm):
     """`GreedyDecoder.step_host`: ids in from pinned host memory, new tokens out to pinned host memory, the two copies
     captured in the same CUDA graph as the step — the token stream equals the device-resident loop, and unpinned or
